@@ -1,0 +1,16 @@
+"""B200-native (sm_100a) sparse-decode path of HashAttention behind the reference's Python API.
+
+The directory name is not a Python identifier; load it under the module name
+``hashattention_b200`` (``__graft_entry__.load_package()`` does that), after which
+``from hashattention_b200 import load_usa, convert_usa`` mirrors
+``from hashattention.hashattention_llama import load_usa, convert_usa``.
+"""
+from . import _lib
+from .cache import PagedHashKVCache
+from .ops import Budget, HostStepBuffers, SparseDecodeContext, decode_step_host
+from .usa import USA, PackedHashWeights
+
+__all__ = [
+    "USA", "PackedHashWeights", "PagedHashKVCache", "Budget", "SparseDecodeContext", "HostStepBuffers",
+    "decode_step_host", "_lib",
+]

@@ -1,0 +1,377 @@
+// extern "C" entry points of libhashattn.so (declared in include/hashattn.h): argument checks,
+// workspace carving and kernel launches. No allocation, no host synchronisation (except where
+// ha_decode_step_host is asked for it), no exceptions.
+#include <cmath>
+#include <utility>
+
+#include "common.cuh"
+#include "hash_decode.cuh"
+#include "score_select.cuh"
+#include "sparse_decode.cuh"
+
+#ifndef HA_USE_PDL
+#define HA_USE_PDL 1
+#endif
+
+namespace ha {
+namespace {
+
+constexpr size_t kAlign = 256;
+inline size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+int check_shape(const ha_shape_t* s) {
+    if (s == nullptr) return HA_ERR_BAD_ARG;
+    if (s->gqa_group != kGroup || s->head_dim != kHeadDim || s->page_size != kPage)
+        return HA_ERR_UNSUPPORTED_DIM;
+    if (s->batch < 1 || s->num_kv_heads < 1 || s->max_pages < 1 || s->num_pages < 1 ||
+        s->sel_stride < 1)
+        return HA_ERR_BAD_ARG;
+    if (s->batch > 65535 || s->num_kv_heads * kGroup > 65535 || s->max_pages > 65535)
+        return HA_ERR_UNSUPPORTED_DIM;
+    return HA_OK;
+}
+
+int check_budget(const ha_budget_t* b) {
+    if (b == nullptr) return HA_ERR_BAD_ARG;
+    if (b->init_budget < 0 || b->recent_budget < 0) return HA_ERR_BAD_ARG;
+    if (!(b->heavy_budget >= 0.0) || !std::isfinite(b->heavy_budget)) return HA_ERR_BAD_ARG;
+    return HA_OK;
+}
+
+int check_weights(const ha_hash_weights_t* w, bool need_q, bool need_k) {
+    if (w == nullptr) return HA_ERR_BAD_ARG;
+    if (w->dtype != HA_WEIGHTS_BF16 && w->dtype != HA_WEIGHTS_F32) return HA_ERR_BAD_ARG;
+    if (need_q && (w->wq == nullptr || w->bq == nullptr)) return HA_ERR_BAD_ARG;
+    if (need_k && (w->wk == nullptr || w->bk == nullptr)) return HA_ERR_BAD_ARG;
+    return HA_OK;
+}
+
+// Attention splits: the rows of one (sequence, query head) never exceed
+// init + recent + sel_stride, nor the longest sequence the page table can describe.
+int num_splits(const ha_shape_t* s, const ha_budget_t* b) {
+    long long rows = (long long)s->sel_stride + b->init_budget + b->recent_budget;
+    const long long cap = (long long)s->max_pages * kPage;
+    if (rows > cap) rows = cap;
+    return (int)((rows + kAttRows - 1) / kAttRows);
+}
+
+struct Workspace {
+    unsigned int* counters;  // [B][Hq]
+    uint32_t* hist;          // [B][Hkv][nchunks][4*33]
+    float* partials;         // [B][Hq][nsplits][130]
+    size_t bytes;
+};
+
+Workspace carve(const ha_shape_t* s, const ha_budget_t* b, void* base) {
+    const size_t Hq = (size_t)s->num_kv_heads * kGroup;
+    const size_t n_counters = (size_t)s->batch * Hq;
+    const size_t n_hist = (size_t)s->batch * s->num_kv_heads * num_chunks_for(s->max_pages) * kGroup * kBins;
+    const size_t n_part = (size_t)s->batch * Hq * num_splits(s, b) * kPartStride;
+    char* p = static_cast<char*>(base);
+    Workspace w;
+    size_t off = 0;
+    w.counters = reinterpret_cast<unsigned int*>(p + off);
+    off += align_up(n_counters * sizeof(unsigned int));
+    w.hist = reinterpret_cast<uint32_t*>(p + off);
+    off += align_up(n_hist * sizeof(uint32_t));
+    w.partials = reinterpret_cast<float*>(p + off);
+    off += align_up(n_part * sizeof(float));
+    w.bytes = off;
+    return w;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+}  // namespace
+}  // namespace ha
+
+using namespace ha;
+
+extern "C" {
+
+int ha_abi_version(void) { return HA_ABI_VERSION; }
+
+const char* ha_status_str(int status) {
+    switch (status) {
+        case HA_OK: return "ok";
+        case HA_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size or inconsistent shape)";
+        case HA_ERR_UNSUPPORTED_DIM: return "unsupported dimension (needs head_dim 128, gqa_group 4, page_size 256)";
+        case HA_ERR_WORKSPACE: return "workspace missing or too small";
+        case HA_ERR_LAUNCH: return "CUDA launch or copy failed";
+        case HA_ERR_TIMEOUT: return "bounded device-side wait ran out";
+        case HA_ERR_BAD_PAGE: return "page id outside the page pool";
+        case HA_ERR_BAD_SEQ_LEN: return "sequence length < 1 or beyond the page table";
+        case HA_ERR_SEL_OVERFLOW: return "heavy budget exceeds sel_stride";
+        default: return "unknown status";
+    }
+}
+
+size_t ha_workspace_bytes(const ha_shape_t* shape, const ha_budget_t* budget) {
+    if (check_shape(shape) != HA_OK || check_budget(budget) != HA_OK) return 0;
+    return carve(shape, budget, nullptr).bytes;
+}
+
+int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+    int rc = check_shape(shape);
+    if (rc != HA_OK) return rc;
+    rc = check_budget(budget);
+    if (rc != HA_OK) return rc;
+    if (workspace == nullptr) return HA_ERR_WORKSPACE;
+    const Workspace w = carve(shape, budget, workspace);
+    if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
+    const size_t n = (size_t)shape->batch * shape->num_kv_heads * kGroup * sizeof(unsigned int);
+    if (cudaMemsetAsync(w.counters, 0, n, static_cast<cudaStream_t>(stream)) != cudaSuccess)
+        return HA_ERR_LAUNCH;
+    return HA_OK;
+}
+
+int ha_hash_decode(const ha_shape_t* shape, const ha_hash_weights_t* weights,
+                   const void* q, const void* k_new, const void* v_new,
+                   void* k_pages, void* v_pages, uint32_t* hash_pages,
+                   const int32_t* page_table, const int32_t* seq_lens,
+                   uint32_t* q_codes, float* preact_dbg, int32_t* status, void* stream) {
+    int rc = check_shape(shape);
+    if (rc != HA_OK) return rc;
+    const bool key_side = k_new != nullptr;
+    rc = check_weights(weights, true, key_side);
+    if (rc != HA_OK) return rc;
+    if (q == nullptr || q_codes == nullptr || status == nullptr) return HA_ERR_BAD_ARG;
+    if (key_side && (hash_pages == nullptr || page_table == nullptr || seq_lens == nullptr))
+        return HA_ERR_BAD_ARG;
+    if (key_side && v_new != nullptr && (k_pages == nullptr || v_pages == nullptr)) return HA_ERR_BAD_ARG;
+
+    HashDecodeParams p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k_new = static_cast<const __nv_bfloat16*>(k_new);
+    p.v_new = static_cast<const __nv_bfloat16*>(v_new);
+    p.w[0] = weights->wq;
+    p.w[1] = weights->wk;
+    p.bias[0] = weights->bq;
+    p.bias[1] = weights->bk;
+    p.k_pages = static_cast<__nv_bfloat16*>(k_pages);
+    p.v_pages = static_cast<__nv_bfloat16*>(v_pages);
+    p.hash_pages = hash_pages;
+    p.page_table = page_table;
+    p.seq_lens = seq_lens;
+    p.q_codes = q_codes;
+    p.preact_dbg = preact_dbg;
+    p.status = status;
+    p.B = shape->batch;
+    p.Hkv = shape->num_kv_heads;
+    p.max_pages = shape->max_pages;
+    p.num_pages = shape->num_pages;
+    // Enough CTAs to cover the GPU, but re-use a head's weights (held in registers) across
+    // several sequences once the batch is large.
+    p.batch_per_cta = shape->batch >= 32 ? 4 : (shape->batch >= 8 ? 2 : 1);
+    const dim3 grid(shape->num_kv_heads * kGroup, key_side ? 2 : 1,
+                    (shape->batch + p.batch_per_cta - 1) / p.batch_per_cta);
+    cudaError_t e;
+    if (weights->dtype == HA_WEIGHTS_BF16)
+        e = launch(hash_decode_kernel<__nv_bfloat16>, grid, dim3(kHashDecodeThreads),
+                   static_cast<cudaStream_t>(stream), p);
+    else
+        e = launch(hash_decode_kernel<float>, grid, dim3(kHashDecodeThreads),
+                   static_cast<cudaStream_t>(stream), p);
+    return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+}
+
+int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
+                    const void* k_pages, uint32_t* hash_pages,
+                    const int32_t* page_table, const int32_t* seq_lens,
+                    const int32_t* first_token, int32_t* status, void* stream) {
+    int rc = check_shape(shape);
+    if (rc != HA_OK) return rc;
+    rc = check_weights(weights, false, true);
+    if (rc != HA_OK) return rc;
+    if (k_pages == nullptr || hash_pages == nullptr || page_table == nullptr || seq_lens == nullptr ||
+        status == nullptr)
+        return HA_ERR_BAD_ARG;
+
+    HashPrefillParams p;
+    p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+    p.hash_pages = hash_pages;
+    p.wk = weights->wk;
+    p.bk = weights->bk;
+    p.page_table = page_table;
+    p.seq_lens = seq_lens;
+    p.first_token = first_token;
+    p.status = status;
+    p.B = shape->batch;
+    p.Hkv = shape->num_kv_heads;
+    p.max_pages = shape->max_pages;
+    p.num_pages = shape->num_pages;
+    const dim3 grid(shape->num_kv_heads * kGroup, shape->max_pages, shape->batch);
+    cudaError_t e;
+    if (weights->dtype == HA_WEIGHTS_BF16)
+        e = launch(hash_prefill_simt_kernel<__nv_bfloat16>, grid, dim3(kHashDecodeThreads),
+                   static_cast<cudaStream_t>(stream), p);
+    else
+        e = launch(hash_prefill_simt_kernel<float>, grid, dim3(kHashDecodeThreads),
+                   static_cast<cudaStream_t>(stream), p);
+    return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+}
+
+int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
+                    const uint32_t* q_codes, const uint32_t* hash_pages,
+                    const int32_t* page_table, const int32_t* seq_lens,
+                    int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg,
+                    void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+    int rc = check_shape(shape);
+    if (rc != HA_OK) return rc;
+    rc = check_budget(budget);
+    if (rc != HA_OK) return rc;
+    if (q_codes == nullptr || hash_pages == nullptr || page_table == nullptr || seq_lens == nullptr ||
+        sel_idx == nullptr || sel_cnt == nullptr || status == nullptr)
+        return HA_ERR_BAD_ARG;
+    if (workspace == nullptr) return HA_ERR_WORKSPACE;
+    const Workspace w = carve(shape, budget, workspace);
+    if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
+
+    SelectParams p;
+    p.q_codes = q_codes;
+    p.hash_pages = reinterpret_cast<const uint4*>(hash_pages);
+    p.page_table = page_table;
+    p.seq_lens = seq_lens;
+    p.hist = w.hist;
+    p.sel_idx = sel_idx;
+    p.sel_cnt = sel_cnt;
+    p.scores_dbg = scores_dbg;
+    p.status = status;
+    p.B = shape->batch;
+    p.Hkv = shape->num_kv_heads;
+    p.max_pages = shape->max_pages;
+    p.num_pages = shape->num_pages;
+    p.sel_stride = shape->sel_stride;
+    p.chunk_pages = chunk_pages_for(shape->max_pages);
+    p.nchunks = num_chunks_for(shape->max_pages);
+    p.init_budget = budget->init_budget;
+    p.recent_budget = budget->recent_budget;
+    p.heavy_budget = budget->heavy_budget;
+    const dim3 grid(p.nchunks, shape->num_kv_heads, shape->batch);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (launch(score_hist_kernel, grid, dim3(kSelThreads), s, p) != cudaSuccess) return HA_ERR_LAUNCH;
+    if (launch(select_kernel, grid, dim3(kSelThreads), s, p) != cudaSuccess) return HA_ERR_LAUNCH;
+    return HA_OK;
+}
+
+int ha_sparse_decode(const ha_shape_t* shape, const ha_budget_t* budget,
+                     const void* q, const void* k_pages, const void* v_pages,
+                     const int32_t* page_table, const int32_t* seq_lens,
+                     const int32_t* sel_idx, const int32_t* sel_cnt, float sm_scale,
+                     void* out, void* workspace, size_t workspace_bytes,
+                     int32_t* status, void* stream) {
+    int rc = check_shape(shape);
+    if (rc != HA_OK) return rc;
+    rc = check_budget(budget);
+    if (rc != HA_OK) return rc;
+    if (q == nullptr || k_pages == nullptr || v_pages == nullptr || page_table == nullptr ||
+        seq_lens == nullptr || sel_idx == nullptr || sel_cnt == nullptr || out == nullptr ||
+        status == nullptr || !std::isfinite(sm_scale))
+        return HA_ERR_BAD_ARG;
+    if (workspace == nullptr) return HA_ERR_WORKSPACE;
+    const Workspace w = carve(shape, budget, workspace);
+    if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
+
+    SparseDecodeParams p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+    p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+    p.page_table = page_table;
+    p.seq_lens = seq_lens;
+    p.sel_idx = sel_idx;
+    p.sel_cnt = sel_cnt;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.partials = w.partials;
+    p.counters = w.counters;
+    p.status = status;
+    p.B = shape->batch;
+    p.Hkv = shape->num_kv_heads;
+    p.max_pages = shape->max_pages;
+    p.num_pages = shape->num_pages;
+    p.sel_stride = shape->sel_stride;
+    p.nsplits = num_splits(shape, budget);
+    p.init_budget = budget->init_budget;
+    p.recent_budget = budget->recent_budget;
+    p.heavy_budget = budget->heavy_budget;
+    p.scale_log2e = sm_scale * 1.4426950408889634f;
+    const dim3 grid(p.nsplits, shape->num_kv_heads * kGroup, shape->batch);
+    if (launch(sparse_decode_kernel, grid, dim3(kAttThreads), static_cast<cudaStream_t>(stream), p) !=
+        cudaSuccess)
+        return HA_ERR_LAUNCH;
+    return HA_OK;
+}
+
+int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
+                   const ha_hash_weights_t* weights,
+                   const void* q, const void* k_new, const void* v_new,
+                   void* k_pages, void* v_pages, uint32_t* hash_pages,
+                   const int32_t* page_table, const int32_t* seq_lens,
+                   uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
+                   void* out, void* workspace, size_t workspace_bytes,
+                   int32_t* status, void* stream) {
+    int rc = ha_hash_decode(shape, weights, q, k_new, v_new, k_pages, v_pages, hash_pages, page_table,
+                            seq_lens, q_codes, nullptr, status, stream);
+    if (rc != HA_OK) return rc;
+    rc = ha_score_select(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
+                         nullptr, workspace, workspace_bytes, status, stream);
+    if (rc != HA_OK) return rc;
+    return ha_sparse_decode(shape, budget, q, k_pages, v_pages, page_table, seq_lens, sel_idx, sel_cnt,
+                            sm_scale, out, workspace, workspace_bytes, status, stream);
+}
+
+int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
+                        const ha_hash_weights_t* weights,
+                        const void* q_host, const void* k_new_host, const void* v_new_host,
+                        void* out_host, int32_t* status_host,
+                        void* q_dev, void* k_new_dev, void* v_new_dev, void* out_dev,
+                        void* k_pages, void* v_pages, uint32_t* hash_pages,
+                        const int32_t* page_table, const int32_t* seq_lens,
+                        uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
+                        void* workspace, size_t workspace_bytes,
+                        int32_t* status, void* stream, int synchronize) {
+    int rc = check_shape(shape);
+    if (rc != HA_OK) return rc;
+    if (q_host == nullptr || out_host == nullptr || status_host == nullptr || q_dev == nullptr ||
+        out_dev == nullptr || status == nullptr)
+        return HA_ERR_BAD_ARG;
+    if ((k_new_host == nullptr) != (k_new_dev == nullptr) || (v_new_host == nullptr) != (v_new_dev == nullptr))
+        return HA_ERR_BAD_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t q_bytes = (size_t)shape->batch * shape->num_kv_heads * kGroup * kHeadDim * sizeof(__nv_bfloat16);
+    const size_t kv_bytes = (size_t)shape->batch * shape->num_kv_heads * kHeadDim * sizeof(__nv_bfloat16);
+    if (cudaMemcpyAsync(q_dev, q_host, q_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return HA_ERR_LAUNCH;
+    if (k_new_host != nullptr &&
+        cudaMemcpyAsync(k_new_dev, k_new_host, kv_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+        return HA_ERR_LAUNCH;
+    if (v_new_host != nullptr &&
+        cudaMemcpyAsync(v_new_dev, v_new_host, kv_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+        return HA_ERR_LAUNCH;
+    rc = ha_decode_step(shape, budget, weights, q_dev, k_new_dev, v_new_dev, k_pages, v_pages, hash_pages,
+                        page_table, seq_lens, q_codes, sel_idx, sel_cnt, sm_scale, out_dev, workspace,
+                        workspace_bytes, status, stream);
+    if (rc != HA_OK) return rc;
+    if (cudaMemcpyAsync(out_host, out_dev, q_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess) return HA_ERR_LAUNCH;
+    if (cudaMemcpyAsync(status_host, status, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+        return HA_ERR_LAUNCH;
+    if (synchronize) {
+        if (cudaStreamSynchronize(s) != cudaSuccess) return HA_ERR_LAUNCH;
+        return *status_host;
+    }
+    return HA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,243 @@
+"""Python entry points of the CUDA library: thin, validating wrappers that pass raw device
+pointers and the current stream through the C ABI (include/hashattn.h).
+
+Shape / dtype / device problems raise ``ValueError`` before anything is launched, the way the
+reference raises on mismatching attention shapes (hashattention/hashattention_llama.py:587-620).
+A non-zero library status raises ``RuntimeError``. There is no torch or CPU fallback.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from .cache import GROUP, HEAD_DIM, PAGE, PagedHashKVCache
+from .usa import PackedHashWeights
+
+
+@dataclass(frozen=True)
+class Budget:
+    """init / heavy / recent budgets with the reference's meaning: ``heavy_budget <= 1.0`` is a
+    fraction of the sequence length, ``> 1.0`` an absolute count
+    (hashattention/hashattention_llama.py:431-434)."""
+
+    init_budget: int = 128
+    heavy_budget: float = 1.0 / 32
+    recent_budget: int = 128
+
+    def heavy_tokens(self, seq_len: int) -> int:
+        return int(self.heavy_budget) if self.heavy_budget > 1.0 else int(seq_len * self.heavy_budget)
+
+    def c_struct(self) -> _lib.HaBudget:
+        return _lib.HaBudget(int(self.init_budget), int(self.recent_budget), float(self.heavy_budget))
+
+
+def _check(t: torch.Tensor, name: str, dtype: torch.dtype, shape, device) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise ValueError(f"{name} must be a tensor")
+    if t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} should be of size {tuple(shape)}, but is {tuple(t.shape)}")
+    if t.device != device:
+        raise ValueError(f"{name} must live on {device}, got {t.device}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _raise_on(rc: int, what: str) -> None:
+    if rc != _lib.HA_OK:
+        raise RuntimeError(f"{what} failed: {_lib.status_str(rc)} (status {rc})")
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class SparseDecodeContext:
+    """Everything one layer's decode step needs besides q / k_new / v_new: the paged cache, the
+    budgets, the packed hash weights, the workspace and the intermediate buffers (query codes,
+    selected indices). Creating it allocates; the step functions do not."""
+
+    def __init__(self, cache: PagedHashKVCache, budget: Budget, weights: PackedHashWeights,
+                 max_seq_len: int | None = None, sm_scale: float | None = None):
+        if cache.device.type != "cuda":
+            raise ValueError("the cache must live on a CUDA device")
+        self.lib = _lib.load()
+        self.cache = cache
+        self.budget = budget
+        self.weights = weights
+        self.device = cache.device
+        self.batch = cache.batch
+        self.num_kv_heads = cache.num_kv_heads
+        self.num_q_heads = cache.num_kv_heads * GROUP
+        if weights.wq.shape[0] != self.num_q_heads or weights.wq.device != self.device:
+            raise ValueError("packed hash weights do not match the cache's heads / device")
+        max_seq_len = cache.max_pages * PAGE if max_seq_len is None else max_seq_len
+        self.sel_stride = max(1, min(budget.heavy_tokens(max_seq_len), max_seq_len))
+        self.sm_scale = 1.0 / math.sqrt(HEAD_DIM) if sm_scale is None else float(sm_scale)
+        self.shape = _lib.HaShape(self.batch, self.num_kv_heads, GROUP, HEAD_DIM, PAGE, cache.max_pages,
+                                  cache.num_pages, self.sel_stride)
+        self.c_budget = budget.c_struct()
+        self.c_weights = weights.c_struct()
+        self.workspace_bytes = int(self.lib.ha_workspace_bytes(self.shape, self.c_budget))
+        if self.workspace_bytes == 0:
+            raise ValueError("invalid shape or budget for the CUDA library")
+        dev = self.device
+        self.workspace = torch.empty(self.workspace_bytes, dtype=torch.uint8, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.q_codes = torch.zeros(self.batch, self.num_q_heads, dtype=torch.int32, device=dev)
+        self.sel_idx = torch.zeros(self.batch, self.num_q_heads, self.sel_stride, dtype=torch.int32, device=dev)
+        self.sel_cnt = torch.zeros(self.batch, self.num_q_heads, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            _raise_on(self.lib.ha_workspace_init(self.shape, self.c_budget, self.workspace.data_ptr(),
+                                                 self.workspace_bytes, _stream_ptr(dev)), "ha_workspace_init")
+
+    # -- argument checks -----------------------------------------------------------------
+    def _check_q(self, q):
+        _check(q, "q", torch.bfloat16, (self.batch, self.num_q_heads, HEAD_DIM), self.device)
+
+    def _check_kv_new(self, k_new, v_new):
+        shape = (self.batch, self.num_kv_heads, HEAD_DIM)
+        _check(k_new, "k_new", torch.bfloat16, shape, self.device)
+        if v_new is not None:
+            _check(v_new, "v_new", torch.bfloat16, shape, self.device)
+
+    def check_status(self) -> None:
+        """Reads the device status word (synchronises) and raises if a kernel reported a problem."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"device status: {_lib.status_str(code)} (status {code})")
+
+    # -- stages ------------------------------------------------------------------------------
+    def hash_decode(self, q, k_new=None, v_new=None, preact_dbg: torch.Tensor | None = None) -> torch.Tensor:
+        """Encodes the new query (and key) and appends the key's code / K / V rows to the cache at
+        token ``seq_lens - 1``. Returns the query codes ``[B, Hq]`` (int32 bit patterns)."""
+        self._check_q(q)
+        if k_new is not None:
+            self._check_kv_new(k_new, v_new)
+        elif v_new is not None:
+            raise ValueError("v_new without k_new")
+        if preact_dbg is not None:
+            _check(preact_dbg, "preact_dbg", torch.float32, (self.batch, 2, self.num_q_heads, 32), self.device)
+        c = self.cache
+        with torch.cuda.device(self.device):
+            rc = self.lib.ha_hash_decode(
+                self.shape, self.c_weights, q.data_ptr(), k_new.data_ptr() if k_new is not None else None,
+                v_new.data_ptr() if v_new is not None else None, c.k_pages.data_ptr(), c.v_pages.data_ptr(),
+                c.hash_pages.data_ptr(), c.page_table.data_ptr(), c.seq_lens.data_ptr(), self.q_codes.data_ptr(),
+                preact_dbg.data_ptr() if preact_dbg is not None else None, self.status.data_ptr(),
+                _stream_ptr(self.device))
+        _raise_on(rc, "ha_hash_decode")
+        return self.q_codes
+
+    def hash_prefill(self, first_token: torch.Tensor | None = None) -> None:
+        """Encodes the cached keys ``[first_token[b], seq_lens[b])`` of every sequence into the hash pages."""
+        if first_token is not None:
+            _check(first_token, "first_token", torch.int32, (self.batch,), self.device)
+        c = self.cache
+        with torch.cuda.device(self.device):
+            rc = self.lib.ha_hash_prefill(
+                self.shape, self.c_weights, c.k_pages.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
+                c.seq_lens.data_ptr(), first_token.data_ptr() if first_token is not None else None,
+                self.status.data_ptr(), _stream_ptr(self.device))
+        _raise_on(rc, "ha_hash_prefill")
+
+    def score_select(self, q_codes: torch.Tensor | None = None, scores_dbg: torch.Tensor | None = None):
+        """Hamming scores + budget selection. Returns ``(sel_idx [B,Hq,sel_stride], sel_cnt [B,Hq])``."""
+        q_codes = self.q_codes if q_codes is None else q_codes
+        _check(q_codes, "q_codes", torch.int32, (self.batch, self.num_q_heads), self.device)
+        if scores_dbg is not None:
+            _check(scores_dbg, "scores_dbg", torch.uint8,
+                   (self.batch, self.num_q_heads, self.cache.max_pages * PAGE), self.device)
+        c = self.cache
+        with torch.cuda.device(self.device):
+            rc = self.lib.ha_score_select(
+                self.shape, self.c_budget, q_codes.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
+                c.seq_lens.data_ptr(), self.sel_idx.data_ptr(), self.sel_cnt.data_ptr(),
+                scores_dbg.data_ptr() if scores_dbg is not None else None, self.workspace.data_ptr(),
+                self.workspace_bytes, self.status.data_ptr(), _stream_ptr(self.device))
+        _raise_on(rc, "ha_score_select")
+        return self.sel_idx, self.sel_cnt
+
+    def sparse_decode(self, q, out: torch.Tensor | None = None, sel_idx=None, sel_cnt=None) -> torch.Tensor:
+        """Attention of q over sink + selected + recent rows. Returns ``out [B, Hq, 128]`` bf16."""
+        self._check_q(q)
+        out = torch.empty_like(q) if out is None else out
+        _check(out, "out", torch.bfloat16, (self.batch, self.num_q_heads, HEAD_DIM), self.device)
+        sel_idx = self.sel_idx if sel_idx is None else sel_idx
+        sel_cnt = self.sel_cnt if sel_cnt is None else sel_cnt
+        _check(sel_idx, "sel_idx", torch.int32, (self.batch, self.num_q_heads, self.sel_stride), self.device)
+        _check(sel_cnt, "sel_cnt", torch.int32, (self.batch, self.num_q_heads), self.device)
+        c = self.cache
+        with torch.cuda.device(self.device):
+            rc = self.lib.ha_sparse_decode(
+                self.shape, self.c_budget, q.data_ptr(), c.k_pages.data_ptr(), c.v_pages.data_ptr(),
+                c.page_table.data_ptr(), c.seq_lens.data_ptr(), sel_idx.data_ptr(), sel_cnt.data_ptr(),
+                self.sm_scale, out.data_ptr(), self.workspace.data_ptr(), self.workspace_bytes,
+                self.status.data_ptr(), _stream_ptr(self.device))
+        _raise_on(rc, "ha_sparse_decode")
+        return out
+
+    def decode_step(self, q, k_new, v_new, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The whole step (encode + append, score + select, sparse attention) in one library call."""
+        self._check_q(q)
+        self._check_kv_new(k_new, v_new)
+        out = torch.empty_like(q) if out is None else out
+        _check(out, "out", torch.bfloat16, (self.batch, self.num_q_heads, HEAD_DIM), self.device)
+        c = self.cache
+        with torch.cuda.device(self.device):
+            rc = self.lib.ha_decode_step(
+                self.shape, self.c_budget, self.c_weights, q.data_ptr(), k_new.data_ptr(),
+                v_new.data_ptr() if v_new is not None else None, c.k_pages.data_ptr(), c.v_pages.data_ptr(),
+                c.hash_pages.data_ptr(), c.page_table.data_ptr(), c.seq_lens.data_ptr(), self.q_codes.data_ptr(),
+                self.sel_idx.data_ptr(), self.sel_cnt.data_ptr(), self.sm_scale, out.data_ptr(),
+                self.workspace.data_ptr(), self.workspace_bytes, self.status.data_ptr(), _stream_ptr(self.device))
+        _raise_on(rc, "ha_decode_step")
+        return out
+
+
+class HostStepBuffers:
+    """Pinned host tensors and device staging buffers for :func:`decode_step_host`."""
+
+    def __init__(self, ctx: SparseDecodeContext):
+        B, Hq, Hkv, dev = ctx.batch, ctx.num_q_heads, ctx.num_kv_heads, ctx.device
+        pin = dict(dtype=torch.bfloat16, pin_memory=True)
+        self.q_host = torch.empty(B, Hq, HEAD_DIM, **pin)
+        self.k_host = torch.empty(B, Hkv, HEAD_DIM, **pin)
+        self.v_host = torch.empty(B, Hkv, HEAD_DIM, **pin)
+        self.out_host = torch.empty(B, Hq, HEAD_DIM, **pin)
+        self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self.q_dev = torch.empty(B, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        self.k_dev = torch.empty(B, Hkv, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        self.v_dev = torch.empty(B, Hkv, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        self.out_dev = torch.empty(B, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+
+    @property
+    def h2d_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.q_host, self.k_host, self.v_host))
+
+    @property
+    def d2h_bytes(self) -> int:
+        return self.out_host.numel() * self.out_host.element_size() + 4
+
+
+def decode_step_host(ctx: SparseDecodeContext, buf: HostStepBuffers, synchronize: bool = True) -> torch.Tensor:
+    """Decode step for callers whose q / k_new / v_new / out live in host memory: copies
+    ``buf.q_host, k_host, v_host`` to the device, runs the step, copies the result into
+    ``buf.out_host`` and (if ``synchronize``) waits and checks the device status."""
+    c = ctx.cache
+    with torch.cuda.device(ctx.device):
+        rc = ctx.lib.ha_decode_step_host(
+            ctx.shape, ctx.c_budget, ctx.c_weights, buf.q_host.data_ptr(), buf.k_host.data_ptr(),
+            buf.v_host.data_ptr(), buf.out_host.data_ptr(), buf.status_host.data_ptr(), buf.q_dev.data_ptr(),
+            buf.k_dev.data_ptr(), buf.v_dev.data_ptr(), buf.out_dev.data_ptr(), c.k_pages.data_ptr(),
+            c.v_pages.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(), c.seq_lens.data_ptr(),
+            ctx.q_codes.data_ptr(), ctx.sel_idx.data_ptr(), ctx.sel_cnt.data_ptr(), ctx.sm_scale,
+            ctx.workspace.data_ptr(), ctx.workspace_bytes, ctx.status.data_ptr(), _stream_ptr(ctx.device),
+            1 if synchronize else 0)
+    _raise_on(rc, "ha_decode_step_host")
+    return buf.out_host

@@ -1,0 +1,117 @@
+"""Host-side mirror of the reference's hash encoder module ``USA``.
+
+The module owns the per-query-head hash MLP parameters under the reference's attribute names,
+so a state dict saved by the reference (keys
+``learning_to_hash_transformation_{k,q}.{head}.{0,2,4}.{weight,bias}``;
+hashattention/hashattention_llama.py:99-111) loads unchanged, and a module built here under
+``torch.manual_seed(s)`` holds the same values as the reference's built under the same seed
+(same sub-module construction order: all key nets, then all query nets).
+
+All arithmetic runs in the CUDA library; this class only stores parameters and repacks them
+into the flat buffers the kernels read (:meth:`packed`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import nn
+
+from . import _lib
+
+HIDDEN = 128
+CODE_BITS = 32
+MLP_ELEMS = 128 * 128 + 128 * 128 + 32 * 128
+MLP_BIAS = 128 + 128 + 32
+
+DEFAULT_USA_CFG = {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 3}
+
+
+@dataclass
+class PackedHashWeights:
+    """Flat device buffers in the layout include/hashattn.h documents."""
+
+    wq: torch.Tensor  # [Hq, 36864] bf16 or f32
+    bq: torch.Tensor  # [Hq, 288] f32
+    wk: torch.Tensor
+    bk: torch.Tensor
+    dtype_code: int
+
+    def c_struct(self) -> _lib.HaHashWeights:
+        return _lib.HaHashWeights(self.wq.data_ptr(), self.bq.data_ptr(), self.wk.data_ptr(),
+                                  self.bk.data_ptr(), self.dtype_code)
+
+    def slice_heads(self, h0: int, h1: int) -> "PackedHashWeights":
+        """The weights of query heads [h0, h1): what one GPU of a kv-head partition holds."""
+        return PackedHashWeights(self.wq[h0:h1].contiguous(), self.bq[h0:h1].contiguous(),
+                                 self.wk[h0:h1].contiguous(), self.bk[h0:h1].contiguous(), self.dtype_code)
+
+
+def _mlp(head_dim: int, int_dim: int, final_dim: int) -> nn.Sequential:
+    return nn.Sequential(nn.Linear(head_dim, int_dim), nn.SiLU(), nn.Linear(int_dim, int_dim), nn.SiLU(),
+                         nn.Linear(int_dim, final_dim))
+
+
+class USA(nn.Module):
+    """Parameter container with the reference's constructor signature
+    (hashattention/hashattention_llama.py:87-139).
+
+    Only the configuration the kernels implement is accepted: 3 layers, hidden width 128,
+    32 output bits, head_dim 128. Other ``lth_*`` settings raise ``NotImplementedError``.
+    """
+
+    def __init__(self, num_heads: int, head_dim: int, usa_params: dict = DEFAULT_USA_CFG):
+        super().__init__()
+        self.head_dim = head_dim
+        self.num_heads = num_heads
+        self.int_dim = usa_params["lth_int_dim"]
+        self.lth_final_dim = usa_params["lth_final_dim"]
+        self.lth_thold = usa_params["lth_thold"]
+        self.num_layers = usa_params.get("lth_num_layers", 3)
+        if (self.num_layers, self.int_dim, self.lth_final_dim, head_dim) != (3, HIDDEN, CODE_BITS, 128):
+            raise NotImplementedError(
+                "the sm_100a kernels implement lth_num_layers=3, lth_init_dim=128, lth_final_dim=32, "
+                f"head_dim=128; got layers={self.num_layers}, int_dim={self.int_dim}, "
+                f"final_dim={self.lth_final_dim}, head_dim={head_dim}"
+            )
+        self.learning_to_hash_transformation_k = nn.ModuleList(
+            [_mlp(head_dim, self.int_dim, self.lth_final_dim) for _ in range(num_heads)])
+        self.learning_to_hash_transformation_q = nn.ModuleList(
+            [_mlp(head_dim, self.int_dim, self.lth_final_dim) for _ in range(num_heads)])
+        self._packed: PackedHashWeights | None = None
+        # a state dict loaded through this module or any parent invalidates the packed copy
+        self.register_load_state_dict_post_hook(lambda module, _incompatible: setattr(module, "_packed", None))
+
+    # -- packing ---------------------------------------------------------------------------
+    def _pack_side(self, nets: nn.ModuleList, dtype: torch.dtype, device) -> tuple[torch.Tensor, torch.Tensor]:
+        w = torch.stack([torch.cat([net[0].weight.reshape(-1), net[2].weight.reshape(-1),
+                                    net[4].weight.reshape(-1)]) for net in nets])
+        b = torch.stack([torch.cat([net[0].bias, net[2].bias, net[4].bias]) for net in nets])
+        return (w.detach().to(device=device, dtype=dtype).contiguous(),
+                b.detach().to(device=device, dtype=torch.float32).contiguous())
+
+    def packed(self, device=None, refresh: bool = False) -> PackedHashWeights:
+        """Kernel-side copy of the parameters. bf16 parameters stay bf16 (the kernels up-cast
+        them exactly); anything else is kept as fp32."""
+        device = torch.device(device) if device is not None else self.learning_to_hash_transformation_k[0][0].weight.device
+        if self._packed is not None and not refresh and self._packed.wq.device == device:
+            return self._packed
+        pdtype = self.learning_to_hash_transformation_k[0][0].weight.dtype
+        if pdtype == torch.bfloat16:
+            wdtype, code = torch.bfloat16, _lib.HA_WEIGHTS_BF16
+        else:
+            wdtype, code = torch.float32, _lib.HA_WEIGHTS_F32
+        wq, bq = self._pack_side(self.learning_to_hash_transformation_q, wdtype, device)
+        wk, bk = self._pack_side(self.learning_to_hash_transformation_k, wdtype, device)
+        self._packed = PackedHashWeights(wq, bq, wk, bk, code)
+        return self._packed
+
+    def _apply(self, fn, *args, **kwargs):  # .cuda() / .bfloat16() / .to() invalidate the packed copy
+        self._packed = None
+        return super()._apply(fn, *args, **kwargs)
+
+    def forward(self, K, Q, hard=False):
+        raise RuntimeError(
+            "USA.forward is not evaluated in torch here: the hash codes are produced by the CUDA "
+            "kernels (ops.hash_decode / ops.hash_prefill) and scored by ops.score_select"
+        )

@@ -1,0 +1,189 @@
+/*
+ * hashattn.h — C ABI of libhashattn.so: the HashAttention sparse-decode hot path for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The library replaces, for one attention layer and one decode step, what the reference
+ * does in torch inside hashattention/hashattention_llama.py:
+ *     USA.forward / k_embedding / q_embedding      (:151-226)  -> ha_hash_decode, ha_hash_prefill
+ *     compute_mask_multi, usa_eval_mode == 'simple' (:401-446)  -> ha_score_select
+ *     masked softmax(QK^T/sqrt(d)) . V              (:578-623)  -> ha_sparse_decode
+ *     the three in sequence                         (:571-623)  -> ha_decode_step
+ *
+ * Conventions
+ *   - Every function returns an int status (HA_OK == 0) and never throws.
+ *   - Unless a parameter is documented as a host pointer, every pointer is a DEVICE pointer.
+ *   - Nothing is allocated or freed inside the library; temporaries live in a caller-provided
+ *     workspace of ha_workspace_bytes() bytes that was prepared once by ha_workspace_init().
+ *   - All work is enqueued on the given CUDA stream; no entry point synchronises with the
+ *     host except ha_decode_step_host (documented there).
+ *   - Kernels validate page ids and sizes before touching memory; a violation is reported
+ *     through the 4-byte device word `status` (0 == clean) instead of a fault.
+ *
+ * Data layout in HBM (all little-endian, row-major, dimension names left to right)
+ *   K pages, V pages : [num_pages][num_kv_heads][page_size][head_dim]   bf16
+ *   hash pages       : [num_pages][num_kv_heads][page_size][gqa_group]  u32
+ *                      one 16-byte word per token per kv-head holding the packed 32-bit key
+ *                      code of each of the gqa_group(=4) query heads of that kv-head.
+ *                      bit i of a code == 1 iff output i of the head's hash MLP is > 0
+ *                      (LSB == output 0; efficiency/kernels/torchatt.py:35-36,159).
+ *   page_table       : [batch][max_pages] i32, entry p = page id of tokens [p*page_size, ...)
+ *   seq_lens         : [batch] i32, number of cached tokens INCLUDING the one being decoded
+ *   q, out           : [batch][num_q_heads][head_dim] bf16 (num_q_heads = num_kv_heads*gqa_group,
+ *                      query head h belongs to kv-head h / gqa_group)
+ *   k_new, v_new     : [batch][num_kv_heads][head_dim] bf16 (post-RoPE key of the new token)
+ *   hash weights     : per side (q or k) [num_q_heads][W0 128x128 | W1 128x128 | W2 32x128]
+ *                      row-major [out][in] exactly as torch.nn.Linear stores them, bf16 or f32
+ *                      (HA_WEIGHTS_*), 36864 elements per head;
+ *                      biases [num_q_heads][128 + 128 + 32] f32.
+ */
+#ifndef HASHATTN_H_
+#define HASHATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HA_ABI_VERSION 1
+
+/* status codes (return values and contents of the device status word) */
+#define HA_OK 0
+#define HA_ERR_BAD_ARG 1         /* null pointer, non-positive size, inconsistent shape      */
+#define HA_ERR_UNSUPPORTED_DIM 2 /* head_dim != 128, gqa_group != 4, page_size != 256, ...   */
+#define HA_ERR_WORKSPACE 3       /* workspace missing or smaller than ha_workspace_bytes()   */
+#define HA_ERR_LAUNCH 4          /* the CUDA runtime refused a launch or a copy              */
+#define HA_ERR_TIMEOUT 5         /* a bounded device-side wait ran out                       */
+#define HA_ERR_BAD_PAGE 6        /* device: page id outside [0, num_pages)                   */
+#define HA_ERR_BAD_SEQ_LEN 7     /* device: seq_len < 1 or beyond max_pages * page_size      */
+#define HA_ERR_SEL_OVERFLOW 8    /* device: heavy budget exceeds sel_stride                  */
+
+#define HA_WEIGHTS_BF16 0
+#define HA_WEIGHTS_F32 1
+
+/* Shape of one layer's paged cache as seen by ONE GPU (after any kv-head partitioning). */
+typedef struct ha_shape {
+    int32_t batch;        /* B: sequences decoded together                                   */
+    int32_t num_kv_heads; /* kv heads held by this GPU                                       */
+    int32_t gqa_group;    /* query heads per kv head; must be 4                              */
+    int32_t head_dim;     /* must be 128                                                     */
+    int32_t page_size;    /* tokens per page; must be 256                                    */
+    int32_t max_pages;    /* columns of page_table                                           */
+    int32_t num_pages;    /* pages in the K / V / hash pools (bound for page ids)            */
+    int32_t sel_stride;   /* row pitch (elements) of sel_idx: >= largest heavy budget        */
+} ha_shape_t;
+
+/* Budgets of compute_mask_multi (hashattention/hashattention_llama.py:423-438).
+ * heavy_budget <= 1.0 is a fraction of seq_len, > 1.0 an absolute token count; the product
+ * is formed in double precision and truncated, as Python's int(k * heavy_budget) does. */
+typedef struct ha_budget {
+    int32_t init_budget;   /* sink tokens  [0, init)                                          */
+    int32_t recent_budget; /* recent tokens [S - recent, S)                                   */
+    double heavy_budget;
+} ha_budget_t;
+
+typedef struct ha_hash_weights {
+    const void* wq;    /* query-side weights, layout above                                   */
+    const float* bq;   /* query-side biases                                                  */
+    const void* wk;    /* key-side weights                                                   */
+    const float* bk;   /* key-side biases                                                    */
+    int32_t dtype;     /* HA_WEIGHTS_BF16 or HA_WEIGHTS_F32                                  */
+} ha_hash_weights_t;
+
+int ha_abi_version(void);
+const char* ha_status_str(int status);
+
+/* Bytes of workspace needed by any entry point below for this shape and these budgets
+ * (0 if either is invalid). Host-only arithmetic. */
+size_t ha_workspace_bytes(const ha_shape_t* shape, const ha_budget_t* budget);
+
+/* Zeroes the workspace's arrival counters. Call once after allocating the workspace (and
+ * again only if a kernel was aborted); the kernels leave the counters at zero themselves. */
+int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+/* Decode-time hash encoder + cache append.
+ * Replaces USA.q_embedding for the new query and USA.k_embedding for the new key
+ * (hashattention/hashattention_llama.py:204-226, 411-414) and Cache.update (:573-576).
+ *   - q_codes[b][h]  <- packed sign bits of q-MLP_h(q[b][h])
+ *   - the 4 codes of k-MLP_{4j..4j+3}(k_new[b][j]) are written to the hash page slot of token
+ *     seq_lens[b]-1; k_new / v_new rows are copied to the same slot of the K / V pages.
+ *   - k_new == NULL skips the key side (query-only encode).
+ *   - preact_dbg (optional, may be NULL): [batch][2][num_q_heads][32] f32 final-layer
+ *     pre-activations, side 0 = query, side 1 = key.                                       */
+int ha_hash_decode(const ha_shape_t* shape, const ha_hash_weights_t* weights,
+                   const void* q, const void* k_new, const void* v_new,
+                   void* k_pages, void* v_pages, uint32_t* hash_pages,
+                   const int32_t* page_table, const int32_t* seq_lens,
+                   uint32_t* q_codes, float* preact_dbg, int32_t* status, void* stream);
+
+/* Prefill key-hash build: encodes every cached key of every sequence.
+ * Replaces USA.k_embedding over the whole cache (hashattention/hashattention_llama.py:204-214;
+ * the reference recomputes it on every decode step at :405-406).
+ * Tokens [first_token[b], seq_lens[b]) of sequence b are encoded (first_token == NULL: from 0). */
+int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
+                    const void* k_pages, uint32_t* hash_pages,
+                    const int32_t* page_table, const int32_t* seq_lens,
+                    const int32_t* first_token, int32_t* status, void* stream);
+
+/* Hamming scoring + budget selection, usa_eval_mode == 'simple'.
+ * Replaces the +-1 dot product of USA.forward (hashattention/hashattention_llama.py:171-187)
+ * and compute_mask_multi (:423-438). score = popcount(~(q_code ^ k_code)) in 0..32, which
+ * equals (span + 32) / 2 of the reference. Candidates are tokens [lo, hi) with
+ * lo = min(init, S), hi = max(lo, S - recent); the heavy set is the min(hb, hi - lo) best
+ * candidates, ties at the threshold broken by lowest token index.
+ *   - sel_idx[b][h][0 .. sel_cnt[b][h]) <- heavy token indices in ascending order
+ *   - scores_dbg (optional, may be NULL): [batch][num_q_heads][max_pages*page_size] u8      */
+int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
+                    const uint32_t* q_codes, const uint32_t* hash_pages,
+                    const int32_t* page_table, const int32_t* seq_lens,
+                    int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg,
+                    void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* Sparse GQA flash-decode over sink + heavy + recent tokens.
+ * Replaces hashattention/hashattention_llama.py:578-623 (repeat_kv, QK^T/sqrt(d), mask fill,
+ * fp32 softmax, .V); masked positions contribute exactly 0 there, so the result equals a
+ * softmax over the selected set. fp32 accumulation, bf16 output.                            */
+int ha_sparse_decode(const ha_shape_t* shape, const ha_budget_t* budget,
+                     const void* q, const void* k_pages, const void* v_pages,
+                     const int32_t* page_table, const int32_t* seq_lens,
+                     const int32_t* sel_idx, const int32_t* sel_cnt, float sm_scale,
+                     void* out, void* workspace, size_t workspace_bytes,
+                     int32_t* status, void* stream);
+
+/* One whole decode step of one layer: ha_hash_decode -> ha_score_select -> ha_sparse_decode
+ * enqueued back to back on `stream` (hashattention/hashattention_llama.py:571-623).
+ * q_codes [batch][num_q_heads], sel_idx [batch][num_q_heads][sel_stride] and
+ * sel_cnt [batch][num_q_heads] are caller-owned device buffers that hold the intermediate
+ * results afterwards.                                                                       */
+int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
+                   const ha_hash_weights_t* weights,
+                   const void* q, const void* k_new, const void* v_new,
+                   void* k_pages, void* v_pages, uint32_t* hash_pages,
+                   const int32_t* page_table, const int32_t* seq_lens,
+                   uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
+                   void* out, void* workspace, size_t workspace_bytes,
+                   int32_t* status, void* stream);
+
+/* ha_decode_step for a caller whose per-step tensors live in HOST memory.
+ * q_host, k_new_host, v_new_host (inputs) and out_host (result) are HOST pointers, ideally
+ * pinned; q_dev, k_new_dev, v_new_dev, out_dev are device staging buffers of the same sizes.
+ * The call copies the inputs to the device, runs ha_decode_step, copies `out` and the status
+ * word back and, if `synchronize` is non-zero, waits for the stream and returns the device
+ * status word (HA_OK if clean). status_host is a host int32 (pinned) receiving that word.   */
+int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
+                        const ha_hash_weights_t* weights,
+                        const void* q_host, const void* k_new_host, const void* v_new_host,
+                        void* out_host, int32_t* status_host,
+                        void* q_dev, void* k_new_dev, void* v_new_dev, void* out_dev,
+                        void* k_pages, void* v_pages, uint32_t* hash_pages,
+                        const int32_t* page_table, const int32_t* seq_lens,
+                        uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
+                        void* workspace, size_t workspace_bytes,
+                        int32_t* status, void* stream, int synchronize);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HASHATTN_H_ */
