@@ -253,8 +253,8 @@ hash_prefill_simt_kernel(const HashPrefillParams p) {
     const int kvh = h / kGroup, g = h % kGroup;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-    const int S = p.seq_lens[b];
-    if (S < 1 || S > p.max_pages * kPage) {
+    const int S = p.seq_lens[b];  // 0 is legal here: nothing cached yet, nothing to encode
+    if (S < 0 || S > p.max_pages * kPage) {
         if (tid == 0 && h == 0 && pg == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
         return;
     }

@@ -1,0 +1,380 @@
+"""Parity of the CUDA path (called through the C ABI) with the oracle and with the fixtures
+recorded from the reference. Integer results (codes outside the |x|<1e-5 band, Hamming
+scores, selected sets) must match bit-exactly; the bf16 attention output must be within
+max-abs 2e-2 and rel-L2 1e-2 of the fp32 reference."""
+import pytest
+import torch
+
+import hashattention_b200 as ha
+from hashattention_b200 import synthetic
+from oracle import hashattn_oracle as orc
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+ALL_BITS = 0xFFFFFFFF
+
+
+def build(device, q, k, v, budget, usa, shuffle_seed=11, prefill_to=None, max_seq_len=None):
+    """Cache + context holding k/v [B,Hkv,S,D] (or lists of [Hkv,S_b,D]) up to ``prefill_to`` tokens."""
+    ks = list(k) if not isinstance(k, torch.Tensor) else [k[b] for b in range(k.shape[0])]
+    vs = list(v) if not isinstance(v, torch.Tensor) else [v[b] for b in range(v.shape[0])]
+    lens = [x.shape[1] for x in ks]
+    cache = ha.PagedHashKVCache(len(ks), ks[0].shape[0], max_seq_len or max(lens), device, shuffle_seed=shuffle_seed)
+    for b, S in enumerate(lens):
+        n = S if prefill_to is None else prefill_to[b]
+        if n > 0:
+            cache.write_kv(b, ks[b][:, :n], vs[b][:, :n])
+    ctx = ha.SparseDecodeContext(cache, budget, usa.packed(device))
+    return cache, ctx
+
+
+def heavy_from_device(ctx, b, h):
+    n = int(ctx.sel_cnt[b, h])
+    return ctx.sel_idx[b, h, :n].cpu().to(torch.int64)
+
+
+def budget_of(case):
+    return ha.Budget(case.init, case.heavy, case.recent)
+
+
+def golden_cases(names=("case_a", "edge", "config0")):
+    cases = {}
+    if "case_a" in names:
+        cases["case_a"] = helpers.load_case_a()
+    if "edge" in names:
+        cases.update({f"edge/{n}": c for n, c in helpers.load_edge().items()})
+    if "config0" in names:
+        case, ok = helpers.load_config0(synthetic)
+        if ok:
+            cases["config0"] = case
+    return cases
+
+
+CASE_NAMES = ["case_a", "config0"] + [f"edge/{n}" for n in
+                                     ("short", "one_cand", "p255", "p256", "p257", "abs48", "all", "zero_heavy")]
+
+
+@pytest.fixture(scope="module")
+def cases():
+    return golden_cases()
+
+
+def get_case(cases, name):
+    if name not in cases:
+        pytest.skip("config0 inputs cannot be regenerated bit-exactly on this machine")
+    return cases[name]
+
+
+# ------------------------------------------------------------------------------------------
+# hash encoder
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", CASE_NAMES)
+def test_prefill_codes_match_reference(device, cases, name):
+    case = get_case(cases, name)
+    usa = synthetic.make_usa(case.q.shape[1], 128, 0, True)
+    cache, ctx = build(device, case.q, case.k, case.v, budget_of(case), usa)
+    ctx.hash_prefill()
+    ctx.check_status()
+    for b in range(case.k.shape[0]):
+        assert helpers.codes_match(cache.read_codes(b).cpu(), case.k_codes[b], case.k_must[b])
+
+
+@pytest.mark.parametrize("bf16_weights", [True, False])
+def test_decode_encoder_matches_oracle(device, bf16_weights):
+    """Query codes, appended key codes and the appended K / V rows, bf16 and fp32 weights, batch 5."""
+    Hq, Hkv, lens = 8, 2, [40, 256, 257, 513, 1000]
+    usa = synthetic.make_usa(Hq, 128, 1, bf16_weights)
+    inp = synthetic.make_decode_inputs(92, lens, Hq, Hkv)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, ha.Budget(16, 0.125, 16), usa, prefill_to=[s - 1 for s in lens])
+    cache.seq_lens += 1
+    k_new = torch.stack([k[:, -1] for k in inp.k]).to(device, torch.bfloat16)
+    v_new = torch.stack([v[:, -1] for v in inp.v]).to(device, torch.bfloat16)
+    pre = torch.zeros(len(lens), 2, Hq, 32, device=device)
+    q_codes = ctx.hash_decode(inp.q.to(device, torch.bfloat16), k_new, v_new, preact_dbg=pre)
+    ctx.check_status()
+    q_codes = q_codes.cpu().to(torch.int64) & ALL_BITS
+    worst = 0.0
+    for b, S in enumerate(lens):
+        q_pre, k_pre = helpers.oracle_preacts(usa, inp.q[b:b + 1], inp.k[b][None, :, -1:, :])
+        assert helpers.codes_match(q_codes[b], orc.pack_codes(q_pre[0]), orc.band_mask(q_pre[0]))
+        got_k = cache.read_codes(b).cpu()[:, -1]
+        assert helpers.codes_match(got_k, orc.pack_codes(k_pre[0, :, 0]), orc.band_mask(k_pre[0, :, 0]))
+        worst = max(worst, float((pre[b, 0].cpu() - q_pre[0]).abs().max()),
+                    float((pre[b, 1].cpu() - k_pre[0, :, 0]).abs().max()))
+        k_back, v_back = cache.read_kv(b)
+        assert torch.equal(k_back.float().cpu(), inp.k[b]) and torch.equal(v_back.float().cpu(), inp.v[b])
+    assert worst < 5e-6, f"pre-activation error {worst} would eat into the 1e-5 exclusion band"
+
+
+def test_query_only_encode(device):
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(93, [300], 8, 2)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, ha.Budget(16, 0.125, 16), usa)
+    before = cache.hash_pages.clone()
+    q_codes = ctx.hash_decode(inp.q.to(device, torch.bfloat16)).cpu().to(torch.int64) & ALL_BITS
+    q_pre, _ = helpers.oracle_preacts(usa, inp.q, inp.k[0][None, :, :1])
+    assert helpers.codes_match(q_codes[0], orc.pack_codes(q_pre[0]), orc.band_mask(q_pre[0]))
+    assert torch.equal(before, cache.hash_pages)
+
+
+# ------------------------------------------------------------------------------------------
+# Hamming scores + budget selection: bit-exact on the reference's own codes
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", CASE_NAMES)
+def test_scores_and_selection_match_reference(device, cases, name):
+    case = get_case(cases, name)
+    B, Hq = case.q.shape[0], case.q.shape[1]
+    usa = synthetic.make_usa(Hq, 128, 0, True)
+    cache, ctx = build(device, case.q, case.k, case.v, budget_of(case), usa)
+    for b in range(B):
+        cache.write_codes(b, case.k_codes[b])
+    q_codes = torch.where(case.q_codes >= 2 ** 31, case.q_codes - 2 ** 32, case.q_codes).to(torch.int32).to(device)
+    scores = torch.full((B, Hq, cache.max_pages * 256), 255, dtype=torch.uint8, device=device)
+    ctx.score_select(q_codes, scores_dbg=scores)
+    ctx.check_status()
+    assert torch.equal(scores[:, :, :case.S].cpu().to(torch.int64), case.scores)
+    assert bool((scores[:, :, case.S:] == 255).all()), "wrote scores beyond the sequence"
+    want = orc.heavy_sets(case.mask, case.init, case.recent)
+    for b in range(B):
+        for h in range(Hq):
+            got = heavy_from_device(ctx, b, h)
+            assert torch.equal(got, got.sort().values), "indices not ascending"
+            assert torch.equal(got, want[b][h]), f"{name}: selected set differs at b={b} h={h}"
+
+
+# ------------------------------------------------------------------------------------------
+# sparse attention on the reference's selected sets
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", CASE_NAMES)
+def test_sparse_attention_matches_reference(device, cases, name):
+    case = get_case(cases, name)
+    B, Hq = case.q.shape[0], case.q.shape[1]
+    usa = synthetic.make_usa(Hq, 128, 0, True)
+    cache, ctx = build(device, case.q, case.k, case.v, budget_of(case), usa)
+    want = orc.heavy_sets(case.mask, case.init, case.recent)
+    sel_idx = torch.zeros_like(ctx.sel_idx)
+    sel_cnt = torch.zeros_like(ctx.sel_cnt)
+    for b in range(B):
+        for h in range(Hq):
+            n = len(want[b][h])
+            sel_idx[b, h, :n] = want[b][h].to(torch.int32)
+            sel_cnt[b, h] = n
+    out = ctx.sparse_decode(case.q.to(device, torch.bfloat16), sel_idx=sel_idx, sel_cnt=sel_cnt)
+    ctx.check_status()
+    ok, max_abs, rel = helpers.att_close(out.cpu(), case.out)
+    assert ok, f"{name}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
+
+
+# ------------------------------------------------------------------------------------------
+# the whole step
+# ------------------------------------------------------------------------------------------
+def run_step_and_check(device, usa, q, ks, vs, budget, shuffle_seed=11, via_host=False):
+    """Prefill all but the last token, decode the last one, compare every stage with the oracle.
+    Selection and attention are compared on the device's own codes (a bit inside the exclusion
+    band must not show up as a set mismatch); returns whether the codes were identical."""
+    lens = [k.shape[1] for k in ks]
+    B, Hq = q.shape[0], q.shape[1]
+    cache, ctx = build(device, q, ks, vs, budget, usa, shuffle_seed=shuffle_seed, prefill_to=[s - 1 for s in lens])
+    ctx.hash_prefill()
+    cache.seq_lens += 1
+    k_new = torch.stack([k[:, -1] for k in ks]).to(torch.bfloat16)
+    v_new = torch.stack([v[:, -1] for v in vs]).to(torch.bfloat16)
+    if via_host:
+        buf = ha.HostStepBuffers(ctx)
+        buf.q_host.copy_(q.to(torch.bfloat16)); buf.k_host.copy_(k_new); buf.v_host.copy_(v_new)
+        out = ha.decode_step_host(ctx, buf).clone().float()
+    else:
+        out = ctx.decode_step(q.to(device, torch.bfloat16), k_new.to(device), v_new.to(device)).float().cpu()
+    ctx.check_status()
+    q_codes = ctx.q_codes.cpu().to(torch.int64) & ALL_BITS
+    identical = True
+    for b, S in enumerate(lens):
+        q_pre, k_pre = helpers.oracle_preacts(usa, q[b:b + 1], ks[b][None])
+        k_codes = cache.read_codes(b).cpu()
+        assert helpers.codes_match(k_codes, orc.pack_codes(k_pre[0]), orc.band_mask(k_pre[0]))
+        assert helpers.codes_match(q_codes[b], orc.pack_codes(q_pre[0]), orc.band_mask(q_pre[0]))
+        identical &= bool((k_codes == orc.pack_codes(k_pre[0])).all()) and bool((q_codes[b] == orc.pack_codes(q_pre[0])).all())
+        scores = orc.hamming_scores(q_codes[b][None], k_codes[None])
+        mask = orc.select_mask(scores, budget.init_budget, budget.recent_budget, budget.heavy_budget)
+        want = orc.heavy_sets(mask, budget.init_budget, budget.recent_budget)[0]
+        for h in range(Hq):
+            assert torch.equal(heavy_from_device(ctx, b, h), want[h]), f"set differs b={b} h={h}"
+        ref = orc.masked_attention(q[b:b + 1], ks[b][None], vs[b][None], mask)
+        ok, max_abs, rel = helpers.att_close(out[b:b + 1], ref)
+        assert ok, f"b={b}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
+    return identical, out, ctx, cache
+
+
+@pytest.mark.parametrize("name", ["case_a", "config0", "edge/short", "edge/p256", "edge/abs48"])
+def test_decode_step_end_to_end_against_reference_output(device, cases, name):
+    case = get_case(cases, name)
+    usa = synthetic.make_usa(case.q.shape[1], 128, 0, True)
+    ks, vs = [case.k[b] for b in range(case.k.shape[0])], [case.v[b] for b in range(case.v.shape[0])]
+    identical, out, ctx, cache = run_step_and_check(device, usa, case.q, ks, vs, budget_of(case))
+    codes_equal_ref = all(bool((cache.read_codes(b).cpu() == case.k_codes[b]).all()) for b in range(len(ks)))
+    codes_equal_ref &= bool(((ctx.q_codes.cpu().to(torch.int64) & ALL_BITS) == case.q_codes).all())
+    if codes_equal_ref:  # then everything downstream must equal the recorded reference run
+        want = orc.heavy_sets(case.mask, case.init, case.recent)
+        for b in range(len(ks)):
+            for h in range(case.q.shape[1]):
+                assert torch.equal(heavy_from_device(ctx, b, h), want[b][h])
+        ok, max_abs, rel = helpers.att_close(out, case.out)
+        assert ok, f"{name}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
+
+
+def test_ragged_batch_shuffled_pages(device):
+    Hq, Hkv, lens = 8, 2, [1, 2, 31, 255, 256, 257, 1500, 4097]
+    usa = synthetic.make_usa(Hq, 128, 2, True)
+    inp = synthetic.make_decode_inputs(94, lens, Hq, Hkv)
+    run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(16, 1.0 / 16, 32), shuffle_seed=3)
+
+
+def test_fp32_weights_step(device):
+    usa = synthetic.make_usa(8, 128, 5, bf16=False)
+    inp = synthetic.make_decode_inputs(95, [777, 300], 8, 2)
+    run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(8, 0.25, 8))
+
+
+def test_host_buffer_entry_point_equals_device_entry_point(device):
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(96, [900, 513], 8, 2)
+    budget = ha.Budget(16, 0.125, 16)
+    _, out_dev, _, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget)
+    _, out_host, _, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, via_host=True)
+    assert torch.equal(out_dev, out_host)
+
+
+def test_repeated_steps_grow_the_cache(device):
+    """Five consecutive tokens decoded through the same context: the appended rows and codes of
+    earlier steps are what later steps score and attend to."""
+    Hq, Hkv, S0, steps = 8, 2, 500, 5
+    usa = synthetic.make_usa(Hq, 128, 0, True)
+    inp = synthetic.make_decode_inputs(97, [S0 + steps], Hq, Hkv)
+    budget = ha.Budget(16, 0.125, 16)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, budget, usa, prefill_to=[S0])
+    ctx.hash_prefill()
+    qs = synthetic.make_decode_inputs(98, [steps], Hq, Hkv).k[0]  # any bf16-exact vectors serve as queries
+    for i in range(steps):
+        S = S0 + i + 1
+        cache.seq_lens += 1
+        q = qs[:, i].repeat_interleave(Hq // Hkv, dim=0)[None]
+        out = ctx.decode_step(q.to(device, torch.bfloat16), inp.k[0][None, :, S - 1].to(device, torch.bfloat16),
+                              inp.v[0][None, :, S - 1].to(device, torch.bfloat16)).float().cpu()
+        ctx.check_status()
+        k_codes = cache.read_codes(0).cpu()
+        q_codes = ctx.q_codes.cpu().to(torch.int64) & ALL_BITS
+        scores = orc.hamming_scores(q_codes, k_codes[None])
+        mask = orc.select_mask(scores, 16, 16, 0.125)
+        want = orc.heavy_sets(mask, 16, 16)[0]
+        for h in range(Hq):
+            assert torch.equal(heavy_from_device(ctx, 0, h), want[h])
+        ref = orc.masked_attention(q, inp.k[0][None, :, :S], inp.v[0][None, :, :S], mask)
+        assert helpers.att_close(out, ref)[0]
+    _, k_pre = helpers.oracle_preacts(usa, inp.q, inp.k[0][None])
+    assert helpers.codes_match(cache.read_codes(0).cpu(), orc.pack_codes(k_pre[0]), orc.band_mask(k_pre[0]))
+
+
+def test_kv_head_partition_is_bit_identical(device):
+    """Sharding by kv-head (what multi-GPU runs do) changes no bit: each shard run alone gives the
+    same codes, sets and output as the unsharded run."""
+    Hq, Hkv = 16, 4
+    usa = synthetic.make_usa(Hq, 128, 0, True)
+    inp = synthetic.make_decode_inputs(99, [1300, 700], Hq, Hkv)
+    budget = ha.Budget(16, 1.0 / 16, 16)
+    _, out_full, ctx_full, cache_full = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget)
+    packed = usa.packed(device)
+    for shard in range(2):
+        j0, j1 = shard * 2, shard * 2 + 2
+        ks, vs = [k[j0:j1] for k in inp.k], [v[j0:j1] for v in inp.v]
+        lens = inp.seq_lens
+        cache = ha.PagedHashKVCache(2, 2, max(lens), device, shuffle_seed=21 + shard)
+        for b, S in enumerate(lens):
+            cache.write_kv(b, ks[b][:, :S - 1], vs[b][:, :S - 1])
+        ctx = ha.SparseDecodeContext(cache, budget, packed.slice_heads(j0 * 4, j1 * 4))
+        ctx.hash_prefill()
+        cache.seq_lens += 1
+        out = ctx.decode_step(inp.q[:, j0 * 4:j1 * 4].contiguous().to(device, torch.bfloat16),
+                              torch.stack([k[:, -1] for k in ks]).to(device, torch.bfloat16),
+                              torch.stack([v[:, -1] for v in vs]).to(device, torch.bfloat16)).float().cpu()
+        ctx.check_status()
+        assert torch.equal(out, out_full[:, j0 * 4:j1 * 4])
+        assert torch.equal(ctx.sel_cnt.cpu(), ctx_full.sel_cnt[:, j0 * 4:j1 * 4].cpu())
+        for b in range(2):
+            assert torch.equal(cache.read_codes(b), cache_full.read_codes(b)[j0 * 4:j1 * 4])
+            for h in range(8):
+                assert torch.equal(heavy_from_device(ctx, b, h), heavy_from_device(ctx_full, b, j0 * 4 + h))
+
+
+def test_cuda_graph_replay(device):
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(100, [2000], 8, 2)
+    budget = ha.Budget(16, 0.125, 16)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, budget, usa)
+    ctx.hash_prefill()
+    q = inp.q.to(device, torch.bfloat16)
+    k_new, v_new = inp.k[0][None, :, -1].to(device, torch.bfloat16), inp.v[0][None, :, -1].to(device, torch.bfloat16)
+    out = torch.zeros_like(q)
+    eager = ctx.decode_step(q, k_new, v_new).clone()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            ctx.decode_step(q, k_new, v_new, out=out)
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+    ctx.check_status()
+
+
+# ------------------------------------------------------------------------------------------
+# errors are reported, not faulted
+# ------------------------------------------------------------------------------------------
+def test_wrapper_raises_value_error_on_bad_tensors(device):
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(101, [300], 8, 2)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, ha.Budget(16, 0.125, 16), usa)
+    q = inp.q.to(device, torch.bfloat16)
+    kn = inp.k[0][None, :, -1].to(device, torch.bfloat16)
+    with pytest.raises(ValueError, match="should be of size"):
+        ctx.decode_step(q[:, :4].contiguous(), kn, kn)
+    with pytest.raises(ValueError, match="must be torch.bfloat16"):
+        ctx.decode_step(q.float(), kn, kn)
+    with pytest.raises(ValueError, match="must live on"):
+        ctx.decode_step(q.cpu(), kn, kn)
+    with pytest.raises(ValueError, match="contiguous"):
+        ctx.decode_step(q.transpose(1, 2).contiguous().transpose(1, 2), kn, kn)
+    with pytest.raises(ValueError, match="do not match"):
+        ha.SparseDecodeContext(cache, ha.Budget(), synthetic.make_usa(4, 128, 0, True).packed(device))
+
+
+def test_bad_page_id_and_bad_length_are_reported_through_the_status_word(device):
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(102, [600], 8, 2)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, ha.Budget(16, 0.125, 16), usa)
+    q = inp.q.to(device, torch.bfloat16)
+    kn = inp.k[0][None, :, -1].to(device, torch.bfloat16)
+    good_table = cache.page_table.clone()
+    cache.page_table[0, 1] = cache.num_pages + 5  # out of the pool: must be caught, not dereferenced
+    ctx.decode_step(q, kn, kn)
+    with pytest.raises(RuntimeError, match="page id"):
+        ctx.check_status()
+    cache.page_table.copy_(good_table)
+    cache.seq_lens[0] = 0
+    ctx.decode_step(q, kn, kn)
+    with pytest.raises(RuntimeError, match="sequence length"):
+        ctx.check_status()
+    cache.seq_lens[0] = cache.max_pages * 256 + 1
+    ctx.hash_prefill()
+    with pytest.raises(RuntimeError, match="sequence length"):
+        ctx.check_status()
+    # the context stays usable
+    cache.seq_lens[0] = 600
+    ctx.hash_prefill()
+    out = ctx.decode_step(q, kn, kn)
+    ctx.check_status()
+    assert bool(torch.isfinite(out.float()).all())
