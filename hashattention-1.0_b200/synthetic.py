@@ -142,3 +142,39 @@ def ragged_lengths(config_index: int, batch: int, low: int, high: int) -> list[i
     """Per-sequence context lengths uniform in [low, high] from seed 1000 + config_index."""
     g = torch.Generator().manual_seed(1000 + config_index)
     return torch.randint(low, high + 1, (batch,), generator=g).tolist()
+
+
+def fill_cache_on_device(cache, seq_lens, seed: int) -> None:
+    """Fills a paged cache directly on its device with keys / values of the same distribution as
+    :func:`make_decode_inputs` (N(0,1), outlier channels x8, RoPE, bf16), drawn from the device
+    generator. For benchmarks, where the tensors are too large to draw on the host; parity tests
+    use the host generators above."""
+    dev = cache.device
+    g = torch.Generator(device=dev).manual_seed(seed)
+    inv_freq = 1.0 / (ROPE_THETA ** (torch.arange(0, 128, 2, dtype=torch.float32, device=dev) / 128))
+    for b, S in enumerate(int(s) for s in seq_lens):
+        for start in range(0, S, 32768):
+            n = min(32768, S - start)
+            k = torch.randn(cache.num_kv_heads, n, 128, generator=g, device=dev)
+            v = torch.randn(cache.num_kv_heads, n, 128, generator=g, device=dev)
+            k[..., list(OUTLIER_CHANNELS)] *= OUTLIER_SCALE
+            freqs = torch.arange(start, start + n, device=dev, dtype=torch.float32)[:, None] * inv_freq[None, :]
+            emb = torch.cat([freqs, freqs], dim=-1)
+            k = apply_rope(k, emb.cos(), emb.sin())
+            cache.write_kv(b, k, v, start=start)
+
+
+def algorithmic_bytes(seq_lens, num_q_heads: int, num_kv_heads: int, init_budget: int, recent_budget: int,
+                      heavy_budget: float, head_dim: int = 128) -> dict:
+    """Bytes one decode step of one layer must move: the u32 key codes of every token and query
+    head, a bf16 K row and V row per attended token (sink / recent rows once per kv-head, heavy
+    rows once per query head) and q / out."""
+    hash_b = kv_b = 0
+    for S in (int(s) for s in seq_lens):
+        hb = int(heavy_budget) if heavy_budget > 1.0 else int(S * heavy_budget)
+        edge = min(S, init_budget + recent_budget)
+        heavy = min(hb, max(0, S - init_budget - recent_budget))
+        hash_b += 4 * num_q_heads * S
+        kv_b += 2 * head_dim * 2 * (num_kv_heads * edge + num_q_heads * heavy)
+    qo_b = len(seq_lens) * num_q_heads * head_dim * 2 * 2
+    return {"hash": hash_b, "kv": kv_b, "qo": qo_b, "total": hash_b + kv_b + qo_b}
