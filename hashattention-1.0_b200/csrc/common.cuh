@@ -24,12 +24,13 @@ constexpr int kSelThreads = 256;
 constexpr int kSelWarps = kSelThreads / 32;
 constexpr int kMaxChunkPages = 16;  // <= 16 tokens per lane live in registers
 
-// sparse decode tiling: a CTA of 256 threads = 16 half-warp workers, 8 rows per worker.
+// sparse decode tiling: a cluster of 8 CTAs per (sequence, query head); a CTA of 256 threads =
+// 16 half-warp workers, 8 rows per worker and round.
 constexpr int kAttThreads = 256;
 constexpr int kAttWorkers = kAttThreads / 16;
 constexpr int kAttRowsPerWorker = 8;
-constexpr int kAttRows = kAttWorkers * kAttRowsPerWorker;  // 128 rows per CTA
-constexpr int kPartStride = kHeadDim + 2;                   // m, l, acc[128]
+constexpr int kAttCluster = 8;
+constexpr int kAttClusterRows = kAttCluster * kAttWorkers;  // rows of one register slot across the cluster
 
 struct SeqRange {
     int S;   // cached tokens incl. the current one
@@ -55,11 +56,11 @@ __host__ __device__ inline SeqRange seq_range(int S, int init_budget, int recent
     return r;
 }
 
+// Pages per score/select chunk: 4, 8 or 16 (the kernels are compiled for these), about
+// max_pages / 32 so that a sequence is cut into roughly 32 chunks.
 __host__ __device__ inline int chunk_pages_for(int max_pages) {
-    int cp = (max_pages + 31) / 32;
-    if (cp < 4) cp = 4;
-    if (cp > kMaxChunkPages) cp = kMaxChunkPages;
-    return cp;
+    const int want = (max_pages + 31) / 32;
+    return want <= 4 ? 4 : (want <= 8 ? 8 : kMaxChunkPages);
 }
 
 __host__ __device__ inline int num_chunks_for(int max_pages) {

@@ -11,7 +11,7 @@
 
 namespace ha {
 
-constexpr int kHashDecodeThreads = 256;
+constexpr int kHashDecodeThreads = 512;
 
 struct HashDecodeParams {
     const __nv_bfloat16* q;      // [B][Hq][128]
@@ -83,36 +83,34 @@ __device__ __forceinline__ float half_warp_sum(float v) {
 
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 
-// Thread mapping: 8 warps; a half-warp (16 lanes x 8 columns) covers one 128-wide weight row.
-// In the two hidden layers warp w owns output rows [16w, 16w+16): load j of a lane belongs to
-// row 16w + 2j + (lane >> 4). In the last layer warp w owns rows [4w, 4w+4).
-// One head's MLP held in the registers of a 256-thread CTA.
+// Thread mapping: 16 warps; a half-warp (16 lanes x 8 columns) covers one 128-wide weight row.
+// In the two hidden layers warp w owns output rows [8w, 8w+8): load j of a lane belongs to
+// row 8w + 2j + (lane >> 4). In the last layer warp w owns rows 2w and 2w+1.
+constexpr int kMlpWarps = kHashDecodeThreads / 32;   // 16
+constexpr int kRowLoads = kHidden / kMlpWarps / 2;   // 4 loads per lane and hidden layer
+
+// One head's MLP held in the registers of a 512-thread CTA.
 template <typename WT>
 struct MlpRegs {
-    Row8<WT> w0[8], w1[8], w2[2];
-    float b0[8], b1[8], b2[2];
+    Row8<WT> w0[kRowLoads], w1[kRowLoads], w2;
+    float b0[kRowLoads], b1[kRowLoads], b2;
 
     // All three layers are fetched back to back so that their DRAM latency is paid once.
     __device__ __forceinline__ void load(const WT* W, const float* bias, int warp, int half, int col) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int row = warp * 16 + 2 * j + half;
+        for (int j = 0; j < kRowLoads; ++j) {
+            const int row = warp * (2 * kRowLoads) + 2 * j + half;
             w0[j].load(W + row * kHeadDim + col);
             w1[j].load(W + kHidden * kHeadDim + row * kHidden + col);
         }
+        w2.load(W + kHidden * kHeadDim + kHidden * kHidden + (warp * 2 + half) * kHidden + col);
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int row = warp * 4 + 2 * j + half;
-            w2[j].load(W + kHidden * kHeadDim + kHidden * kHidden + row * kHidden + col);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int row = warp * 16 + 2 * j + half;
+        for (int j = 0; j < kRowLoads; ++j) {
+            const int row = warp * (2 * kRowLoads) + 2 * j + half;
             b0[j] = __ldg(bias + row);
             b1[j] = __ldg(bias + kHidden + row);
         }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) b2[j] = __ldg(bias + 2 * kHidden + warp * 4 + 2 * j + half);
+        b2 = __ldg(bias + 2 * kHidden + warp * 2 + half);
     }
 };
 
@@ -122,13 +120,37 @@ struct MlpSmem {
     float out[kCodeBits];
 };
 
-// Evaluates the MLP on one 128-element bf16 row. Must be called by all 256 threads; on return
-// (after its last barrier) sm.out[0..32) holds the final-layer pre-activations. The caller may
-// call it again without a further barrier: each buffer is rewritten only after barriers that
-// every reader of the previous round has passed.
+__device__ __forceinline__ void load_x8(const float* s, float (&x)[8]) {
+    const float4 lo = *reinterpret_cast<const float4*>(s);
+    const float4 hi = *reinterpret_cast<const float4*>(s + 4);
+    x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
+    x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+}
+
+// One hidden layer: every lane of a half-warp ends up with the kRowLoads row sums of its half;
+// lane j of the half then applies bias + SiLU to row j and stores it (one SiLU per lane).
 template <typename WT>
+__device__ __forceinline__ void hidden_layer(const Row8<WT> (&w)[kRowLoads], const float (&bias)[kRowLoads],
+                                             const float (&x)[8], float* dst, int warp, int lane) {
+    const int half = lane >> 4, sub = lane & 15;
+    float mine = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRowLoads; ++j) {
+        const float s = half_warp_sum(w[j].dot(x)) + bias[j];
+        mine = sub == j ? s : mine;
+    }
+    if (sub < kRowLoads) dst[warp * (2 * kRowLoads) + 2 * sub + half] = silu(mine);
+}
+
+// Evaluates the MLP on one 128-element bf16 row. Must be called by all threads of the CTA; on
+// return (after its last barrier) sm.out[0..32) holds the final-layer pre-activations.
+// `between` runs after the first layer (a place to issue loads whose address depends on a value
+// that was requested before the call). The caller may call mlp_eval again without a further
+// barrier: each buffer is rewritten only after barriers that every reader of the previous
+// round has passed.
+template <typename WT, typename F>
 __device__ __forceinline__ void mlp_eval(const MlpRegs<WT>& r, const __nv_bfloat16* xrow,
-                                         MlpSmem& sm, int warp, int lane) {
+                                         MlpSmem& sm, int warp, int lane, F&& between) {
     const int half = lane >> 4, col = (lane & 15) * 8;
     float x[8];
     {
@@ -138,34 +160,16 @@ __device__ __forceinline__ void mlp_eval(const MlpRegs<WT>& r, const __nv_bfloat
         x[4] = bf16_lo(raw.z); x[5] = bf16_hi(raw.z);
         x[6] = bf16_lo(raw.w); x[7] = bf16_hi(raw.w);
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float s = half_warp_sum(r.w0[j].dot(x)) + r.b0[j];
-        if ((lane & 15) == 0) sm.h0[warp * 16 + 2 * j + half] = silu(s);
-    }
+    hidden_layer(r.w0, r.b0, x, sm.h0, warp, lane);
+    between();
     __syncthreads();
-    {
-        const float4 lo = *reinterpret_cast<const float4*>(sm.h0 + col);
-        const float4 hi = *reinterpret_cast<const float4*>(sm.h0 + col + 4);
-        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
-        x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float s = half_warp_sum(r.w1[j].dot(x)) + r.b1[j];
-        if ((lane & 15) == 0) sm.h1[warp * 16 + 2 * j + half] = silu(s);
-    }
+    load_x8(sm.h0 + col, x);
+    hidden_layer(r.w1, r.b1, x, sm.h1, warp, lane);
     __syncthreads();
+    load_x8(sm.h1 + col, x);
     {
-        const float4 lo = *reinterpret_cast<const float4*>(sm.h1 + col);
-        const float4 hi = *reinterpret_cast<const float4*>(sm.h1 + col + 4);
-        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w;
-        x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
-    }
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const float s = half_warp_sum(r.w2[j].dot(x)) + r.b2[j];
-        if ((lane & 15) == 0) sm.out[warp * 4 + 2 * j + half] = s;
+        const float s = half_warp_sum(r.w2.dot(x)) + r.b2;
+        if ((lane & 15) == 0) sm.out[warp * 2 + half] = s;
     }
     __syncthreads();
 }
@@ -193,7 +197,16 @@ hash_decode_kernel(const HashDecodeParams p) {
     for (int b = b_begin; b < b_end; ++b) {
         const __nv_bfloat16* xrow = side == 0 ? p.q + ((size_t)b * Hq + h) * kHeadDim
                                               : p.k_new + ((size_t)b * p.Hkv + kvh) * kHeadDim;
-        mlp_eval(regs, xrow, sm, warp, lane);
+        // key side: the append slot needs seq_lens[b], then a page-table entry; both are fetched
+        // underneath the MLP arithmetic
+        int S = 1, page = 0;
+        if (side == 1) S = p.seq_lens[b];
+        mlp_eval(regs, xrow, sm, warp, lane, [&] {
+            if (side == 1) {
+                const int pidx = min(max(S - 1, 0) / kPage, p.max_pages - 1);
+                page = p.page_table[(size_t)b * p.max_pages + pidx];
+            }
+        });
         if (warp != 0) continue;
 
         const float pre = sm.out[lane];
@@ -205,13 +218,11 @@ hash_decode_kernel(const HashDecodeParams p) {
             if (lane == 0) p.q_codes[(size_t)b * Hq + h] = code;
             continue;
         }
-        const int S = p.seq_lens[b];
         if (S < 1 || S > p.max_pages * kPage) {
             if (lane == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
             continue;
         }
         const int tok = S - 1;
-        const int page = p.page_table[(size_t)b * p.max_pages + tok / kPage];
         if (page < 0 || page >= p.num_pages) {
             if (lane == 0) report(p.status, HA_ERR_BAD_PAGE);
             continue;
@@ -275,7 +286,7 @@ hash_prefill_simt_kernel(const HashPrefillParams p) {
     const size_t slot0 = ((size_t)page * p.Hkv + kvh) * kPage;
     for (int t = t_begin; t < t_end; ++t) {
         const size_t slot = slot0 + t % kPage;
-        mlp_eval(regs, p.k_pages + slot * kHeadDim, sm, warp, lane);
+        mlp_eval(regs, p.k_pages + slot * kHeadDim, sm, warp, lane, [] {});
         if (warp == 0) {
             const float pre = sm.out[lane];
             const uint32_t code = __ballot_sync(0xffffffffu, pre > 0.0f);

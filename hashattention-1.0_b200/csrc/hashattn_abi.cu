@@ -46,53 +46,99 @@ int check_weights(const ha_hash_weights_t* w, bool need_q, bool need_k) {
     return HA_OK;
 }
 
-// Attention splits: the rows of one (sequence, query head) never exceed
-// init + recent + sel_stride, nor the longest sequence the page table can describe.
-int num_splits(const ha_shape_t* s, const ha_budget_t* b) {
-    long long rows = (long long)s->sel_stride + b->init_budget + b->recent_budget;
-    const long long cap = (long long)s->max_pages * kPage;
-    if (rows > cap) rows = cap;
-    return (int)((rows + kAttRows - 1) / kAttRows);
-}
-
 struct Workspace {
-    unsigned int* counters;  // [B][Hq]
-    uint32_t* hist;          // [B][Hkv][nchunks][4*33]
-    float* partials;         // [B][Hq][nsplits][130]
+    uint32_t* hist;     // [B][Hkv][4*33][nchunks] per-chunk score histograms
+    int32_t* sel_rows;  // [B][Hq][sel_stride] physical rows of the selected tokens
     size_t bytes;
 };
 
-Workspace carve(const ha_shape_t* s, const ha_budget_t* b, void* base) {
+Workspace carve(const ha_shape_t* s, void* base) {
     const size_t Hq = (size_t)s->num_kv_heads * kGroup;
-    const size_t n_counters = (size_t)s->batch * Hq;
     const size_t n_hist = (size_t)s->batch * s->num_kv_heads * num_chunks_for(s->max_pages) * kGroup * kBins;
-    const size_t n_part = (size_t)s->batch * Hq * num_splits(s, b) * kPartStride;
     char* p = static_cast<char*>(base);
     Workspace w;
     size_t off = 0;
-    w.counters = reinterpret_cast<unsigned int*>(p + off);
-    off += align_up(n_counters * sizeof(unsigned int));
     w.hist = reinterpret_cast<uint32_t*>(p + off);
     off += align_up(n_hist * sizeof(uint32_t));
-    w.partials = reinterpret_cast<float*>(p + off);
-    off += align_up(n_part * sizeof(float));
+    w.sel_rows = reinterpret_cast<int32_t*>(p + off);
+    off += align_up((size_t)s->batch * Hq * s->sel_stride * sizeof(int32_t));
     w.bytes = off;
     return w;
 }
 
+// Every kernel is launched with programmatic stream serialization (it may start while its
+// predecessor drains and synchronises itself with griddepcontrol.wait); cluster_x > 1 adds a
+// thread-block cluster along x.
 template <typename... KArgs, typename... Args>
-cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, Args&&... args) {
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t stream, int cluster_x,
+                   Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
-    cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (cluster_x > 1) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = cluster_x;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
+    cfg.attrs = attr;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+}  // namespace
+}  // namespace ha
+
+namespace ha {
+namespace {
+
+// sel == nullptr with physical == true: use the physical rows select_kernel left in the workspace.
+int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
+                       const void* q, const void* k_pages, const void* v_pages,
+                       const int32_t* page_table, const int32_t* seq_lens,
+                       const int32_t* sel, bool physical, float sm_scale,
+                       void* out, void* workspace, size_t workspace_bytes,
+                       int32_t* status, void* stream) {
+    int rc = check_shape(shape);
+    if (rc != HA_OK) return rc;
+    rc = check_budget(budget);
+    if (rc != HA_OK) return rc;
+    if (q == nullptr || k_pages == nullptr || v_pages == nullptr || page_table == nullptr ||
+        seq_lens == nullptr || out == nullptr || status == nullptr || !std::isfinite(sm_scale))
+        return HA_ERR_BAD_ARG;
+    if (workspace == nullptr) return HA_ERR_WORKSPACE;
+    const Workspace w = carve(shape, workspace);
+    if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
+
+    SparseDecodeParams p;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+    p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+    p.page_table = page_table;
+    p.seq_lens = seq_lens;
+    p.sel = physical ? w.sel_rows : sel;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.status = status;
+    p.B = shape->batch;
+    p.Hkv = shape->num_kv_heads;
+    p.max_pages = shape->max_pages;
+    p.num_pages = shape->num_pages;
+    p.sel_stride = shape->sel_stride;
+    p.init_budget = budget->init_budget;
+    p.recent_budget = budget->recent_budget;
+    p.heavy_budget = budget->heavy_budget;
+    p.scale_log2e = sm_scale * 1.4426950408889634f;
+    const dim3 grid(kAttCluster, shape->num_kv_heads * kGroup, shape->batch);
+    const cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const cudaError_t e = physical ? launch(sparse_decode_kernel<true>, grid, dim3(kAttThreads), s, kAttCluster, p)
+                                   : launch(sparse_decode_kernel<false>, grid, dim3(kAttThreads), s, kAttCluster, p);
+    return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
 }  // namespace
@@ -121,7 +167,7 @@ const char* ha_status_str(int status) {
 
 size_t ha_workspace_bytes(const ha_shape_t* shape, const ha_budget_t* budget) {
     if (check_shape(shape) != HA_OK || check_budget(budget) != HA_OK) return 0;
-    return carve(shape, budget, nullptr).bytes;
+    return carve(shape, nullptr).bytes;
 }
 
 int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* workspace,
@@ -131,10 +177,11 @@ int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* 
     rc = check_budget(budget);
     if (rc != HA_OK) return rc;
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
-    const Workspace w = carve(shape, budget, workspace);
+    const Workspace w = carve(shape, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
-    const size_t n = (size_t)shape->batch * shape->num_kv_heads * kGroup * sizeof(unsigned int);
-    if (cudaMemsetAsync(w.counters, 0, n, static_cast<cudaStream_t>(stream)) != cudaSuccess)
+    // the kernels keep no state in the workspace between calls; clearing it only makes runs
+    // that read it before writing (a misuse) reproducible
+    if (cudaMemsetAsync(workspace, 0, w.bytes, static_cast<cudaStream_t>(stream)) != cudaSuccess)
         return HA_ERR_LAUNCH;
     return HA_OK;
 }
@@ -182,10 +229,10 @@ int ha_hash_decode(const ha_shape_t* shape, const ha_hash_weights_t* weights,
     cudaError_t e;
     if (weights->dtype == HA_WEIGHTS_BF16)
         e = launch(hash_decode_kernel<__nv_bfloat16>, grid, dim3(kHashDecodeThreads),
-                   static_cast<cudaStream_t>(stream), p);
+                   static_cast<cudaStream_t>(stream), 1, p);
     else
         e = launch(hash_decode_kernel<float>, grid, dim3(kHashDecodeThreads),
-                   static_cast<cudaStream_t>(stream), p);
+                   static_cast<cudaStream_t>(stream), 1, p);
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
@@ -218,10 +265,10 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
     cudaError_t e;
     if (weights->dtype == HA_WEIGHTS_BF16)
         e = launch(hash_prefill_simt_kernel<__nv_bfloat16>, grid, dim3(kHashDecodeThreads),
-                   static_cast<cudaStream_t>(stream), p);
+                   static_cast<cudaStream_t>(stream), 1, p);
     else
         e = launch(hash_prefill_simt_kernel<float>, grid, dim3(kHashDecodeThreads),
-                   static_cast<cudaStream_t>(stream), p);
+                   static_cast<cudaStream_t>(stream), 1, p);
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
@@ -238,7 +285,7 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
         sel_idx == nullptr || sel_cnt == nullptr || status == nullptr)
         return HA_ERR_BAD_ARG;
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
-    const Workspace w = carve(shape, budget, workspace);
+    const Workspace w = carve(shape, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
 
     SelectParams p;
@@ -248,6 +295,7 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
     p.seq_lens = seq_lens;
     p.hist = w.hist;
     p.sel_idx = sel_idx;
+    p.sel_rows = w.sel_rows;
     p.sel_cnt = sel_cnt;
     p.scores_dbg = scores_dbg;
     p.status = status;
@@ -256,16 +304,28 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
     p.max_pages = shape->max_pages;
     p.num_pages = shape->num_pages;
     p.sel_stride = shape->sel_stride;
-    p.chunk_pages = chunk_pages_for(shape->max_pages);
     p.nchunks = num_chunks_for(shape->max_pages);
     p.init_budget = budget->init_budget;
     p.recent_budget = budget->recent_budget;
     p.heavy_budget = budget->heavy_budget;
     const dim3 grid(p.nchunks, shape->num_kv_heads, shape->batch);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (launch(score_hist_kernel, grid, dim3(kSelThreads), s, p) != cudaSuccess) return HA_ERR_LAUNCH;
-    if (launch(select_kernel, grid, dim3(kSelThreads), s, p) != cudaSuccess) return HA_ERR_LAUNCH;
-    return HA_OK;
+    cudaError_t e1, e2;
+    switch (chunk_pages_for(shape->max_pages)) {
+        case 4:
+            e1 = launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
+            e2 = launch(select_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
+            break;
+        case 8:
+            e1 = launch(score_hist_kernel<8>, grid, dim3(kSelThreads), s, 1, p);
+            e2 = launch(select_kernel<8>, grid, dim3(kSelThreads), s, 1, p);
+            break;
+        default:
+            e1 = launch(score_hist_kernel<16>, grid, dim3(kSelThreads), s, 1, p);
+            e2 = launch(select_kernel<16>, grid, dim3(kSelThreads), s, 1, p);
+            break;
+    }
+    return e1 == cudaSuccess && e2 == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
 int ha_sparse_decode(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -274,45 +334,9 @@ int ha_sparse_decode(const ha_shape_t* shape, const ha_budget_t* budget,
                      const int32_t* sel_idx, const int32_t* sel_cnt, float sm_scale,
                      void* out, void* workspace, size_t workspace_bytes,
                      int32_t* status, void* stream) {
-    int rc = check_shape(shape);
-    if (rc != HA_OK) return rc;
-    rc = check_budget(budget);
-    if (rc != HA_OK) return rc;
-    if (q == nullptr || k_pages == nullptr || v_pages == nullptr || page_table == nullptr ||
-        seq_lens == nullptr || sel_idx == nullptr || sel_cnt == nullptr || out == nullptr ||
-        status == nullptr || !std::isfinite(sm_scale))
-        return HA_ERR_BAD_ARG;
-    if (workspace == nullptr) return HA_ERR_WORKSPACE;
-    const Workspace w = carve(shape, budget, workspace);
-    if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
-
-    SparseDecodeParams p;
-    p.q = static_cast<const __nv_bfloat16*>(q);
-    p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
-    p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
-    p.page_table = page_table;
-    p.seq_lens = seq_lens;
-    p.sel_idx = sel_idx;
-    p.sel_cnt = sel_cnt;
-    p.out = static_cast<__nv_bfloat16*>(out);
-    p.partials = w.partials;
-    p.counters = w.counters;
-    p.status = status;
-    p.B = shape->batch;
-    p.Hkv = shape->num_kv_heads;
-    p.max_pages = shape->max_pages;
-    p.num_pages = shape->num_pages;
-    p.sel_stride = shape->sel_stride;
-    p.nsplits = num_splits(shape, budget);
-    p.init_budget = budget->init_budget;
-    p.recent_budget = budget->recent_budget;
-    p.heavy_budget = budget->heavy_budget;
-    p.scale_log2e = sm_scale * 1.4426950408889634f;
-    const dim3 grid(p.nsplits, shape->num_kv_heads * kGroup, shape->batch);
-    if (launch(sparse_decode_kernel, grid, dim3(kAttThreads), static_cast<cudaStream_t>(stream), p) !=
-        cudaSuccess)
-        return HA_ERR_LAUNCH;
-    return HA_OK;
+    if (sel_idx == nullptr || sel_cnt == nullptr) return check_shape(shape) != HA_OK ? check_shape(shape) : HA_ERR_BAD_ARG;
+    return sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, sel_idx, false,
+                              sm_scale, out, workspace, workspace_bytes, status, stream);
 }
 
 int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -329,8 +353,9 @@ int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
     rc = ha_score_select(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
                          nullptr, workspace, workspace_bytes, status, stream);
     if (rc != HA_OK) return rc;
-    return ha_sparse_decode(shape, budget, q, k_pages, v_pages, page_table, seq_lens, sel_idx, sel_cnt,
-                            sm_scale, out, workspace, workspace_bytes, status, stream);
+    // the selection kernel left the physical rows of the heavy tokens in the workspace
+    return sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, nullptr, true,
+                              sm_scale, out, workspace, workspace_bytes, status, stream);
 }
 
 int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
