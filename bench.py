@@ -342,7 +342,7 @@ def run_gpu_arm(args):
                              f"step, visited round-robin", "launch": "CUDA graph of one step per layer instance",
                        "partition": "each GPU decodes its own sequences (all 8 kv heads); no collective on the path"},
             "roofline": roofline, "pipeline": pipeline, "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks,
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": 5 * args.steps,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

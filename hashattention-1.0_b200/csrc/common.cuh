@@ -24,13 +24,13 @@ constexpr int kSelThreads = 256;
 constexpr int kSelWarps = kSelThreads / 32;
 constexpr int kMaxChunkPages = 16;  // <= 16 tokens per lane live in registers
 
-// sparse decode tiling: a cluster of 8 CTAs per (sequence, query head); a CTA of 256 threads =
-// 16 half-warp workers, 8 rows per worker and round.
-constexpr int kAttThreads = 256;
+// sparse decode tiling: a CTA of 128 threads = 8 half-warp workers, 4 rows per worker and round.
+constexpr int kAttThreads = 128;
 constexpr int kAttWorkers = kAttThreads / 16;
-constexpr int kAttRowsPerWorker = 8;
-constexpr int kAttCluster = 8;
-constexpr int kAttClusterRows = kAttCluster * kAttWorkers;  // rows of one register slot across the cluster
+constexpr int kAttRowsPerWorker = 4;
+constexpr int kAttRoundRows = kAttWorkers * kAttRowsPerWorker;  // 32 rows per CTA and round
+constexpr int kAttMaxRounds = 8;
+constexpr int kPartStride = kHeadDim + 2;                        // m, l, acc[128]
 
 struct SeqRange {
     int S;   // cached tokens incl. the current one

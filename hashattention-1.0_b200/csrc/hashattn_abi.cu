@@ -46,13 +46,35 @@ int check_weights(const ha_hash_weights_t* w, bool need_q, bool need_k) {
     return HA_OK;
 }
 
+// How the attended rows of one (sequence, query head) are cut into CTAs: never more rows than
+// init + recent + sel_stride, nor than the longest sequence the page table can describe; rounds
+// grows with the total so that big problems do not drown in partials.
+struct AttSplit {
+    int rounds, nsplits;
+};
+
+AttSplit att_split(const ha_shape_t* s, const ha_budget_t* b) {
+    long long rows = (long long)s->sel_stride + b->init_budget + b->recent_budget;
+    const long long cap = (long long)s->max_pages * kPage;
+    if (rows > cap) rows = cap;
+    const long long total = rows * s->batch * s->num_kv_heads * kGroup;
+    long long rounds = (total + kAttRoundRows * 4096LL - 1) / (kAttRoundRows * 4096LL);
+    if (rounds < 1) rounds = 1;
+    if (rounds > kAttMaxRounds) rounds = kAttMaxRounds;
+    AttSplit a;
+    a.rounds = (int)rounds;
+    a.nsplits = (int)((rows + kAttRoundRows * rounds - 1) / (kAttRoundRows * rounds));
+    return a;
+}
+
 struct Workspace {
     uint32_t* hist;     // [B][Hkv][4*33][nchunks] per-chunk score histograms
     int32_t* sel_rows;  // [B][Hq][sel_stride] physical rows of the selected tokens
+    float* partials;    // [B][Hq][nsplits][130] attention partials
     size_t bytes;
 };
 
-Workspace carve(const ha_shape_t* s, void* base) {
+Workspace carve(const ha_shape_t* s, const ha_budget_t* b, void* base) {
     const size_t Hq = (size_t)s->num_kv_heads * kGroup;
     const size_t n_hist = (size_t)s->batch * s->num_kv_heads * num_chunks_for(s->max_pages) * kGroup * kBins;
     char* p = static_cast<char*>(base);
@@ -62,6 +84,8 @@ Workspace carve(const ha_shape_t* s, void* base) {
     off += align_up(n_hist * sizeof(uint32_t));
     w.sel_rows = reinterpret_cast<int32_t*>(p + off);
     off += align_up((size_t)s->batch * Hq * s->sel_stride * sizeof(int32_t));
+    w.partials = reinterpret_cast<float*>(p + off);
+    off += align_up((size_t)s->batch * Hq * att_split(s, b).nsplits * kPartStride * sizeof(float));
     w.bytes = off;
     return w;
 }
@@ -113,7 +137,7 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
         seq_lens == nullptr || out == nullptr || status == nullptr || !std::isfinite(sm_scale))
         return HA_ERR_BAD_ARG;
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
-    const Workspace w = carve(shape, workspace);
+    const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
 
     SparseDecodeParams p;
@@ -134,10 +158,16 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     p.recent_budget = budget->recent_budget;
     p.heavy_budget = budget->heavy_budget;
     p.scale_log2e = sm_scale * 1.4426950408889634f;
-    const dim3 grid(kAttCluster, shape->num_kv_heads * kGroup, shape->batch);
+    const AttSplit split = att_split(shape, budget);
+    p.partials = w.partials;
+    p.nsplits = split.nsplits;
+    p.rounds = split.rounds;
+    const dim3 grid(split.nsplits, shape->num_kv_heads * kGroup, shape->batch);
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const cudaError_t e = physical ? launch(sparse_decode_kernel<true>, grid, dim3(kAttThreads), s, kAttCluster, p)
-                                   : launch(sparse_decode_kernel<false>, grid, dim3(kAttThreads), s, kAttCluster, p);
+    cudaError_t e = physical ? launch(sparse_gather_kernel<true>, grid, dim3(kAttThreads), s, 1, p)
+                             : launch(sparse_gather_kernel<false>, grid, dim3(kAttThreads), s, 1, p);
+    if (e == cudaSuccess && split.nsplits > 1)
+        e = launch(sparse_merge_kernel, dim3(shape->num_kv_heads * kGroup, shape->batch), dim3(kHeadDim), s, 1, p);
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
@@ -167,7 +197,7 @@ const char* ha_status_str(int status) {
 
 size_t ha_workspace_bytes(const ha_shape_t* shape, const ha_budget_t* budget) {
     if (check_shape(shape) != HA_OK || check_budget(budget) != HA_OK) return 0;
-    return carve(shape, nullptr).bytes;
+    return carve(shape, budget, nullptr).bytes;
 }
 
 int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* workspace,
@@ -177,7 +207,7 @@ int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* 
     rc = check_budget(budget);
     if (rc != HA_OK) return rc;
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
-    const Workspace w = carve(shape, workspace);
+    const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
     // the kernels keep no state in the workspace between calls; clearing it only makes runs
     // that read it before writing (a misuse) reproducible
@@ -285,7 +315,7 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
         sel_idx == nullptr || sel_cnt == nullptr || status == nullptr)
         return HA_ERR_BAD_ARG;
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
-    const Workspace w = carve(shape, workspace);
+    const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
 
     SelectParams p;

@@ -1,14 +1,15 @@
 // Sparse GQA flash-decode over the selected rows of the paged K / V cache.
 //
 // For query head h of sequence b the attended rows are, in this order, the sink tokens
-// [0, lo), the heavy tokens selected for (b, h) and the recent tokens [hi, S). One thread-block
-// cluster of 8 CTAs owns one (b, h); row position pos goes to CTA (pos / 16) % 8, half-warp
-// pos % 16, so the rows spread evenly over the cluster whatever their number. Each half-warp
-// gathers 8 rows of K and V per round straight into registers (sixteen 16-byte loads in flight
-// per lane), computes the scaled dot products with shuffles and keeps an online softmax. The CTA
-// reduces its 16 half-warps in shared memory; the cluster then merges the 8 CTA partials
-// through distributed shared memory (each CTA finishes 16 of the 128 output dimensions) and
-// writes the bf16 output. Nothing goes through global memory but the rows and the result.
+// [0, lo), the heavy tokens selected for (b, h) and the recent tokens [hi, S). The rows are cut
+// into splits of 32 * rounds rows. Gathering random 256-byte rows is latency bound unless the
+// SM is full of threads that each keep only a few loads in flight, so the gather kernel is
+// built from many light CTAs: 128 threads = 8 half-warps, a half-warp owning four rows per
+// round (lane = 8 of the 128 dimensions, eight 16-byte loads in flight per lane), dot products
+// by shuffles, online softmax in registers, CTA reduction by shuffle and shared memory, one
+// (max, sum, acc[128]) partial per CTA. A second, tiny kernel merges the partials of each
+// (b, h) with a log-sum-exp and writes the bf16 output; a (b, h) that fits one split is
+// finished by the gather kernel itself.
 //
 // Replaces hashattention/hashattention_llama.py:578-623: there every masked position is set
 // to finfo.min before an fp32 softmax, i.e. contributes exactly 0, so the softmax runs
@@ -20,13 +21,9 @@
 // valid row and masked afterwards.
 #pragma once
 
-#include <cooperative_groups.h>
-
 #include "common.cuh"
 
 namespace ha {
-
-namespace cg = cooperative_groups;
 
 struct SparseDecodeParams {
     const __nv_bfloat16* q;        // [B][Hq][128]
@@ -36,8 +33,9 @@ struct SparseDecodeParams {
     const int32_t* seq_lens;
     const int32_t* sel;            // [B][Hq][sel_stride]: token indices, or physical rows (kPhysical)
     __nv_bfloat16* out;            // [B][Hq][128]
+    float* partials;               // workspace: [B][Hq][nsplits][130]
     int32_t* status;
-    int B, Hkv, max_pages, num_pages, sel_stride;
+    int B, Hkv, max_pages, num_pages, sel_stride, nsplits, rounds;
     int init_budget, recent_budget;
     double heavy_budget;
     float scale_log2e;             // sm_scale * log2(e)
@@ -62,27 +60,58 @@ __device__ __forceinline__ float dot8(const uint4& raw, const float (&x)[8]) {
     return s;
 }
 
-struct AttPartial {  // one CTA's softmax state, read by the other CTAs of the cluster
-    float m, l;
-    __align__(16) float acc[kHeadDim];
+// Rows attended by (b, h) and how they are cut; the same arithmetic in both kernels.
+struct AttPlan {
+    SeqRange r;
+    int cnt;      // heavy rows (what select_kernel emitted)
+    int n_total;  // sink + heavy + recent
+    int nsplits;  // CTAs with work
+    bool ok;
 };
+
+__device__ __forceinline__ AttPlan att_plan(const SparseDecodeParams& p, int b) {
+    AttPlan a;
+    const int S = p.seq_lens[b];
+    a.ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by the selection kernels
+    a.r = seq_range(a.ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
+    a.cnt = min(a.r.hb, p.sel_stride);
+    a.n_total = a.ok ? a.r.lo + a.cnt + (a.r.S - a.r.hi) : 0;
+    const int rows_per_cta = kAttRoundRows * p.rounds;
+    a.nsplits = (a.n_total + rows_per_cta - 1) / rows_per_cta;
+    return a;
+}
 
 // kPhysical: `sel` holds page * 256 + slot of each heavy token (written by select_kernel), so a
 // heavy row needs no page-table lookup; otherwise it holds token indices.
 template <bool kPhysical>
-__global__ void __launch_bounds__(kAttThreads) sparse_decode_kernel(const SparseDecodeParams p) {
-    cg::cluster_group cluster = cg::this_cluster();
-    const int rank = (int)cluster.block_rank();  // 0..7 within the (b, h) cluster
-    const int h = blockIdx.y, b = blockIdx.z;
+__global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const SparseDecodeParams p) {
+    const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int Hq = p.Hkv * kGroup, kvh = h / kGroup;
     const int tid = threadIdx.x;
-    const int worker = tid >> 4, sl = tid & 15;
+    const int worker = tid >> 4, sl = tid & 15, warp = tid >> 5;
+    constexpr int kWarps = kAttThreads / 32;
 
-    __shared__ float s_m[kAttWorkers], s_l[kAttWorkers];
-    __shared__ __align__(16) float s_acc[kAttWorkers][kHeadDim];
-    __shared__ AttPartial s_part;
+    __shared__ float s_m[kWarps], s_l[kWarps];
+    __shared__ __align__(16) float s_acc[kWarps][kHeadDim];
 
     // inputs of the step, not products of the preceding kernel: q, seq_lens, the page table
+    const AttPlan a = att_plan(p, b);
+    const int lo = a.r.lo, cnt = a.cnt;
+    const int edge_shift = a.r.hi - lo - cnt;  // recent token = position + edge_shift
+    const int32_t* sel = p.sel + ((size_t)b * Hq + h) * p.sel_stride;
+    const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
+    const int base = split * kAttRoundRows * p.rounds + worker;
+    const unsigned pool_rows = (unsigned)p.num_pages * kPage;
+
+    // page lookups of the first round's sink / recent rows, issued before the dependency wait
+    int pre_page[kAttRowsPerWorker];
+#pragma unroll
+    for (int i = 0; i < kAttRowsPerWorker; ++i) {
+        const int pos = base + i * kAttWorkers;
+        const bool edge = pos < a.n_total && (unsigned)(pos - lo) >= (unsigned)cnt;
+        const int tok = edge ? (pos < lo ? pos : pos + edge_shift) : 0;
+        pre_page[i] = __ldg(pt + tok / kPage);
+    }
     float qf[8];
     {
         const uint4 raw = *reinterpret_cast<const uint4*>(p.q + ((size_t)b * Hq + h) * kHeadDim + sl * 8);
@@ -90,86 +119,61 @@ __global__ void __launch_bounds__(kAttThreads) sparse_decode_kernel(const Sparse
 #pragma unroll
         for (int i = 0; i < 8; ++i) qf[i] *= p.scale_log2e;
     }
-    const int S_raw = p.seq_lens[b];
-    const bool s_ok = S_raw >= 1 && S_raw <= p.max_pages * kPage;  // else reported by the selection kernels
-    const SeqRange r = seq_range(s_ok ? S_raw : 1, p.init_budget, p.recent_budget, p.heavy_budget);
-    const int S = r.S;
-    const int cnt = min(r.hb, p.sel_stride);  // what select_kernel emitted for this head
-    const int n_total = s_ok ? r.lo + cnt + (S - r.hi) : 0;
-    const int32_t* sel = p.sel + ((size_t)b * Hq + h) * p.sel_stride;
-    const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
-
-    // position of row i of round `round` of this half-warp
-    auto position = [&](int round, int i) {
-        return (round * kAttRowsPerWorker + i) * kAttClusterRows + rank * kAttWorkers + worker;
-    };
-    // page lookups of the first round's sink / recent rows, issued before the dependency wait
-    int pre_page[kAttRowsPerWorker];
-#pragma unroll
-    for (int i = 0; i < kAttRowsPerWorker; ++i) {
-        const int pos = position(0, i);
-        const bool edge = pos < n_total && (pos < r.lo || pos >= r.lo + cnt);
-        const int tok = edge ? (pos < r.lo ? pos : r.hi + (pos - r.lo - cnt)) : 0;
-        pre_page[i] = __ldg(pt + tok / kPage);
-    }
 
     pdl_wait();
     pdl_launch_dependents();
+    if (split >= a.nsplits) return;
 
+    const __nv_bfloat16* kbase = p.k_pages + (size_t)kvh * kPage * kHeadDim + sl * 8;
+    const __nv_bfloat16* vbase = p.v_pages + (size_t)kvh * kPage * kHeadDim + sl * 8;
     float m = -INFINITY, l = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     bool bad = false;
-    const int rounds = (n_total + kAttRowsPerWorker * kAttClusterRows - 1) / (kAttRowsPerWorker * kAttClusterRows);
-    for (int round = 0; round < rounds; ++round) {
-        // ---- phase 1: one lookup per row: the heavy list entry, or the page of an edge token ----
+    for (int round = 0; round < p.rounds; ++round) {
+        const int rbase = base + round * kAttRoundRows;
+        if (rbase - worker >= a.n_total) break;
+        // ---- one lookup per row: the heavy list entry, or the page of a sink / recent token ----
         int look[kAttRowsPerWorker], tokv[kAttRowsPerWorker];
         uint32_t valid = 0, heavy = 0;
 #pragma unroll
         for (int i = 0; i < kAttRowsPerWorker; ++i) {
-            const int pos = position(round, i);
-            const bool ok = pos < n_total;
-            const bool is_heavy = ok && pos >= r.lo && pos < r.lo + cnt;
-            const int tok = (ok && !is_heavy) ? (pos < r.lo ? pos : r.hi + (pos - r.lo - cnt)) : 0;
+            const int pos = rbase + i * kAttWorkers;
+            const bool ok = pos < a.n_total;
+            const bool is_heavy = ok && (unsigned)(pos - lo) < (unsigned)cnt;
+            const int tok = (ok && !is_heavy) ? (pos < lo ? pos : pos + edge_shift) : 0;
             tokv[i] = tok;
             valid |= (ok ? 1u : 0u) << i;
             heavy |= (is_heavy ? 1u : 0u) << i;
-            if (is_heavy) look[i] = __ldcg(sel + (pos - r.lo));
+            if (is_heavy) look[i] = __ldcg(sel + (pos - lo));
             else look[i] = round == 0 ? pre_page[i] : __ldg(pt + tok / kPage);
         }
-        // ---- phase 2 (token-index lists only): translate heavy token indices through the page table
-        int row[kAttRowsPerWorker];
+        unsigned row[kAttRowsPerWorker];
 #pragma unroll
         for (int i = 0; i < kAttRowsPerWorker; ++i) {
             const bool is_heavy = (heavy >> i) & 1u;
-            int rr;
-            bool ok_row;
-            if (kPhysical || !is_heavy) {
-                // look = physical row (heavy) or page id (edge token)
-                const bool page_ok = is_heavy || (look[i] >= 0 && look[i] < p.num_pages);
-                rr = is_heavy ? look[i] : (page_ok ? look[i] : 0) * kPage + tokv[i] % kPage;
-                ok_row = page_ok;
-            } else {
-                const int tok = look[i];
-                const bool tok_ok = tok >= r.lo && tok < r.hi;
-                const int page = __ldg(pt + (tok_ok ? tok : 0) / kPage);
-                const bool page_ok = page >= 0 && page < p.num_pages;
-                rr = (page_ok ? page : 0) * kPage + (tok_ok ? tok : 0) % kPage;
-                ok_row = tok_ok && page_ok;
+            unsigned rr;
+            if (kPhysical || !is_heavy) {  // look = physical row (heavy) or page id (sink / recent)
+                rr = is_heavy ? (unsigned)look[i] : (unsigned)look[i] * kPage + (unsigned)(tokv[i] % kPage);
+                if (!is_heavy && (unsigned)look[i] >= (unsigned)p.num_pages) rr = ~0u;
+            } else {  // look = token index of a heavy row: translate through the page table
+                const unsigned tok = (unsigned)look[i];
+                const bool tok_ok = tok - (unsigned)lo < (unsigned)(a.r.hi - lo);
+                const unsigned page = (unsigned)__ldg(pt + (tok_ok ? tok : 0u) / kPage);
+                rr = (tok_ok && page < (unsigned)p.num_pages) ? page * kPage + tok % kPage : ~0u;
             }
-            ok_row = ok_row && rr >= 0 && rr < p.num_pages * kPage;
-            if (((valid >> i) & 1u) && !ok_row) {
-                bad = true;
+            if (rr >= pool_rows) {
+                if ((valid >> i) & 1u) bad = true;
                 valid &= ~(1u << i);
+                rr = 0;
             }
-            row[i] = ok_row ? rr : 0;
+            row[i] = rr;
         }
-        // ---- phase 3: gather, K and V loads all issued before any use -------------------------
+        // ---- gather: K and V loads all issued before any use ---------------------------------
         uint4 kraw[kAttRowsPerWorker], vraw[kAttRowsPerWorker];
 #pragma unroll
         for (int i = 0; i < kAttRowsPerWorker; ++i) {
-            const size_t off =
-                (((size_t)(row[i] / kPage) * p.Hkv + kvh) * kPage + row[i] % kPage) * kHeadDim + sl * 8;
-            kraw[i] = __ldg(reinterpret_cast<const uint4*>(p.k_pages + off));
-            vraw[i] = __ldg(reinterpret_cast<const uint4*>(p.v_pages + off));
+            const size_t off = ((size_t)(row[i] / kPage) * p.Hkv * kPage + row[i] % kPage) * kHeadDim;
+            kraw[i] = __ldg(reinterpret_cast<const uint4*>(kbase + off));
+            vraw[i] = __ldg(reinterpret_cast<const uint4*>(vbase + off));
         }
         // ---- scores (in log2 units), online softmax, weighted V sum ---------------------------
         float sc[kAttRowsPerWorker];
@@ -184,6 +188,7 @@ __global__ void __launch_bounds__(kAttThreads) sparse_decode_kernel(const Sparse
             sc[i] = ((valid >> i) & 1u) ? s : -INFINITY;
             m_new = fmaxf(m_new, sc[i]);
         }
+        // guards instead of branches: a worker may have seen no valid row yet (m_new == -inf)
         const float rescale = m == -INFINITY ? 0.f : exp2f(m - m_new);
         m = m_new;
         l *= rescale;
@@ -201,55 +206,89 @@ __global__ void __launch_bounds__(kAttThreads) sparse_decode_kernel(const Sparse
     }
     if (bad) report(p.status, HA_ERR_BAD_PAGE);
 
-    // ---- reduce the 16 half-warps of the CTA -------------------------------------------------
-    if (sl == 0) {
-        s_m[worker] = m;
-        s_l[worker] = l;
+    // ---- merge the two half-warps of each warp by shuffle, then the warps in shared memory ----
+    {
+        const float mo = __shfl_xor_sync(0xffffffffu, m, 16);
+        const float lo_ = __shfl_xor_sync(0xffffffffu, l, 16);
+        const float M2 = fmaxf(m, mo);
+        const float f = M2 == -INFINITY ? 0.f : exp2f(m - M2);
+        const float fo = M2 == -INFINITY ? 0.f : exp2f(mo - M2);
+        l = l * f + lo_ * fo;
+#pragma unroll
+        for (int d = 0; d < 8; ++d) acc[d] = acc[d] * f + __shfl_xor_sync(0xffffffffu, acc[d], 16) * fo;
+        m = M2;
     }
-    *reinterpret_cast<float4*>(&s_acc[worker][sl * 8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    *reinterpret_cast<float4*>(&s_acc[worker][sl * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if ((tid & 31) == 0) {
+        s_m[warp] = m;
+        s_l[warp] = l;
+    }
+    if ((tid & 16) == 0) {
+        *reinterpret_cast<float4*>(&s_acc[warp][sl * 8]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(&s_acc[warp][sl * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
     __syncthreads();
-    if (tid < kHeadDim) {
-        float M = -INFINITY, L = 0.f, A = 0.f;
+    float M = -INFINITY, L = 0.f, A = 0.f;
 #pragma unroll
-        for (int w = 0; w < kAttWorkers; ++w) M = fmaxf(M, s_m[w]);
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w]);
 #pragma unroll
-        for (int w = 0; w < kAttWorkers; ++w) {
-            const float f = s_m[w] == -INFINITY ? 0.f : exp2f(s_m[w] - M);
-            L = fmaf(s_l[w], f, L);
-            A = fmaf(s_acc[w][tid], f, A);
-        }
-        s_part.acc[tid] = A;
-        if (tid == 0) {
-            s_part.m = M;
-            s_part.l = L;
-        }
+    for (int w = 0; w < kWarps; ++w) {
+        const float f = s_m[w] == -INFINITY ? 0.f : exp2f(s_m[w] - M);
+        L = fmaf(s_l[w], f, L);
+        A = fmaf(s_acc[w][tid], f, A);
     }
+    if (a.nsplits == 1) {  // nothing to merge with
+        p.out[((size_t)b * Hq + h) * kHeadDim + tid] = __float2bfloat16_rn(A / L);
+        return;
+    }
+    float* part = p.partials + (((size_t)b * Hq + h) * p.nsplits + split) * kPartStride;
+    part[2 + tid] = A;
+    if (tid == 0) {
+        part[0] = M;
+        part[1] = L;
+    }
+}
 
-    // ---- merge the 8 CTA partials through distributed shared memory ----------------------------
-    cluster.sync();
-    if (tid < kHeadDim / kAttCluster && n_total > 0) {
-        const int d = rank * (kHeadDim / kAttCluster) + tid;
-        float mc[kAttCluster], lc[kAttCluster], ac[kAttCluster];
+// Log-sum-exp merge of the partials of one (b, h): 128 threads, thread = output dimension; the
+// splits are taken 32 at a time (lane = split for the max / sum pairs), all loads of a block
+// issued together, with a running maximum across blocks.
+__global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDecodeParams p) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int Hq = p.Hkv * kGroup;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const AttPlan a = att_plan(p, b);
+
+    pdl_wait();
+    pdl_launch_dependents();
+    if (a.nsplits <= 1) return;  // written by the gather kernel (or nothing to write)
+
+    const float* base = p.partials + ((size_t)b * Hq + h) * p.nsplits * kPartStride;
+    float Mg = -INFINITY, Lg = 0.f, Ag = 0.f;
+    for (int s0 = 0; s0 < a.nsplits; s0 += 32) {
+        const int n = min(32, a.nsplits - s0);
+        const int s = s0 + min(lane, n - 1);
+        const float ms = __ldcg(base + (size_t)s * kPartStride);
+        const float ls = __ldcg(base + (size_t)s * kPartStride + 1);
+        float av[32];
 #pragma unroll
-        for (int c = 0; c < kAttCluster; ++c) {
-            const AttPartial* rp = cluster.map_shared_rank(&s_part, c);
-            mc[c] = rp->m;
-            lc[c] = rp->l;
-            ac[c] = rp->acc[d];
+        for (int j = 0; j < 32; ++j)
+            av[j] = __ldcg(base + (size_t)(s0 + min(j, n - 1)) * kPartStride + 2 + tid);
+        float mb = lane < n ? ms : -INFINITY;
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, d));
+        const float Mn = fmaxf(Mg, mb);
+        const float rescale = Mg == -INFINITY ? 0.f : exp2f(Mg - Mn);
+        Mg = Mn;
+        Lg *= rescale;
+        Ag *= rescale;
+        const float f = (lane < n && ms != -INFINITY) ? exp2f(ms - Mg) : 0.f;
+        const float lf = ls * f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            Lg += __shfl_sync(0xffffffffu, lf, j);
+            Ag = fmaf(av[j], __shfl_sync(0xffffffffu, f, j), Ag);  // f = 0 beyond n
         }
-        float M = -INFINITY, L = 0.f, A = 0.f;
-#pragma unroll
-        for (int c = 0; c < kAttCluster; ++c) M = fmaxf(M, mc[c]);
-#pragma unroll
-        for (int c = 0; c < kAttCluster; ++c) {
-            const float f = mc[c] == -INFINITY ? 0.f : exp2f(mc[c] - M);
-            L = fmaf(lc[c], f, L);
-            A = fmaf(ac[c], f, A);
-        }
-        p.out[((size_t)b * Hq + h) * kHeadDim + d] = __float2bfloat16_rn(A / L);
     }
-    cluster.sync();  // no CTA may exit while another still reads its shared memory
+    p.out[((size_t)b * Hq + h) * kHeadDim + tid] = __float2bfloat16_rn(Ag / Lg);
 }
 
 }  // namespace ha
