@@ -197,7 +197,9 @@ def run_gpu_arm(args):
 
     w = WORKLOADS[args.workload]
     lens = workload_lens(args.workload)
-    B, L = w["batch"], args.layers or w["layers"]
+    if args.batch:
+        lens = lens[:args.batch]
+    B, L = len(lens), args.layers or w["layers"]
     budget = ha.Budget(INIT, w["heavy"], RECENT)
     nbytes = synthetic.algorithmic_bytes(lens, HQ, HKV, INIT, RECENT, w["heavy"])
 
@@ -357,6 +359,7 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="config1")
     ap.add_argument("--layers", type=int, default=0, help="layer instances kept resident (0 = workload default)")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

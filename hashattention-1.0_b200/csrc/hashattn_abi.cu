@@ -343,16 +343,16 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
     cudaError_t e1, e2;
     switch (chunk_pages_for(shape->max_pages)) {
         case 4:
-            e1 = launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
-            e2 = launch(select_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
+            e1 = launch(score_hist_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
+            e2 = launch(select_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
             break;
         case 8:
-            e1 = launch(score_hist_kernel<8>, grid, dim3(kSelThreads), s, 1, p);
-            e2 = launch(select_kernel<8>, grid, dim3(kSelThreads), s, 1, p);
+            e1 = launch(score_hist_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
+            e2 = launch(select_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
             break;
         default:
-            e1 = launch(score_hist_kernel<16>, grid, dim3(kSelThreads), s, 1, p);
-            e2 = launch(select_kernel<16>, grid, dim3(kSelThreads), s, 1, p);
+            e1 = launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
+            e2 = launch(select_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
             break;
     }
     return e1 == cudaSuccess && e2 == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;

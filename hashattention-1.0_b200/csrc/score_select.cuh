@@ -16,13 +16,22 @@
 // A stable descending sort picks, among tokens tied at the threshold, the lowest indices;
 // the tie fill below reproduces exactly that set.
 //
-// All global loads of a phase are issued together and without branches between them (indices
-// are clamped into range instead of guarded), so a CTA pays one memory round trip per phase.
+// Tiling: a CTA of 256 threads owns a chunk of 4 * ROUNDS pages of one (sequence, kv-head) and
+// walks it in rounds of 1024 tokens; in a round warp w owns tokens [128 w, 128 w + 128) (half a
+// page), four per lane. Only four 16-byte loads are in flight per lane, so many CTAs fit on an
+// SM; the loads of a round are issued together without branches between them (indices are
+// clamped into range instead of guarded). Everything that does not depend on the preceding
+// kernel - the sequence length, page ids and the first round's hash words - is fetched before
+// the grid-dependency wait.
 #pragma once
 
 #include "common.cuh"
 
 namespace ha {
+
+constexpr int kRoundPages = 4;                        // pages per round
+constexpr int kRoundTokens = kRoundPages * kPage;     // 1024
+constexpr int kLaneTokens = kRoundTokens / kSelThreads;  // 4 tokens per lane and round
 
 struct SelectParams {
     const uint32_t* q_codes;   // [B][Hq]
@@ -40,43 +49,34 @@ struct SelectParams {
     double heavy_budget;
 };
 
-// Scores of this lane's tokens. Token `it` of the lane is warp_base + it*32 + lane; all 32
-// lanes of an iteration lie in one page. Returns per token the four scores packed in one u32
-// (byte g = score against query head g of the group) and the token's physical row
-// (page * 256 + slot); bit `it` of `valid` marks existing tokens, of `cand` selection candidates.
-template <int CP>
-struct ChunkScores {
-    uint4 words[CP];
-    uint32_t sc[CP];
-    int32_t row[CP];
-    uint32_t valid, cand;
+// One round of one warp: 128 consecutive tokens of one page, token it*32 + lane for it = 0..3.
+struct RoundWords {
+    uint4 w[kLaneTokens];
+    int page;          // page id of the warp's half page (clamped into the pool)
+    uint32_t valid;    // bit it: token exists
+    uint32_t cand;     // bit it: token is a selection candidate
     bool bad_page;
 
-    // Issues every load that does not depend on the preceding kernel: page ids, then the hash
-    // words of the chunk. Only the word of the newest token (S - 1) may still be in flight from
-    // the encoder kernel; finish() re-reads that one.
-    __device__ __forceinline__ void prefetch(const SelectParams& p, int b, int kvh, int warp_base, int lane,
-                                             const SeqRange& r) {
-        int page[CP];
-        const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
-#pragma unroll
-        for (int it = 0; it < CP; ++it) {
-            const int pidx = min((warp_base + it * 32) / kPage, p.max_pages - 1);
-            page[it] = __ldg(pt + pidx);
-        }
+    // first token of this warp in round `rd` of chunk starting at `chunk_start`
+    static __device__ __forceinline__ int first_token(int chunk_start, int rd, int warp) {
+        return chunk_start + rd * kRoundTokens + warp * (kLaneTokens * 32);
+    }
+
+    __device__ __forceinline__ void load(const SelectParams& p, int b, int kvh, int t0, int lane, const SeqRange& r) {
+        const int pidx = min(t0 / kPage, p.max_pages - 1);
+        const int pg = __ldg(p.page_table + (size_t)b * p.max_pages + pidx);
+        const bool page_ok = pg >= 0 && pg < p.num_pages;
+        page = page_ok ? pg : 0;
         valid = 0;
         cand = 0;
         bad_page = false;
+        const uint4* src = p.hash_pages + ((size_t)page * p.Hkv + kvh) * kPage;
 #pragma unroll
-        for (int it = 0; it < CP; ++it) {
-            const int t = warp_base + it * 32 + lane;
+        for (int it = 0; it < kLaneTokens; ++it) {
+            const int t = t0 + it * 32 + lane;
             const bool ok = t < r.S;
-            const bool page_ok = page[it] >= 0 && page[it] < p.num_pages;
             bad_page |= ok && !page_ok;
-            const int pg = page_ok ? page[it] : 0;
-            const int tc = ok ? t : r.S - 1;  // clamp: the load below is always in range
-            row[it] = pg * kPage + tc % kPage;
-            words[it] = __ldg(p.hash_pages + ((size_t)pg * p.Hkv + kvh) * kPage + tc % kPage);
+            w[it] = __ldg(src + (ok ? t : r.S - 1) % kPage);  // clamp: always an in-range slot
             if (ok && page_ok) {
                 valid |= 1u << it;
                 if (t >= r.lo && t < r.hi) cand |= 1u << it;
@@ -84,44 +84,38 @@ struct ChunkScores {
         }
     }
 
-    // After the grid dependency wait: refresh the newest token's word, then score.
-    __device__ __forceinline__ void finish(const SelectParams& p, int kvh, int warp_base, int lane,
-                                           const SeqRange& r, const uint4 qc) {
+    // Re-reads the newest token's word, which the encoder kernel may have written after load().
+    __device__ __forceinline__ void refresh_newest(const SelectParams& p, int kvh, int t0, int lane, const SeqRange& r) {
 #pragma unroll
-        for (int it = 0; it < CP; ++it) {
-            if (warp_base + it * 32 + lane == r.S - 1 && ((valid >> it) & 1u))
-                words[it] = __ldcg(p.hash_pages + ((size_t)(row[it] / kPage) * p.Hkv + kvh) * kPage + row[it] % kPage);
-        }
-#pragma unroll
-        for (int it = 0; it < CP; ++it) {
-            const uint32_t s0 = __popc(~(qc.x ^ words[it].x));
-            const uint32_t s1 = __popc(~(qc.y ^ words[it].y));
-            const uint32_t s2 = __popc(~(qc.z ^ words[it].z));
-            const uint32_t s3 = __popc(~(qc.w ^ words[it].w));
-            sc[it] = s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
-        }
+        for (int it = 0; it < kLaneTokens; ++it)
+            if (t0 + it * 32 + lane == r.S - 1 && ((valid >> it) & 1u))
+                w[it] = __ldcg(p.hash_pages + ((size_t)page * p.Hkv + kvh) * kPage + (r.S - 1) % kPage);
+    }
+
+    // byte g of the result = score of token `it` against query head g of the group
+    __device__ __forceinline__ uint32_t scores(int it, const uint4 qc) const {
+        return __popc(~(qc.x ^ w[it].x)) | (__popc(~(qc.y ^ w[it].y)) << 8) | (__popc(~(qc.z ^ w[it].z)) << 16) |
+               (__popc(~(qc.w ^ w[it].w)) << 24);
     }
 };
 
-template <int CP>
+template <int ROUNDS>
 __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectParams p) {
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
-    constexpr int chunk_tokens = CP * kPage;
+    constexpr int chunk_tokens = ROUNDS * kRoundTokens;
 
     __shared__ uint32_t s_hist[kSelWarps][kGroup * kBins];
     for (int i = tid; i < kSelWarps * kGroup * kBins; i += kSelThreads) (&s_hist[0][0])[i] = 0;
 
-    // seq_lens, the page table and all hash words but the newest token's are not written by the
-    // kernel before this one, so they are fetched while that kernel is still running
     const int S = p.seq_lens[b];
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage;
-    const bool active = s_ok && c * chunk_tokens < S;
+    const int chunk_start = c * chunk_tokens;
+    const bool active = s_ok && chunk_start < S;
     const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
-    const int warp_base = c * chunk_tokens + warp * 32 * CP;
-    ChunkScores<CP> cs;
-    if (active) cs.prefetch(p, b, kvh, warp_base, lane, r);
+    RoundWords rw;
+    if (active) rw.load(p, b, kvh, RoundWords::first_token(chunk_start, 0, warp), lane, r);
 
     pdl_wait();
     pdl_launch_dependents();
@@ -132,31 +126,35 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     }
     if (!active) return;
     const uint4 qc = __ldcg(reinterpret_cast<const uint4*>(p.q_codes + (size_t)b * Hq + kvh * kGroup));
-    cs.finish(p, kvh, warp_base, lane, r, qc);
-    if (cs.bad_page) report(p.status, HA_ERR_BAD_PAGE);
-    __syncthreads();
+    __syncthreads();  // s_hist is zero
 
-#pragma unroll
-    for (int it = 0; it < CP; ++it) {
-        if ((cs.cand >> it) & 1u) {
-#pragma unroll
-            for (int g = 0; g < kGroup; ++g)
-                atomicAdd(&s_hist[warp][g * kBins + ((cs.sc[it] >> (8 * g)) & 0xffu)], 1u);
+    bool bad_page = false;
+#pragma unroll 1
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+        const int t0 = RoundWords::first_token(chunk_start, rd, warp);
+        if (rd > 0) {
+            if (chunk_start + rd * kRoundTokens >= S) break;
+            rw.load(p, b, kvh, t0, lane, r);
         }
-    }
-    if (p.scores_dbg != nullptr) {
-        const size_t pitch = (size_t)p.max_pages * kPage;
+        rw.refresh_newest(p, kvh, t0, lane, r);
+        bad_page |= rw.bad_page;
 #pragma unroll
-        for (int it = 0; it < CP; ++it) {
-            if ((cs.valid >> it) & 1u) {
-                const int t = warp_base + it * 32 + lane;
+        for (int it = 0; it < kLaneTokens; ++it) {
+            const uint32_t sc = rw.scores(it, qc);
+            if ((rw.cand >> it) & 1u) {
+#pragma unroll
+                for (int g = 0; g < kGroup; ++g) atomicAdd(&s_hist[warp][g * kBins + ((sc >> (8 * g)) & 0xffu)], 1u);
+            }
+            if (p.scores_dbg != nullptr && ((rw.valid >> it) & 1u)) {
+                const size_t pitch = (size_t)p.max_pages * kPage;
 #pragma unroll
                 for (int g = 0; g < kGroup; ++g)
-                    p.scores_dbg[((size_t)b * Hq + kvh * kGroup + g) * pitch + t] =
-                        (uint8_t)((cs.sc[it] >> (8 * g)) & 0xffu);
+                    p.scores_dbg[((size_t)b * Hq + kvh * kGroup + g) * pitch + t0 + it * 32 + lane] =
+                        (uint8_t)((sc >> (8 * g)) & 0xffu);
             }
         }
     }
+    if (bad_page) report(p.status, HA_ERR_BAD_PAGE);
     __syncthreads();
     if (tid < kGroup * kBins) {
         uint32_t v = 0;
@@ -166,39 +164,37 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     }
 }
 
-template <int CP>
-__global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams p) {
+template <int ROUNDS>
+__global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectParams p) {
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
-    constexpr int chunk_tokens = CP * kPage;
+    constexpr int chunk_tokens = ROUNDS * kRoundTokens;
     constexpr int kBinsPerWarp = (kGroup * kBins + kSelWarps - 1) / kSelWarps;  // 17
+    constexpr int kSlots = ROUNDS * kSelWarps;  // (round, warp) pairs in token order
 
     __shared__ int s_tot[kGroup * kBins + kSelWarps];  // padded: warp 7 owns bins up to 135
     __shared__ int s_bef[kGroup * kBins + kSelWarps];
     __shared__ int s_T[kGroup], s_need[kGroup], s_base[kGroup], s_eqb[kGroup];
-    __shared__ int s_wgt[kSelWarps][kGroup], s_weq[kSelWarps][kGroup];
+    __shared__ int s_wgt[kSlots][kGroup], s_weq[kSlots][kGroup];
 
     const int S = p.seq_lens[b];
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
-    const bool active = s_ok && c * chunk_tokens < S;
+    const int chunk_start = c * chunk_tokens;
+    const bool active = s_ok && chunk_start < S;
     const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
     const int nchunks_b = (r.S + chunk_tokens - 1) / chunk_tokens;
-    const int warp_base = c * chunk_tokens + warp * 32 * CP;
-    ChunkScores<CP> cs;
-    if (active) cs.prefetch(p, b, kvh, warp_base, lane, r);
+    RoundWords rw;
+    if (active) rw.load(p, b, kvh, RoundWords::first_token(chunk_start, 0, warp), lane, r);
 
     pdl_wait();
     pdl_launch_dependents();
     if (!active) return;
 
     // --- histogram lines of this warp's bins: warp w reduces bins [17w, 17w+17), lane = chunk;
-    //     the 17 loads of a round are independent and issued together
+    //     the 17 loads of a pass are independent and issued together
     const uint4 qc = __ldcg(reinterpret_cast<const uint4*>(p.q_codes + (size_t)b * Hq + kvh * kGroup));
     const uint32_t* hbase = p.hist + ((size_t)b * p.Hkv + kvh) * (kGroup * kBins) * p.nchunks;
-    int tot[kBinsPerWarp], bef[kBinsPerWarp];
-#pragma unroll
-    for (int k = 0; k < kBinsPerWarp; ++k) tot[k] = bef[k] = 0;
     for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
         const int cc = cc0 + lane;
         const int ccl = min(cc, nchunks_b - 1);
@@ -210,21 +206,31 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         }
 #pragma unroll
         for (int k = 0; k < kBinsPerWarp; ++k) {
-            tot[k] += cc < nchunks_b ? v[k] : 0;
-            bef[k] += cc < c ? v[k] : 0;
+            const int t = __reduce_add_sync(0xffffffffu, cc < nchunks_b ? v[k] : 0);
+            const int f = __reduce_add_sync(0xffffffffu, cc < c ? v[k] : 0);
+            if (lane == 0) {  // only this warp touches these entries: no barrier needed between passes
+                s_tot[warp * kBinsPerWarp + k] = cc0 == 0 ? t : s_tot[warp * kBinsPerWarp + k] + t;
+                s_bef[warp * kBinsPerWarp + k] = cc0 == 0 ? f : s_bef[warp * kBinsPerWarp + k] + f;
+            }
         }
     }
-    cs.finish(p, kvh, warp_base, lane, r, qc);
 
+    // --- this chunk's scores, kept packed in registers (one u32 per token) ------------------------
+    uint32_t sc[ROUNDS][kLaneTokens];
+    int page[ROUNDS];
+    uint32_t cand = 0;  // bit rd * 4 + it
 #pragma unroll
-    for (int k = 0; k < kBinsPerWarp; ++k) {
-        const int t = __reduce_add_sync(0xffffffffu, tot[k]);
-        const int f = __reduce_add_sync(0xffffffffu, bef[k]);
-        if (lane == 0) {
-            s_tot[warp * kBinsPerWarp + k] = t;
-            s_bef[warp * kBinsPerWarp + k] = f;
-        }
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+        const int t0 = RoundWords::first_token(chunk_start, rd, warp);
+        if (rd > 0) rw.load(p, b, kvh, min(t0, S - 1), lane, r);  // beyond S: clamped, nothing valid
+        rw.refresh_newest(p, kvh, t0, lane, r);
+        page[rd] = rw.page;
+        const uint32_t cmask = (rd > 0 && t0 >= S) ? 0u : rw.cand;
+        cand |= cmask << (rd * kLaneTokens);
+#pragma unroll
+        for (int it = 0; it < kLaneTokens; ++it) sc[rd][it] = rw.scores(it, qc);
     }
+
     __syncthreads();
 
     // --- threshold, tie quota and output base per head: warp g scans the 33 bins downwards ---
@@ -281,63 +287,79 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(const SelectParams 
         need[g] = s_need[g];
     }
 
-    // --- per-warp counts of (score > T) and (score == T), then a scan over the 8 warps -----
-    int cgt[kGroup] = {0, 0, 0, 0}, ceq[kGroup] = {0, 0, 0, 0};
+    // --- counts of (score > T) and (score == T) per (round, warp) slot ---------------------------
 #pragma unroll
-    for (int it = 0; it < CP; ++it) {
-        const bool is_cand = (cs.cand >> it) & 1u;
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+        int cgt[kGroup] = {0, 0, 0, 0}, ceq[kGroup] = {0, 0, 0, 0};
 #pragma unroll
-        for (int g = 0; g < kGroup; ++g) {
-            const int v = (int)((cs.sc[it] >> (8 * g)) & 0xffu);
-            cgt[g] += is_cand && v > T[g];
-            ceq[g] += is_cand && v == T[g];
+        for (int it = 0; it < kLaneTokens; ++it) {
+            const bool is_cand = (cand >> (rd * kLaneTokens + it)) & 1u;
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) {
+                const int v = (int)((sc[rd][it] >> (8 * g)) & 0xffu);
+                cgt[g] += is_cand && v > T[g];
+                ceq[g] += is_cand && v == T[g];
+            }
         }
-    }
-#pragma unroll
-    for (int g = 0; g < kGroup; ++g) {
-        cgt[g] = __reduce_add_sync(0xffffffffu, cgt[g]);
-        ceq[g] = __reduce_add_sync(0xffffffffu, ceq[g]);
-    }
-    if (lane == 0) {
 #pragma unroll
         for (int g = 0; g < kGroup; ++g) {
-            s_wgt[warp][g] = cgt[g];
-            s_weq[warp][g] = ceq[g];
+            cgt[g] = __reduce_add_sync(0xffffffffu, cgt[g]);
+            ceq[g] = __reduce_add_sync(0xffffffffu, ceq[g]);
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) {
+                s_wgt[rd * kSelWarps + warp][g] = cgt[g];
+                s_weq[rd * kSelWarps + warp][g] = ceq[g];
+            }
         }
     }
     __syncthreads();
 
-    // --- ordered emission --------------------------------------------------------------
+    // --- ordered emission: slots in token order are (round, warp), then it, then lane -------------
     const uint32_t lt_mask = (1u << lane) - 1u;
 #pragma unroll
     for (int g = 0; g < kGroup; ++g) {
-        if (cgt[g] + ceq[g] == 0) continue;  // nothing of this head in this warp's tokens
+        // running counts over all slots before this warp's first slot (round 0)
         int gt_run = 0, eq_run = s_eqb[g];
-        for (int w = 0; w < warp; ++w) {
-            gt_run += s_wgt[w][g];
-            eq_run += s_weq[w][g];
-        }
-        // selected tokens of this head that precede this warp's first token
-        int out_run = s_base[g] + gt_run + (min(eq_run, need[g]) - min(s_eqb[g], need[g]));
         const size_t off = ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride;
+        int slot_done = 0;
 #pragma unroll
-        for (int it = 0; it < CP; ++it) {
-            const int v = (int)((cs.sc[it] >> (8 * g)) & 0xffu);
-            const bool is_cand = (cs.cand >> it) & 1u;
-            const bool gt = is_cand && v > T[g];
-            const bool eq = is_cand && v == T[g];
-            const uint32_t m_eq = __ballot_sync(0xffffffffu, eq);
-            const bool sel = gt || (eq && eq_run + __popc(m_eq & lt_mask) < need[g]);
-            const uint32_t m_sel = __ballot_sync(0xffffffffu, sel);
-            if (sel) {
-                const int pos = out_run + __popc(m_sel & lt_mask);
-                if (pos < p.sel_stride) {
-                    p.sel_idx[off + pos] = warp_base + it * 32 + lane;
-                    p.sel_rows[off + pos] = cs.row[it];
+        for (int rd = 0; rd < ROUNDS; ++rd) {
+            const int slot = rd * kSelWarps + warp;
+            for (; slot_done < slot; ++slot_done) {
+                gt_run += s_wgt[slot_done][g];
+                eq_run += s_weq[slot_done][g];
+            }
+            const int mine_gt = s_wgt[slot][g], mine_eq = s_weq[slot][g];
+            if (mine_gt + mine_eq != 0) {  // something of this head in this warp's 128 tokens
+                int out_run = s_base[g] + gt_run + (min(eq_run, need[g]) - min(s_eqb[g], need[g]));
+                int eq_here = eq_run;
+                const int t0 = RoundWords::first_token(chunk_start, rd, warp);
+#pragma unroll
+                for (int it = 0; it < kLaneTokens; ++it) {
+                    const int v = (int)((sc[rd][it] >> (8 * g)) & 0xffu);
+                    const bool is_cand = (cand >> (rd * kLaneTokens + it)) & 1u;
+                    const bool gt = is_cand && v > T[g];
+                    const bool eq = is_cand && v == T[g];
+                    const uint32_t m_eq = __ballot_sync(0xffffffffu, eq);
+                    const bool sel = gt || (eq && eq_here + __popc(m_eq & lt_mask) < need[g]);
+                    const uint32_t m_sel = __ballot_sync(0xffffffffu, sel);
+                    if (sel) {
+                        const int pos = out_run + __popc(m_sel & lt_mask);
+                        if (pos < p.sel_stride) {
+                            const int t = t0 + it * 32 + lane;
+                            p.sel_idx[off + pos] = t;
+                            p.sel_rows[off + pos] = page[rd] * kPage + t % kPage;
+                        }
+                    }
+                    out_run += __popc(m_sel);
+                    eq_here += __popc(m_eq);
                 }
             }
-            out_run += __popc(m_sel);
-            eq_run += __popc(m_eq);
+            gt_run += mine_gt;
+            eq_run += mine_eq;
+            slot_done = slot + 1;
         }
     }
 }
