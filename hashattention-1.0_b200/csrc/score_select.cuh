@@ -8,8 +8,9 @@
 //
 // Pass B (select_kernel) re-reads its chunk (L2-resident by then), derives from the chunk
 // histograms the global threshold T of each head, how many tokens tied at T still fit and
-// how many selected tokens precede the chunk, and writes the selected token indices in
-// ascending order with ballot-based compaction - no sort, no atomics, nothing to reset.
+// how many selected tokens precede the chunk, and writes the selected token indices with a
+// packed warp-scan compaction - no sort, no atomics, nothing to reset. The list of a head is
+// ordered by 128-token block; inside a block by lane, i.e. not strictly ascending.
 //
 // Together they replace the +-1 dot product of USA.forward and the sort/scatter of
 // compute_mask_multi in 'simple' mode (hashattention/hashattention_llama.py:171-187, 423-438).
@@ -50,11 +51,14 @@ struct SelectParams {
 };
 
 // One round of one warp: 128 consecutive tokens of one page, token it*32 + lane for it = 0..3.
+// A round whose 128 tokens are all selection candidates (and do not include the newest token,
+// whose hash word the encoder kernel may still be writing) is "interior": no per-token masks.
 struct RoundWords {
     uint4 w[kLaneTokens];
     int page;          // page id of the warp's half page (clamped into the pool)
-    uint32_t valid;    // bit it: token exists
     uint32_t cand;     // bit it: token is a selection candidate
+    uint32_t valid;    // bit it: token exists
+    bool interior;     // warp-uniform: all 128 tokens are candidates, none is the newest token
     bool bad_page;
 
     // first token of this warp in round `rd` of chunk starting at `chunk_start`
@@ -67,10 +71,19 @@ struct RoundWords {
         const int pg = __ldg(p.page_table + (size_t)b * p.max_pages + pidx);
         const bool page_ok = pg >= 0 && pg < p.num_pages;
         page = page_ok ? pg : 0;
+        const uint4* src = p.hash_pages + ((size_t)page * p.Hkv + kvh) * kPage;
+        interior = page_ok && t0 >= r.lo && t0 + kLaneTokens * 32 <= r.hi &&
+                   (unsigned)(r.S - 1 - t0) >= (unsigned)(kLaneTokens * 32);
+        bad_page = false;
+        if (interior) {
+            const uint4* s0 = src + t0 % kPage + lane;
+#pragma unroll
+            for (int it = 0; it < kLaneTokens; ++it) w[it] = __ldg(s0 + it * 32);
+            cand = valid = (1u << kLaneTokens) - 1u;
+            return;
+        }
         valid = 0;
         cand = 0;
-        bad_page = false;
-        const uint4* src = p.hash_pages + ((size_t)page * p.Hkv + kvh) * kPage;
 #pragma unroll
         for (int it = 0; it < kLaneTokens; ++it) {
             const int t = t0 + it * 32 + lane;
@@ -86,18 +99,19 @@ struct RoundWords {
 
     // Re-reads the newest token's word, which the encoder kernel may have written after load().
     __device__ __forceinline__ void refresh_newest(const SelectParams& p, int kvh, int t0, int lane, const SeqRange& r) {
+        if (interior) return;
 #pragma unroll
         for (int it = 0; it < kLaneTokens; ++it)
             if (t0 + it * 32 + lane == r.S - 1 && ((valid >> it) & 1u))
                 w[it] = __ldcg(p.hash_pages + ((size_t)page * p.Hkv + kvh) * kPage + (r.S - 1) % kPage);
     }
-
-    // byte g of the result = score of token `it` against query head g of the group
-    __device__ __forceinline__ uint32_t scores(int it, const uint4 qc) const {
-        return __popc(~(qc.x ^ w[it].x)) | (__popc(~(qc.y ^ w[it].y)) << 8) | (__popc(~(qc.z ^ w[it].z)) << 16) |
-               (__popc(~(qc.w ^ w[it].w)) << 24);
-    }
 };
+
+// qn = ~q_code per head, so that popcount(qn ^ k) = popcount(~(q ^ k)) = number of agreeing bits
+__device__ __forceinline__ uint4 load_qn(const SelectParams& p, int b, int kvh) {
+    const uint4 qc = __ldcg(reinterpret_cast<const uint4*>(p.q_codes + ((size_t)b * p.Hkv + kvh) * kGroup));
+    return make_uint4(~qc.x, ~qc.y, ~qc.z, ~qc.w);
+}
 
 template <int ROUNDS>
 __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectParams p) {
@@ -125,9 +139,10 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
         return;
     }
     if (!active) return;
-    const uint4 qc = __ldcg(reinterpret_cast<const uint4*>(p.q_codes + (size_t)b * Hq + kvh * kGroup));
+    const uint4 qn = load_qn(p, b, kvh);
     __syncthreads();  // s_hist is zero
 
+    uint32_t* h0 = &s_hist[warp][0];
     bool bad_page = false;
 #pragma unroll 1
     for (int rd = 0; rd < ROUNDS; ++rd) {
@@ -140,17 +155,21 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
         bad_page |= rw.bad_page;
 #pragma unroll
         for (int it = 0; it < kLaneTokens; ++it) {
-            const uint32_t sc = rw.scores(it, qc);
-            if ((rw.cand >> it) & 1u) {
-#pragma unroll
-                for (int g = 0; g < kGroup; ++g) atomicAdd(&s_hist[warp][g * kBins + ((sc >> (8 * g)) & 0xffu)], 1u);
+            const uint32_t s0 = __popc(qn.x ^ rw.w[it].x), s1 = __popc(qn.y ^ rw.w[it].y);
+            const uint32_t s2 = __popc(qn.z ^ rw.w[it].z), s3 = __popc(qn.w ^ rw.w[it].w);
+            if (rw.interior || ((rw.cand >> it) & 1u)) {
+                atomicAdd(h0 + s0, 1u);
+                atomicAdd(h0 + kBins + s1, 1u);
+                atomicAdd(h0 + 2 * kBins + s2, 1u);
+                atomicAdd(h0 + 3 * kBins + s3, 1u);
             }
             if (p.scores_dbg != nullptr && ((rw.valid >> it) & 1u)) {
                 const size_t pitch = (size_t)p.max_pages * kPage;
-#pragma unroll
-                for (int g = 0; g < kGroup; ++g)
-                    p.scores_dbg[((size_t)b * Hq + kvh * kGroup + g) * pitch + t0 + it * 32 + lane] =
-                        (uint8_t)((sc >> (8 * g)) & 0xffu);
+                uint8_t* d = p.scores_dbg + ((size_t)b * Hq + kvh * kGroup) * pitch + t0 + it * 32 + lane;
+                d[0] = (uint8_t)s0;
+                d[pitch] = (uint8_t)s1;
+                d[2 * pitch] = (uint8_t)s2;
+                d[3 * pitch] = (uint8_t)s3;
             }
         }
     }
@@ -164,19 +183,28 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     }
 }
 
+// Per-byte flags (bit 7 of each byte) for packed scores a (bytes <= 32) against packed thresholds.
+// gt_add = 0x7F7F7F7F - T4: byte sum a + 127 - T carries into bit 7 iff a > T (no carry across bytes).
+__device__ __forceinline__ uint32_t bytes_gt(uint32_t a, uint32_t gt_add) { return (a + gt_add) & 0x80808080u; }
+__device__ __forceinline__ uint32_t bytes_eq(uint32_t a, uint32_t t4) {
+    return ~((a ^ t4) + 0x7F7F7F7Fu) & 0x80808080u;  // (x + 127) has bit 7 iff x != 0
+}
+// bit 7 of byte g -> bit g
+__device__ __forceinline__ uint32_t flags_to_nibble(uint32_t f) { return (((f >> 7) * 0x01020408u) >> 24) & 0xFu; }
+
 template <int ROUNDS>
-__global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(kSelThreads, ROUNDS >= 4 ? 3 : 4) select_kernel(const SelectParams p) {
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
     constexpr int chunk_tokens = ROUNDS * kRoundTokens;
     constexpr int kBinsPerWarp = (kGroup * kBins + kSelWarps - 1) / kSelWarps;  // 17
-    constexpr int kSlots = ROUNDS * kSelWarps;  // (round, warp) pairs in token order
+    constexpr int kSlots = ROUNDS * kSelWarps;  // (round, warp) pairs in token order, <= 32
 
     __shared__ int s_tot[kGroup * kBins + kSelWarps];  // padded: warp 7 owns bins up to 135
     __shared__ int s_bef[kGroup * kBins + kSelWarps];
     __shared__ int s_T[kGroup], s_need[kGroup], s_base[kGroup], s_eqb[kGroup];
-    __shared__ int s_wgt[kSlots][kGroup], s_weq[kSlots][kGroup];
+    __shared__ uint32_t s_sgt[kSlots], s_seq[kSlots];  // per slot: counts of the 4 heads packed in bytes
 
     const int S = p.seq_lens[b];
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
@@ -193,7 +221,7 @@ __global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectPara
 
     // --- histogram lines of this warp's bins: warp w reduces bins [17w, 17w+17), lane = chunk;
     //     the 17 loads of a pass are independent and issued together
-    const uint4 qc = __ldcg(reinterpret_cast<const uint4*>(p.q_codes + (size_t)b * Hq + kvh * kGroup));
+    const uint4 qn = load_qn(p, b, kvh);
     const uint32_t* hbase = p.hist + ((size_t)b * p.Hkv + kvh) * (kGroup * kBins) * p.nchunks;
     for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
         const int cc = cc0 + lane;
@@ -215,7 +243,7 @@ __global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectPara
         }
     }
 
-    // --- this chunk's scores, kept packed in registers (one u32 per token) ------------------------
+    // --- this chunk's scores, kept packed in registers (one u32 per token: byte g = head g) --------
     uint32_t sc[ROUNDS][kLaneTokens];
     int page[ROUNDS];
     uint32_t cand = 0;  // bit rd * 4 + it
@@ -228,9 +256,10 @@ __global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectPara
         const uint32_t cmask = (rd > 0 && t0 >= S) ? 0u : rw.cand;
         cand |= cmask << (rd * kLaneTokens);
 #pragma unroll
-        for (int it = 0; it < kLaneTokens; ++it) sc[rd][it] = rw.scores(it, qc);
+        for (int it = 0; it < kLaneTokens; ++it)
+            sc[rd][it] = __popc(qn.x ^ rw.w[it].x) | (__popc(qn.y ^ rw.w[it].y) << 8) |
+                         (__popc(qn.z ^ rw.w[it].z) << 16) | (__popc(qn.w ^ rw.w[it].w) << 24);
     }
-
     __syncthreads();
 
     // --- threshold, tie quota and output base per head: warp g scans the 33 bins downwards ---
@@ -280,86 +309,129 @@ __global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectPara
     }
     __syncthreads();
 
-    int T[kGroup], need[kGroup];
-#pragma unroll
-    for (int g = 0; g < kGroup; ++g) {
-        T[g] = s_T[g];
-        need[g] = s_need[g];
-    }
-
-    // --- counts of (score > T) and (score == T) per (round, warp) slot ---------------------------
+    // --- classify: per token and head, (score > T) and (score == T) as byte flags (bit 7 of byte g);
+    //     the flags of non-candidates are masked out -----------------------------------------------
+    const uint32_t t4 = (uint32_t)s_T[0] | ((uint32_t)s_T[1] << 8) | ((uint32_t)s_T[2] << 16) | ((uint32_t)s_T[3] << 24);
+    const uint32_t gt_add = 0x7F7F7F7Fu - t4;
+    // flags of token (rd, it), zero for non-candidates
+    auto flags_gt = [&](int rd, int it) {
+        const uint32_t cm = 0u - ((cand >> (rd * kLaneTokens + it)) & 1u);
+        return bytes_gt(sc[rd][it], gt_add) & cm;
+    };
+    auto flags_eq = [&](int rd, int it) {
+        const uint32_t cm = 0u - ((cand >> (rd * kLaneTokens + it)) & 1u);
+        return bytes_eq(sc[rd][it], t4) & cm;
+    };
 #pragma unroll
     for (int rd = 0; rd < ROUNDS; ++rd) {
-        int cgt[kGroup] = {0, 0, 0, 0}, ceq[kGroup] = {0, 0, 0, 0};
+        uint32_t cg = 0, ce = 0;  // this lane's counts, one byte per head (<= 4 each)
 #pragma unroll
         for (int it = 0; it < kLaneTokens; ++it) {
-            const bool is_cand = (cand >> (rd * kLaneTokens + it)) & 1u;
-#pragma unroll
-            for (int g = 0; g < kGroup; ++g) {
-                const int v = (int)((sc[rd][it] >> (8 * g)) & 0xffu);
-                cgt[g] += is_cand && v > T[g];
-                ceq[g] += is_cand && v == T[g];
-            }
+            cg += flags_gt(rd, it) >> 7;
+            ce += flags_eq(rd, it) >> 7;
         }
-#pragma unroll
-        for (int g = 0; g < kGroup; ++g) {
-            cgt[g] = __reduce_add_sync(0xffffffffu, cgt[g]);
-            ceq[g] = __reduce_add_sync(0xffffffffu, ceq[g]);
-        }
+        cg = __reduce_add_sync(0xffffffffu, cg);  // <= 128 per byte: no carry between heads
+        ce = __reduce_add_sync(0xffffffffu, ce);
         if (lane == 0) {
-#pragma unroll
-            for (int g = 0; g < kGroup; ++g) {
-                s_wgt[rd * kSelWarps + warp][g] = cgt[g];
-                s_weq[rd * kSelWarps + warp][g] = ceq[g];
-            }
+            s_sgt[rd * kSelWarps + warp] = cg;
+            s_seq[rd * kSelWarps + warp] = ce;
         }
     }
     __syncthreads();
 
-    // --- ordered emission: slots in token order are (round, warp), then it, then lane -------------
+    // --- exclusive prefix over the slots (token order), heads in two 16-bit pairs -------------------
+    uint32_t pg01, pg23, pe01, pe23;  // lane = slot
+    {
+        const uint32_t g4 = lane < kSlots ? s_sgt[lane] : 0u, e4 = lane < kSlots ? s_seq[lane] : 0u;
+        const uint32_t g01 = (g4 & 0xffu) | ((g4 & 0xff00u) << 8), g23 = ((g4 >> 16) & 0xffu) | ((g4 >> 24) << 16);
+        const uint32_t e01 = (e4 & 0xffu) | ((e4 & 0xff00u) << 8), e23 = ((e4 >> 16) & 0xffu) | ((e4 >> 24) << 16);
+        pg01 = g01; pg23 = g23; pe01 = e01; pe23 = e23;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t a0 = __shfl_up_sync(0xffffffffu, pg01, d), a1 = __shfl_up_sync(0xffffffffu, pg23, d);
+            const uint32_t a2 = __shfl_up_sync(0xffffffffu, pe01, d), a3 = __shfl_up_sync(0xffffffffu, pe23, d);
+            if (lane >= d) {
+                pg01 += a0; pg23 += a1; pe01 += a2; pe23 += a3;
+            }
+        }
+        pg01 -= g01; pg23 -= g23; pe01 -= e01; pe23 -= e23;
+    }
+    // lane 4 * rd + g works out, for slot (rd, this warp) and head g, where the slot's output starts
+    // and how its ties are treated: 0 = none taken, 1 = all taken, 2 = the tie quota ends inside
+    int my_base = 0, my_eqb = 0, my_mode = 0;
+    {
+        const int rd = (lane >> 2) % ROUNDS, g = lane & 3, slot = rd * kSelWarps + warp;
+        // (shuffle both pairs, then pick: the operand of a shuffle is evaluated by the source lane)
+        const uint32_t sg01 = __shfl_sync(0xffffffffu, pg01, slot), sg23 = __shfl_sync(0xffffffffu, pg23, slot);
+        const uint32_t se01 = __shfl_sync(0xffffffffu, pe01, slot), se23 = __shfl_sync(0xffffffffu, pe23, slot);
+        const uint32_t sg = g < 2 ? sg01 : sg23, se = g < 2 ? se01 : se23;
+        const int gt_b = (int)((sg >> ((g & 1) * 16)) & 0xffffu);
+        const int need = s_need[g];
+        my_eqb = s_eqb[g] + (int)((se >> ((g & 1) * 16)) & 0xffffu);
+        const int eq_in = (int)((s_seq[slot] >> (8 * g)) & 0xffu);
+        my_base = s_base[g] + gt_b + (min(my_eqb, need) - min(s_eqb[g], need));
+        my_mode = my_eqb + eq_in <= need ? 1 : (my_eqb < need ? 2 : 0);
+    }
+
+    // --- emission: positions from one packed warp scan per slot; order inside a slot is lane-major.
     const uint32_t lt_mask = (1u << lane) - 1u;
 #pragma unroll
-    for (int g = 0; g < kGroup; ++g) {
-        // running counts over all slots before this warp's first slot (round 0)
-        int gt_run = 0, eq_run = s_eqb[g];
-        const size_t off = ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride;
-        int slot_done = 0;
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+        const int slot = rd * kSelWarps + warp;
+        if ((s_sgt[slot] | s_seq[slot]) == 0) continue;  // nothing of any head in this warp's 128 tokens
+        int base_pos[kGroup];
+        uint32_t full4 = 0, straddle = 0;
 #pragma unroll
-        for (int rd = 0; rd < ROUNDS; ++rd) {
-            const int slot = rd * kSelWarps + warp;
-            for (; slot_done < slot; ++slot_done) {
-                gt_run += s_wgt[slot_done][g];
-                eq_run += s_weq[slot_done][g];
-            }
-            const int mine_gt = s_wgt[slot][g], mine_eq = s_weq[slot][g];
-            if (mine_gt + mine_eq != 0) {  // something of this head in this warp's 128 tokens
-                int out_run = s_base[g] + gt_run + (min(eq_run, need[g]) - min(s_eqb[g], need[g]));
-                int eq_here = eq_run;
-                const int t0 = RoundWords::first_token(chunk_start, rd, warp);
+        for (int g = 0; g < kGroup; ++g) {
+            base_pos[g] = __shfl_sync(0xffffffffu, my_base, rd * 4 + g);
+            const int mode = __shfl_sync(0xffffffffu, my_mode, rd * 4 + g);
+            full4 |= (mode == 1 ? 0x80u : 0u) << (8 * g);
+            straddle |= (mode == 2 ? 1u : 0u) << g;
+        }
+        uint32_t selm[kLaneTokens];
+#pragma unroll
+        for (int it = 0; it < kLaneTokens; ++it) selm[it] = flags_gt(rd, it) | (flags_eq(rd, it) & full4);
+        if (straddle != 0) {  // warp-uniform, at most once per (sequence, head): rank ties by token index
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) {
+                if (!((straddle >> g) & 1u)) continue;
+                int eq_run = __shfl_sync(0xffffffffu, my_eqb, rd * 4 + g);
 #pragma unroll
                 for (int it = 0; it < kLaneTokens; ++it) {
-                    const int v = (int)((sc[rd][it] >> (8 * g)) & 0xffu);
-                    const bool is_cand = (cand >> (rd * kLaneTokens + it)) & 1u;
-                    const bool gt = is_cand && v > T[g];
-                    const bool eq = is_cand && v == T[g];
+                    const bool eq = (flags_eq(rd, it) >> (8 * g + 7)) & 1u;
                     const uint32_t m_eq = __ballot_sync(0xffffffffu, eq);
-                    const bool sel = gt || (eq && eq_here + __popc(m_eq & lt_mask) < need[g]);
-                    const uint32_t m_sel = __ballot_sync(0xffffffffu, sel);
-                    if (sel) {
-                        const int pos = out_run + __popc(m_sel & lt_mask);
-                        if (pos < p.sel_stride) {
-                            const int t = t0 + it * 32 + lane;
-                            p.sel_idx[off + pos] = t;
-                            p.sel_rows[off + pos] = page[rd] * kPage + t % kPage;
-                        }
-                    }
-                    out_run += __popc(m_sel);
-                    eq_here += __popc(m_eq);
+                    if (eq && eq_run + __popc(m_eq & lt_mask) < s_need[g]) selm[it] |= 0x80u << (8 * g);
+                    eq_run += __popc(m_eq);
                 }
             }
-            gt_run += mine_gt;
-            eq_run += mine_eq;
-            slot_done = slot + 1;
+        }
+        uint32_t cnt4 = 0, bits = 0;  // per-head counts of this lane; bit it*4+g = (it, g) selected
+#pragma unroll
+        for (int it = 0; it < kLaneTokens; ++it) {
+            cnt4 += selm[it] >> 7;
+            bits |= flags_to_nibble(selm[it]) << (4 * it);
+        }
+        uint32_t excl = cnt4;  // exclusive prefix over lanes, 4 heads at once (<= 124 per byte)
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t u = __shfl_up_sync(0xffffffffu, excl, d);
+            if (lane >= d) excl += u;
+        }
+        excl -= cnt4;
+        const int t_lane = RoundWords::first_token(chunk_start, rd, warp) + lane;
+        const int prow0 = page[rd] * kPage + t_lane % kPage;
+        while (bits != 0) {  // a lane holds few selected (token, head) pairs: visit only those
+            const int i = __ffs(bits) - 1;
+            bits &= bits - 1;
+            const int it = i >> 2, g = i & 3;
+            const int bp = g == 0 ? base_pos[0] : (g == 1 ? base_pos[1] : (g == 2 ? base_pos[2] : base_pos[3]));
+            const int pos = bp + (int)((excl >> (8 * g)) & 0xffu);
+            excl += 1u << (8 * g);
+            if (pos < p.sel_stride) {
+                const size_t o = ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride + pos;
+                p.sel_idx[o] = t_lane + it * 32;
+                p.sel_rows[o] = prow0 + it * 32;
+            }
         }
     }
 }
