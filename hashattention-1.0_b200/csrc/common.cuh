@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include "../../include/hashattn.h"
+#include "timeline.cuh"
 
 namespace ha {
 

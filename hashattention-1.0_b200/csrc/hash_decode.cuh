@@ -177,6 +177,7 @@ __device__ __forceinline__ void mlp_eval(const MlpRegs<WT>& r, const __nv_bfloat
 template <typename WT>
 __global__ void __launch_bounds__(kHashDecodeThreads)
 hash_decode_kernel(const HashDecodeParams p) {
+    HA_TL(kTlHashDecode, kTlEntry);
     const int h = blockIdx.x;                // query head whose MLP this CTA evaluates
     const int side = blockIdx.y;             // 0 = query net, 1 = key net
     const int Hq = p.Hkv * kGroup;
@@ -188,6 +189,7 @@ hash_decode_kernel(const HashDecodeParams p) {
     __shared__ MlpSmem sm;
 
     pdl_wait();
+    HA_TL(kTlHashDecode, kTlAfterWait);
     pdl_launch_dependents();
 
     const int b_begin = blockIdx.z * p.batch_per_cta;
@@ -239,6 +241,7 @@ hash_decode_kernel(const HashDecodeParams p) {
             *d = *s;
         }
     }
+    HA_TL(kTlHashDecode, kTlExit);
 }
 
 // Prefill key-hash build on the CUDA cores, exact fp32 arithmetic: CTA (h, page, b) keeps the

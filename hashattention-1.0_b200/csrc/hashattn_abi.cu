@@ -178,6 +178,14 @@ using namespace ha;
 
 extern "C" {
 
+#ifdef HA_TIMELINE
+// Debug builds only: where the kernels stamp their timeline (device buffer of
+// kTlKernels * kTlEvents * 2 unsigned 64-bit words, minima preset to ~0, maxima to 0).
+int ha_debug_set_timeline(unsigned long long* buffer) {
+    return cudaMemcpyToSymbol(g_timeline, &buffer, sizeof(buffer)) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+}
+#endif
+
 int ha_abi_version(void) { return HA_ABI_VERSION; }
 
 const char* ha_status_str(int status) {

@@ -115,6 +115,7 @@ __device__ __forceinline__ uint4 load_qn(const SelectParams& p, int b, int kvh) 
 
 template <int ROUNDS>
 __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectParams p) {
+    HA_TL(kTlScoreHist, kTlEntry);
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
@@ -132,6 +133,7 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     if (active) rw.load(p, b, kvh, RoundWords::first_token(chunk_start, 0, warp), lane, r);
 
     pdl_wait();
+    HA_TL(kTlScoreHist, kTlAfterWait);
     pdl_launch_dependents();
 
     if (!s_ok) {
@@ -181,6 +183,7 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
         for (int w = 0; w < kSelWarps; ++w) v += s_hist[w][tid];
         p.hist[(((size_t)b * p.Hkv + kvh) * (kGroup * kBins) + tid) * p.nchunks + c] = v;
     }
+    HA_TL(kTlScoreHist, kTlExit);
 }
 
 // Per-byte flags (bit 7 of each byte) for packed scores a (bytes <= 32) against packed thresholds.
@@ -194,6 +197,7 @@ __device__ __forceinline__ uint32_t flags_to_nibble(uint32_t f) { return (((f >>
 
 template <int ROUNDS>
 __global__ void __launch_bounds__(kSelThreads, ROUNDS >= 4 ? 3 : 4) select_kernel(const SelectParams p) {
+    HA_TL(kTlSelect, kTlEntry);
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
@@ -216,6 +220,7 @@ __global__ void __launch_bounds__(kSelThreads, ROUNDS >= 4 ? 3 : 4) select_kerne
     if (active) rw.load(p, b, kvh, RoundWords::first_token(chunk_start, 0, warp), lane, r);
 
     pdl_wait();
+    HA_TL(kTlSelect, kTlAfterWait);
     pdl_launch_dependents();
     if (!active) return;
 
@@ -434,6 +439,7 @@ __global__ void __launch_bounds__(kSelThreads, ROUNDS >= 4 ? 3 : 4) select_kerne
             }
         }
     }
+    HA_TL(kTlSelect, kTlExit);
 }
 
 }  // namespace ha

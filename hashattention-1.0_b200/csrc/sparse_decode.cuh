@@ -85,6 +85,7 @@ __device__ __forceinline__ AttPlan att_plan(const SparseDecodeParams& p, int b) 
 // heavy row needs no page-table lookup; otherwise it holds token indices.
 template <bool kPhysical>
 __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const SparseDecodeParams p) {
+    HA_TL(kTlGather, kTlEntry);
     const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int Hq = p.Hkv * kGroup, kvh = h / kGroup;
     const int tid = threadIdx.x;
@@ -121,6 +122,7 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
     }
 
     pdl_wait();
+    HA_TL(kTlGather, kTlAfterWait);
     pdl_launch_dependents();
     if (split >= a.nsplits) return;
 
@@ -246,18 +248,21 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
         part[0] = M;
         part[1] = L;
     }
+    HA_TL(kTlGather, kTlExit);
 }
 
 // Log-sum-exp merge of the partials of one (b, h): 128 threads, thread = output dimension; the
 // splits are taken 32 at a time (lane = split for the max / sum pairs), all loads of a block
 // issued together, with a running maximum across blocks.
 __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDecodeParams p) {
+    HA_TL(kTlMerge, kTlEntry);
     const int h = blockIdx.x, b = blockIdx.y;
     const int Hq = p.Hkv * kGroup;
     const int tid = threadIdx.x, lane = tid & 31;
     const AttPlan a = att_plan(p, b);
 
     pdl_wait();
+    HA_TL(kTlMerge, kTlAfterWait);
     pdl_launch_dependents();
     if (a.nsplits <= 1) return;  // written by the gather kernel (or nothing to write)
 
@@ -289,6 +294,7 @@ __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDeco
         }
     }
     p.out[((size_t)b * Hq + h) * kHeadDim + tid] = __float2bfloat16_rn(Ag / Lg);
+    HA_TL(kTlMerge, kTlExit);
 }
 
 }  // namespace ha
