@@ -21,6 +21,7 @@ HA_ERR_TIMEOUT = 5
 HA_ERR_BAD_PAGE = 6
 HA_ERR_BAD_SEQ_LEN = 7
 HA_ERR_SEL_OVERFLOW = 8
+HA_ERR_SCRATCH_LIMIT = 9
 HA_WEIGHTS_BF16 = 0
 HA_WEIGHTS_F32 = 1
 HA_ABI_VERSION = 1
@@ -53,6 +54,8 @@ PROTOTYPES = {
     "ha_hash_decode": (c_int, [_S, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ha_hash_prefill": (c_int, [_S, _W, _P, _P, _P, _P, _P, _P, _P]),
     "ha_score_select": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P, _P]),
+    "ha_static_scratch_needed": (c_size_t, [_S]),
+    "ha_score_select_static": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ha_sparse_decode": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P, c_size_t, _P, _P]),
     "ha_decode_step": (c_int, [_S, _B, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P,
                                c_size_t, _P, _P]),

@@ -2,6 +2,7 @@
 // workspace carving and kernel launches. No allocation, no host synchronisation (except where
 // ha_decode_step_host is asked for it), no exceptions.
 #include <cmath>
+#include <mutex>
 #include <utility>
 
 #include "common.cuh"
@@ -199,6 +200,7 @@ const char* ha_status_str(int status) {
         case HA_ERR_BAD_PAGE: return "page id outside the page pool";
         case HA_ERR_BAD_SEQ_LEN: return "sequence length < 1 or beyond the page table";
         case HA_ERR_SEL_OVERFLOW: return "heavy budget exceeds sel_stride";
+        case HA_ERR_SCRATCH_LIMIT: return "shape needs more scratch than the library's built-in buffer (HA_STATIC_SCRATCH_BYTES)";
         default: return "unknown status";
     }
 }
@@ -435,6 +437,123 @@ int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
         return *status_host;
     }
     return HA_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// ha_score_select_static: the selection kernels on scratch memory that is part of the library
+// image, for callers that may not allocate (see include/hashattn.h).
+// ------------------------------------------------------------------------------------------
+namespace {
+
+// Lives in every GPU context that loads the library, until the process ends. In host code this
+// name is only a handle for cudaGetSymbolAddress: it is not a device address and must never be
+// passed to a kernel as one.
+static __device__ __align__(256) unsigned char g_static_scratch[HA_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device
+
+struct StaticScratch {
+    uint32_t* hist;     // [B][Hkv][4*33][nchunks]
+    int32_t* sel_rows;  // [B][Hq][sel_stride]
+    size_t bytes;
+};
+
+StaticScratch carve_static(const ha_shape_t* s, void* base) {
+    const size_t n_hist = (size_t)s->batch * s->num_kv_heads * num_chunks_for(s->max_pages) * kGroup * kBins;
+    const size_t n_rows = (size_t)s->batch * s->num_kv_heads * kGroup * s->sel_stride;
+    char* p = static_cast<char*>(base);
+    StaticScratch w;
+    w.hist = reinterpret_cast<uint32_t*>(p);
+    const size_t off = align_up(n_hist * sizeof(uint32_t));
+    w.sel_rows = reinterpret_cast<int32_t*>(p + off);
+    w.bytes = off + align_up(n_rows * sizeof(int32_t));
+    return w;
+}
+
+// Device address of the static buffer on the current device; looked up once per device.
+int static_scratch_address(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return HA_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return HA_ERR_LAUNCH;
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return HA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t ha_static_scratch_needed(const ha_shape_t* shape) {
+    if (check_shape(shape) != HA_OK) return 0;
+    return carve_static(shape, nullptr).bytes;
+}
+
+int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
+                           const uint32_t* q_codes, const uint32_t* hash_pages,
+                           const int32_t* page_table, const int32_t* seq_lens,
+                           int32_t* sel_idx, int32_t* sel_cnt, int32_t* status, void* stream) {
+    int rc = check_shape(shape);
+    if (rc != HA_OK) return rc;
+    rc = check_budget(budget);
+    if (rc != HA_OK) return rc;
+    if (q_codes == nullptr || hash_pages == nullptr || page_table == nullptr || seq_lens == nullptr ||
+        sel_idx == nullptr || sel_cnt == nullptr || status == nullptr)
+        return HA_ERR_BAD_ARG;
+    if (carve_static(shape, nullptr).bytes > HA_STATIC_SCRATCH_BYTES) return HA_ERR_SCRATCH_LIMIT;
+    void* base = nullptr;
+    rc = static_scratch_address(&base);
+    if (rc != HA_OK) return rc;
+    const StaticScratch w = carve_static(shape, base);
+
+    // Every word of hist / sel_rows that a kernel reads was written earlier in the same call,
+    // so nothing left over from the previous call needs clearing.
+    SelectParams p;
+    p.q_codes = q_codes;
+    p.hash_pages = reinterpret_cast<const uint4*>(hash_pages);
+    p.page_table = page_table;
+    p.seq_lens = seq_lens;
+    p.hist = w.hist;
+    p.sel_idx = sel_idx;
+    p.sel_rows = w.sel_rows;
+    p.sel_cnt = sel_cnt;
+    p.scores_dbg = nullptr;
+    p.status = status;
+    p.B = shape->batch;
+    p.Hkv = shape->num_kv_heads;
+    p.max_pages = shape->max_pages;
+    p.num_pages = shape->num_pages;
+    p.sel_stride = shape->sel_stride;
+    p.nchunks = num_chunks_for(shape->max_pages);
+    p.init_budget = budget->init_budget;
+    p.recent_budget = budget->recent_budget;
+    p.heavy_budget = budget->heavy_budget;
+    const dim3 grid(p.nchunks, shape->num_kv_heads, shape->batch);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e1, e2;
+    switch (chunk_pages_for(shape->max_pages)) {
+        case 4:
+            e1 = launch(score_hist_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
+            e2 = launch(select_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
+            break;
+        case 8:
+            e1 = launch(score_hist_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
+            e2 = launch(select_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
+            break;
+        default:
+            e1 = launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
+            e2 = launch(select_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
+            break;
+    }
+    return e1 == cudaSuccess && e2 == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
 }  // extern "C"

@@ -163,6 +163,24 @@ class SparseDecodeContext:
         _raise_on(rc, "ha_score_select")
         return self.sel_idx, self.sel_cnt
 
+    def score_select_static(self, q_codes: torch.Tensor | None = None):
+        """:meth:`score_select` through ``ha_score_select_static``: no workspace is handed over, the
+        kernels use the scratch buffer built into the library. Meant for hosts that are not allowed to
+        allocate device memory for a workspace (a serving plugin's enqueue hook, a process whose pool
+        already owns the device). Raises if the shape needs more than the built-in buffer holds.
+        Results are identical to :meth:`score_select`; calls that could overlap on the GPU must be
+        ordered by the caller, since they all share that one buffer."""
+        q_codes = self.q_codes if q_codes is None else q_codes
+        _check(q_codes, "q_codes", torch.int32, (self.batch, self.num_q_heads), self.device)
+        c = self.cache
+        with torch.cuda.device(self.device):
+            rc = self.lib.ha_score_select_static(
+                self.shape, self.c_budget, q_codes.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
+                c.seq_lens.data_ptr(), self.sel_idx.data_ptr(), self.sel_cnt.data_ptr(), self.status.data_ptr(),
+                _stream_ptr(self.device))
+        _raise_on(rc, "ha_score_select_static")
+        return self.sel_idx, self.sel_cnt
+
     def sparse_decode(self, q, out: torch.Tensor | None = None, sel_idx=None, sel_cnt=None) -> torch.Tensor:
         """Attention of q over sink + selected + recent rows. Returns ``out [B, Hq, 128]`` bf16."""
         self._check_q(q)

@@ -58,6 +58,7 @@ extern "C" {
 #define HA_ERR_BAD_PAGE 6        /* device: page id outside [0, num_pages)                   */
 #define HA_ERR_BAD_SEQ_LEN 7     /* device: seq_len < 1 or beyond max_pages * page_size      */
 #define HA_ERR_SEL_OVERFLOW 8    /* device: heavy budget exceeds sel_stride                  */
+#define HA_ERR_SCRATCH_LIMIT 9   /* problem needs more than HA_STATIC_SCRATCH_BYTES of scratch */
 
 #define HA_WEIGHTS_BF16 0
 #define HA_WEIGHTS_F32 1
@@ -141,6 +142,28 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
                     const int32_t* page_table, const int32_t* seq_lens,
                     int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg,
                     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
+/* ha_score_select without a workspace, for callers that cannot hand the library any scratch
+ * memory of their own. (No counterpart in the reference; it exists for hosts such as an
+ * inference-server plugin whose enqueue hook may not allocate, or a process whose memory pool
+ * already owns the whole device, where a cudaMalloc for the workspace is either forbidden or
+ * fails.) Same inputs, outputs, results and status codes as ha_score_select; the per-chunk
+ * score histograms and the row list live in a buffer of HA_STATIC_SCRATCH_BYTES that is part
+ * of the library image: every GPU that loads libhashattn.so carries it until the process ends.
+ *   - Returns HA_ERR_SCRATCH_LIMIT, launching nothing, when this shape needs more than that
+ *     (ha_static_scratch_needed() tells how much a shape needs).
+ *   - Calls no allocator of any kind. The first call on each device looks the buffer's device
+ *     address up (cudaGetSymbolAddress) and keeps it; make that first call outside any stream
+ *     capture.
+ *   - All calls on a device share the one buffer. Nothing in it has to be zero on entry (each
+ *     call writes every word before reading it), but two calls whose kernels may overlap on
+ *     the GPU - different streams, no ordering between them - overwrite each other: order them. */
+#define HA_STATIC_SCRATCH_BYTES (4u << 20)
+size_t ha_static_scratch_needed(const ha_shape_t* shape);
+int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
+                           const uint32_t* q_codes, const uint32_t* hash_pages,
+                           const int32_t* page_table, const int32_t* seq_lens,
+                           int32_t* sel_idx, int32_t* sel_cnt, int32_t* status, void* stream);
 
 /* Sparse GQA flash-decode over sink + heavy + recent tokens.
  * Replaces hashattention/hashattention_llama.py:578-623 (repeat_kv, QK^T/sqrt(d), mask fill,
