@@ -44,7 +44,7 @@ METRIC, UNIT = "sparse_decode_attn_hbm_gbs", "GB/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # capture summarised in profiles/ (None until a capture of that workload exists)
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {"config1": 17137664}  # sparse_gather_kernel, profiles/decode_kernels_config1_ncu_full.md
 
 
 def peaks():
