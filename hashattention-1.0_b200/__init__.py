@@ -5,12 +5,12 @@ The directory name is not a Python identifier; load it under the module name
 ``from hashattention_b200 import load_usa, convert_usa`` mirrors
 ``from hashattention.hashattention_llama import load_usa, convert_usa``.
 """
-from . import _lib
+from . import _lib, partition
 from .cache import PagedHashKVCache
 from .ops import Budget, HostStepBuffers, SparseDecodeContext, decode_step_host
 from .usa import USA, PackedHashWeights
 
 __all__ = [
     "USA", "PackedHashWeights", "PagedHashKVCache", "Budget", "SparseDecodeContext", "HostStepBuffers",
-    "decode_step_host", "_lib",
+    "decode_step_host", "_lib", "partition",
 ]
