@@ -296,7 +296,7 @@ def run_gpu_arm(args):
     att_bytes = nbytes["kv"] + nbytes["qo"]
     peak, peak_src = peaks()
     att_gbs = att_bytes / (stage_us["sparse_decode"] * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "kernel": "sparse_decode_kernel", "achieved": att_gbs, "peak": peak, "unit": "GB/s",
+    roofline = {"bound": "hbm", "kernel": "sparse_gather_kernel + sparse_merge_kernel", "achieved": att_gbs, "peak": peak, "unit": "GB/s",
                 "frac": att_gbs / peak, "traffic": NCU_TRAFFIC.get(args.workload), "peak_source": peak_src,
                 "algorithmic_bytes_per_launch": att_bytes, "us_per_launch": stage_us["sparse_decode"]}
     pipeline = {"bytes_per_step": nbytes, "achieved": nbytes["total"] / per_step / 1e9, "peak": peak,

@@ -26,9 +26,13 @@
 // the grid-dependency wait.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace ha {
+
+namespace cg = cooperative_groups;
 
 constexpr int kRoundPages = 4;                        // pages per round
 constexpr int kRoundTokens = kRoundPages * kPage;     // 1024
@@ -196,7 +200,7 @@ __device__ __forceinline__ uint32_t bytes_eq(uint32_t a, uint32_t t4) {
 __device__ __forceinline__ uint32_t flags_to_nibble(uint32_t f) { return (((f >> 7) * 0x01020408u) >> 24) & 0xFu; }
 
 template <int ROUNDS>
-__global__ void __launch_bounds__(kSelThreads, ROUNDS >= 4 ? 3 : 4) select_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectParams p) {
     HA_TL(kTlSelect, kTlEntry);
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -216,8 +220,30 @@ __global__ void __launch_bounds__(kSelThreads, ROUNDS >= 4 ? 3 : 4) select_kerne
     const bool active = s_ok && chunk_start < S;
     const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
     const int nchunks_b = (r.S + chunk_tokens - 1) / chunk_tokens;
-    RoundWords rw;
-    if (active) rw.load(p, b, kvh, RoundWords::first_token(chunk_start, 0, warp), lane, r);
+    // --- before the dependency wait: this chunk's scores. The kernel in front of this one
+    //     (score_hist) writes only histograms; the query codes and every hash word, the newest
+    //     token's included, come from the encoder kernel, which had completed before any CTA of
+    //     this kernel could start. Scores are kept packed in registers (byte g = head g).
+    uint32_t sc[ROUNDS][kLaneTokens];
+    int page[ROUNDS];
+    uint32_t cand = 0;  // bit rd * 4 + it
+    if (active) {
+        const uint4 qn = load_qn(p, b, kvh);
+        RoundWords rw;
+#pragma unroll
+        for (int rd = 0; rd < ROUNDS; ++rd) {
+            const int t0 = RoundWords::first_token(chunk_start, rd, warp);
+            rw.load(p, b, kvh, rd > 0 ? min(t0, S - 1) : t0, lane, r);  // beyond S: clamped, nothing valid
+            rw.refresh_newest(p, kvh, t0, lane, r);
+            page[rd] = rw.page;
+            const uint32_t cmask = (rd > 0 && t0 >= S) ? 0u : rw.cand;
+            cand |= cmask << (rd * kLaneTokens);
+#pragma unroll
+            for (int it = 0; it < kLaneTokens; ++it)
+                sc[rd][it] = __popc(qn.x ^ rw.w[it].x) | (__popc(qn.y ^ rw.w[it].y) << 8) |
+                             (__popc(qn.z ^ rw.w[it].z) << 16) | (__popc(qn.w ^ rw.w[it].w) << 24);
+        }
+    }
 
     pdl_wait();
     HA_TL(kTlSelect, kTlAfterWait);
@@ -226,7 +252,6 @@ __global__ void __launch_bounds__(kSelThreads, ROUNDS >= 4 ? 3 : 4) select_kerne
 
     // --- histogram lines of this warp's bins: warp w reduces bins [17w, 17w+17), lane = chunk;
     //     the 17 loads of a pass are independent and issued together
-    const uint4 qn = load_qn(p, b, kvh);
     const uint32_t* hbase = p.hist + ((size_t)b * p.Hkv + kvh) * (kGroup * kBins) * p.nchunks;
     for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
         const int cc = cc0 + lane;
@@ -246,24 +271,6 @@ __global__ void __launch_bounds__(kSelThreads, ROUNDS >= 4 ? 3 : 4) select_kerne
                 s_bef[warp * kBinsPerWarp + k] = cc0 == 0 ? f : s_bef[warp * kBinsPerWarp + k] + f;
             }
         }
-    }
-
-    // --- this chunk's scores, kept packed in registers (one u32 per token: byte g = head g) --------
-    uint32_t sc[ROUNDS][kLaneTokens];
-    int page[ROUNDS];
-    uint32_t cand = 0;  // bit rd * 4 + it
-#pragma unroll
-    for (int rd = 0; rd < ROUNDS; ++rd) {
-        const int t0 = RoundWords::first_token(chunk_start, rd, warp);
-        if (rd > 0) rw.load(p, b, kvh, min(t0, S - 1), lane, r);  // beyond S: clamped, nothing valid
-        rw.refresh_newest(p, kvh, t0, lane, r);
-        page[rd] = rw.page;
-        const uint32_t cmask = (rd > 0 && t0 >= S) ? 0u : rw.cand;
-        cand |= cmask << (rd * kLaneTokens);
-#pragma unroll
-        for (int it = 0; it < kLaneTokens; ++it)
-            sc[rd][it] = __popc(qn.x ^ rw.w[it].x) | (__popc(qn.y ^ rw.w[it].y) << 8) |
-                         (__popc(qn.z ^ rw.w[it].z) << 16) | (__popc(qn.w ^ rw.w[it].w) << 24);
     }
     __syncthreads();
 
@@ -440,6 +447,296 @@ __global__ void __launch_bounds__(kSelThreads, ROUNDS >= 4 ? 3 : 4) select_kerne
         }
     }
     HA_TL(kTlSelect, kTlExit);
+}
+
+// ------------------------------------------------------------------------------------------
+// Single-kernel variant for short sequences (up to ROUNDS * 32768 tokens): one cluster of 8 CTAs
+// x 1024 threads owns one (sequence, kv-head). A CTA scores 4096 tokens per round (4 per lane),
+// keeps the packed scores in registers, and the 8 CTAs exchange their 4 x 33 histograms through
+// distributed shared memory instead of global memory - so the hash pages are read once, there
+// is no second pass, no histogram traffic and no kernel hand-over between scoring and
+// selection. Token order is (round, CTA rank, warp, it, lane); results are identical to
+// score_hist_kernel + select_kernel.
+// ------------------------------------------------------------------------------------------
+constexpr int kClThreads = 1024;
+constexpr int kClWarps = kClThreads / 32;                     // 32 = slots per CTA and round
+constexpr int kClCtas = 8;                                    // portable cluster size
+constexpr int kClCtaTokens = kClThreads * kLaneTokens;        // 4096 tokens per CTA and round
+constexpr int kClRoundTokens = kClCtas * kClCtaTokens;        // 32768 tokens per cluster and round
+constexpr int kClHistCopies = 8;                              // warp w updates copy w % 8
+
+template <int ROUNDS>
+__global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(const SelectParams p) {
+    HA_TL(kTlScoreHist, kTlEntry);
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int kvh = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int Hq = p.Hkv * kGroup;
+    constexpr int kHist = kGroup * kBins;  // 132
+
+    __shared__ uint32_t s_hist[ROUNDS][kClHistCopies][kHist];
+    __shared__ uint32_t s_cta_hist[ROUNDS][kHist];   // read by the other CTAs of the cluster
+    __shared__ int s_tot[kHist];
+    __shared__ int s_bef[ROUNDS][kHist];             // counts in (round, rank) pairs before (rd, this CTA)
+    __shared__ int s_T[kGroup], s_need[kGroup], s_base[ROUNDS][kGroup], s_eqb[ROUNDS][kGroup];
+    __shared__ uint32_t s_sgt[ROUNDS][kClWarps], s_seq[ROUNDS][kClWarps];
+    for (int i = tid; i < ROUNDS * kClHistCopies * kHist; i += kClThreads) (&s_hist[0][0][0])[i] = 0;
+
+    const int S = p.seq_lens[b];
+    const bool s_ok = S >= 1 && S <= p.max_pages * kPage && S <= ROUNDS * kClRoundTokens;
+    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
+    auto first_token = [&](int rd) { return rd * kClRoundTokens + rank * kClCtaTokens + warp * (kLaneTokens * 32); };
+    RoundWords rw;
+    const bool active0 = s_ok && first_token(0) < S;  // warp-uniform
+    if (active0) rw.load(p, b, kvh, first_token(0), lane, r);
+
+    pdl_wait();
+    HA_TL(kTlScoreHist, kTlAfterWait);
+    pdl_launch_dependents();
+    if (!s_ok && tid == 0 && rank == 0 && kvh == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+
+    // --- scores of this thread's tokens (packed, byte g = head g) and the CTA's histograms ---------
+    uint32_t sc[ROUNDS][kLaneTokens];
+    int page[ROUNDS];
+    uint32_t cand = 0;  // bit rd * 4 + it
+    bool bad_page = false;
+    const uint4 qn = load_qn(p, b, kvh);
+    __syncthreads();  // s_hist is zero
+#pragma unroll
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+        const int t0 = first_token(rd);
+        const bool act = s_ok && t0 < S;  // warp-uniform
+        page[rd] = 0;
+#pragma unroll
+        for (int it = 0; it < kLaneTokens; ++it) sc[rd][it] = 0;
+        if (!act) continue;
+        if (rd > 0) rw.load(p, b, kvh, t0, lane, r);
+        rw.refresh_newest(p, kvh, t0, lane, r);
+        bad_page |= rw.bad_page;
+        page[rd] = rw.page;
+        cand |= rw.cand << (rd * kLaneTokens);
+        uint32_t* h0 = &s_hist[rd][warp % kClHistCopies][0];
+#pragma unroll
+        for (int it = 0; it < kLaneTokens; ++it) {
+            const uint32_t s0 = __popc(qn.x ^ rw.w[it].x), s1 = __popc(qn.y ^ rw.w[it].y);
+            const uint32_t s2 = __popc(qn.z ^ rw.w[it].z), s3 = __popc(qn.w ^ rw.w[it].w);
+            sc[rd][it] = s0 | (s1 << 8) | (s2 << 16) | (s3 << 24);
+            if (rw.interior || ((rw.cand >> it) & 1u)) {
+                atomicAdd(h0 + s0, 1u);
+                atomicAdd(h0 + kBins + s1, 1u);
+                atomicAdd(h0 + 2 * kBins + s2, 1u);
+                atomicAdd(h0 + 3 * kBins + s3, 1u);
+            }
+            if (p.scores_dbg != nullptr && ((rw.valid >> it) & 1u)) {
+                const size_t pitch = (size_t)p.max_pages * kPage;
+                uint8_t* d = p.scores_dbg + ((size_t)b * Hq + kvh * kGroup) * pitch + t0 + it * 32 + lane;
+                d[0] = (uint8_t)s0;
+                d[pitch] = (uint8_t)s1;
+                d[2 * pitch] = (uint8_t)s2;
+                d[3 * pitch] = (uint8_t)s3;
+            }
+        }
+    }
+    if (bad_page) report(p.status, HA_ERR_BAD_PAGE);
+    __syncthreads();
+    for (int i = tid; i < ROUNDS * kHist; i += kClThreads) {
+        const int rd = i / kHist, bin = i % kHist;
+        uint32_t v = 0;
+#pragma unroll
+        for (int k = 0; k < kClHistCopies; ++k) v += s_hist[rd][k][bin];
+        s_cta_hist[rd][bin] = v;
+    }
+
+    // --- exchange: every CTA sums the histograms of all (round, rank) pairs, and of those before its own
+    cluster.sync();
+    if (tid < kHist) {
+        int tot = 0, run = 0;
+        int bef[ROUNDS];
+#pragma unroll
+        for (int rd = 0; rd < ROUNDS; ++rd) {
+#pragma unroll
+            for (int rk = 0; rk < kClCtas; ++rk) {
+                if (rk == rank) bef[rd] = run;
+                run += (int)*cluster.map_shared_rank(&s_cta_hist[rd][tid], rk);
+            }
+        }
+        tot = run;
+        s_tot[tid] = tot;
+#pragma unroll
+        for (int rd = 0; rd < ROUNDS; ++rd) s_bef[rd][tid] = bef[rd];
+    }
+    __syncthreads();  // s_tot / s_bef complete (the other CTAs may still be reading s_cta_hist)
+    HA_TL(kTlSelect, kTlAfterWait);
+
+    // --- threshold, tie quota and output bases per head: warp g scans the 33 bins downwards --------
+    if (warp < kGroup) {
+        const int g = warp;
+        int hbe = r.hb;
+        if (hbe > p.sel_stride) {
+            if (lane == 0 && rank == 0) report(p.status, HA_ERR_SEL_OVERFLOW);
+            hbe = p.sel_stride;
+        }
+        if (!s_ok) hbe = 0;
+        const int n = s_tot[g * kBins + 32 - lane];  // lane l holds bin 32 - l; bin 0 is the remainder
+        int cum = n;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, cum, d);
+            if (lane >= d) cum += u;
+        }
+        const uint32_t reached = __ballot_sync(0xffffffffu, cum >= hbe);
+        int T, need, lsel = 31;
+        if (hbe <= 0) {
+            T = kBins; need = 0;  // T = 33: nothing qualifies
+        } else if (reached != 0) {
+            lsel = __ffs(reached) - 1;  // first lane whose cumulative count reaches the budget
+            T = 32 - lsel;
+            need = hbe - __shfl_sync(0xffffffffu, cum - n, lsel);
+        } else {  // bins 32..1 together hold fewer than the budget: the threshold is 0
+            T = 0;
+            need = hbe - __shfl_sync(0xffffffffu, cum, 31);
+        }
+#pragma unroll
+        for (int rd = 0; rd < ROUNDS; ++rd) {
+            const int nb = s_bef[rd][g * kBins + 32 - lane];
+            int cumb = nb;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, cumb, d);
+                if (lane >= d) cumb += u;
+            }
+            int gt_before = 0, eq_before = 0;
+            if (hbe > 0 && reached != 0) {
+                gt_before = __shfl_sync(0xffffffffu, cumb - nb, lsel);
+                eq_before = __shfl_sync(0xffffffffu, nb, lsel);
+            } else if (hbe > 0) {
+                gt_before = __shfl_sync(0xffffffffu, cumb, 31);
+                eq_before = s_bef[rd][g * kBins];
+            }
+            if (lane == 0) {
+                s_eqb[rd][g] = eq_before;
+                s_base[rd][g] = gt_before + min(eq_before, need);
+            }
+        }
+        if (lane == 0) {
+            s_T[g] = T;
+            s_need[g] = need;
+            if (rank == 0 && s_ok) p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = hbe;
+        }
+    }
+    __syncthreads();
+
+    // --- classify and count per (round, warp) slot -------------------------------------------------
+    const uint32_t t4 = (uint32_t)s_T[0] | ((uint32_t)s_T[1] << 8) | ((uint32_t)s_T[2] << 16) | ((uint32_t)s_T[3] << 24);
+    const uint32_t gt_add = 0x7F7F7F7Fu - t4;
+    auto flags_gt = [&](int rd, int it) {
+        const uint32_t cm = 0u - ((cand >> (rd * kLaneTokens + it)) & 1u);
+        return bytes_gt(sc[rd][it], gt_add) & cm;
+    };
+    auto flags_eq = [&](int rd, int it) {
+        const uint32_t cm = 0u - ((cand >> (rd * kLaneTokens + it)) & 1u);
+        return bytes_eq(sc[rd][it], t4) & cm;
+    };
+#pragma unroll
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+        uint32_t cg_ = 0, ce_ = 0;
+#pragma unroll
+        for (int it = 0; it < kLaneTokens; ++it) {
+            cg_ += flags_gt(rd, it) >> 7;
+            ce_ += flags_eq(rd, it) >> 7;
+        }
+        cg_ = __reduce_add_sync(0xffffffffu, cg_);  // <= 128 per byte: no carry between heads
+        ce_ = __reduce_add_sync(0xffffffffu, ce_);
+        if (lane == 0) {
+            s_sgt[rd][warp] = cg_;
+            s_seq[rd][warp] = ce_;
+        }
+    }
+    __syncthreads();
+
+    // --- per round: prefix over the CTA's 32 warps, then emission as in select_kernel ---------------
+    const uint32_t lt_mask = (1u << lane) - 1u;
+#pragma unroll
+    for (int rd = 0; rd < ROUNDS; ++rd) {
+        // lane = warp index of this round: exclusive prefix sums of the packed counts
+        const uint32_t g4 = s_sgt[rd][lane], e4 = s_seq[rd][lane];
+        const uint32_t g01 = (g4 & 0xffu) | ((g4 & 0xff00u) << 8), g23 = ((g4 >> 16) & 0xffu) | ((g4 >> 24) << 16);
+        const uint32_t e01 = (e4 & 0xffu) | ((e4 & 0xff00u) << 8), e23 = ((e4 >> 16) & 0xffu) | ((e4 >> 24) << 16);
+        uint32_t pg01 = g01, pg23 = g23, pe01 = e01, pe23 = e23;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t a0 = __shfl_up_sync(0xffffffffu, pg01, d), a1 = __shfl_up_sync(0xffffffffu, pg23, d);
+            const uint32_t a2 = __shfl_up_sync(0xffffffffu, pe01, d), a3 = __shfl_up_sync(0xffffffffu, pe23, d);
+            if (lane >= d) {
+                pg01 += a0; pg23 += a1; pe01 += a2; pe23 += a3;
+            }
+        }
+        pg01 -= g01; pg23 -= g23; pe01 -= e01; pe23 -= e23;
+        const uint32_t sg01 = __shfl_sync(0xffffffffu, pg01, warp), sg23 = __shfl_sync(0xffffffffu, pg23, warp);
+        const uint32_t se01 = __shfl_sync(0xffffffffu, pe01, warp), se23 = __shfl_sync(0xffffffffu, pe23, warp);
+        const uint32_t mine_g = s_sgt[rd][warp], mine_e = s_seq[rd][warp];
+        if ((mine_g | mine_e) == 0) continue;  // nothing of any head in this warp's 128 tokens
+        int base_pos[kGroup], eqb[kGroup];
+        uint32_t full4 = 0, straddle = 0;
+#pragma unroll
+        for (int g = 0; g < kGroup; ++g) {
+            const int gt_b = (int)(((g < 2 ? sg01 : sg23) >> ((g & 1) * 16)) & 0xffffu);
+            const int need = s_need[g];
+            eqb[g] = s_eqb[rd][g] + (int)(((g < 2 ? se01 : se23) >> ((g & 1) * 16)) & 0xffffu);
+            const int eq_in = (int)((mine_e >> (8 * g)) & 0xffu);
+            base_pos[g] = s_base[rd][g] + gt_b + (min(eqb[g], need) - min(s_eqb[rd][g], need));
+            if (eqb[g] + eq_in <= need) full4 |= 0x80u << (8 * g);
+            else if (eqb[g] < need) straddle |= 1u << g;
+        }
+        uint32_t selm[kLaneTokens];
+#pragma unroll
+        for (int it = 0; it < kLaneTokens; ++it) selm[it] = flags_gt(rd, it) | (flags_eq(rd, it) & full4);
+        if (straddle != 0) {  // warp-uniform, at most once per (sequence, head): rank ties by token index
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) {
+                if (!((straddle >> g) & 1u)) continue;
+                int eq_run = eqb[g];
+#pragma unroll
+                for (int it = 0; it < kLaneTokens; ++it) {
+                    const bool eq = (flags_eq(rd, it) >> (8 * g + 7)) & 1u;
+                    const uint32_t m_eq = __ballot_sync(0xffffffffu, eq);
+                    if (eq && eq_run + __popc(m_eq & lt_mask) < s_need[g]) selm[it] |= 0x80u << (8 * g);
+                    eq_run += __popc(m_eq);
+                }
+            }
+        }
+        uint32_t cnt4 = 0, bits = 0;
+#pragma unroll
+        for (int it = 0; it < kLaneTokens; ++it) {
+            cnt4 += selm[it] >> 7;
+            bits |= flags_to_nibble(selm[it]) << (4 * it);
+        }
+        uint32_t excl = cnt4;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t u = __shfl_up_sync(0xffffffffu, excl, d);
+            if (lane >= d) excl += u;
+        }
+        excl -= cnt4;
+        const int t_lane = first_token(rd) + lane;
+        const int prow0 = page[rd] * kPage + t_lane % kPage;
+        while (bits != 0) {
+            const int i = __ffs(bits) - 1;
+            bits &= bits - 1;
+            const int it = i >> 2, g = i & 3;
+            const int bp = g == 0 ? base_pos[0] : (g == 1 ? base_pos[1] : (g == 2 ? base_pos[2] : base_pos[3]));
+            const int pos = bp + (int)((excl >> (8 * g)) & 0xffu);
+            excl += 1u << (8 * g);
+            if (pos < p.sel_stride) {
+                const size_t o = ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride + pos;
+                p.sel_idx[o] = t_lane + it * 32;
+                p.sel_rows[o] = prow0 + it * 32;
+            }
+        }
+    }
+    HA_TL(kTlSelect, kTlExit);
+    cluster.sync();  // s_cta_hist may be read by the other CTAs until they, too, are past the exchange
 }
 
 }  // namespace ha

@@ -251,15 +251,19 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
     HA_TL(kTlGather, kTlExit);
 }
 
-// Log-sum-exp merge of the partials of one (b, h): 128 threads, thread = output dimension; the
-// splits are taken 32 at a time (lane = split for the max / sum pairs), all loads of a block
-// issued together, with a running maximum across blocks.
+// Log-sum-exp merge of the partials of one (b, h): 128 threads, thread = output dimension. Warp w
+// takes the splits s = w, w + 4, ... (so the dependent accumulate chain is a quarter as long),
+// lane = split for the (max, sum) pairs, all loads of a pass issued together; the four warps'
+// results are combined in shared memory.
 __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDecodeParams p) {
     HA_TL(kTlMerge, kTlEntry);
     const int h = blockIdx.x, b = blockIdx.y;
     const int Hq = p.Hkv * kGroup;
-    const int tid = threadIdx.x, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int kWarps = kHeadDim / 32;
     const AttPlan a = att_plan(p, b);
+    __shared__ float s_m[kWarps], s_l[kWarps];
+    __shared__ float s_a[kWarps][kHeadDim];
 
     pdl_wait();
     HA_TL(kTlMerge, kTlAfterWait);
@@ -267,33 +271,56 @@ __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDeco
     if (a.nsplits <= 1) return;  // written by the gather kernel (or nothing to write)
 
     const float* base = p.partials + ((size_t)b * Hq + h) * p.nsplits * kPartStride;
-    float Mg = -INFINITY, Lg = 0.f, Ag = 0.f;
-    for (int s0 = 0; s0 < a.nsplits; s0 += 32) {
-        const int n = min(32, a.nsplits - s0);
-        const int s = s0 + min(lane, n - 1);
-        const float ms = __ldcg(base + (size_t)s * kPartStride);
-        const float ls = __ldcg(base + (size_t)s * kPartStride + 1);
-        float av[32];
+    // this warp's splits: s = warp + 4 * i; it accumulates all 128 dimensions (4 per lane)
+    const int mine = (a.nsplits - warp + kWarps - 1) / kWarps;
+    float Mg = -INFINITY, Lg = 0.f, Ag[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i0 = 0; i0 < mine; i0 += 8) {
+        const int n = min(8, mine - i0);
+        float ms[8], ls[8];
+        float4 av[8];
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-            av[j] = __ldcg(base + (size_t)(s0 + min(j, n - 1)) * kPartStride + 2 + tid);
-        float mb = lane < n ? ms : -INFINITY;
+        for (int j = 0; j < 8; ++j) {
+            const float* ps = base + (size_t)(warp + kWarps * (i0 + min(j, n - 1))) * kPartStride;
+            ms[j] = __ldcg(ps);
+            ls[j] = __ldcg(ps + 1);
+            av[j] = make_float4(__ldcg(ps + 2 + lane), __ldcg(ps + 34 + lane), __ldcg(ps + 66 + lane), __ldcg(ps + 98 + lane));
+        }
+        float mb = -INFINITY;
 #pragma unroll
-        for (int d = 16; d >= 1; d >>= 1) mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, d));
+        for (int j = 0; j < 8; ++j) mb = fmaxf(mb, j < n ? ms[j] : -INFINITY);
         const float Mn = fmaxf(Mg, mb);
         const float rescale = Mg == -INFINITY ? 0.f : exp2f(Mg - Mn);
         Mg = Mn;
         Lg *= rescale;
-        Ag *= rescale;
-        const float f = (lane < n && ms != -INFINITY) ? exp2f(ms - Mg) : 0.f;
-        const float lf = ls * f;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            Lg += __shfl_sync(0xffffffffu, lf, j);
-            Ag = fmaf(av[j], __shfl_sync(0xffffffffu, f, j), Ag);  // f = 0 beyond n
+        for (int d = 0; d < 4; ++d) Ag[d] *= rescale;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float f = (j < n && ms[j] != -INFINITY) ? exp2f(ms[j] - Mg) : 0.f;
+            Lg = fmaf(ls[j], f, Lg);
+            Ag[0] = fmaf(av[j].x, f, Ag[0]);
+            Ag[1] = fmaf(av[j].y, f, Ag[1]);
+            Ag[2] = fmaf(av[j].z, f, Ag[2]);
+            Ag[3] = fmaf(av[j].w, f, Ag[3]);
         }
     }
-    p.out[((size_t)b * Hq + h) * kHeadDim + tid] = __float2bfloat16_rn(Ag / Lg);
+    if (lane == 0) {
+        s_m[warp] = Mg;
+        s_l[warp] = Lg;
+    }
+#pragma unroll
+    for (int d = 0; d < 4; ++d) s_a[warp][d * 32 + lane] = Ag[d];
+    __syncthreads();
+    float M = -INFINITY, L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w]);
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        const float f = s_m[w] == -INFINITY ? 0.f : exp2f(s_m[w] - M);
+        L = fmaf(s_l[w], f, L);
+        A = fmaf(s_a[w][tid], f, A);
+    }
+    p.out[((size_t)b * Hq + h) * kHeadDim + tid] = __float2bfloat16_rn(A / L);
     HA_TL(kTlMerge, kTlExit);
 }
 

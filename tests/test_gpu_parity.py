@@ -233,6 +233,26 @@ def test_ragged_batch_shuffled_pages(device):
     run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(16, 1.0 / 16, 32), shuffle_seed=3)
 
 
+def test_many_units_take_the_two_pass_selection(device):
+    """40 (sequence, kv-head) units: beyond what the single-pass cluster kernel is used for, so the
+    score_hist + select pair runs (smaller cases in this file run the cluster kernel)."""
+    Hq, Hkv = 16, 4
+    lens = [300, 1025, 64, 2000, 513, 777, 1300, 256, 900, 1500]
+    usa = synthetic.make_usa(Hq, 128, 3, True)
+    inp = synthetic.make_decode_inputs(103, lens, Hq, Hkv)
+    run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(32, 1.0 / 8, 32), shuffle_seed=9)
+
+
+@pytest.mark.parametrize("S", [40000, 70000])
+def test_long_sequence_selection(device, S):
+    """S = 40,000 runs the cluster kernel with two rounds; S = 70,000 (chunks of 8 pages, two rounds
+    per CTA) the two-pass pair. Both against the oracle."""
+    Hq, Hkv = 8, 2
+    usa = synthetic.make_usa(Hq, 128, 4, True)
+    inp = synthetic.make_decode_inputs(104, [S], Hq, Hkv)
+    run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(128, 1.0 / 32, 128), shuffle_seed=2)
+
+
 def test_fp32_weights_step(device):
     usa = synthetic.make_usa(8, 128, 5, bf16=False)
     inp = synthetic.make_decode_inputs(95, [777, 300], 8, 2)
