@@ -285,6 +285,7 @@ hash_prefill_simt_kernel(const HashPrefillParams p) {
     regs.load(static_cast<const WT*>(p.wk) + (size_t)h * kMlpElems, p.bk + (size_t)h * kMlpBias,
               warp, lane >> 4, (lane & 15) * 8);
     __shared__ MlpSmem sm;
+    pdl_wait();  // the keys may have been written by the kernel before this one
 
     const size_t slot0 = ((size_t)page * p.Hkv + kvh) * kPage;
     for (int t = t_begin; t < t_end; ++t) {

@@ -1,0 +1,310 @@
+// Prefill key-hash build on the 5th-generation tensor cores (tcgen05, sm_100a only).
+//
+// For every cached key x (128 bf16) and every query head h of its kv-head the hash MLP
+//     code = signbits( W2 . silu( W1 . silu( W0 x + b0 ) + b1 ) + b2 )
+// is a chain of three GEMMs over a tile of 128 tokens. A CTA owns one head: the head's three
+// weight matrices (72 KB bf16) stay in shared memory in the K-major 128-byte-swizzled layout the
+// UMMA shared-memory descriptors describe, and the CTA walks over token tiles:
+//   1. the 128 x 128 key tile is copied into swizzled shared memory (it is contiguous in a page),
+//   2. one thread issues tcgen05.mma (M = 128, N = 128, K = 16 per instruction, bf16 x bf16 -> fp32)
+//      into tensor memory and commits to an mbarrier,
+//   3. the 8 warps read the accumulator with tcgen05.ld (thread = token row, 64 columns each), add
+//      the bias, apply SiLU in fp32 and split the activation into a hi and a lo bf16 (hi + lo
+//      carries 16 mantissa bits), written back to swizzled shared memory as the next A operand,
+//   4. layer 2 runs two MMAs per k-step (hi and lo against the same weights), layer 3 likewise
+//      with N = 32, and the last epilogue packs the 32 sign bits of a token row into its code.
+// The hi/lo split keeps the pre-activations within ~3e-6 of fp32 arithmetic, which is what makes
+// the packed codes match the reference bit for bit outside the |x| < 1e-5 band.
+//
+// Follows USA.k_embedding(hard=True) (hashattention/hashattention_llama.py:204-214).
+//
+// Every wait on the mbarrier is bounded: if a commit never arrives the CTA records
+// HA_ERR_TIMEOUT, stops issuing work, frees its tensor memory and returns.
+#pragma once
+
+#include "common.cuh"
+
+namespace ha {
+
+constexpr int kTcThreads = 256;
+constexpr int kTcTile = 128;                          // tokens per tile = TMEM lanes
+constexpr uint32_t kTcBlockBytes = 128 * 128;         // one K-half of a 128-row operand: 128 rows x 128 B
+constexpr uint32_t kTcW2BlockBytes = 32 * 128;        // one K-half of W2 (32 rows)
+constexpr uint32_t kTcOffW0 = 0;
+constexpr uint32_t kTcOffW1 = kTcOffW0 + 2 * kTcBlockBytes;
+constexpr uint32_t kTcOffW2 = kTcOffW1 + 2 * kTcBlockBytes;
+constexpr uint32_t kTcOffX = kTcOffW2 + 2 * kTcW2BlockBytes;
+constexpr uint32_t kTcOffHi = kTcOffX + 2 * kTcBlockBytes;
+constexpr uint32_t kTcOffLo = kTcOffHi + 2 * kTcBlockBytes;
+constexpr uint32_t kTcOffBias = kTcOffLo + 2 * kTcBlockBytes;          // 288 floats
+constexpr uint32_t kTcOffBar = kTcOffBias + 1280;                      // mbarrier (8 B) + tmem base (4 B)
+constexpr uint32_t kTcSmemBytes = kTcOffBar + 64 + 1024;               // + slack to align the base to 1024 B
+constexpr uint32_t kTcTmemCols = 512;
+constexpr uint32_t kTcColD1 = 0, kTcColD2 = 128, kTcColD3 = 256;
+constexpr int kTcSpinLimit = 1 << 22;
+
+struct HashPrefillTcParams {
+    const __nv_bfloat16* k_pages;
+    uint32_t* hash_pages;
+    const __nv_bfloat16* wk;   // [Hq][36864] bf16
+    const float* bk;           // [Hq][288]
+    const int32_t* page_table;
+    const int32_t* seq_lens;
+    const int32_t* first_token;  // [B] or null
+    int32_t* status;
+    int B, Hkv, max_pages, num_pages;
+};
+
+__device__ __forceinline__ uint32_t tc_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside one K-half block of a K-major
+// operand with 128-byte swizzle: rows are 128 B apart, 8-row groups 1024 B apart, and the chunk
+// index is XORed with the row's position in its group.
+__device__ __forceinline__ uint32_t tc_swizzled(uint32_t row, uint32_t chunk) {
+    return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+
+// Shared-memory matrix descriptor: K-major, SWIZZLE_128B, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t tc_idesc(uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// Bounded wait for phase `parity` of the mbarrier; false if it ran out.
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity) {
+    for (int spin = 0; spin < kTcSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ uint32_t tc_pack_bf16(float a, float b) {
+    const __nv_bfloat162 t = __floats2bfloat162_rn(a, b);  // .x = a (low half), .y = b
+    return *reinterpret_cast<const uint32_t*>(&t);
+}
+
+// Copies `rows` rows of 128 bf16 (row-major, 256 B apart in global memory) into the two K-half
+// blocks of a swizzled operand; block_bytes = rows * 128.
+__device__ __forceinline__ void tc_load_operand(unsigned char* dst, const __nv_bfloat16* src, int rows,
+                                                uint32_t block_bytes, int tid) {
+    for (int i = tid; i < rows * 16; i += kTcThreads) {
+        const int row = i >> 4, c16 = i & 15;  // c16: 16-byte chunk of the 256-byte row
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + (size_t)row * kHeadDim) + c16);
+        *reinterpret_cast<uint4*>(dst + (c16 >> 3) * block_bytes + tc_swizzled(row, c16 & 7)) = v;
+    }
+}
+
+// bias + SiLU + hi/lo split of 64 accumulator columns (one K-half block of the next A operand).
+__device__ __forceinline__ void tc_hidden_epilogue(uint32_t taddr, const float* bias, unsigned char* hi_blk,
+                                                   unsigned char* lo_blk, uint32_t row) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        float v[32];
+        tc_ld32(taddr + half * 32, v);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // 4 chunks of 8 columns
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float a[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int col = c * 8 + e * 2 + j;
+                    const float x = v[col] + bias[half * 32 + col];
+                    a[j] = x / (1.0f + expf(-x));
+                }
+                const float h0 = __bfloat162float(__float2bfloat16_rn(a[0]));
+                const float h1 = __bfloat162float(__float2bfloat16_rn(a[1]));
+                hi[e] = tc_pack_bf16(h0, h1);
+                lo[e] = tc_pack_bf16(a[0] - h0, a[1] - h1);
+            }
+            const uint32_t off = tc_swizzled(row, half * 4 + c);
+            *reinterpret_cast<uint4*>(hi_blk + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(lo_blk + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const HashPrefillTcParams p) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int h = blockIdx.y, kvh = h / kGroup, g = h % kGroup;
+    float* s_bias = reinterpret_cast<float*>(smem + kTcOffBias);
+    unsigned long long* s_bar = reinterpret_cast<unsigned long long*>(smem + kTcOffBar);
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kTcOffBar + 16);
+
+    // ---- one-time set-up: weights and biases of this head, mbarrier, tensor memory -------------
+    const __nv_bfloat16* W = p.wk + (size_t)h * kMlpElems;
+    tc_load_operand(smem + kTcOffW0, W, 128, kTcBlockBytes, tid);
+    tc_load_operand(smem + kTcOffW1, W + kHidden * kHeadDim, 128, kTcBlockBytes, tid);
+    tc_load_operand(smem + kTcOffW2, W + kHidden * kHeadDim + kHidden * kHidden, 32, kTcW2BlockBytes, tid);
+    for (int i = tid; i < kMlpBias; i += kTcThreads) s_bias[i] = p.bk[(size_t)h * kMlpBias + i];
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(s_bar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(s_tmem)), "r"(kTcTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *s_tmem;
+    const uint32_t bar = tc_smem_u32(s_bar);
+    const uint32_t sbase = tc_smem_u32(smem);
+    const uint32_t idesc128 = tc_idesc(128), idesc32 = tc_idesc(32);
+    // this thread's accumulator slice: TMEM lanes 32 (warp % 4) .. +31, columns 64 (warp / 4) .. +63
+    const uint32_t row = (warp & 3) * 32 + lane, kb = warp >> 2;
+    const uint32_t t_lane = ((warp & 3) * 32u) << 16;
+    uint32_t phase = 0;
+
+    // one K = 128 GEMM: 8 k-steps of 16 (32 bytes inside the swizzled 128-byte rows, 4 per K-half)
+    auto gemm = [&](uint32_t col_d, uint32_t off_a, uint32_t off_b, uint32_t b_block_bytes, uint32_t idesc, bool first) {
+#pragma unroll
+        for (uint32_t ks = 0; ks < 8; ++ks) {
+            const uint32_t a = sbase + off_a + (ks >> 2) * kTcBlockBytes + (ks & 3) * 32;
+            const uint32_t bb = sbase + off_b + (ks >> 2) * b_block_bytes + (ks & 3) * 32;
+            tc_mma(tmem + col_d, tc_smem_desc(a), tc_smem_desc(bb), idesc, (first && ks == 0) ? 0u : 1u);
+        }
+    };
+    // Waits (bounded) for the commit of the GEMMs just issued, then agrees CTA-wide on the outcome,
+    // so that the warp-synchronous tensor-memory loads that follow are never executed by a part of
+    // the CTA only. Returns false for every thread if any thread's wait ran out.
+    auto wait_commit = [&]() -> bool {
+        const bool ok = tc_wait(bar, phase);
+        if (!ok) report(p.status, HA_ERR_TIMEOUT);
+        phase ^= 1;
+        const bool all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        return all_ok;
+    };
+    bool aborted = false;
+    pdl_wait();  // the weights above are constants; everything below may depend on the previous kernel
+
+    const int tiles_per_seq = p.max_pages * (kPage / kTcTile);
+    for (int item = blockIdx.x; item < p.B * tiles_per_seq; item += gridDim.x) {
+        const int b = item / tiles_per_seq, tile = item % tiles_per_seq;
+        const int S = p.seq_lens[b];
+        if (S < 0 || S > p.max_pages * kPage) {
+            if (tid == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+            continue;
+        }
+        const int first = p.first_token != nullptr ? max(0, p.first_token[b]) : 0;
+        const int t0 = tile * kTcTile;
+        if (t0 >= S || t0 + kTcTile <= first) continue;
+        const int page = p.page_table[(size_t)b * p.max_pages + t0 / kPage];
+        if (page < 0 || page >= p.num_pages) {
+            if (tid == 0) report(p.status, HA_ERR_BAD_PAGE);
+            continue;
+        }
+        const size_t slot0 = ((size_t)page * p.Hkv + kvh) * kPage + t0 % kPage;
+
+        // ---- key tile -> swizzled shared memory (generic proxy), then visible to the tensor core
+        tc_load_operand(smem + kTcOffX, p.k_pages + slot0 * kHeadDim, kTcTile, kTcBlockBytes, tid);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+
+        // ---- layer 0: D1 = X W0^T
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            gemm(kTcColD1, kTcOffX, kTcOffW0, kTcBlockBytes, idesc128, true);
+            tc_commit(bar);
+        }
+        if (!wait_commit()) { aborted = true; break; }
+        tc_hidden_epilogue(tmem + t_lane + kTcColD1 + kb * 64, s_bias + kb * 64, smem + kTcOffHi + kb * kTcBlockBytes,
+                           smem + kTcOffLo + kb * kTcBlockBytes, row);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+
+        // ---- layer 1: D2 = (Hhi + Hlo) W1^T
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            gemm(kTcColD2, kTcOffHi, kTcOffW1, kTcBlockBytes, idesc128, true);
+            gemm(kTcColD2, kTcOffLo, kTcOffW1, kTcBlockBytes, idesc128, false);
+            tc_commit(bar);
+        }
+        if (!wait_commit()) { aborted = true; break; }
+        tc_hidden_epilogue(tmem + t_lane + kTcColD2 + kb * 64, s_bias + kHidden + kb * 64,
+                           smem + kTcOffHi + kb * kTcBlockBytes, smem + kTcOffLo + kb * kTcBlockBytes, row);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+
+        // ---- layer 2: D3 = (Hhi + Hlo) W2^T, N = 32
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            gemm(kTcColD3, kTcOffHi, kTcOffW2, kTcW2BlockBytes, idesc32, true);
+            gemm(kTcColD3, kTcOffLo, kTcOffW2, kTcW2BlockBytes, idesc32, false);
+            tc_commit(bar);
+        }
+        if (!wait_commit()) { aborted = true; break; }
+        if (warp < 4) {  // thread = token row: 32 pre-activations -> one packed code
+            float v[32];
+            tc_ld32(tmem + t_lane + kTcColD3, v);
+            uint32_t code = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) code |= (v[i] + s_bias[2 * kHidden + i] > 0.0f ? 1u : 0u) << i;
+            const int t = t0 + (int)row;
+            if (t < S && t >= first) p.hash_pages[(slot0 + row) * kGroup + g] = code;
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();  // the accumulators and the key tile may be overwritten by the next tile
+    }
+
+    // ---- release tensor memory (after a time-out: give in-flight MMAs one more bounded wait) -------
+    __syncthreads();
+    if (aborted && tid == 0) tc_wait(bar, phase ^ 1);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTcTmemCols) : "memory");
+    }
+}
+
+}  // namespace ha

@@ -7,6 +7,7 @@
 
 #include "common.cuh"
 #include "hash_decode.cuh"
+#include "hash_prefill_tc.cuh"
 #include "score_select.cuh"
 #include "sparse_decode.cuh"
 
@@ -288,6 +289,43 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         status == nullptr)
         return HA_ERR_BAD_ARG;
 
+    if (weights->dtype == HA_WEIGHTS_BF16) {
+        // bf16 weights: tcgen05 GEMM chain. One CTA per SM (its shared memory holds a head's weights),
+        // heads in grid.y, token tiles dealt round-robin over grid.x.
+        static const cudaError_t attr = cudaFuncSetAttribute(hash_prefill_tc_kernel,
+                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
+        if (attr != cudaSuccess) return HA_ERR_LAUNCH;
+        HashPrefillTcParams t;
+        t.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+        t.hash_pages = hash_pages;
+        t.wk = static_cast<const __nv_bfloat16*>(weights->wk);
+        t.bk = weights->bk;
+        t.page_table = page_table;
+        t.seq_lens = seq_lens;
+        t.first_token = first_token;
+        t.status = status;
+        t.B = shape->batch;
+        t.Hkv = shape->num_kv_heads;
+        t.max_pages = shape->max_pages;
+        t.num_pages = shape->num_pages;
+        const int Hq = shape->num_kv_heads * kGroup;
+        const long long tiles = (long long)shape->batch * shape->max_pages * (kPage / kTcTile);
+        long long gx = 148 / Hq;
+        if (gx < 1) gx = 1;
+        if (gx > tiles) gx = tiles;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)gx, Hq, 1);
+        cfg.blockDim = dim3(kTcThreads);
+        cfg.dynamicSmemBytes = kTcSmemBytes;
+        cfg.stream = static_cast<cudaStream_t>(stream);
+        cudaLaunchAttribute attr1[1];
+        attr1[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr1[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
+        cfg.attrs = attr1;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, hash_prefill_tc_kernel, t) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    }
+    // fp32 weights: exact fp32 arithmetic on the CUDA cores
     HashPrefillParams p;
     p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
     p.hash_pages = hash_pages;
@@ -302,13 +340,8 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
     p.max_pages = shape->max_pages;
     p.num_pages = shape->num_pages;
     const dim3 grid(shape->num_kv_heads * kGroup, shape->max_pages, shape->batch);
-    cudaError_t e;
-    if (weights->dtype == HA_WEIGHTS_BF16)
-        e = launch(hash_prefill_simt_kernel<__nv_bfloat16>, grid, dim3(kHashDecodeThreads),
-                   static_cast<cudaStream_t>(stream), 1, p);
-    else
-        e = launch(hash_prefill_simt_kernel<float>, grid, dim3(kHashDecodeThreads),
-                   static_cast<cudaStream_t>(stream), 1, p);
+    const cudaError_t e = launch(hash_prefill_simt_kernel<float>, grid, dim3(kHashDecodeThreads),
+                                 static_cast<cudaStream_t>(stream), 1, p);
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
