@@ -55,6 +55,14 @@ def peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
 def workload_lens(name):
     w = WORKLOADS[name]
     if w["lens"] is not None:
@@ -303,6 +311,20 @@ def run_gpu_arm(args):
                 "frac": nbytes["total"] / per_step / 1e9 / peak, "frac_of_8tbs": nbytes["total"] / per_step / 8e12,
                 "stage_us": stage_us}
 
+    # ---- prefill key-hash build (tcgen05 GEMM chain) over the same caches ------------------------
+    n_pre = max(1, min(L, 8))
+    for l in range(min(L, 2)):
+        ctxs[l].hash_prefill()
+    t_pre = timed(lambda n: [ctxs[i % L].hash_prefill() for i in range(n)], n_pre) / n_pre
+    pre_flops = 2.0 * 36864 * HQ * sum(lens)  # 3 GEMMs of the 128-128-128-32 MLP per token and query head
+    tpeak, tpeak_src = tensor_peak()
+    prefill = {"kernel": "hash_prefill_tc_kernel", "tokens": sum(lens), "ms": t_pre * 1e3,
+               "tflops_algorithmic": pre_flops / t_pre / 1e12, "peak_tflops": tpeak, "peak_source": tpeak_src,
+               "frac": pre_flops / t_pre / 1e12 / tpeak,
+               "note": "executed MACs are 1.56x the algorithmic ones (hi/lo bf16 split of the hidden activations)"}
+    for ctx in ctxs:
+        ctx.check_status()
+
     # ---- end to end through the host-buffer entry point --------------------------------------
     bufs = [ha.HostStepBuffers(c) for c in ctxs]
     for l in range(L):
@@ -343,7 +365,7 @@ def run_gpu_arm(args):
                        "l2": f"inputs larger than L2: {L} layer instances x {nbytes['total'] / 1e6:.1f} MB touched per "
                              f"step, visited round-robin", "launch": "CUDA graph of one step per layer instance",
                        "partition": "each GPU decodes its own sequences (all 8 kv heads); no collective on the path"},
-            "roofline": roofline, "pipeline": pipeline, "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks,
+            "roofline": roofline, "pipeline": pipeline, "prefill_hash": prefill, "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks,
             "gpu_launches": 5 * args.steps,
         }
         print(json.dumps(line), flush=True)

@@ -5,10 +5,11 @@
 // is a chain of three GEMMs over a tile of 128 tokens. A CTA owns one head: the head's three
 // weight matrices (72 KB bf16) stay in shared memory in the K-major 128-byte-swizzled layout the
 // UMMA shared-memory descriptors describe, and the CTA walks over token tiles:
-//   1. the 128 x 128 key tile is copied into swizzled shared memory (it is contiguous in a page),
+//   1. the 128 x 128 key tile is copied into swizzled shared memory (it is contiguous in a page) by
+//      cp.async, one tile ahead of the arithmetic (two buffers),
 //   2. one thread issues tcgen05.mma (M = 128, N = 128, K = 16 per instruction, bf16 x bf16 -> fp32)
 //      into tensor memory and commits to an mbarrier,
-//   3. the 8 warps read the accumulator with tcgen05.ld (thread = token row, 64 columns each), add
+//   3. the 16 warps read the accumulator with tcgen05.ld (thread = token row, 32 columns each), add
 //      the bias, apply SiLU in fp32 and split the activation into a hi and a lo bf16 (hi + lo
 //      carries 16 mantissa bits), written back to swizzled shared memory as the next A operand,
 //   4. layer 2 runs two MMAs per k-step (hi and lo against the same weights), layer 3 likewise
@@ -26,15 +27,15 @@
 
 namespace ha {
 
-constexpr int kTcThreads = 256;
+constexpr int kTcThreads = 512;
 constexpr int kTcTile = 128;                          // tokens per tile = TMEM lanes
 constexpr uint32_t kTcBlockBytes = 128 * 128;         // one K-half of a 128-row operand: 128 rows x 128 B
 constexpr uint32_t kTcW2BlockBytes = 32 * 128;        // one K-half of W2 (32 rows)
 constexpr uint32_t kTcOffW0 = 0;
 constexpr uint32_t kTcOffW1 = kTcOffW0 + 2 * kTcBlockBytes;
 constexpr uint32_t kTcOffW2 = kTcOffW1 + 2 * kTcBlockBytes;
-constexpr uint32_t kTcOffX = kTcOffW2 + 2 * kTcW2BlockBytes;
-constexpr uint32_t kTcOffHi = kTcOffX + 2 * kTcBlockBytes;
+constexpr uint32_t kTcOffX = kTcOffW2 + 2 * kTcW2BlockBytes;           // two key-tile buffers (double buffering)
+constexpr uint32_t kTcOffHi = kTcOffX + 4 * kTcBlockBytes;
 constexpr uint32_t kTcOffLo = kTcOffHi + 2 * kTcBlockBytes;
 constexpr uint32_t kTcOffBias = kTcOffLo + 2 * kTcBlockBytes;          // 288 floats
 constexpr uint32_t kTcOffBar = kTcOffBias + 1280;                      // mbarrier (8 B) + tmem base (4 B)
@@ -134,35 +135,44 @@ __device__ __forceinline__ void tc_load_operand(unsigned char* dst, const __nv_b
     }
 }
 
-// bias + SiLU + hi/lo split of 64 accumulator columns (one K-half block of the next A operand).
+// bias + SiLU + hi/lo split of 32 accumulator columns (chunks 4*q4 .. 4*q4+3 of K-half block kb).
 __device__ __forceinline__ void tc_hidden_epilogue(uint32_t taddr, const float* bias, unsigned char* hi_blk,
-                                                   unsigned char* lo_blk, uint32_t row) {
+                                                   unsigned char* lo_blk, uint32_t row, uint32_t chunk0) {
+    float v[32];
+    tc_ld32(taddr, v);
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        float v[32];
-        tc_ld32(taddr + half * 32, v);
+    for (int c = 0; c < 4; ++c) {  // 4 chunks of 8 columns
+        uint32_t hi[4], lo[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {  // 4 chunks of 8 columns
-            uint32_t hi[4], lo[4];
+        for (int e = 0; e < 4; ++e) {
+            float a[2];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float a[2];
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const int col = c * 8 + e * 2 + j;
-                    const float x = v[col] + bias[half * 32 + col];
-                    a[j] = x / (1.0f + expf(-x));
-                }
-                const float h0 = __bfloat162float(__float2bfloat16_rn(a[0]));
-                const float h1 = __bfloat162float(__float2bfloat16_rn(a[1]));
-                hi[e] = tc_pack_bf16(h0, h1);
-                lo[e] = tc_pack_bf16(a[0] - h0, a[1] - h1);
+            for (int j = 0; j < 2; ++j) {
+                const int col = c * 8 + e * 2 + j;
+                const float x = v[col] + bias[col];
+                // SiLU with the hardware exp2 / reciprocal (relative error ~1e-6, well below the
+                // 2^-17 that the hi/lo split itself leaves)
+                a[j] = __fdividef(x, 1.0f + __expf(-x));
             }
-            const uint32_t off = tc_swizzled(row, half * 4 + c);
-            *reinterpret_cast<uint4*>(hi_blk + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<uint4*>(lo_blk + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            const float h0 = __bfloat162float(__float2bfloat16_rn(a[0]));
+            const float h1 = __bfloat162float(__float2bfloat16_rn(a[1]));
+            hi[e] = tc_pack_bf16(h0, h1);
+            lo[e] = tc_pack_bf16(a[0] - h0, a[1] - h1);
         }
+        const uint32_t off = tc_swizzled(row, chunk0 + c);
+        *reinterpret_cast<uint4*>(hi_blk + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(lo_blk + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
+}
+
+// Asynchronous copy (cp.async, 16 bytes per request) of a 128-token key tile into a swizzled buffer.
+__device__ __forceinline__ void tc_prefetch_tile(unsigned char* dst, const __nv_bfloat16* src, int tid) {
+    for (int i = tid; i < kTcTile * 16; i += kTcThreads) {
+        const int row = i >> 4, c16 = i & 15;
+        const uint32_t d = tc_smem_u32(dst + (c16 >> 3) * kTcBlockBytes + tc_swizzled(row, c16 & 7));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + (size_t)row * kHeadDim + c16 * 8) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
 __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const HashPrefillTcParams p) {
@@ -196,8 +206,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
     const uint32_t bar = tc_smem_u32(s_bar);
     const uint32_t sbase = tc_smem_u32(smem);
     const uint32_t idesc128 = tc_idesc(128), idesc32 = tc_idesc(32);
-    // this thread's accumulator slice: TMEM lanes 32 (warp % 4) .. +31, columns 64 (warp / 4) .. +63
-    const uint32_t row = (warp & 3) * 32 + lane, kb = warp >> 2;
+    // this thread's accumulator slice: TMEM lanes 32 (warp % 4) .. +31, columns 32 (warp / 4) .. +31
+    const uint32_t row = (warp & 3) * 32 + lane, cq = warp >> 2;  // cq: column quarter 0..3
+    const uint32_t kb = cq >> 1, chunk0 = (cq & 1) * 4;           // K-half block and first chunk of the next A operand
     const uint32_t t_lane = ((warp & 3) * 32u) << 16;
     uint32_t phase = 0;
 
@@ -224,39 +235,57 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
     bool aborted = false;
     pdl_wait();  // the weights above are constants; everything below may depend on the previous kernel
 
+    // Work items are (sequence, 128-token tile) pairs dealt round-robin over grid.x. next_item() skips
+    // the pairs with nothing to encode; all of its inputs are CTA-uniform.
+    struct Item { int item, S, first, t0; size_t slot0; };
     const int tiles_per_seq = p.max_pages * (kPage / kTcTile);
-    for (int item = blockIdx.x; item < p.B * tiles_per_seq; item += gridDim.x) {
-        const int b = item / tiles_per_seq, tile = item % tiles_per_seq;
-        const int S = p.seq_lens[b];
-        if (S < 0 || S > p.max_pages * kPage) {
-            if (tid == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
-            continue;
+    auto next_item = [&](int item) {
+        Item it;
+        for (; item < p.B * tiles_per_seq; item += gridDim.x) {
+            const int b = item / tiles_per_seq, tile = item % tiles_per_seq;
+            const int S = p.seq_lens[b];
+            if (S < 0 || S > p.max_pages * kPage) {
+                if (tid == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+                continue;
+            }
+            const int first = p.first_token != nullptr ? max(0, p.first_token[b]) : 0;
+            const int t0 = tile * kTcTile;
+            if (t0 >= S || t0 + kTcTile <= first) continue;
+            const int page = p.page_table[(size_t)b * p.max_pages + t0 / kPage];
+            if (page < 0 || page >= p.num_pages) {
+                if (tid == 0) report(p.status, HA_ERR_BAD_PAGE);
+                continue;
+            }
+            it.item = item; it.S = S; it.first = first; it.t0 = t0;
+            it.slot0 = ((size_t)page * p.Hkv + kvh) * kPage + t0 % kPage;
+            return it;
         }
-        const int first = p.first_token != nullptr ? max(0, p.first_token[b]) : 0;
-        const int t0 = tile * kTcTile;
-        if (t0 >= S || t0 + kTcTile <= first) continue;
-        const int page = p.page_table[(size_t)b * p.max_pages + t0 / kPage];
-        if (page < 0 || page >= p.num_pages) {
-            if (tid == 0) report(p.status, HA_ERR_BAD_PAGE);
-            continue;
-        }
-        const size_t slot0 = ((size_t)page * p.Hkv + kvh) * kPage + t0 % kPage;
+        it.item = -1; it.S = 0; it.first = 0; it.t0 = 0; it.slot0 = 0;
+        return it;
+    };
 
-        // ---- key tile -> swizzled shared memory (generic proxy), then visible to the tensor core
-        tc_load_operand(smem + kTcOffX, p.k_pages + slot0 * kHeadDim, kTcTile, kTcBlockBytes, tid);
+    Item cur = next_item(blockIdx.x);
+    if (cur.item >= 0) tc_prefetch_tile(smem + kTcOffX, p.k_pages + cur.slot0 * kHeadDim, tid);
+    for (uint32_t n = 0; cur.item >= 0; ++n) {
+        const uint32_t off_x = kTcOffX + (n & 1) * 2 * kTcBlockBytes;
+        // ---- this tile's keys have landed (cp.async); make them visible to the tensor core
+        asm volatile("cp.async.wait_all;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
 
-        // ---- layer 0: D1 = X W0^T
+        // ---- layer 0: D1 = X W0^T; meanwhile the next tile's keys start streaming in
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            gemm(kTcColD1, kTcOffX, kTcOffW0, kTcBlockBytes, idesc128, true);
+            gemm(kTcColD1, off_x, kTcOffW0, kTcBlockBytes, idesc128, true);
             tc_commit(bar);
         }
+        const Item nxt = next_item(cur.item + gridDim.x);
+        if (nxt.item >= 0)
+            tc_prefetch_tile(smem + kTcOffX + ((n + 1) & 1) * 2 * kTcBlockBytes, p.k_pages + nxt.slot0 * kHeadDim, tid);
         if (!wait_commit()) { aborted = true; break; }
-        tc_hidden_epilogue(tmem + t_lane + kTcColD1 + kb * 64, s_bias + kb * 64, smem + kTcOffHi + kb * kTcBlockBytes,
-                           smem + kTcOffLo + kb * kTcBlockBytes, row);
+        tc_hidden_epilogue(tmem + t_lane + kTcColD1 + cq * 32, s_bias + cq * 32, smem + kTcOffHi + kb * kTcBlockBytes,
+                           smem + kTcOffLo + kb * kTcBlockBytes, row, chunk0);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
@@ -269,8 +298,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
             tc_commit(bar);
         }
         if (!wait_commit()) { aborted = true; break; }
-        tc_hidden_epilogue(tmem + t_lane + kTcColD2 + kb * 64, s_bias + kHidden + kb * 64,
-                           smem + kTcOffHi + kb * kTcBlockBytes, smem + kTcOffLo + kb * kTcBlockBytes, row);
+        tc_hidden_epilogue(tmem + t_lane + kTcColD2 + cq * 32, s_bias + kHidden + cq * 32,
+                           smem + kTcOffHi + kb * kTcBlockBytes, smem + kTcOffLo + kb * kTcBlockBytes, row, chunk0);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
@@ -289,12 +318,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
             uint32_t code = 0;
 #pragma unroll
             for (int i = 0; i < 32; ++i) code |= (v[i] + s_bias[2 * kHidden + i] > 0.0f ? 1u : 0u) << i;
-            const int t = t0 + (int)row;
-            if (t < S && t >= first) p.hash_pages[(slot0 + row) * kGroup + g] = code;
+            const int t = cur.t0 + (int)row;
+            if (t < cur.S && t >= cur.first) p.hash_pages[(cur.slot0 + row) * kGroup + g] = code;
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();  // the accumulators and the key tile may be overwritten by the next tile
+        __syncthreads();  // the accumulators may be overwritten by the next tile
+        cur = nxt;
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
 
     // ---- release tensor memory (after a time-out: give in-flight MMAs one more bounded wait) -------
     __syncthreads();
