@@ -60,6 +60,13 @@ __device__ __forceinline__ float dot8(const uint4& raw, const float (&x)[8]) {
     return s;
 }
 
+// 2^x on the special-function unit (relative error 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Rows attended by (b, h) and how they are cut; the same arithmetic in both kernels.
 struct AttPlan {
     SeqRange r;
@@ -130,10 +137,67 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
     const __nv_bfloat16* vbase = p.v_pages + (size_t)kvh * kPage * kHeadDim + sl * 8;
     float m = -INFINITY, l = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     bool bad = false;
+
+    // gather + online softmax over the rows of one round (row ids resolved, invalid ones masked)
+    auto attend = [&](const unsigned (&row)[kAttRowsPerWorker], uint32_t valid) {
+        uint4 kraw[kAttRowsPerWorker], vraw[kAttRowsPerWorker];
+#pragma unroll
+        for (int i = 0; i < kAttRowsPerWorker; ++i) {  // K and V loads all issued before any use
+            const size_t off = ((size_t)(row[i] / kPage) * p.Hkv * kPage + row[i] % kPage) * kHeadDim;
+            kraw[i] = __ldg(reinterpret_cast<const uint4*>(kbase + off));
+            vraw[i] = __ldg(reinterpret_cast<const uint4*>(vbase + off));
+        }
+        float sc[kAttRowsPerWorker];  // scores in log2 units
+        float m_new = m;
+#pragma unroll
+        for (int i = 0; i < kAttRowsPerWorker; ++i) {
+            float s = dot8(kraw[i], qf);
+            s += __shfl_xor_sync(0xffffffffu, s, 8);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            sc[i] = ((valid >> i) & 1u) ? s : -INFINITY;
+            m_new = fmaxf(m_new, sc[i]);
+        }
+        // guards instead of branches: a worker may have seen no valid row yet (m_new == -inf)
+        const float rescale = m == -INFINITY ? 0.f : fast_exp2(m - m_new);
+        m = m_new;
+        l *= rescale;
+#pragma unroll
+        for (int d = 0; d < 8; ++d) acc[d] *= rescale;
+#pragma unroll
+        for (int i = 0; i < kAttRowsPerWorker; ++i) {
+            const float w = ((valid >> i) & 1u) ? fast_exp2(sc[i] - m) : 0.f;
+            l += w;
+            float v[8];
+            unpack8(vraw[i], v);
+#pragma unroll
+            for (int d = 0; d < 8; ++d) acc[d] = fmaf(w, v[d], acc[d]);
+        }
+    };
+
     for (int round = 0; round < p.rounds; ++round) {
         const int rbase = base + round * kAttRoundRows;
-        if (rbase - worker >= a.n_total) break;
-        // ---- one lookup per row: the heavy list entry, or the page of a sink / recent token ----
+        const int cta_first = rbase - worker;  // first position of the CTA in this round
+        if (cta_first >= a.n_total) break;
+        unsigned row[kAttRowsPerWorker];
+        if (kPhysical && cta_first >= lo && cta_first + kAttRoundRows <= lo + cnt) {
+            // ---- all 32 rows of the round are heavy rows: their physical ids come straight from the list
+            uint32_t valid = (1u << kAttRowsPerWorker) - 1u;
+#pragma unroll
+            for (int i = 0; i < kAttRowsPerWorker; ++i) row[i] = (unsigned)__ldcg(sel + (rbase + i * kAttWorkers - lo));
+#pragma unroll
+            for (int i = 0; i < kAttRowsPerWorker; ++i) {
+                if (row[i] >= pool_rows) {
+                    bad = true;
+                    valid &= ~(1u << i);
+                    row[i] = 0;
+                }
+            }
+            attend(row, valid);
+            continue;
+        }
+        // ---- mixed round: one lookup per row, the heavy list entry or the page of a sink / recent token
         int look[kAttRowsPerWorker], tokv[kAttRowsPerWorker];
         uint32_t valid = 0, heavy = 0;
 #pragma unroll
@@ -148,7 +212,6 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
             if (is_heavy) look[i] = __ldcg(sel + (pos - lo));
             else look[i] = round == 0 ? pre_page[i] : __ldg(pt + tok / kPage);
         }
-        unsigned row[kAttRowsPerWorker];
 #pragma unroll
         for (int i = 0; i < kAttRowsPerWorker; ++i) {
             const bool is_heavy = (heavy >> i) & 1u;
@@ -169,42 +232,7 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
             }
             row[i] = rr;
         }
-        // ---- gather: K and V loads all issued before any use ---------------------------------
-        uint4 kraw[kAttRowsPerWorker], vraw[kAttRowsPerWorker];
-#pragma unroll
-        for (int i = 0; i < kAttRowsPerWorker; ++i) {
-            const size_t off = ((size_t)(row[i] / kPage) * p.Hkv * kPage + row[i] % kPage) * kHeadDim;
-            kraw[i] = __ldg(reinterpret_cast<const uint4*>(kbase + off));
-            vraw[i] = __ldg(reinterpret_cast<const uint4*>(vbase + off));
-        }
-        // ---- scores (in log2 units), online softmax, weighted V sum ---------------------------
-        float sc[kAttRowsPerWorker];
-        float m_new = m;
-#pragma unroll
-        for (int i = 0; i < kAttRowsPerWorker; ++i) {
-            float s = dot8(kraw[i], qf);
-            s += __shfl_xor_sync(0xffffffffu, s, 8);
-            s += __shfl_xor_sync(0xffffffffu, s, 4);
-            s += __shfl_xor_sync(0xffffffffu, s, 2);
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            sc[i] = ((valid >> i) & 1u) ? s : -INFINITY;
-            m_new = fmaxf(m_new, sc[i]);
-        }
-        // guards instead of branches: a worker may have seen no valid row yet (m_new == -inf)
-        const float rescale = m == -INFINITY ? 0.f : exp2f(m - m_new);
-        m = m_new;
-        l *= rescale;
-#pragma unroll
-        for (int d = 0; d < 8; ++d) acc[d] *= rescale;
-#pragma unroll
-        for (int i = 0; i < kAttRowsPerWorker; ++i) {
-            const float w = ((valid >> i) & 1u) ? exp2f(sc[i] - m) : 0.f;
-            l += w;
-            float v[8];
-            unpack8(vraw[i], v);
-#pragma unroll
-            for (int d = 0; d < 8; ++d) acc[d] = fmaf(w, v[d], acc[d]);
-        }
+        attend(row, valid);
     }
     if (bad) report(p.status, HA_ERR_BAD_PAGE);
 
