@@ -73,6 +73,7 @@ struct Workspace {
     uint32_t* hist;     // [B][Hkv][4*33][nchunks] per-chunk score histograms
     int32_t* sel_rows;  // [B][Hq][sel_stride] physical rows of the selected tokens
     float* partials;    // [B][Hq][nsplits][130] attention partials
+    int32_t* plan;      // [B][Hkv][8 + 8 * nchunks] thresholds, tie quotas and per-chunk output bases
     size_t bytes;
 };
 
@@ -88,6 +89,8 @@ Workspace carve(const ha_shape_t* s, const ha_budget_t* b, void* base) {
     off += align_up((size_t)s->batch * Hq * s->sel_stride * sizeof(int32_t));
     w.partials = reinterpret_cast<float*>(p + off);
     off += align_up((size_t)s->batch * Hq * att_split(s, b).nsplits * kPartStride * sizeof(float));
+    w.plan = reinterpret_cast<int32_t*>(p + off);
+    off += align_up((size_t)s->batch * s->num_kv_heads * (8 + 8 * (size_t)num_chunks_for(s->max_pages)) * sizeof(int32_t));
     w.bytes = off;
     return w;
 }
@@ -116,6 +119,28 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t
     }
     cfg.attrs = attr;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+// The two-pass selection: chunk histograms, the plan (thresholds and output bases) derived from
+// them once per (sequence, kv-head), then the compaction.
+cudaError_t launch_two_pass_select(const ha_shape_t* shape, const SelectParams& p, cudaStream_t s) {
+    const dim3 grid(p.nchunks, shape->num_kv_heads, shape->batch);
+    const dim3 pgrid(shape->num_kv_heads, shape->batch);
+    const int chunk_pages = chunk_pages_for(shape->max_pages);
+    cudaError_t e1, e2, e3;
+    switch (chunk_pages) {
+        case 4: e1 = launch(score_hist_kernel<1>, grid, dim3(kSelThreads), s, 1, p); break;
+        case 8: e1 = launch(score_hist_kernel<2>, grid, dim3(kSelThreads), s, 1, p); break;
+        default: e1 = launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p); break;
+    }
+    e2 = launch(select_plan_kernel, pgrid, dim3(kGroup * 32), s, 1, p, chunk_pages * kPage);
+    switch (chunk_pages) {
+        case 4: e3 = launch(select_kernel<1>, grid, dim3(kSelThreads), s, 1, p); break;
+        case 8: e3 = launch(select_kernel<2>, grid, dim3(kSelThreads), s, 1, p); break;
+        default: e3 = launch(select_kernel<4>, grid, dim3(kSelThreads), s, 1, p); break;
+    }
+    if (e1 != cudaSuccess) return e1;
+    return e2 != cudaSuccess ? e2 : e3;
 }
 
 }  // namespace
@@ -367,6 +392,7 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
     p.page_table = page_table;
     p.seq_lens = seq_lens;
     p.hist = w.hist;
+    p.plan = w.plan;
     p.sel_idx = sel_idx;
     p.sel_rows = w.sel_rows;
     p.sel_cnt = sel_cnt;
@@ -395,23 +421,7 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
             : launch(score_select_cluster_kernel<2>, cgrid, dim3(kClThreads), s, kClCtas, p);
         return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
     }
-    const dim3 grid(p.nchunks, shape->num_kv_heads, shape->batch);
-    cudaError_t e1, e2;
-    switch (chunk_pages_for(shape->max_pages)) {
-        case 4:
-            e1 = launch(score_hist_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
-            e2 = launch(select_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
-            break;
-        case 8:
-            e1 = launch(score_hist_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
-            e2 = launch(select_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
-            break;
-        default:
-            e1 = launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
-            e2 = launch(select_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
-            break;
-    }
-    return e1 == cudaSuccess && e2 == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    return launch_two_pass_select(shape, p, s) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
 int ha_sparse_decode(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -505,6 +515,7 @@ void* g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_sc
 struct StaticScratch {
     uint32_t* hist;     // [B][Hkv][4*33][nchunks]
     int32_t* sel_rows;  // [B][Hq][sel_stride]
+    int32_t* plan;      // [B][Hkv][8 + 8 * nchunks]
     size_t bytes;
 };
 
@@ -516,7 +527,9 @@ StaticScratch carve_static(const ha_shape_t* s, void* base) {
     w.hist = reinterpret_cast<uint32_t*>(p);
     const size_t off = align_up(n_hist * sizeof(uint32_t));
     w.sel_rows = reinterpret_cast<int32_t*>(p + off);
-    w.bytes = off + align_up(n_rows * sizeof(int32_t));
+    const size_t off2 = off + align_up(n_rows * sizeof(int32_t));
+    w.plan = reinterpret_cast<int32_t*>(p + off2);
+    w.bytes = off2 + align_up((size_t)s->batch * s->num_kv_heads * (8 + 8 * (size_t)num_chunks_for(s->max_pages)) * sizeof(int32_t));
     return w;
 }
 
@@ -560,7 +573,7 @@ int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
     if (rc != HA_OK) return rc;
     const StaticScratch w = carve_static(shape, base);
 
-    // Every word of hist / sel_rows that a kernel reads was written earlier in the same call,
+    // Every word of hist / plan / sel_rows that a kernel reads was written earlier in the same call,
     // so nothing left over from the previous call needs clearing.
     SelectParams p;
     p.q_codes = q_codes;
@@ -568,6 +581,7 @@ int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
     p.page_table = page_table;
     p.seq_lens = seq_lens;
     p.hist = w.hist;
+    p.plan = w.plan;
     p.sel_idx = sel_idx;
     p.sel_rows = w.sel_rows;
     p.sel_cnt = sel_cnt;
@@ -582,24 +596,7 @@ int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
     p.init_budget = budget->init_budget;
     p.recent_budget = budget->recent_budget;
     p.heavy_budget = budget->heavy_budget;
-    const dim3 grid(p.nchunks, shape->num_kv_heads, shape->batch);
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    cudaError_t e1, e2;
-    switch (chunk_pages_for(shape->max_pages)) {
-        case 4:
-            e1 = launch(score_hist_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
-            e2 = launch(select_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
-            break;
-        case 8:
-            e1 = launch(score_hist_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
-            e2 = launch(select_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
-            break;
-        default:
-            e1 = launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
-            e2 = launch(select_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
-            break;
-    }
-    return e1 == cudaSuccess && e2 == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    return launch_two_pass_select(shape, p, static_cast<cudaStream_t>(stream)) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
 }  // extern "C"

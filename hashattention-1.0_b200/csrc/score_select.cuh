@@ -6,11 +6,15 @@
 // 4 x 33 histogram of the scores of the candidate tokens of its chunk, stored bin-major
 // ([bin][chunk]) so that pass B reads the counts of one bin over all chunks as one line.
 //
-// Pass B (select_kernel) re-reads its chunk (L2-resident by then), derives from the chunk
-// histograms the global threshold T of each head, how many tokens tied at T still fit and
-// how many selected tokens precede the chunk, and writes the selected token indices with a
+// A small kernel in between (select_plan_kernel, one CTA per (sequence, kv-head)) derives from the
+// chunk histograms the global threshold T of each head, how many tokens tied at T still fit and how
+// many selected / tied tokens precede each chunk.
+//
+// Pass B (select_kernel) re-reads its chunk (L2-resident by then), classifies its tokens against T
+// and writes the selected token indices with a
 // packed warp-scan compaction - no sort, no atomics, nothing to reset. The list of a head is
-// ordered by 128-token block; inside a block by lane, i.e. not strictly ascending.
+// ordered by the token range of the emitting warp (128 ROUNDS tokens); inside it by lane, i.e.
+// not strictly ascending.
 //
 // Together they replace the +-1 dot product of USA.forward and the sort/scatter of
 // compute_mask_multi in 'simple' mode (hashattention/hashattention_llama.py:171-187, 423-438).
@@ -47,6 +51,7 @@ struct SelectParams {
     int32_t* sel_idx;          // [B][Hq][sel_stride] token indices
     int32_t* sel_rows;         // workspace: [B][Hq][sel_stride] page * 256 + slot of the same tokens
     int32_t* sel_cnt;          // [B][Hq]
+    int32_t* plan;             // workspace: [B][Hkv][8 + 8 * nchunks]: T[4], need[4], then per chunk base[4], eqb[4]
     uint8_t* scores_dbg;       // [B][Hq][max_pages*256] or null
     int32_t* status;
     int B, Hkv, max_pages, num_pages, sel_stride, nchunks;
@@ -199,6 +204,99 @@ __device__ __forceinline__ uint32_t bytes_eq(uint32_t a, uint32_t t4) {
 // bit 7 of byte g -> bit g
 __device__ __forceinline__ uint32_t flags_to_nibble(uint32_t f) { return (((f >> 7) * 0x01020408u) >> 24) & 0xFu; }
 
+// Between the two passes: one CTA per (sequence, kv-head), warp g = query head g of the group.
+// From the per-chunk histograms it derives, once instead of in every CTA of pass B, the global
+// threshold T and the tie quota of the head, and for every chunk the number of selected tokens
+// and of tied tokens that precede it. Lane = chunk (32 chunks per pass); a lane holds the 33
+// counts of its chunk in registers.
+__global__ void __launch_bounds__(kGroup * 32) select_plan_kernel(const SelectParams p, int chunk_tokens) {
+    const int kvh = blockIdx.x, b = blockIdx.y;
+    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int Hq = p.Hkv * kGroup;
+    const int S = p.seq_lens[b];
+    const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
+    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
+    const int nchunks_b = (r.S + chunk_tokens - 1) / chunk_tokens;
+
+    pdl_wait();
+    pdl_launch_dependents();
+    if (!s_ok) return;
+
+    int hbe = r.hb;
+    if (hbe > p.sel_stride) {
+        if (lane == 0 && g == 0) report(p.status, HA_ERR_SEL_OVERFLOW);
+        hbe = p.sel_stride;
+    }
+    const uint32_t* hbase = p.hist + (((size_t)b * p.Hkv + kvh) * (kGroup * kBins) + g * kBins) * p.nchunks;
+    int32_t* plan = p.plan + ((size_t)b * p.Hkv + kvh) * (8 + 8 * p.nchunks);
+
+    // totals per bin over all chunks -> T and the tie quota (lane l then holds bin 32 - l; bin 0 apart)
+    int tot_hi = 0, tot0 = 0;  // tot_hi: total of bin 32 - lane
+    for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
+        const int cc = cc0 + lane;
+#pragma unroll
+        for (int s = 0; s < kBins; ++s) {
+            const int v = cc < nchunks_b ? (int)__ldcg(hbase + (size_t)s * p.nchunks + cc) : 0;
+            const int t = __reduce_add_sync(0xffffffffu, v);
+            if (s == 0) tot0 += t;
+            else if (lane == 32 - s) tot_hi += t;
+        }
+    }
+    (void)tot0;
+    int cum = tot_hi;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, cum, d);
+        if (lane >= d) cum += u;
+    }
+    const uint32_t reached = __ballot_sync(0xffffffffu, cum >= hbe);
+    int T, need;
+    if (hbe <= 0) {
+        T = kBins; need = 0;  // T = 33: nothing qualifies
+    } else if (reached != 0) {
+        const int l = __ffs(reached) - 1;  // first lane whose cumulative count reaches the budget
+        T = 32 - l;
+        need = hbe - __shfl_sync(0xffffffffu, cum - tot_hi, l);
+    } else {  // bins 32..1 together hold fewer than the budget: the threshold is 0
+        T = 0;
+        need = hbe - __shfl_sync(0xffffffffu, cum, 31);
+    }
+    if (lane == 0) {
+        plan[g] = T;
+        plan[4 + g] = need;
+        p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = hbe;
+    }
+
+    // per chunk: tokens above T and tokens at T, then exclusive prefixes over the chunks
+    int gt_carry = 0, eq_carry = 0;
+    for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
+        const int cc = cc0 + lane;
+        int gt = 0, eq = 0;
+#pragma unroll
+        for (int s = 0; s < kBins; ++s) {
+            const int v = cc < nchunks_b ? (int)__ldcg(hbase + (size_t)s * p.nchunks + cc) : 0;  // L1/L2 hit: read above
+            gt += s > T ? v : 0;
+            eq += s == T ? v : 0;
+        }
+        int pg = gt, pe = eq;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u0 = __shfl_up_sync(0xffffffffu, pg, d), u1 = __shfl_up_sync(0xffffffffu, pe, d);
+            if (lane >= d) {
+                pg += u0;
+                pe += u1;
+            }
+        }
+        const int gt_before = gt_carry + pg - gt, eq_before = eq_carry + pe - eq;
+        if (cc < nchunks_b) {
+            plan[8 + 8 * cc + g] = gt_before + min(eq_before, need);
+            plan[8 + 8 * cc + 4 + g] = eq_before;
+        }
+        gt_carry += __shfl_sync(0xffffffffu, pg, 31);
+        eq_carry += __shfl_sync(0xffffffffu, pe, 31);
+    }
+}
+
 template <int ROUNDS>
 __global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectParams p) {
     HA_TL(kTlSelect, kTlEntry);
@@ -206,24 +304,22 @@ __global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectPara
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
     constexpr int chunk_tokens = ROUNDS * kRoundTokens;
-    constexpr int kBinsPerWarp = (kGroup * kBins + kSelWarps - 1) / kSelWarps;  // 17
-    constexpr int kSlots = ROUNDS * kSelWarps;  // (round, warp) pairs in token order, <= 32
-
-    __shared__ int s_tot[kGroup * kBins + kSelWarps];  // padded: warp 7 owns bins up to 135
-    __shared__ int s_bef[kGroup * kBins + kSelWarps];
     __shared__ int s_T[kGroup], s_need[kGroup], s_base[kGroup], s_eqb[kGroup];
-    __shared__ uint32_t s_sgt[kSlots], s_seq[kSlots];  // per slot: counts of the 4 heads packed in bytes
+    __shared__ uint32_t s_wg[kSelWarps][2], s_we[kSelWarps][2];  // per warp: counts of heads (0,1) / (2,3), 16 bits each
 
     const int S = p.seq_lens[b];
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
     const int chunk_start = c * chunk_tokens;
     const bool active = s_ok && chunk_start < S;
     const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
-    const int nchunks_b = (r.S + chunk_tokens - 1) / chunk_tokens;
-    // --- before the dependency wait: this chunk's scores. The kernel in front of this one
-    //     (score_hist) writes only histograms; the query codes and every hash word, the newest
+    // --- before the dependency wait: this chunk's scores. The two kernels in front of this one
+    //     (score_hist, select_plan) write only histograms and the plan; the query codes and every hash word, the newest
     //     token's included, come from the encoder kernel, which had completed before any CTA of
     //     this kernel could start. Scores are kept packed in registers (byte g = head g).
+    // In this kernel warp w owns the contiguous tokens [chunk_start + 128 ROUNDS w, + 128 ROUNDS), so
+    // that everything it selects lands in one contiguous piece of the output and one scan serves
+    // all its rounds. (The histograms of pass A are per chunk and do not care about the order inside.)
+    auto first_token = [&](int rd) { return chunk_start + warp * (ROUNDS * kLaneTokens * 32) + rd * (kLaneTokens * 32); };
     uint32_t sc[ROUNDS][kLaneTokens];
     int page[ROUNDS];
     uint32_t cand = 0;  // bit rd * 4 + it
@@ -232,12 +328,11 @@ __global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectPara
         RoundWords rw;
 #pragma unroll
         for (int rd = 0; rd < ROUNDS; ++rd) {
-            const int t0 = RoundWords::first_token(chunk_start, rd, warp);
-            rw.load(p, b, kvh, rd > 0 ? min(t0, S - 1) : t0, lane, r);  // beyond S: clamped, nothing valid
+            const int t0 = first_token(rd);
+            rw.load(p, b, kvh, t0, lane, r);  // beyond S every access is clamped and nothing is valid
             rw.refresh_newest(p, kvh, t0, lane, r);
             page[rd] = rw.page;
-            const uint32_t cmask = (rd > 0 && t0 >= S) ? 0u : rw.cand;
-            cand |= cmask << (rd * kLaneTokens);
+            cand |= rw.cand << (rd * kLaneTokens);
 #pragma unroll
             for (int it = 0; it < kLaneTokens; ++it)
                 sc[rd][it] = __popc(qn.x ^ rw.w[it].x) | (__popc(qn.y ^ rw.w[it].y) << 8) |
@@ -250,199 +345,150 @@ __global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectPara
     pdl_launch_dependents();
     if (!active) return;
 
-    // --- histogram lines of this warp's bins: warp w reduces bins [17w, 17w+17), lane = chunk;
-    //     the 17 loads of a pass are independent and issued together
-    const uint32_t* hbase = p.hist + ((size_t)b * p.Hkv + kvh) * (kGroup * kBins) * p.nchunks;
-    for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
-        const int cc = cc0 + lane;
-        const int ccl = min(cc, nchunks_b - 1);
-        int v[kBinsPerWarp];
-#pragma unroll
-        for (int k = 0; k < kBinsPerWarp; ++k) {
-            const int bin = min(warp * kBinsPerWarp + k, kGroup * kBins - 1);
-            v[k] = (int)__ldcg(hbase + (size_t)bin * p.nchunks + ccl);
-        }
-#pragma unroll
-        for (int k = 0; k < kBinsPerWarp; ++k) {
-            const int t = __reduce_add_sync(0xffffffffu, cc < nchunks_b ? v[k] : 0);
-            const int f = __reduce_add_sync(0xffffffffu, cc < c ? v[k] : 0);
-            if (lane == 0) {  // only this warp touches these entries: no barrier needed between passes
-                s_tot[warp * kBinsPerWarp + k] = cc0 == 0 ? t : s_tot[warp * kBinsPerWarp + k] + t;
-                s_bef[warp * kBinsPerWarp + k] = cc0 == 0 ? f : s_bef[warp * kBinsPerWarp + k] + f;
-            }
-        }
+    // --- the plan of this (sequence, kv-head), written by select_plan_kernel: thresholds, tie quotas,
+    //     and for this chunk where its output starts and how many tied tokens precede it
+    if (tid < 16) {
+        const int32_t* plan = p.plan + ((size_t)b * p.Hkv + kvh) * (8 + 8 * p.nchunks);
+        const int v = __ldcg(plan + (tid < 8 ? tid : 8 + 8 * c + (tid - 8)));
+        if (tid < 4) s_T[tid] = v;
+        else if (tid < 8) s_need[tid - 4] = v;
+        else if (tid < 12) s_base[tid - 8] = v;
+        else s_eqb[tid - 12] = v;
     }
     __syncthreads();
+    HA_TL(kTlSelect, kTlMarkB);
 
-    // --- threshold, tie quota and output base per head: warp g scans the 33 bins downwards ---
-    if (warp < kGroup) {
-        const int g = warp;
-        int hbe = r.hb;
-        if (hbe > p.sel_stride) {
-            if (lane == 0) report(p.status, HA_ERR_SEL_OVERFLOW);
-            hbe = p.sel_stride;
-        }
-        // lane l holds bin 32 - l (bins 32..1); bin 0 is the remainder
-        const int n = s_tot[g * kBins + 32 - lane], nb = s_bef[g * kBins + 32 - lane];
-        int cum = n, cumb = nb;  // inclusive scans over lanes
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int u = __shfl_up_sync(0xffffffffu, cum, d);
-            const int ub = __shfl_up_sync(0xffffffffu, cumb, d);
-            if (lane >= d) {
-                cum += u;
-                cumb += ub;
-            }
-        }
-        const uint32_t reached = __ballot_sync(0xffffffffu, cum >= hbe);
-        int T, need, gt_before, eq_before;
-        if (hbe <= 0) {
-            T = kBins; need = 0; gt_before = 0; eq_before = 0;  // T = 33: nothing qualifies
-        } else if (reached != 0) {
-            const int l = __ffs(reached) - 1;  // first lane whose cumulative count reaches the budget
-            T = 32 - l;
-            const int above = __shfl_sync(0xffffffffu, cum - n, l);
-            need = hbe - above;
-            gt_before = __shfl_sync(0xffffffffu, cumb - nb, l);
-            eq_before = __shfl_sync(0xffffffffu, nb, l);
-        } else {  // bins 32..1 together hold fewer than the budget: the threshold is 0
-            T = 0;
-            need = hbe - __shfl_sync(0xffffffffu, cum, 31);
-            gt_before = __shfl_sync(0xffffffffu, cumb, 31);
-            eq_before = s_bef[g * kBins];
-        }
-        if (lane == 0) {
-            s_T[g] = T;
-            s_need[g] = need;
-            s_eqb[g] = eq_before;
-            s_base[g] = gt_before + min(eq_before, need);
-            if (c == 0) p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = hbe;
-        }
-    }
-    __syncthreads();
-
-    // --- classify: per token and head, (score > T) and (score == T) as byte flags (bit 7 of byte g);
-    //     the flags of non-candidates are masked out -----------------------------------------------
+    // --- classify once: per token and head (score > T) and (score == T), kept as bit sets of this
+    //     lane: bit ((rd & 1) * 4 + it) * 4 + g of word rd / 2. Everything after this works on the
+    //     bit sets (counts are popcounts under a per-head mask), not on the tokens again.
+    constexpr int kWords = (ROUNDS + 1) / 2;
     const uint32_t t4 = (uint32_t)s_T[0] | ((uint32_t)s_T[1] << 8) | ((uint32_t)s_T[2] << 16) | ((uint32_t)s_T[3] << 24);
     const uint32_t gt_add = 0x7F7F7F7Fu - t4;
-    // flags of token (rd, it), zero for non-candidates
-    auto flags_gt = [&](int rd, int it) {
-        const uint32_t cm = 0u - ((cand >> (rd * kLaneTokens + it)) & 1u);
-        return bytes_gt(sc[rd][it], gt_add) & cm;
-    };
-    auto flags_eq = [&](int rd, int it) {
-        const uint32_t cm = 0u - ((cand >> (rd * kLaneTokens + it)) & 1u);
-        return bytes_eq(sc[rd][it], t4) & cm;
-    };
+    uint32_t gtb[kWords], eqb[kWords];
 #pragma unroll
-    for (int rd = 0; rd < ROUNDS; ++rd) {
-        uint32_t cg = 0, ce = 0;  // this lane's counts, one byte per head (<= 4 each)
+    for (int i = 0; i < kWords; ++i) gtb[i] = eqb[i] = 0;
+    const bool all_cand = __all_sync(0xffffffffu, cand == (ROUNDS * kLaneTokens == 32 ? 0xffffffffu : (1u << (ROUNDS * kLaneTokens)) - 1u));
+#pragma unroll
+    for (int rd = 0; rd < ROUNDS; ++rd)
 #pragma unroll
         for (int it = 0; it < kLaneTokens; ++it) {
-            cg += flags_gt(rd, it) >> 7;
-            ce += flags_eq(rd, it) >> 7;
+            uint32_t fg = bytes_gt(sc[rd][it], gt_add), fe = bytes_eq(sc[rd][it], t4);
+            if (!all_cand) {  // warp-uniform: only warps that touch the sink / recent / tail region
+                const uint32_t cm = 0u - ((cand >> (rd * kLaneTokens + it)) & 1u);
+                fg &= cm;
+                fe &= cm;
+            }
+            const int sh = ((rd & 1) * kLaneTokens + it) * 4;
+            gtb[rd >> 1] |= flags_to_nibble(fg) << sh;
+            eqb[rd >> 1] |= flags_to_nibble(fe) << sh;
         }
-        cg = __reduce_add_sync(0xffffffffu, cg);  // <= 128 per byte: no carry between heads
-        ce = __reduce_add_sync(0xffffffffu, ce);
+    // per-head popcounts of a bit set, as two words of 16-bit fields: heads (0,1) and (2,3)
+    auto head_counts = [&](const uint32_t (&w)[kWords], uint32_t& c01, uint32_t& c23) {
+        uint32_t c[kGroup] = {0, 0, 0, 0};
+#pragma unroll
+        for (int i = 0; i < kWords; ++i)
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) c[g] += __popc(w[i] & (0x11111111u << g));
+        c01 = c[0] | (c[1] << 16);
+        c23 = c[2] | (c[3] << 16);
+    };
+    {
+        uint32_t g01, g23, e01, e23;
+        head_counts(gtb, g01, g23);
+        head_counts(eqb, e01, e23);
+        g01 = __reduce_add_sync(0xffffffffu, g01);  // a warp holds up to 512 tokens: 16-bit fields do not overflow
+        g23 = __reduce_add_sync(0xffffffffu, g23);
+        e01 = __reduce_add_sync(0xffffffffu, e01);
+        e23 = __reduce_add_sync(0xffffffffu, e23);
         if (lane == 0) {
-            s_sgt[rd * kSelWarps + warp] = cg;
-            s_seq[rd * kSelWarps + warp] = ce;
+            s_wg[warp][0] = g01; s_wg[warp][1] = g23;
+            s_we[warp][0] = e01; s_we[warp][1] = e23;
         }
     }
     __syncthreads();
+    HA_TL(kTlSelect, kTlMarkC);
 
-    // --- exclusive prefix over the slots (token order), heads in two 16-bit pairs -------------------
-    uint32_t pg01, pg23, pe01, pe23;  // lane = slot
-    {
-        const uint32_t g4 = lane < kSlots ? s_sgt[lane] : 0u, e4 = lane < kSlots ? s_seq[lane] : 0u;
-        const uint32_t g01 = (g4 & 0xffu) | ((g4 & 0xff00u) << 8), g23 = ((g4 >> 16) & 0xffu) | ((g4 >> 24) << 16);
-        const uint32_t e01 = (e4 & 0xffu) | ((e4 & 0xff00u) << 8), e23 = ((e4 >> 16) & 0xffu) | ((e4 >> 24) << 16);
-        pg01 = g01; pg23 = g23; pe01 = e01; pe23 = e23;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const uint32_t a0 = __shfl_up_sync(0xffffffffu, pg01, d), a1 = __shfl_up_sync(0xffffffffu, pg23, d);
-            const uint32_t a2 = __shfl_up_sync(0xffffffffu, pe01, d), a3 = __shfl_up_sync(0xffffffffu, pe23, d);
-            if (lane >= d) {
-                pg01 += a0; pg23 += a1; pe01 += a2; pe23 += a3;
-            }
-        }
-        pg01 -= g01; pg23 -= g23; pe01 -= e01; pe23 -= e23;
-    }
-    // lane 4 * rd + g works out, for slot (rd, this warp) and head g, where the slot's output starts
-    // and how its ties are treated: 0 = none taken, 1 = all taken, 2 = the tie quota ends inside
+    // --- where this warp's output starts and how it treats ties, per head (lane g works head g out):
+    //     0 = takes no tied token, 1 = takes all, 2 = the tie quota ends inside this warp's tokens
     int my_base = 0, my_eqb = 0, my_mode = 0;
     {
-        const int rd = (lane >> 2) % ROUNDS, g = lane & 3, slot = rd * kSelWarps + warp;
-        // (shuffle both pairs, then pick: the operand of a shuffle is evaluated by the source lane)
-        const uint32_t sg01 = __shfl_sync(0xffffffffu, pg01, slot), sg23 = __shfl_sync(0xffffffffu, pg23, slot);
-        const uint32_t se01 = __shfl_sync(0xffffffffu, pe01, slot), se23 = __shfl_sync(0xffffffffu, pe23, slot);
-        const uint32_t sg = g < 2 ? sg01 : sg23, se = g < 2 ? se01 : se23;
-        const int gt_b = (int)((sg >> ((g & 1) * 16)) & 0xffffu);
+        const int g = lane & 3;
+        int gt_b = 0, eq_b = 0;
+        for (int w = 0; w < warp; ++w) {
+            gt_b += (int)((s_wg[w][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
+            eq_b += (int)((s_we[w][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
+        }
+        const int eq_in = (int)((s_we[warp][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
         const int need = s_need[g];
-        my_eqb = s_eqb[g] + (int)((se >> ((g & 1) * 16)) & 0xffffu);
-        const int eq_in = (int)((s_seq[slot] >> (8 * g)) & 0xffu);
+        my_eqb = s_eqb[g] + eq_b;
         my_base = s_base[g] + gt_b + (min(my_eqb, need) - min(s_eqb[g], need));
         my_mode = my_eqb + eq_in <= need ? 1 : (my_eqb < need ? 2 : 0);
     }
+    if ((s_wg[warp][0] | s_wg[warp][1] | s_we[warp][0] | s_we[warp][1]) == 0) return;  // nothing of any head here
 
-    // --- emission: positions from one packed warp scan per slot; order inside a slot is lane-major.
-    const uint32_t lt_mask = (1u << lane) - 1u;
+    int base_pos[kGroup];
+    uint32_t full_bits = 0, straddle = 0;  // full_bits: the heads whose tied tokens are all taken, as a per-nibble mask
 #pragma unroll
-    for (int rd = 0; rd < ROUNDS; ++rd) {
-        const int slot = rd * kSelWarps + warp;
-        if ((s_sgt[slot] | s_seq[slot]) == 0) continue;  // nothing of any head in this warp's 128 tokens
-        int base_pos[kGroup];
-        uint32_t full4 = 0, straddle = 0;
+    for (int g = 0; g < kGroup; ++g) {
+        base_pos[g] = __shfl_sync(0xffffffffu, my_base, g);
+        const int mode = __shfl_sync(0xffffffffu, my_mode, g);
+        full_bits |= mode == 1 ? (0x11111111u << g) : 0u;
+        straddle |= (mode == 2 ? 1u : 0u) << g;
+    }
+    uint32_t bits[kWords];  // selected (token, head) pairs of this lane
+#pragma unroll
+    for (int i = 0; i < kWords; ++i) bits[i] = gtb[i] | (eqb[i] & full_bits);
+    if (straddle != 0) {  // warp-uniform, at most once per (sequence, head): rank ties by token index
+        const uint32_t lt_mask = (1u << lane) - 1u;
 #pragma unroll
         for (int g = 0; g < kGroup; ++g) {
-            base_pos[g] = __shfl_sync(0xffffffffu, my_base, rd * 4 + g);
-            const int mode = __shfl_sync(0xffffffffu, my_mode, rd * 4 + g);
-            full4 |= (mode == 1 ? 0x80u : 0u) << (8 * g);
-            straddle |= (mode == 2 ? 1u : 0u) << g;
-        }
-        uint32_t selm[kLaneTokens];
+            if (!((straddle >> g) & 1u)) continue;
+            int eq_run = __shfl_sync(0xffffffffu, my_eqb, g);
 #pragma unroll
-        for (int it = 0; it < kLaneTokens; ++it) selm[it] = flags_gt(rd, it) | (flags_eq(rd, it) & full4);
-        if (straddle != 0) {  // warp-uniform, at most once per (sequence, head): rank ties by token index
-#pragma unroll
-            for (int g = 0; g < kGroup; ++g) {
-                if (!((straddle >> g) & 1u)) continue;
-                int eq_run = __shfl_sync(0xffffffffu, my_eqb, rd * 4 + g);
+            for (int rd = 0; rd < ROUNDS; ++rd)
 #pragma unroll
                 for (int it = 0; it < kLaneTokens; ++it) {
-                    const bool eq = (flags_eq(rd, it) >> (8 * g + 7)) & 1u;
+                    const int bit = ((rd & 1) * kLaneTokens + it) * 4 + g;
+                    const bool eq = (eqb[rd >> 1] >> bit) & 1u;
                     const uint32_t m_eq = __ballot_sync(0xffffffffu, eq);
-                    if (eq && eq_run + __popc(m_eq & lt_mask) < s_need[g]) selm[it] |= 0x80u << (8 * g);
+                    if (eq && eq_run + __popc(m_eq & lt_mask) < s_need[g]) bits[rd >> 1] |= 1u << bit;
                     eq_run += __popc(m_eq);
                 }
-            }
         }
-        uint32_t cnt4 = 0, bits = 0;  // per-head counts of this lane; bit it*4+g = (it, g) selected
-#pragma unroll
-        for (int it = 0; it < kLaneTokens; ++it) {
-            cnt4 += selm[it] >> 7;
-            bits |= flags_to_nibble(selm[it]) << (4 * it);
-        }
-        uint32_t excl = cnt4;  // exclusive prefix over lanes, 4 heads at once (<= 124 per byte)
+    }
+    // exclusive prefix over lanes of the per-head counts
+    uint32_t ex01, ex23;
+    head_counts(bits, ex01, ex23);
+    {
+        const uint32_t own01 = ex01, own23 = ex23;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            const uint32_t u = __shfl_up_sync(0xffffffffu, excl, d);
-            if (lane >= d) excl += u;
+            const uint32_t u0 = __shfl_up_sync(0xffffffffu, ex01, d), u1 = __shfl_up_sync(0xffffffffu, ex23, d);
+            if (lane >= d) {
+                ex01 += u0;
+                ex23 += u1;
+            }
         }
-        excl -= cnt4;
-        const int t_lane = RoundWords::first_token(chunk_start, rd, warp) + lane;
-        const int prow0 = page[rd] * kPage + t_lane % kPage;
-        while (bits != 0) {  // a lane holds few selected (token, head) pairs: visit only those
-            const int i = __ffs(bits) - 1;
-            bits &= bits - 1;
-            const int it = i >> 2, g = i & 3;
-            const int bp = g == 0 ? base_pos[0] : (g == 1 ? base_pos[1] : (g == 2 ? base_pos[2] : base_pos[3]));
-            const int pos = bp + (int)((excl >> (8 * g)) & 0xffu);
-            excl += 1u << (8 * g);
-            if (pos < p.sel_stride) {
-                const size_t o = ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride + pos;
-                p.sel_idx[o] = t_lane + it * 32;
-                p.sel_rows[o] = prow0 + it * 32;
+        ex01 -= own01;
+        ex23 -= own23;
+    }
+    int pos[kGroup] = {base_pos[0] + (int)(ex01 & 0xffffu), base_pos[1] + (int)(ex01 >> 16),
+                       base_pos[2] + (int)(ex23 & 0xffffu), base_pos[3] + (int)(ex23 >> 16)};
+    // --- emission: order inside a warp's piece is lane-major; a lane visits only its selected pairs
+#pragma unroll
+    for (int half = 0; half < kWords; ++half) {
+        uint32_t m = bits[half];
+        while (m != 0) {
+            const int i = __ffs(m) - 1;
+            m &= m - 1;
+            const int g = i & 3, it = (i >> 2) & (kLaneTokens - 1), rd = half * 2 + (i >> 4);
+            const int t = first_token(rd) + it * 32 + lane;
+            const int pg = rd == 0 ? page[0] : (rd == 1 ? page[ROUNDS > 1 ? 1 : 0] : (rd == 2 ? page[ROUNDS > 2 ? 2 : 0] : page[ROUNDS > 3 ? 3 : 0]));
+            const int o = g == 0 ? pos[0]++ : (g == 1 ? pos[1]++ : (g == 2 ? pos[2]++ : pos[3]++));
+            if (o < p.sel_stride) {
+                const size_t dst = ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride + o;
+                p.sel_idx[dst] = t;
+                p.sel_rows[dst] = pg * kPage + t % kPage;
             }
         }
     }

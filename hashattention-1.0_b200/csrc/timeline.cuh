@@ -10,7 +10,7 @@
 namespace ha {
 
 enum TimelineKernel { kTlHashDecode = 0, kTlScoreHist, kTlSelect, kTlGather, kTlMerge, kTlKernels };
-enum TimelineEvent { kTlEntry = 0, kTlAfterWait, kTlExit, kTlEvents };
+enum TimelineEvent { kTlEntry = 0, kTlAfterWait, kTlExit, kTlMarkA, kTlMarkB, kTlMarkC, kTlEvents };
 
 #ifdef HA_TIMELINE
 __device__ unsigned long long* g_timeline = nullptr;

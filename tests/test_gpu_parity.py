@@ -253,6 +253,25 @@ def test_long_sequence_selection(device, S):
     run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(128, 1.0 / 32, 128), shuffle_seed=2)
 
 
+def test_two_pass_selection_with_two_rounds_per_cta(device):
+    """S = 40,000 through the workspace-free entry point, which always runs the score_hist + select
+    pair (8-page chunks, two rounds per CTA here), against the oracle on the device's own codes."""
+    Hq, Hkv, S = 8, 2, 40000
+    usa = synthetic.make_usa(Hq, 128, 6, True)
+    inp = synthetic.make_decode_inputs(105, [S], Hq, Hkv)
+    budget = ha.Budget(128, 1.0 / 32, 128)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, budget, usa)
+    ctx.hash_prefill()
+    ctx.hash_decode(inp.q.to(device, torch.bfloat16))
+    ctx.score_select_static()
+    ctx.check_status()
+    q_codes = ctx.q_codes.cpu().to(torch.int64) & ALL_BITS
+    scores = orc.hamming_scores(q_codes, cache.read_codes(0).cpu()[None])
+    want = orc.heavy_sets(orc.select_mask(scores, 128, 128, 1.0 / 32), 128, 128)[0]
+    for h in range(Hq):
+        assert torch.equal(heavy_from_device(ctx, 0, h), want[h])
+
+
 def test_fp32_weights_step(device):
     usa = synthetic.make_usa(8, 128, 5, bf16=False)
     inp = synthetic.make_decode_inputs(95, [777, 300], 8, 2)
