@@ -74,8 +74,14 @@ struct Workspace {
     int32_t* sel_rows;  // [B][Hq][sel_stride] physical rows of the selected tokens
     float* partials;    // [B][Hq][nsplits][130] attention partials
     int32_t* plan;      // [B][Hkv][8 + 8 * nchunks] thresholds, tie quotas and per-chunk output bases
+    uint32_t* scores;   // [B][Hkv][nchunks * chunk tokens] packed scores of the 4 heads of a group, one byte each
     size_t bytes;
 };
+
+size_t scores_bytes(const ha_shape_t* s) {
+    return (size_t)s->batch * s->num_kv_heads * num_chunks_for(s->max_pages) * chunk_pages_for(s->max_pages) * kPage *
+           sizeof(uint32_t);
+}
 
 Workspace carve(const ha_shape_t* s, const ha_budget_t* b, void* base) {
     const size_t Hq = (size_t)s->num_kv_heads * kGroup;
@@ -91,6 +97,8 @@ Workspace carve(const ha_shape_t* s, const ha_budget_t* b, void* base) {
     off += align_up((size_t)s->batch * Hq * att_split(s, b).nsplits * kPartStride * sizeof(float));
     w.plan = reinterpret_cast<int32_t*>(p + off);
     off += align_up((size_t)s->batch * s->num_kv_heads * (8 + 8 * (size_t)num_chunks_for(s->max_pages)) * sizeof(int32_t));
+    w.scores = reinterpret_cast<uint32_t*>(p + off);
+    off += align_up(scores_bytes(s));
     w.bytes = off;
     return w;
 }
@@ -393,6 +401,7 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
     p.seq_lens = seq_lens;
     p.hist = w.hist;
     p.plan = w.plan;
+    p.scores = w.scores;
     p.sel_idx = sel_idx;
     p.sel_rows = w.sel_rows;
     p.sel_cnt = sel_cnt;
@@ -516,6 +525,7 @@ struct StaticScratch {
     uint32_t* hist;     // [B][Hkv][4*33][nchunks]
     int32_t* sel_rows;  // [B][Hq][sel_stride]
     int32_t* plan;      // [B][Hkv][8 + 8 * nchunks]
+    uint32_t* scores;   // [B][Hkv][nchunks * chunk tokens]
     size_t bytes;
 };
 
@@ -529,7 +539,9 @@ StaticScratch carve_static(const ha_shape_t* s, void* base) {
     w.sel_rows = reinterpret_cast<int32_t*>(p + off);
     const size_t off2 = off + align_up(n_rows * sizeof(int32_t));
     w.plan = reinterpret_cast<int32_t*>(p + off2);
-    w.bytes = off2 + align_up((size_t)s->batch * s->num_kv_heads * (8 + 8 * (size_t)num_chunks_for(s->max_pages)) * sizeof(int32_t));
+    const size_t off3 = off2 + align_up((size_t)s->batch * s->num_kv_heads * (8 + 8 * (size_t)num_chunks_for(s->max_pages)) * sizeof(int32_t));
+    w.scores = reinterpret_cast<uint32_t*>(p + off3);
+    w.bytes = off3 + align_up(ha::scores_bytes(s));
     return w;
 }
 
@@ -573,7 +585,7 @@ int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
     if (rc != HA_OK) return rc;
     const StaticScratch w = carve_static(shape, base);
 
-    // Every word of hist / plan / sel_rows that a kernel reads was written earlier in the same call,
+    // Every word of hist / plan / scores / sel_rows that a kernel reads was written earlier in the same call,
     // so nothing left over from the previous call needs clearing.
     SelectParams p;
     p.q_codes = q_codes;
@@ -582,6 +594,7 @@ int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
     p.seq_lens = seq_lens;
     p.hist = w.hist;
     p.plan = w.plan;
+    p.scores = w.scores;
     p.sel_idx = sel_idx;
     p.sel_rows = w.sel_rows;
     p.sel_cnt = sel_cnt;

@@ -52,6 +52,7 @@ struct SelectParams {
     int32_t* sel_rows;         // workspace: [B][Hq][sel_stride] page * 256 + slot of the same tokens
     int32_t* sel_cnt;          // [B][Hq]
     int32_t* plan;             // workspace: [B][Hkv][8 + 8 * nchunks]: T[4], need[4], then per chunk base[4], eqb[4]
+    uint32_t* scores;          // workspace: [B][Hkv][nchunks * chunk tokens]: byte g = score of head g + 1, 0 = not a candidate
     uint8_t* scores_dbg;       // [B][Hq][max_pages*256] or null
     int32_t* status;
     int B, Hkv, max_pages, num_pages, sel_stride, nchunks;
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     __syncthreads();  // s_hist is zero
 
     uint32_t* h0 = &s_hist[warp][0];
+    uint32_t* srow = p.scores + ((size_t)b * p.Hkv + kvh) * ((size_t)p.nchunks * chunk_tokens);
     bool bad_page = false;
 #pragma unroll 1
     for (int rd = 0; rd < ROUNDS; ++rd) {
@@ -168,12 +170,15 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
         for (int it = 0; it < kLaneTokens; ++it) {
             const uint32_t s0 = __popc(qn.x ^ rw.w[it].x), s1 = __popc(qn.y ^ rw.w[it].y);
             const uint32_t s2 = __popc(qn.z ^ rw.w[it].z), s3 = __popc(qn.w ^ rw.w[it].w);
-            if (rw.interior || ((rw.cand >> it) & 1u)) {
+            const bool is_cand = rw.interior || ((rw.cand >> it) & 1u);
+            if (is_cand) {
                 atomicAdd(h0 + s0, 1u);
                 atomicAdd(h0 + kBins + s1, 1u);
                 atomicAdd(h0 + 2 * kBins + s2, 1u);
                 atomicAdd(h0 + 3 * kBins + s3, 1u);
             }
+            // pass B works from these 4 bytes per token instead of the 16-byte hash word
+            srow[t0 + it * 32 + lane] = is_cand ? (s0 | (s1 << 8) | (s2 << 16) | (s3 << 24)) + 0x01010101u : 0u;
             if (p.scores_dbg != nullptr && ((rw.valid >> it) & 1u)) {
                 const size_t pitch = (size_t)p.max_pages * kPage;
                 uint8_t* d = p.scores_dbg + ((size_t)b * Hq + kvh * kGroup) * pitch + t0 + it * 32 + lane;
@@ -210,6 +215,7 @@ __device__ __forceinline__ uint32_t flags_to_nibble(uint32_t f) { return (((f >>
 // and of tied tokens that precede it. Lane = chunk (32 chunks per pass); a lane holds the 33
 // counts of its chunk in registers.
 __global__ void __launch_bounds__(kGroup * 32) select_plan_kernel(const SelectParams p, int chunk_tokens) {
+    HA_TL(kTlSelectPlan, kTlEntry);
     const int kvh = blockIdx.x, b = blockIdx.y;
     const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int Hq = p.Hkv * kGroup;
@@ -219,6 +225,7 @@ __global__ void __launch_bounds__(kGroup * 32) select_plan_kernel(const SelectPa
     const int nchunks_b = (r.S + chunk_tokens - 1) / chunk_tokens;
 
     pdl_wait();
+    HA_TL(kTlSelectPlan, kTlAfterWait);
     pdl_launch_dependents();
     if (!s_ok) return;
 
@@ -295,15 +302,17 @@ __global__ void __launch_bounds__(kGroup * 32) select_plan_kernel(const SelectPa
         gt_carry += __shfl_sync(0xffffffffu, pg, 31);
         eq_carry += __shfl_sync(0xffffffffu, pe, 31);
     }
+    HA_TL(kTlSelectPlan, kTlExit);
 }
 
 template <int ROUNDS>
-__global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectParams p) {
     HA_TL(kTlSelect, kTlEntry);
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
     constexpr int chunk_tokens = ROUNDS * kRoundTokens;
+    constexpr int kWarpTokens = ROUNDS * kLaneTokens * 32;  // 128 ROUNDS contiguous tokens per warp
     __shared__ int s_T[kGroup], s_need[kGroup], s_base[kGroup], s_eqb[kGroup];
     __shared__ uint32_t s_wg[kSelWarps][2], s_we[kSelWarps][2];  // per warp: counts of heads (0,1) / (2,3), 16 bits each
 
@@ -311,33 +320,28 @@ __global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectPara
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
     const int chunk_start = c * chunk_tokens;
     const bool active = s_ok && chunk_start < S;
-    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
-    // --- before the dependency wait: this chunk's scores. The two kernels in front of this one
-    //     (score_hist, select_plan) write only histograms and the plan; the query codes and every hash word, the newest
-    //     token's included, come from the encoder kernel, which had completed before any CTA of
-    //     this kernel could start. Scores are kept packed in registers (byte g = head g).
-    // In this kernel warp w owns the contiguous tokens [chunk_start + 128 ROUNDS w, + 128 ROUNDS), so
-    // that everything it selects lands in one contiguous piece of the output and one scan serves
-    // all its rounds. (The histograms of pass A are per chunk and do not care about the order inside.)
-    auto first_token = [&](int rd) { return chunk_start + warp * (ROUNDS * kLaneTokens * 32) + rd * (kLaneTokens * 32); };
-    uint32_t sc[ROUNDS][kLaneTokens];
-    int page[ROUNDS];
-    uint32_t cand = 0;  // bit rd * 4 + it
+    // --- before the dependency wait: this chunk's packed scores, 4 consecutive tokens per 16-byte load
+    //     (token wbase + 128 j + 4 lane + k is component k of load j). They were written by
+    //     score_hist, two kernels ahead in the stream: select_plan, the kernel directly in front,
+    //     could only start its wait-release after score_hist had completed, and this kernel's CTAs
+    //     start after that. Pass A wrote whole rounds of 1024 tokens up to the one containing S - 1.
+    const int wbase = chunk_start + warp * kWarpTokens;
+    uint4 sc[ROUNDS];
+    int pg0 = 0, pg1 = 0;  // the (at most two) pages this warp's tokens lie in
     if (active) {
-        const uint4 qn = load_qn(p, b, kvh);
-        RoundWords rw;
+        const uint32_t* srow = p.scores + ((size_t)b * p.Hkv + kvh) * ((size_t)p.nchunks * chunk_tokens);
+        const int written_end = (S + kRoundTokens - 1) / kRoundTokens * kRoundTokens;
 #pragma unroll
-        for (int rd = 0; rd < ROUNDS; ++rd) {
-            const int t0 = first_token(rd);
-            rw.load(p, b, kvh, t0, lane, r);  // beyond S every access is clamped and nothing is valid
-            rw.refresh_newest(p, kvh, t0, lane, r);
-            page[rd] = rw.page;
-            cand |= rw.cand << (rd * kLaneTokens);
-#pragma unroll
-            for (int it = 0; it < kLaneTokens; ++it)
-                sc[rd][it] = __popc(qn.x ^ rw.w[it].x) | (__popc(qn.y ^ rw.w[it].y) << 8) |
-                             (__popc(qn.z ^ rw.w[it].z) << 16) | (__popc(qn.w ^ rw.w[it].w) << 24);
+        for (int j = 0; j < ROUNDS; ++j) {
+            const int t = wbase + j * 128 + lane * kLaneTokens;
+            sc[j] = t < written_end ? __ldcg(reinterpret_cast<const uint4*>(srow + t)) : make_uint4(0u, 0u, 0u, 0u);
         }
+        const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
+        const int pi = wbase / kPage;
+        pg0 = __ldg(pt + min(pi, p.max_pages - 1));
+        pg1 = ROUNDS == 4 ? __ldg(pt + min(pi + 1, p.max_pages - 1)) : pg0;
+        pg0 = pg0 >= 0 && pg0 < p.num_pages ? pg0 : 0;  // tokens of a bad page are no candidates: never emitted
+        pg1 = pg1 >= 0 && pg1 < p.num_pages ? pg1 : 0;
     }
 
     pdl_wait();
@@ -359,38 +363,34 @@ __global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectPara
     HA_TL(kTlSelect, kTlMarkB);
 
     // --- classify once: per token and head (score > T) and (score == T), kept as bit sets of this
-    //     lane: bit ((rd & 1) * 4 + it) * 4 + g of word rd / 2. Everything after this works on the
-    //     bit sets (counts are popcounts under a per-head mask), not on the tokens again.
+    //     lane: bit ((j & 1) * 4 + k) * 4 + g of word j / 2. Stored bytes are score + 1 (0 for a token
+    //     that is no candidate), so they are compared with T + 1 >= 1 and non-candidates never match.
+    //     Everything after this works on the bit sets (counts are popcounts under a per-head mask).
     constexpr int kWords = (ROUNDS + 1) / 2;
-    const uint32_t t4 = (uint32_t)s_T[0] | ((uint32_t)s_T[1] << 8) | ((uint32_t)s_T[2] << 16) | ((uint32_t)s_T[3] << 24);
+    const uint32_t t4 = ((uint32_t)s_T[0] | ((uint32_t)s_T[1] << 8) | ((uint32_t)s_T[2] << 16) | ((uint32_t)s_T[3] << 24)) + 0x01010101u;
     const uint32_t gt_add = 0x7F7F7F7Fu - t4;
     uint32_t gtb[kWords], eqb[kWords];
 #pragma unroll
     for (int i = 0; i < kWords; ++i) gtb[i] = eqb[i] = 0;
-    const bool all_cand = __all_sync(0xffffffffu, cand == (ROUNDS * kLaneTokens == 32 ? 0xffffffffu : (1u << (ROUNDS * kLaneTokens)) - 1u));
 #pragma unroll
-    for (int rd = 0; rd < ROUNDS; ++rd)
+    for (int j = 0; j < ROUNDS; ++j) {
+        const uint32_t a[kLaneTokens] = {sc[j].x, sc[j].y, sc[j].z, sc[j].w};
 #pragma unroll
-        for (int it = 0; it < kLaneTokens; ++it) {
-            uint32_t fg = bytes_gt(sc[rd][it], gt_add), fe = bytes_eq(sc[rd][it], t4);
-            if (!all_cand) {  // warp-uniform: only warps that touch the sink / recent / tail region
-                const uint32_t cm = 0u - ((cand >> (rd * kLaneTokens + it)) & 1u);
-                fg &= cm;
-                fe &= cm;
-            }
-            const int sh = ((rd & 1) * kLaneTokens + it) * 4;
-            gtb[rd >> 1] |= flags_to_nibble(fg) << sh;
-            eqb[rd >> 1] |= flags_to_nibble(fe) << sh;
+        for (int k = 0; k < kLaneTokens; ++k) {
+            const int sh = ((j & 1) * kLaneTokens + k) * 4;
+            gtb[j >> 1] |= flags_to_nibble(bytes_gt(a[k], gt_add)) << sh;
+            eqb[j >> 1] |= flags_to_nibble(bytes_eq(a[k], t4)) << sh;
         }
+    }
     // per-head popcounts of a bit set, as two words of 16-bit fields: heads (0,1) and (2,3)
     auto head_counts = [&](const uint32_t (&w)[kWords], uint32_t& c01, uint32_t& c23) {
-        uint32_t c[kGroup] = {0, 0, 0, 0};
+        uint32_t cnt[kGroup] = {0, 0, 0, 0};
 #pragma unroll
         for (int i = 0; i < kWords; ++i)
 #pragma unroll
-            for (int g = 0; g < kGroup; ++g) c[g] += __popc(w[i] & (0x11111111u << g));
-        c01 = c[0] | (c[1] << 16);
-        c23 = c[2] | (c[3] << 16);
+            for (int g = 0; g < kGroup; ++g) cnt[g] += __popc(w[i] & (0x11111111u << g));
+        c01 = cnt[0] | (cnt[1] << 16);
+        c23 = cnt[2] | (cnt[3] << 16);
     };
     {
         uint32_t g01, g23, e01, e23;
@@ -445,15 +445,27 @@ __global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectPara
             if (!((straddle >> g) & 1u)) continue;
             int eq_run = __shfl_sync(0xffffffffu, my_eqb, g);
 #pragma unroll
-            for (int rd = 0; rd < ROUNDS; ++rd)
+            for (int j = 0; j < ROUNDS; ++j) {
+                // token order inside a load block is (lane, k): ties in lower lanes come first
+                int before = 0, total = 0;
 #pragma unroll
-                for (int it = 0; it < kLaneTokens; ++it) {
-                    const int bit = ((rd & 1) * kLaneTokens + it) * 4 + g;
-                    const bool eq = (eqb[rd >> 1] >> bit) & 1u;
+                for (int k = 0; k < kLaneTokens; ++k) {
+                    const bool eq = (eqb[j >> 1] >> (((j & 1) * kLaneTokens + k) * 4 + g)) & 1u;
                     const uint32_t m_eq = __ballot_sync(0xffffffffu, eq);
-                    if (eq && eq_run + __popc(m_eq & lt_mask) < s_need[g]) bits[rd >> 1] |= 1u << bit;
-                    eq_run += __popc(m_eq);
+                    before += __popc(m_eq & lt_mask);
+                    total += __popc(m_eq);
                 }
+                int own = 0;
+#pragma unroll
+                for (int k = 0; k < kLaneTokens; ++k) {
+                    const int bit = ((j & 1) * kLaneTokens + k) * 4 + g;
+                    if ((eqb[j >> 1] >> bit) & 1u) {
+                        if (eq_run + before + own < s_need[g]) bits[j >> 1] |= 1u << bit;
+                        ++own;
+                    }
+                }
+                eq_run += total;
+            }
         }
     }
     // exclusive prefix over lanes of the per-head counts
@@ -481,9 +493,9 @@ __global__ void __launch_bounds__(kSelThreads, 3) select_kernel(const SelectPara
         while (m != 0) {
             const int i = __ffs(m) - 1;
             m &= m - 1;
-            const int g = i & 3, it = (i >> 2) & (kLaneTokens - 1), rd = half * 2 + (i >> 4);
-            const int t = first_token(rd) + it * 32 + lane;
-            const int pg = rd == 0 ? page[0] : (rd == 1 ? page[ROUNDS > 1 ? 1 : 0] : (rd == 2 ? page[ROUNDS > 2 ? 2 : 0] : page[ROUNDS > 3 ? 3 : 0]));
+            const int g = i & 3, k = (i >> 2) & (kLaneTokens - 1), j = half * 2 + (i >> 4);
+            const int t = wbase + j * 128 + lane * kLaneTokens + k;
+            const int pg = (ROUNDS == 4 && j >= 2) ? pg1 : pg0;
             const int o = g == 0 ? pos[0]++ : (g == 1 ? pos[1]++ : (g == 2 ? pos[2]++ : pos[3]++));
             if (o < p.sel_stride) {
                 const size_t dst = ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride + o;

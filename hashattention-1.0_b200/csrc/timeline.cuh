@@ -9,7 +9,7 @@
 
 namespace ha {
 
-enum TimelineKernel { kTlHashDecode = 0, kTlScoreHist, kTlSelect, kTlGather, kTlMerge, kTlKernels };
+enum TimelineKernel { kTlHashDecode = 0, kTlScoreHist, kTlSelect, kTlGather, kTlMerge, kTlSelectPlan, kTlKernels };
 enum TimelineEvent { kTlEntry = 0, kTlAfterWait, kTlExit, kTlMarkA, kTlMarkB, kTlMarkC, kTlEvents };
 
 #ifdef HA_TIMELINE

@@ -60,27 +60,27 @@ def capture(layers):
     return g
 
 g_all = capture(range(L)); singles = [capture([l]) for l in range(L)]
-NE = 6
-tl = torch.zeros(5 * NE * 2, dtype=torch.int64, device=dev)
-names = ["hash_decode", "score_hist", "select", "gather", "merge"]
-acc = np.zeros((5, NE, 2))
+NE, NK = 6, 6
+tl = torch.zeros(NK * NE * 2, dtype=torch.int64, device=dev)
+names = ["hash_decode", "score_hist", "select", "gather", "merge", "select_plan"]
+acc = np.zeros((NK, NE, 2))
 n = 0
 for rep in range(3):
     for l in range(L):
         g_all.replay(); torch.cuda.synchronize()       # makes layer l's data cold again
-        init = torch.tensor([-1, 0] * (5 * NE), dtype=torch.int64, device=dev)
+        init = torch.tensor([-1, 0] * (NK * NE), dtype=torch.int64, device=dev)
         tl.copy_(init); torch.cuda.synchronize()
         lib.ha_debug_set_timeline(tl.data_ptr())
         singles[l].replay(); torch.cuda.synchronize()
         lib.ha_debug_set_timeline(None)
-        t = tl.cpu().numpy().astype(np.uint64).reshape(5, NE, 2)
+        t = tl.cpu().numpy().astype(np.uint64).reshape(NK, NE, 2)
         t0 = t[0, 0, 0]
         acc += (t.astype(np.float64) - float(t0)) / 1000.0
         n += 1
 acc /= n
 print(f"{workload} B={B}: mean over {n} isolated steps, microseconds from the first CTA of hash_decode")
 print(f"{'kernel':12s} {'entry min':>9s} {'entry max':>9s} {'wait min':>9s} {'wait max':>9s} {'exit min':>9s} {'exit max':>9s}   marks A/B/C (min max each, where stamped)")
-for k in range(5):
+for k in range(NK):
     cells = []
     for e in range(NE):
         for m in range(2):

@@ -60,7 +60,8 @@ def test_static_scratch_selection_equals_workspace_selection_on_two_calls_in_a_r
         for b in range(len(lens)):
             for h in range(Hq):
                 n = int(want_cnt[b, h])
-                assert torch.equal(got_idx[b, h, :n], want_idx[b, h, :n]), f"call {call}: b={b} h={h}"
+                # the order inside a head's list is not part of the contract (each token once)
+                assert torch.equal(got_idx[b, h, :n].sort().values, want_idx[b, h, :n].sort().values), f"call {call}: b={b} h={h}"
     # the Python wrapper drives the same entry point
     ctx.sel_idx.fill_(-1)
     idx, cnt = ctx.score_select_static(q_codes)
@@ -68,4 +69,4 @@ def test_static_scratch_selection_equals_workspace_selection_on_two_calls_in_a_r
     for b in range(len(lens)):
         for h in range(Hq):
             n = int(want_cnt[b, h])
-            assert torch.equal(idx[b, h, :n], want_idx[b, h, :n])
+            assert torch.equal(idx[b, h, :n].sort().values, want_idx[b, h, :n].sort().values)
