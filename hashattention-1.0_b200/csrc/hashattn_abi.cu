@@ -129,8 +129,8 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-// The two-pass selection: chunk histograms, the plan (thresholds and output bases) derived from
-// them once per (sequence, kv-head), then the compaction.
+// The two-pass selection: chunk histograms and packed scores, the plan (thresholds and output
+// bases) derived from the histograms once per (sequence, kv-head), then the compaction.
 cudaError_t launch_two_pass_select(const ha_shape_t* shape, const SelectParams& p, cudaStream_t s) {
     const dim3 grid(p.nchunks, shape->num_kv_heads, shape->batch);
     const dim3 pgrid(shape->num_kv_heads, shape->batch);
@@ -141,11 +141,11 @@ cudaError_t launch_two_pass_select(const ha_shape_t* shape, const SelectParams& 
         case 8: e1 = launch(score_hist_kernel<2>, grid, dim3(kSelThreads), s, 1, p); break;
         default: e1 = launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p); break;
     }
-    e2 = launch(select_plan_kernel, pgrid, dim3(kGroup * 32), s, 1, p, chunk_pages * kPage);
+    e2 = launch(select_plan_kernel, pgrid, dim3(kSelThreads), s, 1, p, chunk_pages * kPage);
     switch (chunk_pages) {
-        case 4: e3 = launch(select_kernel<1>, grid, dim3(kSelThreads), s, 1, p); break;
-        case 8: e3 = launch(select_kernel<2>, grid, dim3(kSelThreads), s, 1, p); break;
-        default: e3 = launch(select_kernel<4>, grid, dim3(kSelThreads), s, 1, p); break;
+        case 4: e3 = launch(select_kernel<1>, grid, dim3(kSelBThreads), s, 1, p); break;
+        case 8: e3 = launch(select_kernel<2>, grid, dim3(kSelBThreads), s, 1, p); break;
+        default: e3 = launch(select_kernel<4>, grid, dim3(kSelBThreads), s, 1, p); break;
     }
     if (e1 != cudaSuccess) return e1;
     return e2 != cudaSuccess ? e2 : e3;
@@ -295,9 +295,18 @@ int ha_hash_decode(const ha_shape_t* shape, const ha_hash_weights_t* weights,
     p.Hkv = shape->num_kv_heads;
     p.max_pages = shape->max_pages;
     p.num_pages = shape->num_pages;
-    // Enough CTAs to cover the GPU, but re-use a head's weights (held in registers) across
-    // several sequences once the batch is large.
-    p.batch_per_cta = shape->batch >= 32 ? 4 : (shape->batch >= 8 ? 2 : 1);
+    // One CTA (512 threads, the head's weights in registers) fits per SM: give each CTA as many
+    // sequences as it takes for the whole grid to be resident at once, instead of a second wave
+    // that would fetch the weights again.
+    {
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+            return HA_ERR_LAUNCH;
+        const long long nets = (long long)shape->num_kv_heads * kGroup * (key_side ? 2 : 1);
+        const long long slices = sms / nets > 0 ? sms / nets : 1;  // batch slices that fit in one wave
+        p.batch_per_cta = (int)((shape->batch + slices - 1) / slices);
+    }
     const dim3 grid(shape->num_kv_heads * kGroup, key_side ? 2 : 1,
                     (shape->batch + p.batch_per_cta - 1) / p.batch_per_cta);
     cudaError_t e;
@@ -585,8 +594,8 @@ int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
     if (rc != HA_OK) return rc;
     const StaticScratch w = carve_static(shape, base);
 
-    // Every word of hist / plan / scores / sel_rows that a kernel reads was written earlier in the same call,
-    // so nothing left over from the previous call needs clearing.
+    // Every word of hist / plan / scores / sel_rows that a kernel reads was written earlier in the same
+    // call, so nothing left over from the previous call needs clearing.
     SelectParams p;
     p.q_codes = q_codes;
     p.hash_pages = reinterpret_cast<const uint4*>(hash_pages);

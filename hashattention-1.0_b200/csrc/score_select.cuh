@@ -123,6 +123,138 @@ __device__ __forceinline__ uint4 load_qn(const SelectParams& p, int b, int kvh) 
     return make_uint4(~qc.x, ~qc.y, ~qc.z, ~qc.w);
 }
 
+// Per-byte flags (bit 7 of each byte) for packed scores a (bytes <= 32) against packed thresholds.
+// gt_add = 0x7F7F7F7F - T4: byte sum a + 127 - T carries into bit 7 iff a > T (no carry across bytes).
+__device__ __forceinline__ uint32_t bytes_gt(uint32_t a, uint32_t gt_add) { return (a + gt_add) & 0x80808080u; }
+__device__ __forceinline__ uint32_t bytes_eq(uint32_t a, uint32_t t4) {
+    return ~((a ^ t4) + 0x7F7F7F7Fu) & 0x80808080u;  // (x + 127) has bit 7 iff x != 0
+}
+// bit 7 of byte g -> bit g
+__device__ __forceinline__ uint32_t flags_to_nibble(uint32_t f) { return (((f >> 7) * 0x01020408u) >> 24) & 0xFu; }
+
+// The plan of one (sequence, kv-head), worked out by one CTA of 256 threads between the two passes.
+// From the per-chunk histograms it derives, once instead of in every CTA of pass B, the global
+// threshold T and the tie quota of each head, and for every chunk the number of selected tokens
+// and of tied tokens that precede it. The counts of 32 chunks at a time are staged
+// in shared memory ([head][bin][chunk], all 8 warps load: warp w the bins of head w % 4, lower or
+// upper half), then warp g works head g out with lane = chunk.
+constexpr int kPlanHalf = (kBins + 1) / 2;  // 17 bins per loading warp
+
+__device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kvh, const SeqRange& r, int nchunks_b,
+                                            uint32_t (*stage)[kBins][32], int tid) {
+    const int lane = tid & 31, warp = tid >> 5, g = warp & 3;
+    const int Hq = p.Hkv * kGroup;
+    int hbe = r.hb;
+    if (hbe > p.sel_stride) {
+        if (tid == 0) report(p.status, HA_ERR_SEL_OVERFLOW);
+        hbe = p.sel_stride;
+    }
+    const uint32_t* hbase = p.hist + (((size_t)b * p.Hkv + kvh) * (kGroup * kBins) + g * kBins) * p.nchunks;
+    int32_t* plan = p.plan + ((size_t)b * p.Hkv + kvh) * (8 + 8 * p.nchunks);
+    auto stage_pass = [&](int cc0) {
+        const int s0 = (warp >> 2) * kPlanHalf, cc = cc0 + lane;
+        uint32_t v[kPlanHalf];
+#pragma unroll
+        for (int k = 0; k < kPlanHalf; ++k)
+            v[k] = cc < nchunks_b ? __ldcg(hbase + (size_t)min(s0 + k, kBins - 1) * p.nchunks + cc) : 0u;
+#pragma unroll
+        for (int k = 0; k < kPlanHalf; ++k)
+            if (s0 + k < kBins) stage[g][s0 + k][lane] = v[k];
+    };
+    const bool one_pass = nchunks_b <= 32;
+
+    // totals per bin over all chunks -> T and the tie quota (lane l holds bin 32 - l)
+    int tot_hi = 0;
+    for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
+        if (cc0 > 0) __syncthreads();
+        stage_pass(cc0);
+        __syncthreads();
+        if (warp < kGroup) {
+#pragma unroll 8
+            for (int s = 1; s < kBins; ++s) {
+                const int t = __reduce_add_sync(0xffffffffu, (int)stage[g][s][lane]);
+                if (lane == 32 - s) tot_hi += t;
+            }
+        }
+    }
+    int T = kBins, need = 0;
+    if (warp < kGroup) {
+        int cum = tot_hi;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, cum, d);
+            if (lane >= d) cum += u;
+        }
+        const uint32_t reached = __ballot_sync(0xffffffffu, cum >= hbe);
+        if (hbe <= 0) {
+            T = kBins; need = 0;  // T = 33: nothing qualifies
+        } else if (reached != 0) {
+            const int l = __ffs(reached) - 1;  // first lane whose cumulative count reaches the budget
+            T = 32 - l;
+            need = hbe - __shfl_sync(0xffffffffu, cum - tot_hi, l);
+        } else {  // bins 32..1 together hold fewer than the budget: the threshold is 0
+            T = 0;
+            need = hbe - __shfl_sync(0xffffffffu, cum, 31);
+        }
+        if (lane == 0) {
+            plan[g] = T;
+            plan[4 + g] = need;
+            p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = hbe;
+        }
+    }
+
+    // per chunk: tokens above T and tokens at T, then exclusive prefixes over the chunks
+    int gt_carry = 0, eq_carry = 0;
+    for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
+        if (!one_pass) {  // otherwise the counts of the only pass are still staged
+            __syncthreads();
+            stage_pass(cc0);
+            __syncthreads();
+        }
+        if (warp < kGroup) {
+            const int cc = cc0 + lane;
+            int gt = 0, eq = 0;
+#pragma unroll 8
+            for (int s = 0; s < kBins; ++s) {
+                const int v = (int)stage[g][s][lane];
+                gt += s > T ? v : 0;
+                eq += s == T ? v : 0;
+            }
+            int pg = gt, pe = eq;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int u0 = __shfl_up_sync(0xffffffffu, pg, d), u1 = __shfl_up_sync(0xffffffffu, pe, d);
+                if (lane >= d) {
+                    pg += u0;
+                    pe += u1;
+                }
+            }
+            const int gt_before = gt_carry + pg - gt, eq_before = eq_carry + pe - eq;
+            if (cc < nchunks_b) {
+                plan[8 + 8 * cc + g] = gt_before + min(eq_before, need);
+                plan[8 + 8 * cc + 4 + g] = eq_before;
+            }
+            gt_carry += __shfl_sync(0xffffffffu, pg, 31);
+            eq_carry += __shfl_sync(0xffffffffu, pe, 31);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kSelThreads) select_plan_kernel(const SelectParams p, int chunk_tokens) {
+    HA_TL(kTlSelectPlan, kTlEntry);
+    __shared__ uint32_t s_stage[kGroup][kBins][32];
+    const int kvh = blockIdx.x, b = blockIdx.y;
+    const int S = p.seq_lens[b];
+    const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
+    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
+    pdl_wait();
+    HA_TL(kTlSelectPlan, kTlAfterWait);
+    pdl_launch_dependents();
+    if (!s_ok) return;
+    select_plan(p, b, kvh, r, (r.S + chunk_tokens - 1) / chunk_tokens, s_stage, threadIdx.x);
+    HA_TL(kTlSelectPlan, kTlExit);
+}
+
 template <int ROUNDS>
 __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectParams p) {
     HA_TL(kTlScoreHist, kTlEntry);
@@ -200,148 +332,70 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     HA_TL(kTlScoreHist, kTlExit);
 }
 
-// Per-byte flags (bit 7 of each byte) for packed scores a (bytes <= 32) against packed thresholds.
-// gt_add = 0x7F7F7F7F - T4: byte sum a + 127 - T carries into bit 7 iff a > T (no carry across bytes).
-__device__ __forceinline__ uint32_t bytes_gt(uint32_t a, uint32_t gt_add) { return (a + gt_add) & 0x80808080u; }
-__device__ __forceinline__ uint32_t bytes_eq(uint32_t a, uint32_t t4) {
-    return ~((a ^ t4) + 0x7F7F7F7Fu) & 0x80808080u;  // (x + 127) has bit 7 iff x != 0
-}
-// bit 7 of byte g -> bit g
-__device__ __forceinline__ uint32_t flags_to_nibble(uint32_t f) { return (((f >> 7) * 0x01020408u) >> 24) & 0xFu; }
+// Pass B. A CTA of 128 threads owns the chunk of pass A; warp w owns the 256 ROUNDS contiguous
+// tokens [chunk_start + 256 ROUNDS w, ...), lane l the tokens 128 j + 4 l + k of it (j = 0 ..
+// 2 ROUNDS - 1 one 16-byte load each, k = 0..3 its components), 8 ROUNDS tokens in all, numbered
+// n = 4 j + k in ascending token order.
+constexpr int kSelBThreads = 128;
+constexpr int kSelBWarps = kSelBThreads / 32;
 
-// Between the two passes: one CTA per (sequence, kv-head), warp g = query head g of the group.
-// From the per-chunk histograms it derives, once instead of in every CTA of pass B, the global
-// threshold T and the tie quota of the head, and for every chunk the number of selected tokens
-// and of tied tokens that precede it. Lane = chunk (32 chunks per pass); a lane holds the 33
-// counts of its chunk in registers.
-__global__ void __launch_bounds__(kGroup * 32) select_plan_kernel(const SelectParams p, int chunk_tokens) {
-    HA_TL(kTlSelectPlan, kTlEntry);
-    const int kvh = blockIdx.x, b = blockIdx.y;
-    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
-    const int Hq = p.Hkv * kGroup;
-    const int S = p.seq_lens[b];
-    const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
-    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
-    const int nchunks_b = (r.S + chunk_tokens - 1) / chunk_tokens;
-
-    pdl_wait();
-    HA_TL(kTlSelectPlan, kTlAfterWait);
-    pdl_launch_dependents();
-    if (!s_ok) return;
-
-    int hbe = r.hb;
-    if (hbe > p.sel_stride) {
-        if (lane == 0 && g == 0) report(p.status, HA_ERR_SEL_OVERFLOW);
-        hbe = p.sel_stride;
+// byte g of each of the NW words, gathered into one word (byte w of the result = byte g of a[w])
+template <int NW>
+__device__ __forceinline__ uint32_t gather_byte(const uint32_t (&a)[NW], int g) {
+    if constexpr (NW == 4) {
+        const uint32_t sel = 0x0040u + 0x11u * g;  // bytes g of x (index g) and of y (index 4 + g)
+        return __byte_perm(__byte_perm(a[0], a[1], sel), __byte_perm(a[2], a[3], sel), 0x5410u);
+    } else if constexpr (NW == 2) {
+        return __byte_perm(a[0], a[1], 0x4440u + 0x11u * g) & 0xffffu;
+    } else {
+        return (a[0] >> (8 * g)) & 0xffu;
     }
-    const uint32_t* hbase = p.hist + (((size_t)b * p.Hkv + kvh) * (kGroup * kBins) + g * kBins) * p.nchunks;
-    int32_t* plan = p.plan + ((size_t)b * p.Hkv + kvh) * (8 + 8 * p.nchunks);
-
-    // totals per bin over all chunks -> T and the tie quota (lane l then holds bin 32 - l; bin 0 apart)
-    int tot_hi = 0, tot0 = 0;  // tot_hi: total of bin 32 - lane
-    for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
-        const int cc = cc0 + lane;
-#pragma unroll
-        for (int s = 0; s < kBins; ++s) {
-            const int v = cc < nchunks_b ? (int)__ldcg(hbase + (size_t)s * p.nchunks + cc) : 0;
-            const int t = __reduce_add_sync(0xffffffffu, v);
-            if (s == 0) tot0 += t;
-            else if (lane == 32 - s) tot_hi += t;
-        }
-    }
-    (void)tot0;
-    int cum = tot_hi;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const int u = __shfl_up_sync(0xffffffffu, cum, d);
-        if (lane >= d) cum += u;
-    }
-    const uint32_t reached = __ballot_sync(0xffffffffu, cum >= hbe);
-    int T, need;
-    if (hbe <= 0) {
-        T = kBins; need = 0;  // T = 33: nothing qualifies
-    } else if (reached != 0) {
-        const int l = __ffs(reached) - 1;  // first lane whose cumulative count reaches the budget
-        T = 32 - l;
-        need = hbe - __shfl_sync(0xffffffffu, cum - tot_hi, l);
-    } else {  // bins 32..1 together hold fewer than the budget: the threshold is 0
-        T = 0;
-        need = hbe - __shfl_sync(0xffffffffu, cum, 31);
-    }
-    if (lane == 0) {
-        plan[g] = T;
-        plan[4 + g] = need;
-        p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = hbe;
-    }
-
-    // per chunk: tokens above T and tokens at T, then exclusive prefixes over the chunks
-    int gt_carry = 0, eq_carry = 0;
-    for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
-        const int cc = cc0 + lane;
-        int gt = 0, eq = 0;
-#pragma unroll
-        for (int s = 0; s < kBins; ++s) {
-            const int v = cc < nchunks_b ? (int)__ldcg(hbase + (size_t)s * p.nchunks + cc) : 0;  // L1/L2 hit: read above
-            gt += s > T ? v : 0;
-            eq += s == T ? v : 0;
-        }
-        int pg = gt, pe = eq;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int u0 = __shfl_up_sync(0xffffffffu, pg, d), u1 = __shfl_up_sync(0xffffffffu, pe, d);
-            if (lane >= d) {
-                pg += u0;
-                pe += u1;
-            }
-        }
-        const int gt_before = gt_carry + pg - gt, eq_before = eq_carry + pe - eq;
-        if (cc < nchunks_b) {
-            plan[8 + 8 * cc + g] = gt_before + min(eq_before, need);
-            plan[8 + 8 * cc + 4 + g] = eq_before;
-        }
-        gt_carry += __shfl_sync(0xffffffffu, pg, 31);
-        eq_carry += __shfl_sync(0xffffffffu, pe, 31);
-    }
-    HA_TL(kTlSelectPlan, kTlExit);
 }
 
 template <int ROUNDS>
-__global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(kSelBThreads, 8) select_kernel(const SelectParams p) {
     HA_TL(kTlSelect, kTlEntry);
     const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
     constexpr int chunk_tokens = ROUNDS * kRoundTokens;
-    constexpr int kWarpTokens = ROUNDS * kLaneTokens * 32;  // 128 ROUNDS contiguous tokens per warp
-    __shared__ int s_T[kGroup], s_need[kGroup], s_base[kGroup], s_eqb[kGroup];
-    __shared__ uint32_t s_wg[kSelWarps][2], s_we[kSelWarps][2];  // per warp: counts of heads (0,1) / (2,3), 16 bits each
+    constexpr int kWarpTokens = chunk_tokens / kSelBWarps;  // 256 ROUNDS
+    constexpr int kLoads = kWarpTokens / 128;                // 2 ROUNDS 16-byte loads per lane
+    constexpr int kWords = ROUNDS;                           // flag words: 8 tokens x 4 heads each
+    __shared__ int s_plan[16];  // T[4], need[4], base[4], eqb[4]
+    __shared__ uint32_t s_wg[kSelBWarps][2], s_we[kSelBWarps][2];  // per warp: counts of heads (0,1) / (2,3), 16 bits each
 
+    // --- before the dependency wait: the sequence length, the page ids of this warp's tokens
+    //     (ROUNDS pages) and its packed scores
     const int S = p.seq_lens[b];
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
     const int chunk_start = c * chunk_tokens;
     const bool active = s_ok && chunk_start < S;
-    // --- before the dependency wait: this chunk's packed scores, 4 consecutive tokens per 16-byte load
-    //     (token wbase + 128 j + 4 lane + k is component k of load j). They were written by
-    //     score_hist, two kernels ahead in the stream: select_plan, the kernel directly in front,
-    //     could only start its wait-release after score_hist had completed, and this kernel's CTAs
-    //     start after that. Pass A wrote whole rounds of 1024 tokens up to the one containing S - 1.
     const int wbase = chunk_start + warp * kWarpTokens;
-    uint4 sc[ROUNDS];
-    int pg0 = 0, pg1 = 0;  // the (at most two) pages this warp's tokens lie in
-    if (active) {
-        const uint32_t* srow = p.scores + ((size_t)b * p.Hkv + kvh) * ((size_t)p.nchunks * chunk_tokens);
-        const int written_end = (S + kRoundTokens - 1) / kRoundTokens * kRoundTokens;
-#pragma unroll
-        for (int j = 0; j < ROUNDS; ++j) {
-            const int t = wbase + j * 128 + lane * kLaneTokens;
-            sc[j] = t < written_end ? __ldcg(reinterpret_cast<const uint4*>(srow + t)) : make_uint4(0u, 0u, 0u, 0u);
-        }
+    int pg[ROUNDS];
+    {
         const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
-        const int pi = wbase / kPage;
-        pg0 = __ldg(pt + min(pi, p.max_pages - 1));
-        pg1 = ROUNDS == 4 ? __ldg(pt + min(pi + 1, p.max_pages - 1)) : pg0;
-        pg0 = pg0 >= 0 && pg0 < p.num_pages ? pg0 : 0;  // tokens of a bad page are no candidates: never emitted
-        pg1 = pg1 >= 0 && pg1 < p.num_pages ? pg1 : 0;
+#pragma unroll
+        for (int i = 0; i < ROUNDS; ++i) {
+            const int v = __ldg(pt + min(wbase / kPage + i, p.max_pages - 1));
+            pg[i] = v >= 0 && v < p.num_pages ? v : 0;  // tokens of a bad page are no candidates: never emitted
+        }
+    }
+
+    // this warp's packed scores. They were written by score_hist, two kernels ahead in the stream:
+    // select_plan, the kernel directly in front, could only pass its dependency wait after score_hist
+    // had completed, and this kernel's CTAs start after that. Pass A wrote whole rounds of 1024
+    // tokens up to the one that contains S - 1.
+    uint4 sc[kLoads];
+    {
+        const uint32_t* srow = p.scores + ((size_t)b * p.Hkv + kvh) * ((size_t)p.nchunks * chunk_tokens);
+        const int written_end = s_ok ? (S + kRoundTokens - 1) / kRoundTokens * kRoundTokens : 0;
+        // loaded whatever S is (always inside the buffer), so that the loads do not wait for seq_lens
+#pragma unroll
+        for (int j = 0; j < kLoads; ++j) sc[j] = __ldcg(reinterpret_cast<const uint4*>(srow + wbase + j * 128 + lane * 4));
+#pragma unroll
+        for (int j = 0; j < kLoads; ++j)
+            if (wbase + j * 128 + lane * 4 >= written_end) sc[j] = make_uint4(0u, 0u, 0u, 0u);  // stale words of an earlier call
     }
 
     pdl_wait();
@@ -349,54 +403,49 @@ __global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectPara
     pdl_launch_dependents();
     if (!active) return;
 
-    // --- the plan of this (sequence, kv-head), written by select_plan_kernel: thresholds, tie quotas,
-    //     and for this chunk where its output starts and how many tied tokens precede it
+    // --- the plan of this (sequence, kv-head): thresholds, tie quotas, and for this chunk where its
+    //     output starts and how many tied tokens precede it
     if (tid < 16) {
         const int32_t* plan = p.plan + ((size_t)b * p.Hkv + kvh) * (8 + 8 * p.nchunks);
-        const int v = __ldcg(plan + (tid < 8 ? tid : 8 + 8 * c + (tid - 8)));
-        if (tid < 4) s_T[tid] = v;
-        else if (tid < 8) s_need[tid - 4] = v;
-        else if (tid < 12) s_base[tid - 8] = v;
-        else s_eqb[tid - 12] = v;
+        s_plan[tid] = __ldcg(plan + (tid < 8 ? tid : 8 + 8 * c + (tid - 8)));
     }
     __syncthreads();
     HA_TL(kTlSelect, kTlMarkB);
+    const int* s_T = s_plan;
+    const int* s_need = s_plan + 4;
+    const int* s_base = s_plan + 8;
+    const int* s_eqb = s_plan + 12;
 
-    // --- classify once: per token and head (score > T) and (score == T), kept as bit sets of this
-    //     lane: bit ((j & 1) * 4 + k) * 4 + g of word j / 2. Stored bytes are score + 1 (0 for a token
-    //     that is no candidate), so they are compared with T + 1 >= 1 and non-candidates never match.
-    //     Everything after this works on the bit sets (counts are popcounts under a per-head mask).
-    constexpr int kWords = (ROUNDS + 1) / 2;
+    // --- classify: stored bytes are score + 1 (0 for a token that is no candidate) and are compared
+    //     with T + 1 >= 1, so non-candidates never match. a + (127 - T') carries into bit 7 of a byte
+    //     iff a > T', a + (128 - T') iff a >= T' (bytes <= 33: no carry between bytes). Flag words: bit
+    //     8 g + (n & 7) of word n / 8 for token n of this lane and head g.
     const uint32_t t4 = ((uint32_t)s_T[0] | ((uint32_t)s_T[1] << 8) | ((uint32_t)s_T[2] << 16) | ((uint32_t)s_T[3] << 24)) + 0x01010101u;
-    const uint32_t gt_add = 0x7F7F7F7Fu - t4;
-    uint32_t gtb[kWords], eqb[kWords];
+    const uint32_t gt_add = 0x7F7F7F7Fu - t4, ge_add = 0x80808080u - t4;
+    uint32_t gtw[kWords], gew[kWords];
 #pragma unroll
-    for (int i = 0; i < kWords; ++i) gtb[i] = eqb[i] = 0;
+    for (int i = 0; i < kWords; ++i) gtw[i] = gew[i] = 0;
 #pragma unroll
-    for (int j = 0; j < ROUNDS; ++j) {
-        const uint32_t a[kLaneTokens] = {sc[j].x, sc[j].y, sc[j].z, sc[j].w};
+    for (int j = 0; j < kLoads; ++j) {
+        const uint32_t a[4] = {sc[j].x, sc[j].y, sc[j].z, sc[j].w};
 #pragma unroll
-        for (int k = 0; k < kLaneTokens; ++k) {
-            const int sh = ((j & 1) * kLaneTokens + k) * 4;
-            gtb[j >> 1] |= flags_to_nibble(bytes_gt(a[k], gt_add)) << sh;
-            eqb[j >> 1] |= flags_to_nibble(bytes_eq(a[k], t4)) << sh;
+        for (int k = 0; k < 4; ++k) {
+            const int pos = (j & 1) * 4 + k;
+            gtw[j >> 1] |= ((a[k] + gt_add) >> (7 - pos)) & (0x01010101u << pos);
+            gew[j >> 1] |= ((a[k] + ge_add) >> (7 - pos)) & (0x01010101u << pos);
         }
     }
-    // per-head popcounts of a bit set, as two words of 16-bit fields: heads (0,1) and (2,3)
-    auto head_counts = [&](const uint32_t (&w)[kWords], uint32_t& c01, uint32_t& c23) {
-        uint32_t cnt[kGroup] = {0, 0, 0, 0};
+    // per head: bit n = token n of this lane
+    uint32_t gt[kGroup], eq[kGroup];
 #pragma unroll
-        for (int i = 0; i < kWords; ++i)
-#pragma unroll
-            for (int g = 0; g < kGroup; ++g) cnt[g] += __popc(w[i] & (0x11111111u << g));
-        c01 = cnt[0] | (cnt[1] << 16);
-        c23 = cnt[2] | (cnt[3] << 16);
-    };
+    for (int g = 0; g < kGroup; ++g) {
+        gt[g] = gather_byte<kWords>(gtw, g);
+        eq[g] = gather_byte<kWords>(gew, g) & ~gt[g];
+    }
     {
-        uint32_t g01, g23, e01, e23;
-        head_counts(gtb, g01, g23);
-        head_counts(eqb, e01, e23);
-        g01 = __reduce_add_sync(0xffffffffu, g01);  // a warp holds up to 512 tokens: 16-bit fields do not overflow
+        uint32_t g01 = __popc(gt[0]) | (__popc(gt[1]) << 16), g23 = __popc(gt[2]) | (__popc(gt[3]) << 16);
+        uint32_t e01 = __popc(eq[0]) | (__popc(eq[1]) << 16), e23 = __popc(eq[2]) | (__popc(eq[3]) << 16);
+        g01 = __reduce_add_sync(0xffffffffu, g01);  // a warp holds up to 1024 tokens: 16-bit fields do not overflow
         g23 = __reduce_add_sync(0xffffffffu, g23);
         e01 = __reduce_add_sync(0xffffffffu, e01);
         e23 = __reduce_add_sync(0xffffffffu, e23);
@@ -414,9 +463,12 @@ __global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectPara
     {
         const int g = lane & 3;
         int gt_b = 0, eq_b = 0;
-        for (int w = 0; w < warp; ++w) {
-            gt_b += (int)((s_wg[w][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
-            eq_b += (int)((s_we[w][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
+#pragma unroll
+        for (int w = 0; w < kSelBWarps - 1; ++w) {
+            const int cg = (int)((s_wg[w][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
+            const int ce = (int)((s_we[w][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
+            gt_b += w < warp ? cg : 0;
+            eq_b += w < warp ? ce : 0;
         }
         const int eq_in = (int)((s_we[warp][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
         const int need = s_need[g];
@@ -426,82 +478,77 @@ __global__ void __launch_bounds__(kSelThreads, 4) select_kernel(const SelectPara
     }
     if ((s_wg[warp][0] | s_wg[warp][1] | s_we[warp][0] | s_we[warp][1]) == 0) return;  // nothing of any head here
 
+    // --- per head: the selected tokens of this lane, their positions from a packed warp scan, emission
+    uint32_t sel[kGroup];
+    uint32_t cnt01 = 0, cnt23 = 0;
     int base_pos[kGroup];
-    uint32_t full_bits = 0, straddle = 0;  // full_bits: the heads whose tied tokens are all taken, as a per-nibble mask
 #pragma unroll
     for (int g = 0; g < kGroup; ++g) {
         base_pos[g] = __shfl_sync(0xffffffffu, my_base, g);
         const int mode = __shfl_sync(0xffffffffu, my_mode, g);
-        full_bits |= mode == 1 ? (0x11111111u << g) : 0u;
-        straddle |= (mode == 2 ? 1u : 0u) << g;
-    }
-    uint32_t bits[kWords];  // selected (token, head) pairs of this lane
-#pragma unroll
-    for (int i = 0; i < kWords; ++i) bits[i] = gtb[i] | (eqb[i] & full_bits);
-    if (straddle != 0) {  // warp-uniform, at most once per (sequence, head): rank ties by token index
-        const uint32_t lt_mask = (1u << lane) - 1u;
-#pragma unroll
-        for (int g = 0; g < kGroup; ++g) {
-            if (!((straddle >> g) & 1u)) continue;
+        sel[g] = gt[g] | (mode == 1 ? eq[g] : 0u);
+        if (mode == 2) {  // warp-uniform, at most once per (sequence, head): rank the tied tokens by token index
+            const uint32_t lt_mask = (1u << lane) - 1u;
             int eq_run = __shfl_sync(0xffffffffu, my_eqb, g);
+            const int need = s_need[g];
 #pragma unroll
-            for (int j = 0; j < ROUNDS; ++j) {
-                // token order inside a load block is (lane, k): ties in lower lanes come first
+            for (int j = 0; j < kLoads; ++j) {
+                // token order inside a block of 128 tokens is (lane, k): ties in lower lanes come first
+                const uint32_t nib = (eq[g] >> (4 * j)) & 0xFu;
                 int before = 0, total = 0;
 #pragma unroll
-                for (int k = 0; k < kLaneTokens; ++k) {
-                    const bool eq = (eqb[j >> 1] >> (((j & 1) * kLaneTokens + k) * 4 + g)) & 1u;
-                    const uint32_t m_eq = __ballot_sync(0xffffffffu, eq);
+                for (int k = 0; k < 4; ++k) {
+                    const uint32_t m_eq = __ballot_sync(0xffffffffu, (nib >> k) & 1u);
                     before += __popc(m_eq & lt_mask);
                     total += __popc(m_eq);
                 }
                 int own = 0;
 #pragma unroll
-                for (int k = 0; k < kLaneTokens; ++k) {
-                    const int bit = ((j & 1) * kLaneTokens + k) * 4 + g;
-                    if ((eqb[j >> 1] >> bit) & 1u) {
-                        if (eq_run + before + own < s_need[g]) bits[j >> 1] |= 1u << bit;
+                for (int k = 0; k < 4; ++k)
+                    if ((nib >> k) & 1u) {
+                        if (eq_run + before + own < need) sel[g] |= 1u << (4 * j + k);
                         ++own;
                     }
-                }
                 eq_run += total;
             }
         }
+        if (g < 2) cnt01 |= __popc(sel[g]) << (16 * g);
+        else cnt23 |= __popc(sel[g]) << (16 * (g - 2));
     }
-    // exclusive prefix over lanes of the per-head counts
-    uint32_t ex01, ex23;
-    head_counts(bits, ex01, ex23);
-    {
-        const uint32_t own01 = ex01, own23 = ex23;
+    uint32_t ex01 = cnt01, ex23 = cnt23;  // exclusive prefix over lanes of the per-head counts
 #pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const uint32_t u0 = __shfl_up_sync(0xffffffffu, ex01, d), u1 = __shfl_up_sync(0xffffffffu, ex23, d);
-            if (lane >= d) {
-                ex01 += u0;
-                ex23 += u1;
-            }
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t u0 = __shfl_up_sync(0xffffffffu, ex01, d), u1 = __shfl_up_sync(0xffffffffu, ex23, d);
+        if (lane >= d) {
+            ex01 += u0;
+            ex23 += u1;
         }
-        ex01 -= own01;
-        ex23 -= own23;
     }
-    int pos[kGroup] = {base_pos[0] + (int)(ex01 & 0xffffu), base_pos[1] + (int)(ex01 >> 16),
-                       base_pos[2] + (int)(ex23 & 0xffffu), base_pos[3] + (int)(ex23 >> 16)};
-    // --- emission: order inside a warp's piece is lane-major; a lane visits only its selected pairs
+    ex01 -= cnt01;
+    ex23 -= cnt23;
+    const int pos0[kGroup] = {base_pos[0] + (int)(ex01 & 0xffffu), base_pos[1] + (int)(ex01 >> 16),
+                              base_pos[2] + (int)(ex23 & 0xffffu), base_pos[3] + (int)(ex23 >> 16)};
+    // order inside a warp's piece of a head's list is lane-major; a lane visits only its selected tokens
+    const int tok0 = wbase + lane * 4;          // token n of this lane = tok0 + 128 (n / 4) + n % 4
+    const int slot0 = (lane * 4) & (kPage - 1);  // wbase is page aligned
 #pragma unroll
-    for (int half = 0; half < kWords; ++half) {
-        uint32_t m = bits[half];
+    for (int g = 0; g < kGroup; ++g) {
+        uint32_t m = sel[g];
+        int o = pos0[g];
+        int32_t* idx = p.sel_idx + ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride;
+        int32_t* rows = p.sel_rows + ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride;
         while (m != 0) {
-            const int i = __ffs(m) - 1;
+            const int n = __ffs(m) - 1;
             m &= m - 1;
-            const int g = i & 3, k = (i >> 2) & (kLaneTokens - 1), j = half * 2 + (i >> 4);
-            const int t = wbase + j * 128 + lane * kLaneTokens + k;
-            const int pg = (ROUNDS == 4 && j >= 2) ? pg1 : pg0;
-            const int o = g == 0 ? pos[0]++ : (g == 1 ? pos[1]++ : (g == 2 ? pos[2]++ : pos[3]++));
+            const int off = (n >> 2) * 128 + (n & 3);  // offset inside the warp's tokens, minus 4 lane
+            int page = pg[0];
+#pragma unroll
+            for (int i = 1; i < ROUNDS; ++i) page = (n >> 3) == i ? pg[i] : page;
             if (o < p.sel_stride) {
-                const size_t dst = ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride + o;
-                p.sel_idx[dst] = t;
-                p.sel_rows[dst] = pg * kPage + t % kPage;
+                idx[o] = tok0 + off;
+                rows[o] = page * kPage + ((slot0 + off) & (kPage - 1));
             }
+            ++o;
         }
     }
     HA_TL(kTlSelect, kTlExit);

@@ -12,7 +12,7 @@
 What runs where
   * q_len == 1 (decode): q/k/v projections, RoPE and o_proj stay torch ops; the hash encode of
     the new query and key, the cache append, Hamming scoring, budget selection and the sparse
-    attention are one call into the CUDA library (ops.SparseDecodeContext.decode_step).
+    attention are one call into the CUDA library (the registered operator torch.ops.hashattn.decode_step).
   * q_len > 128 (prefill): the original attention forward runs, as in the reference (:529-550);
     afterwards the layer's keys / values are copied into this module's paged cache and the key
     hashes are built once by the CUDA library. (The reference keeps no key hashes and re-encodes
@@ -30,6 +30,7 @@ from torch import nn
 
 from .cache import PAGE, PagedHashKVCache
 from .ops import Budget, SparseDecodeContext
+from .torch_ops import decode_step_op
 from .usa import USA
 
 __all__ = ["USA", "LlamaAttention_heavy_hitter", "load_usa", "convert_usa", "reset_usa", "set_eval_usa_mode"]
@@ -164,8 +165,8 @@ class LlamaAttention_heavy_hitter(nn.Module):
 
         ctx = self._context(bsz, hidden_states.device)
         ctx.cache.seq_lens += 1
-        out = ctx.decode_step(q[:, :, 0].to(torch.bfloat16).contiguous(), k[:, :, 0].to(torch.bfloat16).contiguous(),
-                              v[:, :, 0].to(torch.bfloat16).contiguous())
+        out = decode_step_op(ctx, q[:, :, 0].to(torch.bfloat16).contiguous(),
+                             k[:, :, 0].to(torch.bfloat16).contiguous(), v[:, :, 0].to(torch.bfloat16).contiguous())
         attn_output = self.o_proj(out.reshape(bsz, 1, self.hidden_size).to(hidden_states.dtype))
         if new_style:
             return attn_output, None

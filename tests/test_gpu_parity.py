@@ -348,6 +348,33 @@ def test_kv_head_partition_is_bit_identical(device):
                 assert torch.equal(heavy_from_device(ctx, b, h), heavy_from_device(ctx_full, b, j0 * 4 + h))
 
 
+@pytest.mark.gpu
+def test_registered_torch_operator_gives_the_library_result_eagerly_and_in_a_graph(device):
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(101, [1500, 300], 8, 2)
+    budget = ha.Budget(16, 0.125, 16)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, budget, usa)
+    ctx.hash_prefill()
+    q = inp.q.to(device, torch.bfloat16)
+    k_new = torch.stack([inp.k[b][:, -1] for b in range(2)]).to(device, torch.bfloat16)
+    v_new = torch.stack([inp.v[b][:, -1] for b in range(2)]).to(device, torch.bfloat16)
+    want = ctx.decode_step(q, k_new, v_new).clone()
+    got = ha.decode_step_op(ctx, q, k_new, v_new)
+    assert torch.equal(got, want)
+    out = torch.zeros_like(q)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            ha.decode_step_op(ctx, q, k_new, v_new, out=out)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    ctx.check_status()
+
+
+@pytest.mark.gpu
 def test_cuda_graph_replay(device):
     usa = synthetic.make_usa(8, 128, 0, True)
     inp = synthetic.make_decode_inputs(100, [2000], 8, 2)

@@ -120,3 +120,31 @@ def test_rope_is_a_rotation():
     y = synthetic.apply_rope(x, cos, sin)
     assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), rtol=1e-5)
     assert torch.equal(y[:, 0], x[:, 0])
+
+
+def test_decode_step_is_a_registered_torch_operator_without_a_cpu_kernel():
+    """torch.ops.hashattn.decode_step: schema declares what it mutates, the fake implementation runs
+    on meta tensors (what a tracer sees), and CPU tensors are refused - there is no CPU fallback."""
+    import hashattention_b200  # noqa: F401  (registers the operator)
+    op = torch.ops.hashattn.decode_step.default
+    schema = str(op._schema)
+    for name in ("k_pages", "v_pages", "hash_pages", "q_codes", "sel_idx", "sel_cnt", "workspace", "status", "out"):
+        assert f"Tensor(a" in schema and f") {name}" in schema, name
+    for name in ("q", "k_new", "page_table", "seq_lens", "wq"):
+        assert f"Tensor {name}" in schema, name
+
+    def args(device):
+        bf = dict(dtype=torch.bfloat16, device=device)
+        i32 = dict(dtype=torch.int32, device=device)
+        return (torch.empty(1, 8, 128, **bf), torch.empty(1, 2, 128, **bf), torch.empty(1, 2, 128, **bf),
+                torch.empty(4, 2, 256, 128, **bf), torch.empty(4, 2, 256, 128, **bf), torch.empty(4, 2, 256, 4, **i32),
+                torch.zeros(1, 4, **i32), torch.ones(1, **i32),
+                torch.empty(8, 36864, **bf), torch.empty(8, 288, dtype=torch.float32, device=device),
+                torch.empty(8, 36864, **bf), torch.empty(8, 288, dtype=torch.float32, device=device),
+                torch.empty(1, 8, **i32), torch.empty(1, 8, 64, **i32), torch.empty(1, 8, **i32),
+                torch.empty(1 << 20, dtype=torch.uint8, device=device), torch.zeros(1, **i32),
+                torch.empty(1, 8, 128, **bf), 16, 16, 0.125, 0.0884)
+
+    assert op(*args("meta")) is None
+    with pytest.raises(NotImplementedError):
+        op(*args("cpu"))
