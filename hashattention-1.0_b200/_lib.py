@@ -55,6 +55,7 @@ PROTOTYPES = {
     "ha_hash_prefill": (c_int, [_S, _W, _P, _P, _P, _P, _P, _P, _P]),
     "ha_score_select": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P, _P]),
     "ha_static_scratch_needed": (c_size_t, [_S]),
+    "ha_decode_step_launches": (c_int, [_S, _B]),
     "ha_score_select_static": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ha_sparse_decode": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P, c_size_t, _P, _P]),
     "ha_decode_step": (c_int, [_S, _B, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P,

@@ -1,7 +1,9 @@
 // extern "C" entry points of libhashattn.so (declared in include/hashattn.h): argument checks,
 // workspace carving and kernel launches. No allocation, no host synchronisation (except where
 // ha_decode_step_host is asked for it), no exceptions.
+#include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <mutex>
 #include <utility>
 
@@ -103,6 +105,16 @@ Workspace carve(const ha_shape_t* s, const ha_budget_t* b, void* base) {
     return w;
 }
 
+// Priority given to the kernels launched inside a PriorityScope (0 = the stream's own). Used only
+// by the staggered decode step, where the short latency-bound kernels of one half must get SM
+// slots ahead of the queued CTAs of the other half's streaming kernels.
+thread_local int t_launch_priority = 0;
+struct PriorityScope {
+    int saved;
+    explicit PriorityScope(int p) : saved(t_launch_priority) { t_launch_priority = p; }
+    ~PriorityScope() { t_launch_priority = saved; }
+};
+
 // Every kernel is launched with programmatic stream serialization (it may start while its
 // predecessor drains and synchronises itself with griddepcontrol.wait); cluster_x > 1 adds a
 // thread-block cluster along x.
@@ -114,41 +126,66 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[3];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
     cfg.numAttrs = 1;
     if (cluster_x > 1) {
-        attr[1].id = cudaLaunchAttributeClusterDimension;
-        attr[1].val.clusterDim.x = cluster_x;
-        attr[1].val.clusterDim.y = 1;
-        attr[1].val.clusterDim.z = 1;
-        cfg.numAttrs = 2;
+        attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+        attr[cfg.numAttrs].val.clusterDim.x = cluster_x;
+        attr[cfg.numAttrs].val.clusterDim.y = 1;
+        attr[cfg.numAttrs].val.clusterDim.z = 1;
+        ++cfg.numAttrs;
+    }
+    if (t_launch_priority != 0) {
+        attr[cfg.numAttrs].id = cudaLaunchAttributePriority;
+        attr[cfg.numAttrs].val.priority = t_launch_priority;
+        ++cfg.numAttrs;
     }
     cfg.attrs = attr;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-// The two-pass selection: chunk histograms and packed scores, the plan (thresholds and output
-// bases) derived from the histograms once per (sequence, kv-head), then the compaction.
-cudaError_t launch_two_pass_select(const ha_shape_t* shape, const SelectParams& p, cudaStream_t s) {
-    const dim3 grid(p.nchunks, shape->num_kv_heads, shape->batch);
-    const dim3 pgrid(shape->num_kv_heads, shape->batch);
+// The two-pass selection on the kv-heads [p.kvh0, p.kvh0 + nkvh): chunk histograms and packed
+// scores (launch_score_hist), then the plan (thresholds and output bases, derived from the
+// histograms once per (sequence, kv-head)) and the compaction (launch_plan_select).
+cudaError_t launch_score_hist(const ha_shape_t* shape, const SelectParams& p, int nkvh, cudaStream_t s) {
+    const dim3 grid(p.nchunks, nkvh, shape->batch);
+    switch (chunk_pages_for(shape->max_pages)) {
+        case 4: return launch(score_hist_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
+        case 8: return launch(score_hist_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
+        default: return launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
+    }
+}
+
+cudaError_t launch_plan_select(const ha_shape_t* shape, const SelectParams& p, int nkvh, cudaStream_t s,
+                               int priority = 0) {
+    const dim3 grid(p.nchunks, nkvh, shape->batch);
     const int chunk_pages = chunk_pages_for(shape->max_pages);
-    cudaError_t e1, e2, e3;
+    PriorityScope scope(priority);
+    const cudaError_t e = launch(select_plan_kernel, dim3(nkvh, shape->batch), dim3(kSelThreads), s, 1, p,
+                                 chunk_pages * kPage);
+    if (e != cudaSuccess) return e;
     switch (chunk_pages) {
-        case 4: e1 = launch(score_hist_kernel<1>, grid, dim3(kSelThreads), s, 1, p); break;
-        case 8: e1 = launch(score_hist_kernel<2>, grid, dim3(kSelThreads), s, 1, p); break;
-        default: e1 = launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p); break;
+        case 4: return launch(select_kernel<1>, grid, dim3(kSelBThreads), s, 1, p);
+        case 8: return launch(select_kernel<2>, grid, dim3(kSelBThreads), s, 1, p);
+        default: return launch(select_kernel<4>, grid, dim3(kSelBThreads), s, 1, p);
     }
-    e2 = launch(select_plan_kernel, pgrid, dim3(kSelThreads), s, 1, p, chunk_pages * kPage);
-    switch (chunk_pages) {
-        case 4: e3 = launch(select_kernel<1>, grid, dim3(kSelBThreads), s, 1, p); break;
-        case 8: e3 = launch(select_kernel<2>, grid, dim3(kSelBThreads), s, 1, p); break;
-        default: e3 = launch(select_kernel<4>, grid, dim3(kSelBThreads), s, 1, p); break;
-    }
-    if (e1 != cudaSuccess) return e1;
-    return e2 != cudaSuccess ? e2 : e3;
+}
+
+cudaError_t launch_two_pass_select(const ha_shape_t* shape, const SelectParams& p, int nkvh, cudaStream_t s) {
+    const cudaError_t e = launch_score_hist(shape, p, nkvh, s);
+    return e != cudaSuccess ? e : launch_plan_select(shape, p, nkvh, s);
+}
+
+// One cluster kernel scores and selects in a single pass when the sequences are short and the
+// (sequence, kv-head) units few: all clusters resident at once, at most two rounds each (measured
+// 6.7 us against 8.5 us at B=1, S=32K). Longer or more numerous sequences are bandwidth- rather
+// than latency-bound and run faster as the two-pass pair (45 us against 62 us at B=4, S=128K).
+bool use_cluster_select(const ha_shape_t* shape) {
+    const long long max_tokens = (long long)shape->max_pages * kPage;
+    const long long units = (long long)shape->batch * shape->num_kv_heads;
+    return max_tokens <= 2LL * kClRoundTokens && units * kClCtas <= 148;
 }
 
 }  // namespace
@@ -157,13 +194,43 @@ cudaError_t launch_two_pass_select(const ha_shape_t* shape, const SelectParams& 
 namespace ha {
 namespace {
 
+SelectParams select_params(const ha_shape_t* shape, const ha_budget_t* budget, const uint32_t* q_codes,
+                           const uint32_t* hash_pages, const int32_t* page_table, const int32_t* seq_lens,
+                           int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg, int32_t* status,
+                           uint32_t* hist, int32_t* plan, uint32_t* scores, int32_t* sel_rows) {
+    SelectParams p;
+    p.q_codes = q_codes;
+    p.hash_pages = reinterpret_cast<const uint4*>(hash_pages);
+    p.page_table = page_table;
+    p.seq_lens = seq_lens;
+    p.hist = hist;
+    p.plan = plan;
+    p.scores = scores;
+    p.sel_idx = sel_idx;
+    p.sel_rows = sel_rows;
+    p.sel_cnt = sel_cnt;
+    p.scores_dbg = scores_dbg;
+    p.status = status;
+    p.B = shape->batch;
+    p.Hkv = shape->num_kv_heads;
+    p.max_pages = shape->max_pages;
+    p.num_pages = shape->num_pages;
+    p.sel_stride = shape->sel_stride;
+    p.nchunks = num_chunks_for(shape->max_pages);
+    p.kvh0 = 0;
+    p.init_budget = budget->init_budget;
+    p.recent_budget = budget->recent_budget;
+    p.heavy_budget = budget->heavy_budget;
+    return p;
+}
+
 // sel == nullptr with physical == true: use the physical rows select_kernel left in the workspace.
 int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                        const void* q, const void* k_pages, const void* v_pages,
                        const int32_t* page_table, const int32_t* seq_lens,
                        const int32_t* sel, bool physical, float sm_scale,
                        void* out, void* workspace, size_t workspace_bytes,
-                       int32_t* status, void* stream) {
+                       int32_t* status, void* stream, int kvh0 = 0, int nkvh = -1, int merge_priority = 0) {
     int rc = check_shape(shape);
     if (rc != HA_OK) return rc;
     rc = check_budget(budget);
@@ -171,6 +238,7 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     if (q == nullptr || k_pages == nullptr || v_pages == nullptr || page_table == nullptr ||
         seq_lens == nullptr || out == nullptr || status == nullptr || !std::isfinite(sm_scale))
         return HA_ERR_BAD_ARG;
+    const int nheads = (nkvh < 0 ? shape->num_kv_heads : nkvh) * kGroup;  // heads [4 kvh0, 4 kvh0 + nheads)
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
     const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
@@ -197,13 +265,130 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     p.partials = w.partials;
     p.nsplits = split.nsplits;
     p.rounds = split.rounds;
-    const dim3 grid(split.nsplits, shape->num_kv_heads * kGroup, shape->batch);
+    p.h0 = kvh0 * kGroup;
+    const dim3 grid(split.nsplits, nheads, shape->batch);
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e = physical ? launch(sparse_gather_kernel<true>, grid, dim3(kAttThreads), s, 1, p)
                              : launch(sparse_gather_kernel<false>, grid, dim3(kAttThreads), s, 1, p);
-    if (e == cudaSuccess && split.nsplits > 1)
-        e = launch(sparse_merge_kernel, dim3(shape->num_kv_heads * kGroup, shape->batch), dim3(kHeadDim), s, 1, p);
+    if (e == cudaSuccess && split.nsplits > 1) {
+        PriorityScope light(merge_priority);
+        e = launch(sparse_merge_kernel, dim3(nheads, shape->batch), dim3(kHeadDim), s, 1, p);
+    }
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+}
+
+}  // namespace
+}  // namespace ha
+
+// ------------------------------------------------------------------------------------------
+// Staggered decode step. Between the histogram pass and the gather of one set of kv-heads lie
+// the plan and the compaction, short kernels that leave HBM idle. For large problems the step is
+// therefore run as two halves of the kv-heads, the second one a histogram pass behind the
+// first, so that one half's short kernels overlap the other half's streaming kernels. The second
+// half runs on a stream that belongs to the library (one per device, created at the first such
+// call) and is forked from / joined to the caller's stream with events, which also works under
+// stream capture. Every (sequence, kv-head) is independent, so the result is bit-identical.
+// ------------------------------------------------------------------------------------------
+namespace ha {
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+constexpr int kMaxParts = 4;
+
+struct StaggerResources {
+    cudaStream_t aux[kMaxParts - 1] = {};           // parts 1.. run here; part 0 on the caller's stream
+    cudaEvent_t fork[kMaxParts - 1] = {}, join[kMaxParts - 1] = {};
+    int light_priority = 0;  // for the short kernels: the most urgent priority the device offers
+    bool ready = false;
+};
+std::mutex g_stagger_mutex;  // held while a staggered step is enqueued: the events are shared
+StaggerResources g_stagger[kMaxDevices];
+
+// Environment override HA_STAGGER: "0" never, "1" whenever the two-pass selection runs on at
+// least two kv-heads; otherwise only when the hash pages of the step exceed 32 MB.
+bool use_stagger(const ha_shape_t* shape) {
+    if (use_cluster_select(shape) || shape->num_kv_heads < 2) return false;
+    const char* env = std::getenv("HA_STAGGER");
+    if (env != nullptr && env[0] == '0') return false;
+    if (env != nullptr && env[0] == '1') return true;
+    const long long hash_bytes = (long long)shape->batch * shape->num_kv_heads * shape->max_pages * kPage * 16;
+    return hash_bytes >= (32LL << 20);
+}
+
+// Two parts measured best (B=4, S=128K: 82.9 us per step against 83.8 with three and 91.5 with four
+// parts, 88.2 without staggering); HA_STAGGER_PARTS is an experiment knob.
+int stagger_parts(const ha_shape_t* shape) {
+    int parts = 2;
+    if (const char* env = std::getenv("HA_STAGGER_PARTS")) parts = std::atoi(env);
+    return std::max(2, std::min(parts, std::min(kMaxParts, shape->num_kv_heads)));
+}
+
+// Caller holds g_stagger_mutex.
+StaggerResources* stagger_resources() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    StaggerResources& r = g_stagger[dev];
+    if (!r.ready) {
+        int least = 0, greatest = 0;
+        if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return nullptr;
+        for (int i = 0; i < kMaxParts - 1; ++i)
+            if (cudaStreamCreateWithFlags(&r.aux[i], cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&r.fork[i], cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&r.join[i], cudaEventDisableTiming) != cudaSuccess)
+                return nullptr;
+        r.light_priority = greatest;
+        r.ready = true;
+    }
+    return &r;
+}
+
+int staggered_select_attend(const ha_shape_t* shape, const ha_budget_t* budget, const void* q,
+                            const void* k_pages, const void* v_pages, const uint32_t* hash_pages,
+                            const int32_t* page_table, const int32_t* seq_lens, const uint32_t* q_codes,
+                            int32_t* sel_idx, int32_t* sel_cnt, float sm_scale, void* out, void* workspace,
+                            size_t workspace_bytes, int32_t* status, cudaStream_t s) {
+    int rc = check_budget(budget);
+    if (rc != HA_OK) return rc;
+    if (q_codes == nullptr || hash_pages == nullptr || page_table == nullptr || seq_lens == nullptr ||
+        sel_idx == nullptr || sel_cnt == nullptr || status == nullptr)
+        return HA_ERR_BAD_ARG;
+    if (workspace == nullptr) return HA_ERR_WORKSPACE;
+    const Workspace w = carve(shape, budget, workspace);
+    if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
+    const int parts = stagger_parts(shape);
+    const SelectParams base = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx,
+                                            sel_cnt, nullptr, status, w.hist, w.plan, w.scores, w.sel_rows);
+
+    std::lock_guard<std::mutex> lock(g_stagger_mutex);
+    StaggerResources* r = stagger_resources();
+    if (r == nullptr) return HA_ERR_LAUNCH;
+    const int light = r->light_priority;
+    // Part i covers kv-heads [first, first + n) (the larger parts first) on stream i (0 = the caller's) and
+    // starts when the histogram pass of part i - 1 is done.
+    bool ok = true;
+    int first = 0;
+    for (int i = 0; i < parts; ++i) {
+        const int n = shape->num_kv_heads / parts + (i < shape->num_kv_heads % parts ? 1 : 0);
+        cudaStream_t si = i == 0 ? s : r->aux[i - 1];
+        SelectParams p = base;
+        p.kvh0 = first;
+        ok = ok && launch_score_hist(shape, p, n, si) == cudaSuccess;
+        if (i + 1 < parts) {  // even after a failed launch: every stream that forks is also joined below
+            if (cudaEventRecord(r->fork[i], si) != cudaSuccess ||
+                cudaStreamWaitEvent(r->aux[i], r->fork[i], 0) != cudaSuccess)
+                return HA_ERR_LAUNCH;
+        }
+        ok = ok && launch_plan_select(shape, p, n, si, light) == cudaSuccess;
+        ok = ok && sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, nullptr, true,
+                                      sm_scale, out, workspace, workspace_bytes, status, si, first, n, light) == HA_OK;
+        first += n;
+    }
+    for (int i = 1; i < parts; ++i)
+        if (cudaEventRecord(r->join[i - 1], r->aux[i - 1]) != cudaSuccess ||
+            cudaStreamWaitEvent(s, r->join[i - 1], 0) != cudaSuccess)
+            return HA_ERR_LAUNCH;
+    return ok ? HA_OK : HA_ERR_LAUNCH;
 }
 
 }  // namespace
@@ -403,43 +588,18 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
     const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
 
-    SelectParams p;
-    p.q_codes = q_codes;
-    p.hash_pages = reinterpret_cast<const uint4*>(hash_pages);
-    p.page_table = page_table;
-    p.seq_lens = seq_lens;
-    p.hist = w.hist;
-    p.plan = w.plan;
-    p.scores = w.scores;
-    p.sel_idx = sel_idx;
-    p.sel_rows = w.sel_rows;
-    p.sel_cnt = sel_cnt;
-    p.scores_dbg = scores_dbg;
-    p.status = status;
-    p.B = shape->batch;
-    p.Hkv = shape->num_kv_heads;
-    p.max_pages = shape->max_pages;
-    p.num_pages = shape->num_pages;
-    p.sel_stride = shape->sel_stride;
-    p.nchunks = num_chunks_for(shape->max_pages);
-    p.init_budget = budget->init_budget;
-    p.recent_budget = budget->recent_budget;
-    p.heavy_budget = budget->heavy_budget;
+    const SelectParams p = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
+                                         scores_dbg, status, w.hist, w.plan, w.scores, w.sel_rows);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // Short sequences and few (sequence, kv-head) units - all clusters resident at once, at most two
-    // rounds each: one cluster kernel that scores and selects in a single pass (measured 6.7 us
-    // against 8.5 us at B=1, S=32K). Longer or more numerous sequences are bandwidth- rather than
-    // latency-bound and run faster as the two-pass pair (45 us against 62 us at B=4, S=128K).
     const long long max_tokens = (long long)shape->max_pages * kPage;
-    const long long units = (long long)shape->batch * shape->num_kv_heads;
-    if (max_tokens <= 2LL * kClRoundTokens && units * kClCtas <= 148) {
+    if (use_cluster_select(shape)) {
         const dim3 cgrid(kClCtas, shape->num_kv_heads, shape->batch);
         const cudaError_t e = max_tokens <= kClRoundTokens
             ? launch(score_select_cluster_kernel<1>, cgrid, dim3(kClThreads), s, kClCtas, p)
             : launch(score_select_cluster_kernel<2>, cgrid, dim3(kClThreads), s, kClCtas, p);
         return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
     }
-    return launch_two_pass_select(shape, p, s) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    return launch_two_pass_select(shape, p, shape->num_kv_heads, s) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
 int ha_sparse_decode(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -464,12 +624,24 @@ int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
     int rc = ha_hash_decode(shape, weights, q, k_new, v_new, k_pages, v_pages, hash_pages, page_table,
                             seq_lens, q_codes, nullptr, status, stream);
     if (rc != HA_OK) return rc;
+    if (use_stagger(shape))
+        return staggered_select_attend(shape, budget, q, k_pages, v_pages, hash_pages, page_table, seq_lens, q_codes,
+                                       sel_idx, sel_cnt, sm_scale, out, workspace, workspace_bytes, status,
+                                       static_cast<cudaStream_t>(stream));
     rc = ha_score_select(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
                          nullptr, workspace, workspace_bytes, status, stream);
     if (rc != HA_OK) return rc;
     // the selection kernel left the physical rows of the heavy tokens in the workspace
     return sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, nullptr, true,
                               sm_scale, out, workspace, workspace_bytes, status, stream);
+}
+
+int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget) {
+    if (check_shape(shape) != HA_OK || check_budget(budget) != HA_OK) return 0;
+    const int merge = att_split(shape, budget).nsplits > 1 ? 1 : 0;
+    if (use_cluster_select(shape)) return 3 + merge;  // encoder, cluster selection, gather (+ merge)
+    const int parts = use_stagger(shape) ? stagger_parts(shape) : 1;
+    return 1 + parts * (4 + merge);  // encoder; per part: histograms, plan, compaction, gather (+ merge)
 }
 
 int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -526,7 +698,6 @@ namespace {
 // passed to a kernel as one.
 static __device__ __align__(256) unsigned char g_static_scratch[HA_STATIC_SCRATCH_BYTES];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_static_scratch_mutex;
 void* g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device
 
@@ -596,29 +767,9 @@ int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
 
     // Every word of hist / plan / scores / sel_rows that a kernel reads was written earlier in the same
     // call, so nothing left over from the previous call needs clearing.
-    SelectParams p;
-    p.q_codes = q_codes;
-    p.hash_pages = reinterpret_cast<const uint4*>(hash_pages);
-    p.page_table = page_table;
-    p.seq_lens = seq_lens;
-    p.hist = w.hist;
-    p.plan = w.plan;
-    p.scores = w.scores;
-    p.sel_idx = sel_idx;
-    p.sel_rows = w.sel_rows;
-    p.sel_cnt = sel_cnt;
-    p.scores_dbg = nullptr;
-    p.status = status;
-    p.B = shape->batch;
-    p.Hkv = shape->num_kv_heads;
-    p.max_pages = shape->max_pages;
-    p.num_pages = shape->num_pages;
-    p.sel_stride = shape->sel_stride;
-    p.nchunks = num_chunks_for(shape->max_pages);
-    p.init_budget = budget->init_budget;
-    p.recent_budget = budget->recent_budget;
-    p.heavy_budget = budget->heavy_budget;
-    return launch_two_pass_select(shape, p, static_cast<cudaStream_t>(stream)) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    const SelectParams p = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
+                                         nullptr, status, w.hist, w.plan, w.scores, w.sel_rows);
+    return launch_two_pass_select(shape, p, shape->num_kv_heads, static_cast<cudaStream_t>(stream)) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
 }  // extern "C"

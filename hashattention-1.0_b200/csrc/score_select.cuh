@@ -56,6 +56,7 @@ struct SelectParams {
     uint8_t* scores_dbg;       // [B][Hq][max_pages*256] or null
     int32_t* status;
     int B, Hkv, max_pages, num_pages, sel_stride, nchunks;
+    int kvh0;                  // first kv-head of this launch (a launch may cover a slice of the kv-heads)
     int init_budget, recent_budget;
     double heavy_budget;
 };
@@ -243,7 +244,7 @@ __device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kv
 __global__ void __launch_bounds__(kSelThreads) select_plan_kernel(const SelectParams p, int chunk_tokens) {
     HA_TL(kTlSelectPlan, kTlEntry);
     __shared__ uint32_t s_stage[kGroup][kBins][32];
-    const int kvh = blockIdx.x, b = blockIdx.y;
+    const int kvh = p.kvh0 + blockIdx.x, b = blockIdx.y;
     const int S = p.seq_lens[b];
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
     const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
@@ -258,7 +259,7 @@ __global__ void __launch_bounds__(kSelThreads) select_plan_kernel(const SelectPa
 template <int ROUNDS>
 __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectParams p) {
     HA_TL(kTlScoreHist, kTlEntry);
-    const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int c = blockIdx.x, kvh = p.kvh0 + blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
     constexpr int chunk_tokens = ROUNDS * kRoundTokens;
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     pdl_launch_dependents();
 
     if (!s_ok) {
-        if (tid == 0 && c == 0 && kvh == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+        if (tid == 0 && c == 0 && blockIdx.y == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
         return;
     }
     if (!active) return;
@@ -355,7 +356,7 @@ __device__ __forceinline__ uint32_t gather_byte(const uint32_t (&a)[NW], int g) 
 template <int ROUNDS>
 __global__ void __launch_bounds__(kSelBThreads, 8) select_kernel(const SelectParams p) {
     HA_TL(kTlSelect, kTlEntry);
-    const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int c = blockIdx.x, kvh = p.kvh0 + blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
     constexpr int chunk_tokens = ROUNDS * kRoundTokens;
@@ -575,7 +576,7 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
     HA_TL(kTlScoreHist, kTlEntry);
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
-    const int kvh = blockIdx.y, b = blockIdx.z;
+    const int kvh = p.kvh0 + blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
     constexpr int kHist = kGroup * kBins;  // 132
@@ -599,7 +600,7 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
     pdl_wait();
     HA_TL(kTlScoreHist, kTlAfterWait);
     pdl_launch_dependents();
-    if (!s_ok && tid == 0 && rank == 0 && kvh == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+    if (!s_ok && tid == 0 && rank == 0 && blockIdx.y == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
 
     // --- scores of this thread's tokens (packed, byte g = head g) and the CTA's histograms ---------
     uint32_t sc[ROUNDS][kLaneTokens];

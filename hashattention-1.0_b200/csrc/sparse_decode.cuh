@@ -36,6 +36,7 @@ struct SparseDecodeParams {
     float* partials;               // workspace: [B][Hq][nsplits][130]
     int32_t* status;
     int B, Hkv, max_pages, num_pages, sel_stride, nsplits, rounds;
+    int h0;                        // first query head of this launch (a launch may cover a slice of the heads)
     int init_budget, recent_budget;
     double heavy_budget;
     float scale_log2e;             // sm_scale * log2(e)
@@ -93,7 +94,7 @@ __device__ __forceinline__ AttPlan att_plan(const SparseDecodeParams& p, int b) 
 template <bool kPhysical>
 __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const SparseDecodeParams p) {
     HA_TL(kTlGather, kTlEntry);
-    const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int split = blockIdx.x, h = p.h0 + blockIdx.y, b = blockIdx.z;
     const int Hq = p.Hkv * kGroup, kvh = h / kGroup;
     const int tid = threadIdx.x;
     const int worker = tid >> 4, sl = tid & 15, warp = tid >> 5;
@@ -285,7 +286,7 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
 // results are combined in shared memory.
 __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDecodeParams p) {
     HA_TL(kTlMerge, kTlEntry);
-    const int h = blockIdx.x, b = blockIdx.y;
+    const int h = p.h0 + blockIdx.x, b = blockIdx.y;
     const int Hq = p.Hkv * kGroup;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int kWarps = kHeadDim / 32;

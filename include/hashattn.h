@@ -190,6 +190,11 @@ int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
                    void* out, void* workspace, size_t workspace_bytes,
                    int32_t* status, void* stream);
 
+/* Number of kernels one ha_decode_step call enqueues for this shape and budget (the library picks
+ * between a single-pass and a two-pass selection, and may run large steps as two staggered halves
+ * of the kv-heads); 0 for an invalid shape. For launch accounting; no reference counterpart.     */
+int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget);
+
 /* ha_decode_step for a caller whose per-step tensors live in HOST memory.
  * q_host, k_new_host, v_new_host (inputs) and out_host (result) are HOST pointers, ideally
  * pinned; q_dev, k_new_dev, v_new_dev, out_dev are device staging buffers of the same sizes.

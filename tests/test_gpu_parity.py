@@ -243,6 +243,44 @@ def test_many_units_take_the_two_pass_selection(device):
     run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(32, 1.0 / 8, 32), shuffle_seed=9)
 
 
+@pytest.mark.parametrize("Hkv", [4, 3])
+def test_staggered_step_is_bit_identical_to_the_plain_step(device, monkeypatch, Hkv):
+    """HA_STAGGER=1 runs the step as two halves of the kv-heads on two streams (what large problems
+    do by default); every (sequence, kv-head) is independent, so nothing may change - eagerly and
+    when the step is captured into a CUDA graph. Hkv = 3 splits unevenly (1 + 2)."""
+    Hq = 4 * Hkv
+    lens = [300, 1025, 64, 2000, 513, 777, 1300, 256, 900, 1500]
+    usa = synthetic.make_usa(Hq, 128, 3, True)
+    inp = synthetic.make_decode_inputs(103, lens, Hq, Hkv)
+    budget = ha.Budget(32, 1.0 / 8, 32)
+    monkeypatch.setenv("HA_STAGGER", "0")
+    _, out0, ctx0, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
+    monkeypatch.setenv("HA_STAGGER", "1")
+    _, out1, ctx1, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
+    assert torch.equal(out0, out1)
+    assert torch.equal(ctx0.sel_cnt, ctx1.sel_cnt)
+    for b in range(len(lens)):
+        for h in range(Hq):
+            assert torch.equal(heavy_from_device(ctx0, b, h), heavy_from_device(ctx1, b, h))
+    # captured: the second stream joins the capture through the fork event and leaves it at the join
+    q = inp.q.to(device, torch.bfloat16)
+    k_new = torch.stack([k[:, -1] for k in inp.k]).to(device, torch.bfloat16)
+    v_new = torch.stack([v[:, -1] for v in inp.v]).to(device, torch.bfloat16)
+    out = torch.zeros_like(q)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            ctx1.decode_step(q, k_new, v_new, out=out)
+    for _ in range(2):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.float().cpu(), out1)
+    ctx1.check_status()
+
+
 @pytest.mark.parametrize("S", [40000, 70000])
 def test_long_sequence_selection(device, S):
     """S = 40,000 runs the cluster kernel with two rounds; S = 70,000 (chunks of 8 pages, two rounds
