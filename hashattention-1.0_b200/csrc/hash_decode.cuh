@@ -26,6 +26,8 @@ struct HashDecodeParams {
     const int32_t* seq_lens;
     uint32_t* q_codes;   // [B][Hq]
     float* preact_dbg;   // [B][2][Hq][32] or null
+    __nv_bfloat16* q_stage;  // [B][Hq][128] or null: a device copy of q for the attention kernels, written when
+                             // q itself lives in mapped host memory (read once here instead of by every gather CTA)
     int32_t* status;
     int B, Hkv, max_pages, num_pages, batch_per_cta;
 };
@@ -142,19 +144,19 @@ __device__ __forceinline__ void hidden_layer(const Row8<WT> (&w)[kRowLoads], con
     if (sub < kRowLoads) dst[warp * (2 * kRowLoads) + 2 * sub + half] = silu(mine);
 }
 
-// Evaluates the MLP on one 128-element bf16 row. Must be called by all threads of the CTA; on
+// Evaluates the MLP on one 128-element bf16 row, of which `raw` holds this lane's 8 elements
+// (load_x_row). Must be called by all threads of the CTA; on
 // return (after its last barrier) sm.out[0..32) holds the final-layer pre-activations.
 // `between` runs after the first layer (a place to issue loads whose address depends on a value
 // that was requested before the call). The caller may call mlp_eval again without a further
 // barrier: each buffer is rewritten only after barriers that every reader of the previous
 // round has passed.
 template <typename WT, typename F>
-__device__ __forceinline__ void mlp_eval(const MlpRegs<WT>& r, const __nv_bfloat16* xrow,
+__device__ __forceinline__ void mlp_eval(const MlpRegs<WT>& r, const uint4 raw,
                                          MlpSmem& sm, int warp, int lane, F&& between) {
     const int half = lane >> 4, col = (lane & 15) * 8;
     float x[8];
     {
-        const uint4 raw = *reinterpret_cast<const uint4*>(xrow + col);
         x[0] = bf16_lo(raw.x); x[1] = bf16_hi(raw.x);
         x[2] = bf16_lo(raw.y); x[3] = bf16_hi(raw.y);
         x[4] = bf16_lo(raw.z); x[5] = bf16_hi(raw.z);
@@ -172,6 +174,11 @@ __device__ __forceinline__ void mlp_eval(const MlpRegs<WT>& r, const __nv_bfloat
         if ((lane & 15) == 0) sm.out[warp * 2 + half] = s;
     }
     __syncthreads();
+}
+
+// This lane's 8 consecutive elements (columns 8 * (lane % 16) ...) of a 128-element bf16 row.
+__device__ __forceinline__ uint4 load_x_row(const __nv_bfloat16* xrow, int lane) {
+    return *reinterpret_cast<const uint4*>(xrow + (lane & 15) * 8);
 }
 
 template <typename WT>
@@ -196,14 +203,29 @@ hash_decode_kernel(const HashDecodeParams p) {
     const int b_end = min(p.B, b_begin + p.batch_per_cta);
     const int kvh = h / kGroup, g = h % kGroup;
 
+    // The input row and (key side) the sequence length of the next sequence are requested while the
+    // current one is evaluated; the page-table entry of the append slot, whose address depends on
+    // the length, is fetched underneath the MLP arithmetic.
+    auto x_row = [&](int b) {
+        return side == 0 ? p.q + ((size_t)b * Hq + h) * kHeadDim : p.k_new + ((size_t)b * p.Hkv + kvh) * kHeadDim;
+    };
+    uint4 raw_next = make_uint4(0u, 0u, 0u, 0u);
+    int S_next = 1;
+    if (b_begin < b_end) {
+        raw_next = load_x_row(x_row(b_begin), lane);
+        if (side == 1) S_next = p.seq_lens[b_begin];
+    }
     for (int b = b_begin; b < b_end; ++b) {
-        const __nv_bfloat16* xrow = side == 0 ? p.q + ((size_t)b * Hq + h) * kHeadDim
-                                              : p.k_new + ((size_t)b * p.Hkv + kvh) * kHeadDim;
-        // key side: the append slot needs seq_lens[b], then a page-table entry; both are fetched
-        // underneath the MLP arithmetic
-        int S = 1, page = 0;
-        if (side == 1) S = p.seq_lens[b];
-        mlp_eval(regs, xrow, sm, warp, lane, [&] {
+        const uint4 raw = raw_next;
+        const int S = S_next;
+        if (b + 1 < b_end) {
+            raw_next = load_x_row(x_row(b + 1), lane);
+            if (side == 1) S_next = p.seq_lens[b + 1];
+        }
+        if (side == 0 && p.q_stage != nullptr && warp == 0 && lane < 16)
+            *reinterpret_cast<uint4*>(p.q_stage + ((size_t)b * Hq + h) * kHeadDim + lane * 8) = raw;
+        int page = 0;
+        mlp_eval(regs, raw, sm, warp, lane, [&] {
             if (side == 1) {
                 const int pidx = min(max(S - 1, 0) / kPage, p.max_pages - 1);
                 page = p.page_table[(size_t)b * p.max_pages + pidx];
@@ -288,9 +310,12 @@ hash_prefill_simt_kernel(const HashPrefillParams p) {
     pdl_wait();  // the keys may have been written by the kernel before this one
 
     const size_t slot0 = ((size_t)page * p.Hkv + kvh) * kPage;
+    uint4 raw_next = load_x_row(p.k_pages + (slot0 + t_begin % kPage) * kHeadDim, lane);
     for (int t = t_begin; t < t_end; ++t) {
         const size_t slot = slot0 + t % kPage;
-        mlp_eval(regs, p.k_pages + slot * kHeadDim, sm, warp, lane, [] {});
+        const uint4 raw = raw_next;  // the next token's row is requested while this one is evaluated
+        if (t + 1 < t_end) raw_next = load_x_row(p.k_pages + (slot + 1) * kHeadDim, lane);
+        mlp_eval(regs, raw, sm, warp, lane, [] {});
         if (warp == 0) {
             const float pre = sm.out[lane];
             const uint32_t code = __ballot_sync(0xffffffffu, pre > 0.0f);

@@ -343,6 +343,17 @@ StaggerResources* stagger_resources() {
     return &r;
 }
 
+// The device-side address of a page-locked, device-addressable host buffer; null for anything else
+// (pageable memory, device memory).
+void* mapped_host_pointer(const void* host) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, host) != cudaSuccess) {
+        (void)cudaGetLastError();  // an unregistered pointer is not an error of this library
+        return nullptr;
+    }
+    return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+}
+
 int staggered_select_attend(const ha_shape_t* shape, const ha_budget_t* budget, const void* q,
                             const void* k_pages, const void* v_pages, const uint32_t* hash_pages,
                             const int32_t* page_table, const int32_t* seq_lens, const uint32_t* q_codes,
@@ -445,11 +456,12 @@ int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* 
     return HA_OK;
 }
 
-int ha_hash_decode(const ha_shape_t* shape, const ha_hash_weights_t* weights,
-                   const void* q, const void* k_new, const void* v_new,
-                   void* k_pages, void* v_pages, uint32_t* hash_pages,
-                   const int32_t* page_table, const int32_t* seq_lens,
-                   uint32_t* q_codes, float* preact_dbg, int32_t* status, void* stream) {
+// ha_hash_decode with an optional device copy of q (q_stage) for the kernels that follow.
+static int hash_decode_impl(const ha_shape_t* shape, const ha_hash_weights_t* weights,
+                            const void* q, const void* k_new, const void* v_new,
+                            void* k_pages, void* v_pages, uint32_t* hash_pages,
+                            const int32_t* page_table, const int32_t* seq_lens,
+                            uint32_t* q_codes, float* preact_dbg, void* q_stage, int32_t* status, void* stream) {
     int rc = check_shape(shape);
     if (rc != HA_OK) return rc;
     const bool key_side = k_new != nullptr;
@@ -475,6 +487,7 @@ int ha_hash_decode(const ha_shape_t* shape, const ha_hash_weights_t* weights,
     p.seq_lens = seq_lens;
     p.q_codes = q_codes;
     p.preact_dbg = preact_dbg;
+    p.q_stage = static_cast<__nv_bfloat16*>(q_stage);
     p.status = status;
     p.B = shape->batch;
     p.Hkv = shape->num_kv_heads;
@@ -502,6 +515,15 @@ int ha_hash_decode(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         e = launch(hash_decode_kernel<float>, grid, dim3(kHashDecodeThreads),
                    static_cast<cudaStream_t>(stream), 1, p);
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+}
+
+int ha_hash_decode(const ha_shape_t* shape, const ha_hash_weights_t* weights,
+                   const void* q, const void* k_new, const void* v_new,
+                   void* k_pages, void* v_pages, uint32_t* hash_pages,
+                   const int32_t* page_table, const int32_t* seq_lens,
+                   uint32_t* q_codes, float* preact_dbg, int32_t* status, void* stream) {
+    return hash_decode_impl(shape, weights, q, k_new, v_new, k_pages, v_pages, hash_pages, page_table, seq_lens,
+                            q_codes, preact_dbg, nullptr, status, stream);
 }
 
 int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
@@ -613,6 +635,32 @@ int ha_sparse_decode(const ha_shape_t* shape, const ha_budget_t* budget,
                               sm_scale, out, workspace, workspace_bytes, status, stream);
 }
 
+// The step; q_stage, if given, receives a device copy of q from the encoder kernel and the
+// attention kernels read that copy instead of q (used when q is mapped host memory).
+static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
+                            const ha_hash_weights_t* weights,
+                            const void* q, const void* k_new, const void* v_new, void* q_stage,
+                            void* k_pages, void* v_pages, uint32_t* hash_pages,
+                            const int32_t* page_table, const int32_t* seq_lens,
+                            uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
+                            void* out, void* workspace, size_t workspace_bytes,
+                            int32_t* status, void* stream) {
+    int rc = hash_decode_impl(shape, weights, q, k_new, v_new, k_pages, v_pages, hash_pages, page_table,
+                              seq_lens, q_codes, nullptr, q_stage, status, stream);
+    if (rc != HA_OK) return rc;
+    const void* q_att = q_stage != nullptr ? q_stage : q;
+    if (use_stagger(shape))
+        return staggered_select_attend(shape, budget, q_att, k_pages, v_pages, hash_pages, page_table, seq_lens,
+                                       q_codes, sel_idx, sel_cnt, sm_scale, out, workspace, workspace_bytes, status,
+                                       static_cast<cudaStream_t>(stream));
+    rc = ha_score_select(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
+                         nullptr, workspace, workspace_bytes, status, stream);
+    if (rc != HA_OK) return rc;
+    // the selection kernel left the physical rows of the heavy tokens in the workspace
+    return sparse_decode_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, nullptr, true,
+                              sm_scale, out, workspace, workspace_bytes, status, stream);
+}
+
 int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
                    const ha_hash_weights_t* weights,
                    const void* q, const void* k_new, const void* v_new,
@@ -621,19 +669,9 @@ int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
                    uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
                    void* out, void* workspace, size_t workspace_bytes,
                    int32_t* status, void* stream) {
-    int rc = ha_hash_decode(shape, weights, q, k_new, v_new, k_pages, v_pages, hash_pages, page_table,
-                            seq_lens, q_codes, nullptr, status, stream);
-    if (rc != HA_OK) return rc;
-    if (use_stagger(shape))
-        return staggered_select_attend(shape, budget, q, k_pages, v_pages, hash_pages, page_table, seq_lens, q_codes,
-                                       sel_idx, sel_cnt, sm_scale, out, workspace, workspace_bytes, status,
-                                       static_cast<cudaStream_t>(stream));
-    rc = ha_score_select(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
-                         nullptr, workspace, workspace_bytes, status, stream);
-    if (rc != HA_OK) return rc;
-    // the selection kernel left the physical rows of the heavy tokens in the workspace
-    return sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, nullptr, true,
-                              sm_scale, out, workspace, workspace_bytes, status, stream);
+    return decode_step_impl(shape, budget, weights, q, k_new, v_new, nullptr, k_pages, v_pages, hash_pages,
+                            page_table, seq_lens, q_codes, sel_idx, sel_cnt, sm_scale, out, workspace,
+                            workspace_bytes, status, stream);
 }
 
 int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget) {
@@ -664,18 +702,35 @@ int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t q_bytes = (size_t)shape->batch * shape->num_kv_heads * kGroup * kHeadDim * sizeof(__nv_bfloat16);
     const size_t kv_bytes = (size_t)shape->batch * shape->num_kv_heads * kHeadDim * sizeof(__nv_bfloat16);
-    if (cudaMemcpyAsync(q_dev, q_host, q_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return HA_ERR_LAUNCH;
-    if (k_new_host != nullptr &&
-        cudaMemcpyAsync(k_new_dev, k_new_host, kv_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
-        return HA_ERR_LAUNCH;
-    if (v_new_host != nullptr &&
-        cudaMemcpyAsync(v_new_dev, v_new_host, kv_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
-        return HA_ERR_LAUNCH;
-    rc = ha_decode_step(shape, budget, weights, q_dev, k_new_dev, v_new_dev, k_pages, v_pages, hash_pages,
-                        page_table, seq_lens, q_codes, sel_idx, sel_cnt, sm_scale, out_dev, workspace,
-                        workspace_bytes, status, stream);
-    if (rc != HA_OK) return rc;
-    if (cudaMemcpyAsync(out_host, out_dev, q_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess) return HA_ERR_LAUNCH;
+    // Page-locked host buffers that the device can address are used in place: the encoder kernel
+    // reads q / k_new / v_new over the bus exactly once (and leaves a device copy of q in q_dev for
+    // the attention kernels), the last kernel stores the result straight into out_host. That removes
+    // four copy operations and their launch gaps from the step. Pageable buffers are staged.
+    void* q_map = mapped_host_pointer(q_host);
+    void* k_map = k_new_host != nullptr ? mapped_host_pointer(k_new_host) : nullptr;
+    void* v_map = v_new_host != nullptr ? mapped_host_pointer(v_new_host) : nullptr;
+    void* out_map = mapped_host_pointer(out_host);
+    const bool in_place = q_map != nullptr && out_map != nullptr && (k_new_host == nullptr || k_map != nullptr) &&
+                          (v_new_host == nullptr || v_map != nullptr);
+    if (in_place) {
+        rc = decode_step_impl(shape, budget, weights, q_map, k_map, v_map, q_dev, k_pages, v_pages, hash_pages,
+                              page_table, seq_lens, q_codes, sel_idx, sel_cnt, sm_scale, out_map, workspace,
+                              workspace_bytes, status, stream);
+        if (rc != HA_OK) return rc;
+    } else {
+        if (cudaMemcpyAsync(q_dev, q_host, q_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return HA_ERR_LAUNCH;
+        if (k_new_host != nullptr &&
+            cudaMemcpyAsync(k_new_dev, k_new_host, kv_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+            return HA_ERR_LAUNCH;
+        if (v_new_host != nullptr &&
+            cudaMemcpyAsync(v_new_dev, v_new_host, kv_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+            return HA_ERR_LAUNCH;
+        rc = ha_decode_step(shape, budget, weights, q_dev, k_new_dev, v_new_dev, k_pages, v_pages, hash_pages,
+                            page_table, seq_lens, q_codes, sel_idx, sel_cnt, sm_scale, out_dev, workspace,
+                            workspace_bytes, status, stream);
+        if (rc != HA_OK) return rc;
+        if (cudaMemcpyAsync(out_host, out_dev, q_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess) return HA_ERR_LAUNCH;
+    }
     if (cudaMemcpyAsync(status_host, status, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess)
         return HA_ERR_LAUNCH;
     if (synchronize) {

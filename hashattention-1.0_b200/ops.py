@@ -7,6 +7,7 @@ A non-zero library status raises ``RuntimeError``. There is no torch or CPU fall
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from dataclasses import dataclass
 
@@ -219,20 +220,39 @@ class SparseDecodeContext:
 
 
 class HostStepBuffers:
-    """Pinned host tensors and device staging buffers for :func:`decode_step_host`."""
+    """Host tensors and device staging buffers for :func:`decode_step_host`. Page-locked host
+    tensors (the default) are read and written by the kernels in place; pageable ones
+    (``pinned=False``) are copied through the staging buffers."""
 
-    def __init__(self, ctx: SparseDecodeContext):
+    def __init__(self, ctx: SparseDecodeContext, pinned: bool = True):
         B, Hq, Hkv, dev = ctx.batch, ctx.num_q_heads, ctx.num_kv_heads, ctx.device
-        pin = dict(dtype=torch.bfloat16, pin_memory=True)
+        pin = dict(dtype=torch.bfloat16, pin_memory=pinned)
         self.q_host = torch.empty(B, Hq, HEAD_DIM, **pin)
         self.k_host = torch.empty(B, Hkv, HEAD_DIM, **pin)
         self.v_host = torch.empty(B, Hkv, HEAD_DIM, **pin)
         self.out_host = torch.empty(B, Hq, HEAD_DIM, **pin)
-        self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pinned)
         self.q_dev = torch.empty(B, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
         self.k_dev = torch.empty(B, Hkv, HEAD_DIM, dtype=torch.bfloat16, device=dev)
         self.v_dev = torch.empty(B, Hkv, HEAD_DIM, dtype=torch.bfloat16, device=dev)
         self.out_dev = torch.empty(B, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
+        self._bound = None
+
+    def bound_call(self, ctx: SparseDecodeContext):
+        """``ha_decode_step_host`` with every argument but (stream, synchronize) bound to the buffers
+        of ``ctx`` and of this object. The buffers never move, so the argument list is converted to
+        C types once instead of at every step."""
+        if self._bound is None or self._bound[0] is not ctx:
+            c = ctx.cache
+            vp, i32, f32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+            fixed = [ctypes.byref(ctx.shape), ctypes.byref(ctx.c_budget), ctypes.byref(ctx.c_weights)] + [vp(t.data_ptr()) for t in (
+                self.q_host, self.k_host, self.v_host, self.out_host, self.status_host, self.q_dev, self.k_dev,
+                self.v_dev, self.out_dev, c.k_pages, c.v_pages, c.hash_pages, c.page_table, c.seq_lens, ctx.q_codes,
+                ctx.sel_idx, ctx.sel_cnt)] + [f32(ctx.sm_scale), vp(ctx.workspace.data_ptr()),
+                                              sz(ctx.workspace_bytes), vp(ctx.status.data_ptr())]
+            fn = ctx.lib.ha_decode_step_host
+            self._bound = (ctx, lambda stream, sync: fn(*fixed, vp(stream), i32(sync)))
+        return self._bound[1]
 
     @property
     def h2d_bytes(self) -> int:
@@ -244,18 +264,15 @@ class HostStepBuffers:
 
 
 def decode_step_host(ctx: SparseDecodeContext, buf: HostStepBuffers, synchronize: bool = True) -> torch.Tensor:
-    """Decode step for callers whose q / k_new / v_new / out live in host memory: copies
-    ``buf.q_host, k_host, v_host`` to the device, runs the step, copies the result into
-    ``buf.out_host`` and (if ``synchronize``) waits and checks the device status."""
-    c = ctx.cache
-    with torch.cuda.device(ctx.device):
-        rc = ctx.lib.ha_decode_step_host(
-            ctx.shape, ctx.c_budget, ctx.c_weights, buf.q_host.data_ptr(), buf.k_host.data_ptr(),
-            buf.v_host.data_ptr(), buf.out_host.data_ptr(), buf.status_host.data_ptr(), buf.q_dev.data_ptr(),
-            buf.k_dev.data_ptr(), buf.v_dev.data_ptr(), buf.out_dev.data_ptr(), c.k_pages.data_ptr(),
-            c.v_pages.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(), c.seq_lens.data_ptr(),
-            ctx.q_codes.data_ptr(), ctx.sel_idx.data_ptr(), ctx.sel_cnt.data_ptr(), ctx.sm_scale,
-            ctx.workspace.data_ptr(), ctx.workspace_bytes, ctx.status.data_ptr(), _stream_ptr(ctx.device),
-            1 if synchronize else 0)
+    """Decode step for callers whose q / k_new / v_new / out live in host memory: the step reads
+    ``buf.q_host, k_host, v_host`` (in place if page-locked, else through a copy), leaves the result
+    in ``buf.out_host`` and (if ``synchronize``) waits and checks the device status."""
+    call = buf.bound_call(ctx)
+    stream = torch.cuda.current_stream(ctx.device).cuda_stream
+    if torch.cuda.current_device() == ctx.device.index:
+        rc = call(stream, 1 if synchronize else 0)
+    else:
+        with torch.cuda.device(ctx.device):
+            rc = call(stream, 1 if synchronize else 0)
     _raise_on(rc, "ha_decode_step_host")
     return buf.out_host

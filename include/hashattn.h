@@ -14,8 +14,9 @@
  *   - Unless a parameter is documented as a host pointer, every pointer is a DEVICE pointer.
  *   - Nothing is allocated or freed inside the library; temporaries live in a caller-provided
  *     workspace of ha_workspace_bytes() bytes that was prepared once by ha_workspace_init().
- *   - All work is enqueued on the given CUDA stream; no entry point synchronises with the
- *     host except ha_decode_step_host (documented there).
+ *   - All work is ordered on the given CUDA stream (large decode steps fork part of it onto a
+ *     library-owned stream and join it back before returning); no entry point synchronises
+ *     with the host except ha_decode_step_host (documented there).
  *   - Kernels validate page ids and sizes before touching memory; a violation is reported
  *     through the 4-byte device word `status` (0 == clean) instead of a fault.
  *
@@ -196,11 +197,20 @@ int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
 int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget);
 
 /* ha_decode_step for a caller whose per-step tensors live in HOST memory.
- * q_host, k_new_host, v_new_host (inputs) and out_host (result) are HOST pointers, ideally
- * pinned; q_dev, k_new_dev, v_new_dev, out_dev are device staging buffers of the same sizes.
- * The call copies the inputs to the device, runs ha_decode_step, copies `out` and the status
- * word back and, if `synchronize` is non-zero, waits for the stream and returns the device
- * status word (HA_OK if clean). status_host is a host int32 (pinned) receiving that word.   */
+ * q_host, k_new_host, v_new_host (inputs) and out_host (result) are HOST pointers; q_dev,
+ * k_new_dev, v_new_dev, out_dev are device staging buffers of the same sizes.
+ * If all host buffers are page-locked and device-addressable (cudaHostAlloc / cudaHostRegister,
+ * torch pin_memory) the kernels use them in place: the encoder kernel reads the inputs over the
+ * bus once (keeping a device copy of q in q_dev), the last kernel stores the result into
+ * out_host; only the status word is copied. Otherwise the inputs are copied to the staging
+ * buffers, ha_decode_step runs on those, and `out` is copied back. Either way the host buffers
+ * must stay untouched until the stream has reached the end of the call. If `synchronize` is
+ * non-zero the call waits for the stream and returns the device status word (HA_OK if clean).
+ * status_host is a host int32 receiving that word.
+ * Besides the caller's stream, steps with more than 32 MB of hash pages use streams and events
+ * that belong to the library (created at the first such call on a device, never during the
+ * caller's stream capture if an eager call came first) and are joined back before the call
+ * returns; this holds for ha_decode_step too.                                               */
 int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
                         const ha_hash_weights_t* weights,
                         const void* q_host, const void* k_new_host, const void* v_new_host,

@@ -172,7 +172,7 @@ def test_sparse_attention_matches_reference(device, cases, name):
 # ------------------------------------------------------------------------------------------
 # the whole step
 # ------------------------------------------------------------------------------------------
-def run_step_and_check(device, usa, q, ks, vs, budget, shuffle_seed=11, via_host=False):
+def run_step_and_check(device, usa, q, ks, vs, budget, shuffle_seed=11, via_host=False, pinned=True):
     """Prefill all but the last token, decode the last one, compare every stage with the oracle.
     Selection and attention are compared on the device's own codes (a bit inside the exclusion
     band must not show up as a set mismatch); returns whether the codes were identical."""
@@ -184,7 +184,8 @@ def run_step_and_check(device, usa, q, ks, vs, budget, shuffle_seed=11, via_host
     k_new = torch.stack([k[:, -1] for k in ks]).to(torch.bfloat16)
     v_new = torch.stack([v[:, -1] for v in vs]).to(torch.bfloat16)
     if via_host:
-        buf = ha.HostStepBuffers(ctx)
+        buf = ha.HostStepBuffers(ctx, pinned=pinned)
+        assert buf.q_host.is_pinned() == pinned
         buf.q_host.copy_(q.to(torch.bfloat16)); buf.k_host.copy_(k_new); buf.v_host.copy_(v_new)
         out = ha.decode_step_host(ctx, buf).clone().float()
     else:
@@ -322,7 +323,9 @@ def test_host_buffer_entry_point_equals_device_entry_point(device):
     budget = ha.Budget(16, 0.125, 16)
     _, out_dev, _, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget)
     _, out_host, _, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, via_host=True)
-    assert torch.equal(out_dev, out_host)
+    assert torch.equal(out_dev, out_host)  # page-locked buffers: read and written in place by the kernels
+    _, out_paged, _, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, via_host=True, pinned=False)
+    assert torch.equal(out_dev, out_paged)  # pageable buffers: staged through device copies
 
 
 def test_repeated_steps_grow_the_cache(device):
