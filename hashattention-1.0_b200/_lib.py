@@ -24,7 +24,9 @@ HA_ERR_SEL_OVERFLOW = 8
 HA_ERR_SCRATCH_LIMIT = 9
 HA_WEIGHTS_BF16 = 0
 HA_WEIGHTS_F32 = 1
-HA_ABI_VERSION = 1
+HA_ABI_VERSION = 2
+HA_EVAL_SIMPLE = 0
+HA_EVAL_DEPTH = 1
 
 
 class HaShape(ctypes.Structure):
@@ -35,7 +37,8 @@ class HaShape(ctypes.Structure):
 
 
 class HaBudget(ctypes.Structure):
-    _fields_ = [("init_budget", c_int32), ("recent_budget", c_int32), ("heavy_budget", c_double)]
+    _fields_ = [("init_budget", c_int32), ("recent_budget", c_int32), ("heavy_budget", c_double),
+                ("eval_mode", c_int32), ("retrieve_depth", c_int32)]
 
 
 class HaHashWeights(ctypes.Structure):

@@ -39,6 +39,8 @@ int check_budget(const ha_budget_t* b) {
     if (b == nullptr) return HA_ERR_BAD_ARG;
     if (b->init_budget < 0 || b->recent_budget < 0) return HA_ERR_BAD_ARG;
     if (!(b->heavy_budget >= 0.0) || !std::isfinite(b->heavy_budget)) return HA_ERR_BAD_ARG;
+    if (b->eval_mode != HA_EVAL_SIMPLE && b->eval_mode != HA_EVAL_DEPTH) return HA_ERR_BAD_ARG;
+    if (b->eval_mode == HA_EVAL_DEPTH && (b->retrieve_depth < -64 || b->retrieve_depth > 64)) return HA_ERR_BAD_ARG;
     return HA_OK;
 }
 
@@ -221,6 +223,8 @@ SelectParams select_params(const ha_shape_t* shape, const ha_budget_t* budget, c
     p.init_budget = budget->init_budget;
     p.recent_budget = budget->recent_budget;
     p.heavy_budget = budget->heavy_budget;
+    p.eval_mode = budget->eval_mode;
+    p.depth = budget->retrieve_depth;
     return p;
 }
 
@@ -228,7 +232,7 @@ SelectParams select_params(const ha_shape_t* shape, const ha_budget_t* budget, c
 int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                        const void* q, const void* k_pages, const void* v_pages,
                        const int32_t* page_table, const int32_t* seq_lens,
-                       const int32_t* sel, bool physical, float sm_scale,
+                       const int32_t* sel, const int32_t* sel_cnt, bool physical, float sm_scale,
                        void* out, void* workspace, size_t workspace_bytes,
                        int32_t* status, void* stream, int kvh0 = 0, int nkvh = -1, int merge_priority = 0) {
     int rc = check_shape(shape);
@@ -238,6 +242,7 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     if (q == nullptr || k_pages == nullptr || v_pages == nullptr || page_table == nullptr ||
         seq_lens == nullptr || out == nullptr || status == nullptr || !std::isfinite(sm_scale))
         return HA_ERR_BAD_ARG;
+    if (budget->eval_mode != HA_EVAL_SIMPLE && sel_cnt == nullptr) return HA_ERR_BAD_ARG;  // variable-size sets
     const int nheads = (nkvh < 0 ? shape->num_kv_heads : nkvh) * kGroup;  // heads [4 kvh0, 4 kvh0 + nheads)
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
     const Workspace w = carve(shape, budget, workspace);
@@ -250,6 +255,7 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     p.page_table = page_table;
     p.seq_lens = seq_lens;
     p.sel = physical ? w.sel_rows : sel;
+    p.sel_cnt = budget->eval_mode == HA_EVAL_SIMPLE ? nullptr : sel_cnt;  // simple: the count follows from the budget
     p.out = static_cast<__nv_bfloat16*>(out);
     p.status = status;
     p.B = shape->batch;
@@ -391,7 +397,7 @@ int staggered_select_attend(const ha_shape_t* shape, const ha_budget_t* budget, 
                 return HA_ERR_LAUNCH;
         }
         ok = ok && launch_plan_select(shape, p, n, si, light) == cudaSuccess;
-        ok = ok && sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, nullptr, true,
+        ok = ok && sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, nullptr, sel_cnt, true,
                                       sm_scale, out, workspace, workspace_bytes, status, si, first, n, light) == HA_OK;
         first += n;
     }
@@ -631,7 +637,7 @@ int ha_sparse_decode(const ha_shape_t* shape, const ha_budget_t* budget,
                      void* out, void* workspace, size_t workspace_bytes,
                      int32_t* status, void* stream) {
     if (sel_idx == nullptr || sel_cnt == nullptr) return check_shape(shape) != HA_OK ? check_shape(shape) : HA_ERR_BAD_ARG;
-    return sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, sel_idx, false,
+    return sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, sel_idx, sel_cnt, false,
                               sm_scale, out, workspace, workspace_bytes, status, stream);
 }
 
@@ -657,7 +663,7 @@ static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                          nullptr, workspace, workspace_bytes, status, stream);
     if (rc != HA_OK) return rc;
     // the selection kernel left the physical rows of the heavy tokens in the workspace
-    return sparse_decode_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, nullptr, true,
+    return sparse_decode_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, nullptr, sel_cnt, true,
                               sm_scale, out, workspace, workspace_bytes, status, stream);
 }
 

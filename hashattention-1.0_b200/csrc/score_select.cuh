@@ -59,6 +59,7 @@ struct SelectParams {
     int kvh0;                  // first kv-head of this launch (a launch may cover a slice of the kv-heads)
     int init_budget, recent_budget;
     double heavy_budget;
+    int eval_mode, depth;      // HA_EVAL_*; usa_retrieve_depth (HA_EVAL_DEPTH only)
 };
 
 // One round of one warp: 128 consecutive tokens of one page, token it*32 + lane for it = 0..3.
@@ -133,6 +134,57 @@ __device__ __forceinline__ uint32_t bytes_eq(uint32_t a, uint32_t t4) {
 // bit 7 of byte g -> bit g
 __device__ __forceinline__ uint32_t flags_to_nibble(uint32_t f) { return (((f >> 7) * 0x01020408u) >> 24) & 0xFu; }
 
+// What is kept of one head's candidates, worked out from the totals per score bin by one full
+// warp: lane l passes n = total of bin 32 - l and cum = the inclusive prefix of n over the lanes
+// (candidates scoring >= 32 - l); tot0 = total of bin 0; hb = min(budget, candidates).
+//   T      tokens scoring above T are kept, of those scoring T the first `need` by token index;
+//          T = 33 keeps nothing
+//   count  tokens kept in all, cut to sel_stride (`overflow` says whether it had to be)
+// HA_EVAL_SIMPLE: the hb best (hashattention/hashattention_llama.py:436-438). HA_EVAL_DEPTH: every
+// candidate scoring at least max(best - depth, score of the hb-th best) (:439-443; one score step
+// is a span step of 2).
+struct Threshold {
+    int T, need, count;
+};
+
+__device__ __forceinline__ Threshold pick_threshold(const SelectParams& p, int n, int cum, int tot0, int hb,
+                                                    bool& overflow) {
+    Threshold t;
+    t.T = kBins; t.need = 0; t.count = 0;
+    overflow = false;
+    int hbe = hb;
+    if (p.eval_mode == HA_EVAL_SIMPLE && hbe > p.sel_stride) {
+        overflow = true;
+        hbe = p.sel_stride;
+    }
+    if (hbe <= 0) return t;
+    // the score of the hbe-th best candidate and the number of candidates above it
+    const uint32_t reached = __ballot_sync(0xffffffffu, cum >= hbe);
+    const int l = reached != 0 ? __ffs(reached) - 1 : 31;  // first lane whose cumulative count reaches the budget
+    const int cum31 = __shfl_sync(0xffffffffu, cum, 31);
+    const int above_l = __shfl_sync(0xffffffffu, cum - n, l);
+    const int T_num = reached != 0 ? 32 - l : 0;  // bins 32..1 hold fewer than the budget: the threshold is 0
+    const int above = reached != 0 ? above_l : cum31;
+    if (p.eval_mode == HA_EVAL_SIMPLE) {
+        t.T = T_num;
+        t.need = hbe - above;
+        t.count = hbe;
+        return t;
+    }
+    const uint32_t nonzero = __ballot_sync(0xffffffffu, n > 0);
+    const int top = nonzero != 0 ? 32 - (__ffs(nonzero) - 1) : 0;  // hbe >= 1: some candidate exists
+    const int T = min(max(top - p.depth, T_num), kBins);
+    const int at_least = __shfl_sync(0xffffffffu, cum, min(max(32 - T, 0), 31));
+    t.T = T;
+    t.need = 0x3fffffff;  // every tied token
+    t.count = T >= kBins ? 0 : (T >= 1 ? at_least : cum31 + tot0);
+    if (t.count > p.sel_stride) {
+        overflow = true;
+        t.count = p.sel_stride;
+    }
+    return t;
+}
+
 // The plan of one (sequence, kv-head), worked out by one CTA of 256 threads between the two passes.
 // From the per-chunk histograms it derives, once instead of in every CTA of pass B, the global
 // threshold T and the tie quota of each head, and for every chunk the number of selected tokens
@@ -145,11 +197,6 @@ __device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kv
                                             uint32_t (*stage)[kBins][32], int tid) {
     const int lane = tid & 31, warp = tid >> 5, g = warp & 3;
     const int Hq = p.Hkv * kGroup;
-    int hbe = r.hb;
-    if (hbe > p.sel_stride) {
-        if (tid == 0) report(p.status, HA_ERR_SEL_OVERFLOW);
-        hbe = p.sel_stride;
-    }
     const uint32_t* hbase = p.hist + (((size_t)b * p.Hkv + kvh) * (kGroup * kBins) + g * kBins) * p.nchunks;
     int32_t* plan = p.plan + ((size_t)b * p.Hkv + kvh) * (8 + 8 * p.nchunks);
     auto stage_pass = [&](int cc0) {
@@ -165,12 +212,13 @@ __device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kv
     const bool one_pass = nchunks_b <= 32;
 
     // totals per bin over all chunks -> T and the tie quota (lane l holds bin 32 - l)
-    int tot_hi = 0;
+    int tot_hi = 0, tot0 = 0;
     for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
         if (cc0 > 0) __syncthreads();
         stage_pass(cc0);
         __syncthreads();
         if (warp < kGroup) {
+            tot0 += __reduce_add_sync(0xffffffffu, (int)stage[g][0][lane]);
 #pragma unroll 8
             for (int s = 1; s < kBins; ++s) {
                 const int t = __reduce_add_sync(0xffffffffu, (int)stage[g][s][lane]);
@@ -186,21 +234,15 @@ __device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kv
             const int u = __shfl_up_sync(0xffffffffu, cum, d);
             if (lane >= d) cum += u;
         }
-        const uint32_t reached = __ballot_sync(0xffffffffu, cum >= hbe);
-        if (hbe <= 0) {
-            T = kBins; need = 0;  // T = 33: nothing qualifies
-        } else if (reached != 0) {
-            const int l = __ffs(reached) - 1;  // first lane whose cumulative count reaches the budget
-            T = 32 - l;
-            need = hbe - __shfl_sync(0xffffffffu, cum - tot_hi, l);
-        } else {  // bins 32..1 together hold fewer than the budget: the threshold is 0
-            T = 0;
-            need = hbe - __shfl_sync(0xffffffffu, cum, 31);
-        }
+        bool overflow;
+        const Threshold th = pick_threshold(p, tot_hi, cum, tot0, r.hb, overflow);
+        T = th.T;
+        need = th.need;
         if (lane == 0) {
+            if (overflow) report(p.status, HA_ERR_SEL_OVERFLOW);
             plan[g] = T;
             plan[4 + g] = need;
-            p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = hbe;
+            p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = th.count;
         }
     }
 
@@ -678,33 +720,20 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
     // --- threshold, tie quota and output bases per head: warp g scans the 33 bins downwards --------
     if (warp < kGroup) {
         const int g = warp;
-        int hbe = r.hb;
-        if (hbe > p.sel_stride) {
-            if (lane == 0 && rank == 0) report(p.status, HA_ERR_SEL_OVERFLOW);
-            hbe = p.sel_stride;
-        }
-        if (!s_ok) hbe = 0;
-        const int n = s_tot[g * kBins + 32 - lane];  // lane l holds bin 32 - l; bin 0 is the remainder
+        const int n = s_tot[g * kBins + 32 - lane];  // lane l holds bin 32 - l; bin 0 apart
         int cum = n;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const int u = __shfl_up_sync(0xffffffffu, cum, d);
             if (lane >= d) cum += u;
         }
-        const uint32_t reached = __ballot_sync(0xffffffffu, cum >= hbe);
-        int T, need, lsel = 31;
-        if (hbe <= 0) {
-            T = kBins; need = 0;  // T = 33: nothing qualifies
-        } else if (reached != 0) {
-            lsel = __ffs(reached) - 1;  // first lane whose cumulative count reaches the budget
-            T = 32 - lsel;
-            need = hbe - __shfl_sync(0xffffffffu, cum - n, lsel);
-        } else {  // bins 32..1 together hold fewer than the budget: the threshold is 0
-            T = 0;
-            need = hbe - __shfl_sync(0xffffffffu, cum, 31);
-        }
+        bool overflow;
+        const Threshold th = pick_threshold(p, n, cum, s_tot[g * kBins], s_ok ? r.hb : 0, overflow);
+        const int T = th.T;
+        if (overflow && lane == 0 && rank == 0) report(p.status, HA_ERR_SEL_OVERFLOW);
 #pragma unroll
         for (int rd = 0; rd < ROUNDS; ++rd) {
+            // tokens above T / at T in the (round, rank) pairs before (rd, this CTA)
             const int nb = s_bef[rd][g * kBins + 32 - lane];
             int cumb = nb;
 #pragma unroll
@@ -712,23 +741,26 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
                 const int u = __shfl_up_sync(0xffffffffu, cumb, d);
                 if (lane >= d) cumb += u;
             }
+            const int lt = min(max(32 - T, 0), 31);
+            const int gt_l = __shfl_sync(0xffffffffu, cumb - nb, lt), eq_l = __shfl_sync(0xffffffffu, nb, lt);
+            const int all31 = __shfl_sync(0xffffffffu, cumb, 31);
             int gt_before = 0, eq_before = 0;
-            if (hbe > 0 && reached != 0) {
-                gt_before = __shfl_sync(0xffffffffu, cumb - nb, lsel);
-                eq_before = __shfl_sync(0xffffffffu, nb, lsel);
-            } else if (hbe > 0) {
-                gt_before = __shfl_sync(0xffffffffu, cumb, 31);
+            if (T >= 1 && T <= 32) {
+                gt_before = gt_l;
+                eq_before = eq_l;
+            } else if (T == 0) {
+                gt_before = all31;
                 eq_before = s_bef[rd][g * kBins];
             }
             if (lane == 0) {
                 s_eqb[rd][g] = eq_before;
-                s_base[rd][g] = gt_before + min(eq_before, need);
+                s_base[rd][g] = gt_before + min(eq_before, th.need);
             }
         }
         if (lane == 0) {
             s_T[g] = T;
-            s_need[g] = need;
-            if (rank == 0 && s_ok) p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = hbe;
+            s_need[g] = th.need;
+            if (rank == 0 && s_ok) p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = th.count;
         }
     }
     __syncthreads();

@@ -32,6 +32,8 @@ struct SparseDecodeParams {
     const int32_t* page_table;
     const int32_t* seq_lens;
     const int32_t* sel;            // [B][Hq][sel_stride]: token indices, or physical rows (kPhysical)
+    const int32_t* sel_cnt;        // [B][Hq] entries of `sel` in use, or null: min(heavy budget, candidates),
+                                   // which needs no load (HA_EVAL_SIMPLE always selects exactly that many)
     __nv_bfloat16* out;            // [B][Hq][128]
     float* partials;               // workspace: [B][Hq][nsplits][130]
     int32_t* status;
@@ -77,12 +79,13 @@ struct AttPlan {
     bool ok;
 };
 
-__device__ __forceinline__ AttPlan att_plan(const SparseDecodeParams& p, int b) {
+// listed: number of entries in the heavy list as read from sel_cnt, or -1 if it follows from the budget
+__device__ __forceinline__ AttPlan att_plan(const SparseDecodeParams& p, int b, int listed = -1) {
     AttPlan a;
     const int S = p.seq_lens[b];
     a.ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by the selection kernels
     a.r = seq_range(a.ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
-    a.cnt = min(a.r.hb, p.sel_stride);
+    a.cnt = listed >= 0 ? min(listed, min(a.r.hi - a.r.lo, p.sel_stride)) : min(a.r.hb, p.sel_stride);
     a.n_total = a.ok ? a.r.lo + a.cnt + (a.r.S - a.r.hi) : 0;
     const int rows_per_cta = kAttRoundRows * p.rounds;
     a.nsplits = (a.n_total + rows_per_cta - 1) / rows_per_cta;
@@ -104,9 +107,10 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
     __shared__ __align__(16) float s_acc[kWarps][kHeadDim];
 
     // inputs of the step, not products of the preceding kernel: q, seq_lens, the page table
-    const AttPlan a = att_plan(p, b);
-    const int lo = a.r.lo, cnt = a.cnt;
-    const int edge_shift = a.r.hi - lo - cnt;  // recent token = position + edge_shift
+    AttPlan a = att_plan(p, b);
+    const int lo = a.r.lo;
+    int cnt = a.cnt;
+    int edge_shift = a.r.hi - lo - cnt;  // recent token = position + edge_shift
     const int32_t* sel = p.sel + ((size_t)b * Hq + h) * p.sel_stride;
     const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
     const int base = split * kAttRoundRows * p.rounds + worker;
@@ -114,13 +118,16 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
 
     // page lookups of the first round's sink / recent rows, issued before the dependency wait
     int pre_page[kAttRowsPerWorker];
+    auto first_round_pages = [&] {
 #pragma unroll
-    for (int i = 0; i < kAttRowsPerWorker; ++i) {
-        const int pos = base + i * kAttWorkers;
-        const bool edge = pos < a.n_total && (unsigned)(pos - lo) >= (unsigned)cnt;
-        const int tok = edge ? (pos < lo ? pos : pos + edge_shift) : 0;
-        pre_page[i] = __ldg(pt + tok / kPage);
-    }
+        for (int i = 0; i < kAttRowsPerWorker; ++i) {
+            const int pos = base + i * kAttWorkers;
+            const bool edge = pos < a.n_total && (unsigned)(pos - lo) >= (unsigned)cnt;
+            const int tok = edge ? (pos < lo ? pos : pos + edge_shift) : 0;
+            pre_page[i] = __ldg(pt + tok / kPage);
+        }
+    };
+    if (p.sel_cnt == nullptr) first_round_pages();
     float qf[8];
     {
         const uint4 raw = *reinterpret_cast<const uint4*>(p.q + ((size_t)b * Hq + h) * kHeadDim + sl * 8);
@@ -132,6 +139,12 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
     pdl_wait();
     HA_TL(kTlGather, kTlAfterWait);
     pdl_launch_dependents();
+    if (p.sel_cnt != nullptr) {  // the length of the heavy list is a product of the selection kernels
+        a = att_plan(p, b, __ldcg(p.sel_cnt + (size_t)b * Hq + h));
+        cnt = a.cnt;
+        edge_shift = a.r.hi - lo - cnt;
+        first_round_pages();
+    }
     if (split >= a.nsplits) return;
 
     const __nv_bfloat16* kbase = p.k_pages + (size_t)kvh * kPage * kHeadDim + sl * 8;
@@ -290,13 +303,14 @@ __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDeco
     const int Hq = p.Hkv * kGroup;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int kWarps = kHeadDim / 32;
-    const AttPlan a = att_plan(p, b);
+    AttPlan a = att_plan(p, b);
     __shared__ float s_m[kWarps], s_l[kWarps];
     __shared__ float s_a[kWarps][kHeadDim];
 
     pdl_wait();
     HA_TL(kTlMerge, kTlAfterWait);
     pdl_launch_dependents();
+    if (p.sel_cnt != nullptr) a = att_plan(p, b, __ldcg(p.sel_cnt + (size_t)b * Hq + h));
     if (a.nsplits <= 1) return;  // written by the gather kernel (or nothing to write)
 
     const float* base = p.partials + ((size_t)b * Hq + h) * p.nsplits * kPartStride;

@@ -17,8 +17,10 @@ What runs where
     afterwards the layer's keys / values are copied into this module's paged cache and the key
     hashes are built once by the CUDA library. (The reference keeps no key hashes and re-encodes
     every cached key on every decode step, :405-408.)
-  * 2 <= q_len <= 128, training (``train_usa``), statistics (``collect_stats``) and
-    ``usa_eval_mode != 'simple'`` are not implemented and raise ``NotImplementedError``.
+  * Both ``usa_eval_mode`` settings are implemented: 'simple' (the ``hb`` best candidates) and the
+    depth rule of every other mode string (:439-443).
+  * 2 <= q_len <= 128, training (``train_usa``) and statistics (``collect_stats``) are not
+    implemented and raise ``NotImplementedError``.
 """
 from __future__ import annotations
 
@@ -87,8 +89,6 @@ class LlamaAttention_heavy_hitter(nn.Module):
         self.recent_budget = config.recent_budget
         self.usa_retrieve_depth = getattr(config, "usa_retrieve_depth", -1)
         self.usa_eval_mode = config.usa_eval_mode
-        if self.usa_eval_mode != "simple":
-            raise NotImplementedError("only usa_eval_mode='simple' is implemented")
         self.usa_module: Optional[USA] = None
         self.usa_module_dtype = None
         self.collect_stats = False
@@ -113,7 +113,8 @@ class LlamaAttention_heavy_hitter(nn.Module):
             if self.usa_module is None:
                 raise RuntimeError("no usa_module attached: build the model with convert_usa")
             cache = PagedHashKVCache(batch, self.num_key_value_heads, self.max_seq_len, device)
-            budget = Budget(self.init_budget, self.heavy_budget, self.recent_budget)
+            budget = Budget(self.init_budget, self.heavy_budget, self.recent_budget,
+                            "simple" if self.usa_eval_mode == "simple" else "depth", int(self.usa_retrieve_depth))
             self._ctx = SparseDecodeContext(cache, budget, self.usa_module.packed(device))
         return self._ctx
 

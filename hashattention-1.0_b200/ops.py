@@ -22,17 +22,32 @@ from .usa import PackedHashWeights
 class Budget:
     """init / heavy / recent budgets with the reference's meaning: ``heavy_budget <= 1.0`` is a
     fraction of the sequence length, ``> 1.0`` an absolute count
-    (hashattention/hashattention_llama.py:431-434)."""
+    (hashattention/hashattention_llama.py:431-434). ``eval_mode`` / ``retrieve_depth`` are the
+    reference's ``usa_eval_mode`` / ``usa_retrieve_depth``: 'simple' keeps the ``hb`` best
+    candidates, any other mode every candidate whose score is within ``retrieve_depth`` bits of the
+    best one or at least that of the ``hb``-th best (:436-443)."""
 
     init_budget: int = 128
     heavy_budget: float = 1.0 / 32
     recent_budget: int = 128
+    eval_mode: str = "simple"
+    retrieve_depth: int = -1
 
     def heavy_tokens(self, seq_len: int) -> int:
         return int(self.heavy_budget) if self.heavy_budget > 1.0 else int(seq_len * self.heavy_budget)
 
     def c_struct(self) -> _lib.HaBudget:
-        return _lib.HaBudget(int(self.init_budget), int(self.recent_budget), float(self.heavy_budget))
+        simple = self.eval_mode == "simple"
+        return _lib.HaBudget(int(self.init_budget), int(self.recent_budget), float(self.heavy_budget),
+                             _lib.HA_EVAL_SIMPLE if simple else _lib.HA_EVAL_DEPTH,
+                             0 if simple else int(self.retrieve_depth))
+
+    def max_selected(self, max_seq_len: int) -> int:
+        """Upper bound on the heavy tokens of one head: the budget in 'simple' mode, every token otherwise
+        (the depth rule keeps all ties, so its sets have no fixed size)."""
+        if self.eval_mode == "simple":
+            return max(1, min(self.heavy_tokens(max_seq_len), max_seq_len))
+        return max(1, max_seq_len)
 
 
 def _check(t: torch.Tensor, name: str, dtype: torch.dtype, shape, device) -> None:
@@ -77,7 +92,7 @@ class SparseDecodeContext:
         if weights.wq.shape[0] != self.num_q_heads or weights.wq.device != self.device:
             raise ValueError("packed hash weights do not match the cache's heads / device")
         max_seq_len = cache.max_pages * PAGE if max_seq_len is None else max_seq_len
-        self.sel_stride = max(1, min(budget.heavy_tokens(max_seq_len), max_seq_len))
+        self.sel_stride = budget.max_selected(max_seq_len)
         self.sm_scale = 1.0 / math.sqrt(HEAD_DIM) if sm_scale is None else float(sm_scale)
         self.shape = _lib.HaShape(self.batch, self.num_kv_heads, GROUP, HEAD_DIM, PAGE, cache.max_pages,
                                   cache.num_pages, self.sel_stride)

@@ -47,7 +47,7 @@
 extern "C" {
 #endif
 
-#define HA_ABI_VERSION 1
+#define HA_ABI_VERSION 2
 
 /* status codes (return values and contents of the device status word) */
 #define HA_OK 0
@@ -76,13 +76,24 @@ typedef struct ha_shape {
     int32_t sel_stride;   /* row pitch (elements) of sel_idx: >= largest heavy budget        */
 } ha_shape_t;
 
-/* Budgets of compute_mask_multi (hashattention/hashattention_llama.py:423-438).
+/* Budgets of compute_mask_multi (hashattention/hashattention_llama.py:423-443).
  * heavy_budget <= 1.0 is a fraction of seq_len, > 1.0 an absolute token count; the product
- * is formed in double precision and truncated, as Python's int(k * heavy_budget) does. */
+ * is formed in double precision and truncated, as Python's int(k * heavy_budget) does.
+ * eval_mode selects what is kept among the candidates:
+ *   HA_EVAL_SIMPLE  usa_eval_mode == 'simple' (:436-438): the hb best, ties by lowest index.
+ *   HA_EVAL_DEPTH   any other usa_eval_mode (:439-443): every candidate whose score is at least
+ *                   max(best score - retrieve_depth, score of the hb-th best); a variable
+ *                   number, all ties included. (One mismatching bit lowers the reference's
+ *                   +-1 span by 2, hence its `2 * usa_retrieve_depth`.) hb == 0 keeps nothing
+ *                   (the reference raises there). sel_stride must cover the largest set.      */
+#define HA_EVAL_SIMPLE 0
+#define HA_EVAL_DEPTH 1
 typedef struct ha_budget {
     int32_t init_budget;   /* sink tokens  [0, init)                                          */
     int32_t recent_budget; /* recent tokens [S - recent, S)                                   */
     double heavy_budget;
+    int32_t eval_mode;      /* HA_EVAL_SIMPLE or HA_EVAL_DEPTH                                */
+    int32_t retrieve_depth; /* usa_retrieve_depth, only read in HA_EVAL_DEPTH; |depth| <= 64  */
 } ha_budget_t;
 
 typedef struct ha_hash_weights {
@@ -129,7 +140,8 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
                     const int32_t* page_table, const int32_t* seq_lens,
                     const int32_t* first_token, int32_t* status, void* stream);
 
-/* Hamming scoring + budget selection, usa_eval_mode == 'simple'.
+/* Hamming scoring + budget selection (both usa_eval_modes, see ha_budget_t; the text below
+ * describes HA_EVAL_SIMPLE).
  * Replaces the +-1 dot product of USA.forward (hashattention/hashattention_llama.py:171-187)
  * and compute_mask_multi (:423-438). score = popcount(~(q_code ^ k_code)) in 0..32, which
  * equals (span + 32) / 2 of the reference. Candidates are tokens [lo, hi) with

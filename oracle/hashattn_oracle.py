@@ -93,11 +93,16 @@ def heavy_tokens(seq_len: int, heavy_budget: float) -> int:
 
 
 def select_mask(span: torch.Tensor, init_budget: int, recent_budget: int, heavy_budget: float,
-                stable: bool = True) -> torch.Tensor:
-    """compute_mask_multi for q_len == 1, usa_eval_mode == 'simple' (hashattention_llama.py:423-438).
+                stable: bool = True, eval_mode: str = "simple", retrieve_depth: int = -1,
+                bit_step: float = 1.0) -> torch.Tensor:
+    """compute_mask_multi for q_len == 1 (hashattention_llama.py:423-443).
 
     ``span`` is ``[B, H, S]`` (any monotone score: the +-1 dot product or the Hamming count).
-    Returns the bool keep-mask ``[B, H, S]``.
+    ``eval_mode == 'simple'`` keeps the ``hb`` best candidates (:436-438); any other mode keeps
+    every candidate scoring at least ``max(best - bit_step * retrieve_depth, hb-th best)``
+    (:439-443), where ``bit_step`` is what one mismatching bit costs in the units of ``span``
+    (2 for the reference's +-1 dot product, 1 for the Hamming count). Returns the bool keep-mask
+    ``[B, H, S]``. In the non-simple mode ``hb == 0`` keeps no candidate (the reference raises there).
     """
     B, H, S = span.shape
     idx = torch.arange(S)
@@ -105,9 +110,18 @@ def select_mask(span: torch.Tensor, init_budget: int, recent_budget: int, heavy_
     cand[:init_budget] = False                   # (:424)
     span = span.to(torch.float32).masked_fill(~cand, torch.finfo(torch.float32).min)   # (:426)
     mask = (~cand)[None, None, :].expand(B, H, S).clone()    # all-true causal row times ~cand   (:427-428)
-    _, indices = span.sort(dim=-1, descending=True, stable=stable)                      # (:430)
+    values, indices = span.sort(dim=-1, descending=True, stable=stable)                 # (:430)
     hb = heavy_tokens(S, heavy_budget)
-    mask.scatter_(2, indices[:, :, :hb], True)                                          # (:437-438)
+    if eval_mode == "simple":
+        mask.scatter_(2, indices[:, :, :hb], True)                                      # (:437-438)
+        return mask
+    if hb < 1:
+        return mask
+    hb = min(hb, S)  # (the reference raises for hb > S; here the smallest value stands in)
+    depth_thold = values[:, :, :1] - bit_step * retrieve_depth                           # (:440)
+    num_thold = values[:, :, hb - 1:hb]                                                 # (:441)
+    thold = torch.maximum(depth_thold, num_thold)                                       # (:442)
+    mask |= (span >= thold) & cand[None, None, :]                                       # (:443) masked entries never count
     return mask
 
 
@@ -152,7 +166,8 @@ def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
 # the whole step, structured like the reference (re-hashes every key, full sort, dense softmax)
 # ------------------------------------------------------------------------------------------
 def decode_step(usa, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, init_budget: int,
-                recent_budget: int, heavy_budget: float, return_parts: bool = False):
+                recent_budget: int, heavy_budget: float, return_parts: bool = False,
+                eval_mode: str = "simple", retrieve_depth: int = -1):
     """One layer's decode attention for one uniform batch, with the cost structure of the
     reference's forward (hashattention_llama.py:578-623 + compute_mask_multi :401-446):
     every key is hashed again with the 32 key MLPs, scores are sorted in full, attention is
@@ -165,7 +180,8 @@ def decode_step(usa, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, init_bud
     k_pre = mlp_preact(nets_from_usa(usa, "k"), k_rep)                           # (:168)
     q_pre = mlp_preact(nets_from_usa(usa, "q"), q[:, :, None, :])                # (:169)
     span = span_scores(q_pre, k_pre)                                             # (:171-187)
-    mask = select_mask(span, init_budget, recent_budget, heavy_budget)           # (:423-438)
+    mask = select_mask(span, init_budget, recent_budget, heavy_budget, eval_mode=eval_mode,
+                       retrieve_depth=retrieve_depth, bit_step=2.0)              # (:423-443)
     out = masked_attention(q, k, v, mask)                                        # (:585-615)
     if return_parts:
         return out, dict(q_pre=q_pre[:, :, 0, :], k_pre=k_pre, span=span, mask=mask)

@@ -78,13 +78,13 @@ class ListCache:
         return self.key_cache[layer_idx], self.value_cache[layer_idx]
 
 
-def reference_modules(Hq, Hkv, init, recent, heavy, seed=0, bf16_weights=True):
+def reference_modules(Hq, Hkv, init, recent, heavy, seed=0, bf16_weights=True, eval_mode="simple", depth=-1):
     cfg = LlamaConfig(hidden_size=Hq * 128, num_attention_heads=Hq, num_key_value_heads=Hkv, num_hidden_layers=1,
                       intermediate_size=256, vocab_size=128, max_position_embeddings=131072,
                       rope_parameters={"rope_theta": 500000.0, "rope_type": "default"})
     cfg.rope_theta = 500000.0
     for k, v in dict(lth_init_dim=128, lth_final_dim=32, lth_thold=0, lth_num_layers=3, init_budget=init,
-                     heavy_budget=heavy, recent_budget=recent, usa_eval_mode="simple", usa_retrieve_depth=-1).items():
+                     heavy_budget=heavy, recent_budget=recent, usa_eval_mode=eval_mode, usa_retrieve_depth=depth).items():
         setattr(cfg, k, v)
     torch.manual_seed(seed)
     usa = H.USA(Hq, 128, {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 3})
@@ -211,10 +211,38 @@ def config0():
     np.savez_compressed(os.path.join(HERE, "config0.npz"), **arrays)
 
 
+DEPTH_SUBCASES = [
+    # name, heavy, usa_retrieve_depth   (usa_eval_mode = "depth": the non-'simple' branch, :439-443)
+    ("d0", 1.0 / 8, 0),        # only the tokens tied at the best score
+    ("d2", 1.0 / 8, 2),
+    ("d6", 1.0 / 8, 6),        # the rank threshold wins: every token tied with the hb-th best is kept
+    ("neg", 1.0 / 8, -1),      # threshold above the best score: no heavy token
+    ("big_hb", 1.0, 3),        # hb beyond the candidates: the depth rule alone decides
+    ("abs5", 5.0, 4),          # absolute budget of 5 tokens
+]
+
+
+def depth():
+    """The inputs of case_a under the depth rule; codes and spans are those of case_a.npz."""
+    Hq, Hkv, S, init, recent = 8, 2, 520, 16, 16
+    inp = synthetic.make_decode_inputs(90, [S, S], Hq, Hkv, bf16=True)
+    q, k, v = inp.q, torch.stack(inp.k), torch.stack(inp.v)
+    arrays = dict(meta=np.array([Hq, Hkv, S, init, recent], dtype=np.int64),
+                  names=np.array([c[0] for c in DEPTH_SUBCASES]),
+                  heavy=np.array([c[1] for c in DEPTH_SUBCASES], dtype=np.float64),
+                  depth=np.array([c[2] for c in DEPTH_SUBCASES], dtype=np.int64))
+    for name, heavy, d in DEPTH_SUBCASES:
+        _, usa, att = reference_modules(Hq, Hkv, init, recent, heavy, eval_mode="depth", depth=d)
+        r = run_reference(att, usa, q, k, v)
+        arrays[name + "/mask"] = np.packbits(r["mask"].numpy(), axis=-1)
+        arrays[name + "/out"] = r["out"].numpy().astype(np.float32)
+    np.savez_compressed(os.path.join(HERE, "depth.npz"), **arrays)
+
+
 if __name__ == "__main__":
-    case_a()
-    edge()
-    config0()
+    which = sys.argv[1:] or ["case_a", "edge", "config0", "depth"]
+    for name in which:
+        {"case_a": case_a, "edge": edge, "config0": config0, "depth": depth}[name]()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

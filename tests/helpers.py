@@ -52,6 +52,25 @@ def load_case_a() -> GoldenCase:
                       float(z["heavy"]))
 
 
+class DepthCase:
+    """case_a's inputs under the depth rule (usa_eval_mode != 'simple'): budget, depth, the
+    reference's keep-mask and attention output."""
+
+    def __init__(self, base: GoldenCase, heavy: float, depth: int, mask, out):
+        self.base, self.heavy, self.depth, self.mask, self.out = base, float(heavy), int(depth), mask, out
+
+
+def load_depth() -> dict[str, DepthCase]:
+    base = load_case_a()
+    z = np.load(os.path.join(GOLDEN, "depth.npz"))
+    assert [int(x) for x in z["meta"]][2:] == [base.S, base.init, base.recent]
+    out = {}
+    for name, heavy, depth in zip(z["names"], z["heavy"], z["depth"]):
+        mask = torch.from_numpy(np.unpackbits(z[f"{name}/mask"], axis=-1)[..., :base.S].astype(bool))
+        out[str(name)] = DepthCase(base, heavy, depth, mask, torch.from_numpy(z[f"{name}/out"]))
+    return out
+
+
 def load_edge() -> dict[str, GoldenCase]:
     z = np.load(os.path.join(GOLDEN, "edge.npz"))
     q, k, v = from_bf16_bits(z["q"]), from_bf16_bits(z["k"]), from_bf16_bits(z["v"])

@@ -200,7 +200,8 @@ def run_step_and_check(device, usa, q, ks, vs, budget, shuffle_seed=11, via_host
         assert helpers.codes_match(q_codes[b], orc.pack_codes(q_pre[0]), orc.band_mask(q_pre[0]))
         identical &= bool((k_codes == orc.pack_codes(k_pre[0])).all()) and bool((q_codes[b] == orc.pack_codes(q_pre[0])).all())
         scores = orc.hamming_scores(q_codes[b][None], k_codes[None])
-        mask = orc.select_mask(scores, budget.init_budget, budget.recent_budget, budget.heavy_budget)
+        mask = orc.select_mask(scores, budget.init_budget, budget.recent_budget, budget.heavy_budget,
+                               eval_mode=budget.eval_mode, retrieve_depth=budget.retrieve_depth)
         want = orc.heavy_sets(mask, budget.init_budget, budget.recent_budget)[0]
         for h in range(Hq):
             assert torch.equal(heavy_from_device(ctx, b, h), want[h]), f"set differs b={b} h={h}"
@@ -225,6 +226,43 @@ def test_decode_step_end_to_end_against_reference_output(device, cases, name):
                 assert torch.equal(heavy_from_device(ctx, b, h), want[b][h])
         ok, max_abs, rel = helpers.att_close(out, case.out)
         assert ok, f"{name}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
+
+
+@pytest.mark.parametrize("name", ["d0", "d2", "d6", "neg", "big_hb", "abs5"])
+def test_depth_rule_step_against_reference_output(device, name):
+    """usa_eval_mode != 'simple': variable-size sets with every tie kept (single-pass cluster
+    selection at this size); against the oracle on the device's codes and, when those equal the
+    reference's, against the recorded reference mask and output."""
+    c = helpers.load_depth()[name]
+    case = c.base
+    usa = synthetic.make_usa(case.q.shape[1], 128, 0, True)
+    ks, vs = [case.k[b] for b in range(case.k.shape[0])], [case.v[b] for b in range(case.v.shape[0])]
+    budget = ha.Budget(case.init, c.heavy, case.recent, "depth", c.depth)
+    _, out, ctx, cache = run_step_and_check(device, usa, case.q, ks, vs, budget)
+    codes_equal_ref = all(bool((cache.read_codes(b).cpu() == case.k_codes[b]).all()) for b in range(len(ks)))
+    codes_equal_ref &= bool(((ctx.q_codes.cpu().to(torch.int64) & ALL_BITS) == case.q_codes).all())
+    if codes_equal_ref:
+        want = orc.heavy_sets(c.mask, case.init, case.recent)
+        for b in range(len(ks)):
+            for h in range(case.q.shape[1]):
+                assert torch.equal(heavy_from_device(ctx, b, h), want[b][h])
+        ok, max_abs, rel = helpers.att_close(out, c.out)
+        assert ok, f"{name}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
+
+
+@pytest.mark.parametrize("depth", [1, 4])
+def test_depth_rule_on_the_two_pass_selection(device, monkeypatch, depth):
+    """40 units (two-pass selection, plan kernel) under the depth rule, plain and as staggered halves."""
+    Hq, Hkv = 16, 4
+    lens = [300, 1025, 64, 2000, 513, 777, 1300, 256, 900, 1500]
+    usa = synthetic.make_usa(Hq, 128, 3, True)
+    inp = synthetic.make_decode_inputs(103, lens, Hq, Hkv)
+    budget = ha.Budget(32, 1.0 / 8, 32, "depth", depth)
+    monkeypatch.setenv("HA_STAGGER", "0")
+    _, out0, ctx0, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
+    monkeypatch.setenv("HA_STAGGER", "1")
+    _, out1, ctx1, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
+    assert torch.equal(out0, out1) and torch.equal(ctx0.sel_cnt, ctx1.sel_cnt)
 
 
 def test_ragged_batch_shuffled_pages(device):

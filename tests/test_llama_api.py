@@ -58,9 +58,9 @@ def test_convert_usa_swaps_attention_and_keeps_weights():
 
 def test_unsupported_modes_raise():
     cfg = tiny_config(1)
-    cfg.usa_eval_mode = "depth"
-    with pytest.raises(NotImplementedError):
-        hal.LlamaAttention_heavy_hitter(cfg, 0)
+    cfg.usa_eval_mode, cfg.usa_retrieve_depth = "depth", 3   # the depth rule is supported
+    att = hal.LlamaAttention_heavy_hitter(cfg, 0)
+    assert (att.usa_eval_mode, att.usa_retrieve_depth) == ("depth", 3)
     cfg = tiny_config(1)
     cfg.num_key_value_heads = 2
     with pytest.raises(NotImplementedError):
