@@ -63,6 +63,8 @@ PROTOTYPES = {
     "ha_sparse_decode": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P, c_size_t, _P, _P]),
     "ha_decode_step": (c_int, [_S, _B, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P,
                                c_size_t, _P, _P]),
+    "ha_decode_step_rows": (c_int, [_S, _B, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P,
+                                    c_size_t, _P, _P]),
     "ha_decode_step_host": (c_int, [_S, _B, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                     _P, _P, _P, c_float, _P, c_size_t, _P, _P, c_int]),
 }

@@ -42,15 +42,17 @@ struct SeqRange {
 
 // Budget arithmetic of compute_mask_multi (hashattention/hashattention_llama.py:423-435):
 // candidates exclude the first init and last recent tokens; the heavy budget is
-// int(k * heavy_budget) for heavy_budget <= 1.0, int(heavy_budget) otherwise.
+// int(k * heavy_budget) for heavy_budget <= 1.0, int(heavy_budget) otherwise. k is the length of the
+// key sequence: S itself for a single query token; for a row of a multi-token chunk the length
+// after the whole chunk (budget_len), while S is what the row's own token may see.
 __host__ __device__ inline SeqRange seq_range(int S, int init_budget, int recent_budget,
-                                              double heavy_budget) {
+                                              double heavy_budget, int budget_len = -1) {
     SeqRange r;
     r.S = S;
     r.lo = init_budget < S ? init_budget : S;
     int tail = S - recent_budget;
     r.hi = tail > r.lo ? tail : r.lo;
-    int hb = heavy_budget > 1.0 ? (int)heavy_budget : (int)((double)S * heavy_budget);
+    int hb = heavy_budget > 1.0 ? (int)heavy_budget : (int)((double)(budget_len >= 0 ? budget_len : S) * heavy_budget);
     if (hb < 0) hb = 0;
     int ncand = r.hi - r.lo;
     r.hb = hb < ncand ? hb : ncand;

@@ -199,12 +199,14 @@ namespace {
 SelectParams select_params(const ha_shape_t* shape, const ha_budget_t* budget, const uint32_t* q_codes,
                            const uint32_t* hash_pages, const int32_t* page_table, const int32_t* seq_lens,
                            int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg, int32_t* status,
-                           uint32_t* hist, int32_t* plan, uint32_t* scores, int32_t* sel_rows) {
+                           uint32_t* hist, int32_t* plan, uint32_t* scores, int32_t* sel_rows,
+                           const int32_t* budget_lens = nullptr) {
     SelectParams p;
     p.q_codes = q_codes;
     p.hash_pages = reinterpret_cast<const uint4*>(hash_pages);
     p.page_table = page_table;
     p.seq_lens = seq_lens;
+    p.budget_lens = budget_lens;
     p.hist = hist;
     p.plan = plan;
     p.scores = scores;
@@ -234,7 +236,8 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                        const int32_t* page_table, const int32_t* seq_lens,
                        const int32_t* sel, const int32_t* sel_cnt, bool physical, float sm_scale,
                        void* out, void* workspace, size_t workspace_bytes,
-                       int32_t* status, void* stream, int kvh0 = 0, int nkvh = -1, int merge_priority = 0) {
+                       int32_t* status, void* stream, int kvh0 = 0, int nkvh = -1, int merge_priority = 0,
+                       const int32_t* budget_lens = nullptr) {
     int rc = check_shape(shape);
     if (rc != HA_OK) return rc;
     rc = check_budget(budget);
@@ -254,6 +257,7 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
     p.page_table = page_table;
     p.seq_lens = seq_lens;
+    p.budget_lens = budget_lens;
     p.sel = physical ? w.sel_rows : sel;
     p.sel_cnt = budget->eval_mode == HA_EVAL_SIMPLE ? nullptr : sel_cnt;  // simple: the count follows from the budget
     p.out = static_cast<__nv_bfloat16*>(out);
@@ -364,7 +368,7 @@ int staggered_select_attend(const ha_shape_t* shape, const ha_budget_t* budget, 
                             const void* k_pages, const void* v_pages, const uint32_t* hash_pages,
                             const int32_t* page_table, const int32_t* seq_lens, const uint32_t* q_codes,
                             int32_t* sel_idx, int32_t* sel_cnt, float sm_scale, void* out, void* workspace,
-                            size_t workspace_bytes, int32_t* status, cudaStream_t s) {
+                            size_t workspace_bytes, int32_t* status, cudaStream_t s, const int32_t* budget_lens) {
     int rc = check_budget(budget);
     if (rc != HA_OK) return rc;
     if (q_codes == nullptr || hash_pages == nullptr || page_table == nullptr || seq_lens == nullptr ||
@@ -375,7 +379,8 @@ int staggered_select_attend(const ha_shape_t* shape, const ha_budget_t* budget, 
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
     const int parts = stagger_parts(shape);
     const SelectParams base = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx,
-                                            sel_cnt, nullptr, status, w.hist, w.plan, w.scores, w.sel_rows);
+                                            sel_cnt, nullptr, status, w.hist, w.plan, w.scores, w.sel_rows,
+                                            budget_lens);
 
     std::lock_guard<std::mutex> lock(g_stagger_mutex);
     StaggerResources* r = stagger_resources();
@@ -398,7 +403,8 @@ int staggered_select_attend(const ha_shape_t* shape, const ha_budget_t* budget, 
         }
         ok = ok && launch_plan_select(shape, p, n, si, light) == cudaSuccess;
         ok = ok && sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, nullptr, sel_cnt, true,
-                                      sm_scale, out, workspace, workspace_bytes, status, si, first, n, light) == HA_OK;
+                                      sm_scale, out, workspace, workspace_bytes, status, si, first, n, light,
+                                      budget_lens) == HA_OK;
         first += n;
     }
     for (int i = 1; i < parts; ++i)
@@ -600,11 +606,11 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
-int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
-                    const uint32_t* q_codes, const uint32_t* hash_pages,
-                    const int32_t* page_table, const int32_t* seq_lens,
-                    int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg,
-                    void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+static int score_select_impl(const ha_shape_t* shape, const ha_budget_t* budget,
+                             const uint32_t* q_codes, const uint32_t* hash_pages,
+                             const int32_t* page_table, const int32_t* seq_lens, const int32_t* budget_lens,
+                             int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg,
+                             void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
     int rc = check_shape(shape);
     if (rc != HA_OK) return rc;
     rc = check_budget(budget);
@@ -617,7 +623,7 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
 
     const SelectParams p = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
-                                         scores_dbg, status, w.hist, w.plan, w.scores, w.sel_rows);
+                                         scores_dbg, status, w.hist, w.plan, w.scores, w.sel_rows, budget_lens);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const long long max_tokens = (long long)shape->max_pages * kPage;
     if (use_cluster_select(shape)) {
@@ -628,6 +634,15 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
         return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
     }
     return launch_two_pass_select(shape, p, shape->num_kv_heads, s) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+}
+
+int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
+                    const uint32_t* q_codes, const uint32_t* hash_pages,
+                    const int32_t* page_table, const int32_t* seq_lens,
+                    int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg,
+                    void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+    return score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, nullptr, sel_idx, sel_cnt,
+                             scores_dbg, workspace, workspace_bytes, status, stream);
 }
 
 int ha_sparse_decode(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -647,7 +662,7 @@ static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                             const ha_hash_weights_t* weights,
                             const void* q, const void* k_new, const void* v_new, void* q_stage,
                             void* k_pages, void* v_pages, uint32_t* hash_pages,
-                            const int32_t* page_table, const int32_t* seq_lens,
+                            const int32_t* page_table, const int32_t* seq_lens, const int32_t* budget_lens,
                             uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
                             void* out, void* workspace, size_t workspace_bytes,
                             int32_t* status, void* stream) {
@@ -658,13 +673,13 @@ static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     if (use_stagger(shape))
         return staggered_select_attend(shape, budget, q_att, k_pages, v_pages, hash_pages, page_table, seq_lens,
                                        q_codes, sel_idx, sel_cnt, sm_scale, out, workspace, workspace_bytes, status,
-                                       static_cast<cudaStream_t>(stream));
-    rc = ha_score_select(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
-                         nullptr, workspace, workspace_bytes, status, stream);
+                                       static_cast<cudaStream_t>(stream), budget_lens);
+    rc = score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, budget_lens, sel_idx, sel_cnt,
+                           nullptr, workspace, workspace_bytes, status, stream);
     if (rc != HA_OK) return rc;
     // the selection kernel left the physical rows of the heavy tokens in the workspace
     return sparse_decode_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, nullptr, sel_cnt, true,
-                              sm_scale, out, workspace, workspace_bytes, status, stream);
+                              sm_scale, out, workspace, workspace_bytes, status, stream, 0, -1, 0, budget_lens);
 }
 
 int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -676,7 +691,21 @@ int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
                    void* out, void* workspace, size_t workspace_bytes,
                    int32_t* status, void* stream) {
     return decode_step_impl(shape, budget, weights, q, k_new, v_new, nullptr, k_pages, v_pages, hash_pages,
-                            page_table, seq_lens, q_codes, sel_idx, sel_cnt, sm_scale, out, workspace,
+                            page_table, seq_lens, nullptr, q_codes, sel_idx, sel_cnt, sm_scale, out, workspace,
+                            workspace_bytes, status, stream);
+}
+
+int ha_decode_step_rows(const ha_shape_t* shape, const ha_budget_t* budget,
+                        const ha_hash_weights_t* weights,
+                        const void* q, const void* k_new, const void* v_new,
+                        void* k_pages, void* v_pages, uint32_t* hash_pages,
+                        const int32_t* page_table, const int32_t* seq_lens, const int32_t* budget_lens,
+                        uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
+                        void* out, void* workspace, size_t workspace_bytes,
+                        int32_t* status, void* stream) {
+    if (budget_lens == nullptr) return check_shape(shape) != HA_OK ? check_shape(shape) : HA_ERR_BAD_ARG;
+    return decode_step_impl(shape, budget, weights, q, k_new, v_new, nullptr, k_pages, v_pages, hash_pages,
+                            page_table, seq_lens, budget_lens, q_codes, sel_idx, sel_cnt, sm_scale, out, workspace,
                             workspace_bytes, status, stream);
 }
 
@@ -720,7 +749,7 @@ int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
                           (v_new_host == nullptr || v_map != nullptr);
     if (in_place) {
         rc = decode_step_impl(shape, budget, weights, q_map, k_map, v_map, q_dev, k_pages, v_pages, hash_pages,
-                              page_table, seq_lens, q_codes, sel_idx, sel_cnt, sm_scale, out_map, workspace,
+                              page_table, seq_lens, nullptr, q_codes, sel_idx, sel_cnt, sm_scale, out_map, workspace,
                               workspace_bytes, status, stream);
         if (rc != HA_OK) return rc;
     } else {

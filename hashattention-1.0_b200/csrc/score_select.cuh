@@ -47,6 +47,7 @@ struct SelectParams {
     const uint4* hash_pages;   // [num_pages][Hkv][256] x 16 B
     const int32_t* page_table;
     const int32_t* seq_lens;
+    const int32_t* budget_lens;  // [B] or null: the length the heavy budget is a fraction of, if not seq_lens
     uint32_t* hist;            // workspace: [B][Hkv][4*33][nchunks]
     int32_t* sel_idx;          // [B][Hq][sel_stride] token indices
     int32_t* sel_rows;         // workspace: [B][Hq][sel_stride] page * 256 + slot of the same tokens
@@ -289,7 +290,8 @@ __global__ void __launch_bounds__(kSelThreads) select_plan_kernel(const SelectPa
     const int kvh = p.kvh0 + blockIdx.x, b = blockIdx.y;
     const int S = p.seq_lens[b];
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
-    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
+    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget,
+                                 p.budget_lens != nullptr ? p.budget_lens[b] : -1);
     pdl_wait();
     HA_TL(kTlSelectPlan, kTlAfterWait);
     pdl_launch_dependents();
@@ -313,7 +315,8 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage;
     const int chunk_start = c * chunk_tokens;
     const bool active = s_ok && chunk_start < S;
-    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
+    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget,
+                                 p.budget_lens != nullptr ? p.budget_lens[b] : -1);
     RoundWords rw;
     if (active) rw.load(p, b, kvh, RoundWords::first_token(chunk_start, 0, warp), lane, r);
 
@@ -633,7 +636,8 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
 
     const int S = p.seq_lens[b];
     const bool s_ok = S >= 1 && S <= p.max_pages * kPage && S <= ROUNDS * kClRoundTokens;
-    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
+    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget,
+                                 p.budget_lens != nullptr ? p.budget_lens[b] : -1);
     auto first_token = [&](int rd) { return rd * kClRoundTokens + rank * kClCtaTokens + warp * (kLaneTokens * 32); };
     RoundWords rw;
     const bool active0 = s_ok && first_token(0) < S;  // warp-uniform

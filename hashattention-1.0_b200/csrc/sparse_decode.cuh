@@ -31,6 +31,7 @@ struct SparseDecodeParams {
     const __nv_bfloat16* v_pages;
     const int32_t* page_table;
     const int32_t* seq_lens;
+    const int32_t* budget_lens;    // [B] or null: the length the heavy budget is a fraction of, if not seq_lens
     const int32_t* sel;            // [B][Hq][sel_stride]: token indices, or physical rows (kPhysical)
     const int32_t* sel_cnt;        // [B][Hq] entries of `sel` in use, or null: min(heavy budget, candidates),
                                    // which needs no load (HA_EVAL_SIMPLE always selects exactly that many)
@@ -84,7 +85,8 @@ __device__ __forceinline__ AttPlan att_plan(const SparseDecodeParams& p, int b, 
     AttPlan a;
     const int S = p.seq_lens[b];
     a.ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by the selection kernels
-    a.r = seq_range(a.ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget);
+    a.r = seq_range(a.ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget,
+                    p.budget_lens != nullptr ? p.budget_lens[b] : -1);
     a.cnt = listed >= 0 ? min(listed, min(a.r.hi - a.r.lo, p.sel_stride)) : min(a.r.hb, p.sel_stride);
     a.n_total = a.ok ? a.r.lo + a.cnt + (a.r.S - a.r.hi) : 0;
     const int rows_per_cta = kAttRoundRows * p.rounds;

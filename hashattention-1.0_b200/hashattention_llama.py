@@ -19,8 +19,10 @@ What runs where
     every cached key on every decode step, :405-408.)
   * Both ``usa_eval_mode`` settings are implemented: 'simple' (the ``hb`` best candidates) and the
     depth rule of every other mode string (:439-443).
-  * 2 <= q_len <= 128, training (``train_usa``) and statistics (``collect_stats``) are not
-    implemented and raise ``NotImplementedError``.
+  * 2 <= q_len <= 128 (chunked / speculative decode, :529): the same library path with one row per
+    (sequence, new token); needs ``recent_budget >= q_len - 1``.
+  * Training (``train_usa``) and statistics (``collect_stats``) are not implemented and raise
+    ``NotImplementedError``.
 """
 from __future__ import annotations
 
@@ -31,7 +33,7 @@ import torch
 from torch import nn
 
 from .cache import PAGE, PagedHashKVCache
-from .ops import Budget, SparseDecodeContext
+from .ops import Budget, ChunkRows, SparseDecodeContext
 from .torch_ops import decode_step_op
 from .usa import USA
 
@@ -97,6 +99,7 @@ class LlamaAttention_heavy_hitter(nn.Module):
         # longest sequence the paged cache is sized for; set config.usa_max_seq_len to change it
         self.max_seq_len = int(getattr(config, "usa_max_seq_len", self.max_position_embeddings))
         self._ctx: Optional[SparseDecodeContext] = None
+        self._row_ctx: dict = {}  # (id of the decode context, q_len) -> context over ChunkRows
 
     def __repr__(self):
         return (f"{super().__repr__()}\nSparsification Setting(topk:{self.heavy_budget}  edge:{self.init_budget, self.recent_budget} \n"
@@ -117,6 +120,14 @@ class LlamaAttention_heavy_hitter(nn.Module):
                             "simple" if self.usa_eval_mode == "simple" else "depth", int(self.usa_retrieve_depth))
             self._ctx = SparseDecodeContext(cache, budget, self.usa_module.packed(device))
         return self._ctx
+
+    def _rows_context(self, ctx: SparseDecodeContext, q_len: int) -> SparseDecodeContext:
+        """The context of a multi-token step of ``q_len`` tokens per sequence: rows over the same cache."""
+        key = (id(ctx), q_len)
+        if key not in self._row_ctx:
+            self._row_ctx = {k: v for k, v in self._row_ctx.items() if k[0] == id(ctx)}  # drop rows of an old cache
+            self._row_ctx[key] = SparseDecodeContext(ChunkRows(ctx.cache, q_len), ctx.budget, ctx.weights)
+        return self._row_ctx[key]
 
     def _prefill(self, hidden_states, past, kwargs, new_style):
         if self.flash_forward is None:
@@ -151,24 +162,35 @@ class LlamaAttention_heavy_hitter(nn.Module):
                        **kwargs)
             fwd["past_key_values" if new_style else "past_key_value"] = past
             return self._prefill(hidden_states, past, fwd, new_style)
-        if q_len != 1:
-            raise NotImplementedError("multi-token decode (2 <= q_len <= 128) is not implemented")
+        if q_len > 1 and self.recent_budget < q_len - 1:
+            raise NotImplementedError("multi-token decode needs recent_budget >= q_len - 1")
         if position_embeddings is None:
             raise ValueError("position_embeddings=(cos, sin) is required")
 
-        q = self.q_proj(hidden_states).view(bsz, 1, self.num_heads, self.head_dim).transpose(1, 2)
-        k = self.k_proj(hidden_states).view(bsz, 1, self.num_key_value_heads, self.head_dim).transpose(1, 2)
-        v = self.v_proj(hidden_states).view(bsz, 1, self.num_key_value_heads, self.head_dim).transpose(1, 2)
+        q = self.q_proj(hidden_states).view(bsz, q_len, self.num_heads, self.head_dim).transpose(1, 2)
+        k = self.k_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim).transpose(1, 2)
+        v = self.v_proj(hidden_states).view(bsz, q_len, self.num_key_value_heads, self.head_dim).transpose(1, 2)
         cos, sin = position_embeddings
         q, k = _apply_rotary(q, k, cos, sin)
         if past is not None:  # keeps the caller's cache object consistent (sequence length bookkeeping)
             past.update(k, v, self.layer_idx, {"sin": sin, "cos": cos, "cache_position": cache_position})
 
         ctx = self._context(bsz, hidden_states.device)
-        ctx.cache.seq_lens += 1
-        out = decode_step_op(ctx, q[:, :, 0].to(torch.bfloat16).contiguous(),
-                             k[:, :, 0].to(torch.bfloat16).contiguous(), v[:, :, 0].to(torch.bfloat16).contiguous())
-        attn_output = self.o_proj(out.reshape(bsz, 1, self.hidden_size).to(hidden_states.dtype))
+        if q_len == 1:
+            ctx.cache.seq_lens += 1
+            out = decode_step_op(ctx, q[:, :, 0].to(torch.bfloat16).contiguous(),
+                                 k[:, :, 0].to(torch.bfloat16).contiguous(), v[:, :, 0].to(torch.bfloat16).contiguous())
+        else:
+            # 2 <= q_len <= 128 (:529): one row per (sequence, new token), each a single-token problem on
+            # the keys up to its own with the budget of the whole length (:423-434)
+            rctx = self._rows_context(ctx, q_len)
+            rctx.cache.advance()
+
+            def rows(t):  # [B, heads, q_len, D] -> [B * q_len, heads, D]
+                return t.transpose(1, 2).reshape(bsz * q_len, t.shape[1], self.head_dim).to(torch.bfloat16).contiguous()
+
+            out = rctx.decode_step_rows(rows(q), rows(k), rows(v))
+        attn_output = self.o_proj(out.reshape(bsz, q_len, self.hidden_size).to(hidden_states.dtype))
         if new_style:
             return attn_output, None
         return attn_output, None, past

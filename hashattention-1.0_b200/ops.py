@@ -216,6 +216,31 @@ class SparseDecodeContext:
         _raise_on(rc, "ha_sparse_decode")
         return out
 
+    def decode_step_rows(self, q, k_new, v_new, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Multi-token decode on a context built over :class:`ChunkRows` (``ha_decode_step_rows``):
+        ``q [rows, Hq, 128]``, ``k_new / v_new [rows, Hkv, 128]`` in the rows' order; the rows' lengths
+        must have been set with ``ChunkRows.advance()``."""
+        c = self.cache
+        if not isinstance(c, ChunkRows):
+            raise ValueError("decode_step_rows needs a context built on ChunkRows")
+        if self.budget.recent_budget < c.q_len - 1:
+            raise NotImplementedError("multi-token decode needs recent_budget >= q_len - 1")
+        self._check_q(q)
+        self._check_kv_new(k_new, v_new)
+        if v_new is None:
+            raise ValueError("v_new is required")
+        out = torch.empty_like(q) if out is None else out
+        _check(out, "out", torch.bfloat16, (self.batch, self.num_q_heads, HEAD_DIM), self.device)
+        with torch.cuda.device(self.device):
+            rc = self.lib.ha_decode_step_rows(
+                self.shape, self.c_budget, self.c_weights, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
+                c.k_pages.data_ptr(), c.v_pages.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
+                c.seq_lens.data_ptr(), c.budget_lens.data_ptr(), self.q_codes.data_ptr(), self.sel_idx.data_ptr(),
+                self.sel_cnt.data_ptr(), self.sm_scale, out.data_ptr(), self.workspace.data_ptr(),
+                self.workspace_bytes, self.status.data_ptr(), _stream_ptr(self.device))
+        _raise_on(rc, "ha_decode_step_rows")
+        return out
+
     def decode_step(self, q, k_new, v_new, out: torch.Tensor | None = None) -> torch.Tensor:
         """The whole step (encode + append, score + select, sparse attention) in one library call."""
         self._check_q(q)
@@ -232,6 +257,34 @@ class SparseDecodeContext:
                 self.workspace.data_ptr(), self.workspace_bytes, self.status.data_ptr(), _stream_ptr(self.device))
         _raise_on(rc, "ha_decode_step")
         return out
+
+
+class ChunkRows:
+    """A multi-token decode step laid out as rows for ``ha_decode_step_rows``: ``q_len`` new tokens
+    for each of the ``B`` sequences of ``cache`` become ``B * q_len`` rows (sequence-major) that share
+    the cache's page pools; row ``b * q_len + i`` sees the first ``old_len[b] + i + 1`` tokens and
+    appends token ``old_len[b] + i``. It quacks like a :class:`PagedHashKVCache` with ``B * q_len``
+    sequences, so a :class:`SparseDecodeContext` can be built on it (one per chunk length)."""
+
+    def __init__(self, cache: PagedHashKVCache, q_len: int):
+        if q_len < 1:
+            raise ValueError("q_len must be positive")
+        self.base, self.q_len = cache, q_len
+        self.device, self.batch, self.num_kv_heads = cache.device, cache.batch * q_len, cache.num_kv_heads
+        self.max_pages, self.num_pages = cache.max_pages, cache.num_pages
+        self.k_pages, self.v_pages, self.hash_pages = cache.k_pages, cache.v_pages, cache.hash_pages
+        self.page_table = cache.page_table.repeat_interleave(q_len, dim=0).contiguous()
+        self.seq_lens = torch.zeros(self.batch, dtype=torch.int32, device=self.device)
+        self.budget_lens = torch.zeros(self.batch, dtype=torch.int32, device=self.device)
+        self._offsets = torch.arange(1, q_len + 1, dtype=torch.int32, device=self.device)
+
+    def advance(self) -> None:
+        """Sets the rows' lengths for a chunk that starts at the base cache's current lengths and
+        moves the base cache's lengths past the chunk."""
+        old = self.base.seq_lens
+        self.seq_lens.copy_((old[:, None] + self._offsets[None, :]).reshape(-1))
+        self.budget_lens.copy_((old + self.q_len).repeat_interleave(self.q_len))
+        old += self.q_len
 
 
 class HostStepBuffers:

@@ -203,6 +203,25 @@ int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
                    void* out, void* workspace, size_t workspace_bytes,
                    int32_t* status, void* stream);
 
+/* Multi-token decode: 2 <= q_len <= 128 new tokens per sequence in one call (the reference sends
+ * them through the same sparse path: hashattention/hashattention_llama.py:529, with the causal /
+ * recent diagonal of compute_mask_multi :423-428). The caller lays the step out as ROWS, one per
+ * (sequence, new token): shape->batch = number of rows; q, k_new, v_new, out, q_codes, sel_idx,
+ * sel_cnt are indexed by row; page_table row r repeats the page list of the row's sequence;
+ * seq_lens[r] = position of the row's token + 1 (what that query may see, its own key included and
+ * appended by this call); budget_lens[r] = length of the sequence after the whole chunk, the k of
+ * int(k * heavy_budget) (:431-434). Every row is then exactly one ha_decode_step problem.
+ * Requires recent_budget >= q_len - 1: a token of the chunk is then never a selection candidate
+ * of a later row of the same call (its hash word is written by this call).                      */
+int ha_decode_step_rows(const ha_shape_t* shape, const ha_budget_t* budget,
+                        const ha_hash_weights_t* weights,
+                        const void* q, const void* k_new, const void* v_new,
+                        void* k_pages, void* v_pages, uint32_t* hash_pages,
+                        const int32_t* page_table, const int32_t* seq_lens, const int32_t* budget_lens,
+                        uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
+                        void* out, void* workspace, size_t workspace_bytes,
+                        int32_t* status, void* stream);
+
 /* Number of kernels one ha_decode_step call enqueues for this shape and budget (the library picks
  * between a single-pass and a two-pass selection, and may run large steps as two staggered halves
  * of the kv-heads); 0 for an invalid shape. For launch accounting; no reference counterpart.     */

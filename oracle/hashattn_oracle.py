@@ -163,6 +163,67 @@ def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: to
 
 
 # ------------------------------------------------------------------------------------------
+# multi-token decode (2 <= q_len <= 128 query tokens in one call)
+# ------------------------------------------------------------------------------------------
+def select_mask_rows(span: torch.Tensor, init_budget: int, recent_budget: int, heavy_budget: float,
+                     stable: bool = True, eval_mode: str = "simple", retrieve_depth: int = -1,
+                     bit_step: float = 1.0) -> torch.Tensor:
+    """compute_mask_multi for ``q`` query tokens against ``k`` keys (hashattention_llama.py:423-443):
+    ``span [B,H,q,k]`` -> keep-mask ``[B,H,q,k]``. Query ``i`` sits at key position ``k - q + i``; its
+    candidates are the keys ``init <= j <= k - q + i - recent`` (:423-424), the budget is
+    ``int(k * heavy_budget)`` for every row (:431-434). As in the reference, surplus budget of a row
+    (``hb`` > its candidates) falls on masked positions in index order, which can include positions
+    after the query; the causal attention mask removes those again (masked_attention_rows)."""
+    B, H, q, k = span.shape
+    cand = torch.tril(torch.ones(q, k), diagonal=k - q - recent_budget).bool()            # (:423)
+    cand[:, :init_budget] = False                                                         # (:424)
+    span = span.to(torch.float32).masked_fill(~cand, torch.finfo(torch.float32).min)      # (:426)
+    causal = torch.tril(torch.ones(q, k), diagonal=k - q).bool()                          # (:427)
+    mask = (causal & ~cand)[None, None].expand(B, H, q, k).clone()                        # (:428)
+    values, indices = span.sort(dim=-1, descending=True, stable=stable)                   # (:430)
+    hb = heavy_tokens(k, heavy_budget)
+    if eval_mode == "simple":
+        mask.scatter_(3, indices[..., :hb], True)                                         # (:437-438)
+        return mask
+    if hb < 1:
+        return mask
+    hb = min(hb, k)
+    thold = torch.maximum(values[..., :1] - bit_step * retrieve_depth, values[..., hb - 1:hb])   # (:440-442)
+    mask |= (span >= thold) & cand[None, None]                                            # (:443)
+    return mask
+
+
+def masked_attention_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """hashattention_llama.py:578-623 for q_len > 1 in fp32 with the causal attention mask a decoder
+    passes (:593-598): ``q [B,Hq,q,D]``, ``k,v [B,Hkv,S,D]``, ``mask [B,Hq,q,S]`` -> ``[B,Hq,q,D]``."""
+    B, Hq, ql, D = q.shape
+    S = k.shape[2]
+    group = Hq // k.shape[1]
+    kk = k.to(torch.float32).repeat_interleave(group, dim=1)
+    vv = v.to(torch.float32).repeat_interleave(group, dim=1)
+    w = torch.einsum("bhqd,bhsd->bhqs", q.to(torch.float32), kk) / math.sqrt(D)           # (:585)
+    causal = torch.tril(torch.ones(ql, S), diagonal=S - ql).bool()
+    w = w + torch.zeros(ql, S).masked_fill(~causal, torch.finfo(torch.float32).min)       # (:593-598)
+    w = w.masked_fill(~mask, torch.finfo(torch.float32).min)                              # (:606)
+    w = torch.softmax(w, dim=-1, dtype=torch.float32)                                     # (:613)
+    return torch.einsum("bhqs,bhsd->bhqd", w, vv)                                         # (:615)
+
+
+def decode_chunk(usa, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, init_budget: int, recent_budget: int,
+                 heavy_budget: float, eval_mode: str = "simple", retrieve_depth: int = -1) -> torch.Tensor:
+    """decode_step for ``q_len`` query tokens: ``q [B,Hq,q_len,D]``, ``k,v [B,Hkv,S,D]`` with the chunk's
+    tokens last -> ``[B,Hq,q_len,D]`` (hashattention_llama.py:529-623 with a causal attention mask)."""
+    group = q.shape[1] // k.shape[1]
+    k_rep = k.to(torch.float32).repeat_interleave(group, dim=1)
+    k_pre = mlp_preact(nets_from_usa(usa, "k"), k_rep)
+    q_pre = mlp_preact(nets_from_usa(usa, "q"), q)
+    span = torch.einsum("bhqd,bhsd->bhqs", torch.sign(q_pre), torch.sign(k_pre))          # (:171-187)
+    mask = select_mask_rows(span, init_budget, recent_budget, heavy_budget, eval_mode=eval_mode,
+                            retrieve_depth=retrieve_depth, bit_step=2.0)
+    return masked_attention_rows(q, k, v, mask)
+
+
+# ------------------------------------------------------------------------------------------
 # the whole step, structured like the reference (re-hashes every key, full sort, dense softmax)
 # ------------------------------------------------------------------------------------------
 def decode_step(usa, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, init_budget: int,

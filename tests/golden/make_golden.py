@@ -120,6 +120,29 @@ def run_reference(att, usa, q, k, v):
     return dict(k_pre=k_pre, q_pre=q_pre, span=span[:, :, 0], mask=mask[:, :, 0], out=out.reshape(B, Hq, D))
 
 
+def run_reference_rows(att, usa, q, k, v):
+    """Multi-token decode through the reference: q [B,Hq,ql,128] (the last ql tokens' queries), k/v
+    [B,Hkv,S,128] with the ql new tokens last. The decoder's causal attention mask is passed as a
+    transformers model would (:593-598)."""
+    B, Hq, ql, D = q.shape
+    Hkv, S = k.shape[1], k.shape[2]
+    group = Hq // Hkv
+    with torch.no_grad(), stable_sort():
+        k_rep = H.repeat_kv(k, group)
+        span, _ = usa(k_rep, q, hard=True)
+        mask = att.compute_mask_multi(k_rep.clone(), q)
+        att.q_proj = Const(q.transpose(1, 2).reshape(B, ql, Hq * D))
+        att.k_proj = Const(k[:, :, -ql:].transpose(1, 2).reshape(B, ql, Hkv * D))
+        att.v_proj = Const(v[:, :, -ql:].transpose(1, 2).reshape(B, ql, Hkv * D))
+        att.o_proj = nn.Identity()
+        cache = ListCache(k[:, :, :-ql].clone(), v[:, :, :-ql].clone())
+        pos = (torch.ones(B, ql, D), torch.zeros(B, ql, D))
+        causal = torch.tril(torch.ones(ql, S), diagonal=S - ql).bool()
+        amask = torch.zeros(ql, S).masked_fill(~causal, torch.finfo(torch.float32).min)[None, None].expand(B, 1, ql, S)
+        out, _, _ = att(torch.zeros(B, ql, Hq * D), attention_mask=amask, past_key_value=cache, position_embeddings=pos)
+    return dict(span=span, mask=mask, out=out.reshape(B, ql, Hq, D).transpose(1, 2))
+
+
 def pack(pre):
     w = 2 ** torch.arange(32, dtype=torch.int64)
     return ((pre > 0).to(torch.int64) * w).sum(-1)
@@ -239,10 +262,43 @@ def depth():
     np.savez_compressed(os.path.join(HERE, "depth.npz"), **arrays)
 
 
+ROWS_SUBCASES = [
+    # name, S (after the chunk), q_len, init, recent, heavy, eval_mode, depth
+    ("q5", 520, 5, 16, 16, 1.0 / 8, "simple", -1),
+    ("q16_page", 260, 16, 8, 16, 1.0 / 8, "simple", -1),    # the chunk crosses the page boundary at 256
+    ("q3_short", 40, 3, 16, 16, 1.0 / 8, "simple", -1),     # rows without any candidate, budget surplus
+    ("q4_depth", 520, 4, 16, 16, 1.0 / 8, "depth", 3),
+]
+
+
+def rows():
+    """Multi-token decode (2 <= q_len <= 128): queries of the last q_len tokens of case_a-like inputs."""
+    Hq, Hkv = 8, 2
+    arrays = dict(names=np.array([c[0] for c in ROWS_SUBCASES]),
+                  params=np.array([[c[1], c[2], c[3], c[4], c[7]] for c in ROWS_SUBCASES], dtype=np.int64),
+                  heavy=np.array([c[5] for c in ROWS_SUBCASES], dtype=np.float64),
+                  modes=np.array([c[6] for c in ROWS_SUBCASES]), meta=np.array([Hq, Hkv], dtype=np.int64))
+    inp = synthetic.make_decode_inputs(92, [520, 520], Hq, Hkv, bf16=True)
+    k_all, v_all = torch.stack(inp.k), torch.stack(inp.v)   # every subcase uses the first S tokens of these
+    arrays.update(k=bf16_bits(k_all), v=bf16_bits(v_all))
+    for name, S, ql, init, recent, heavy, mode, d in ROWS_SUBCASES:
+        k, v = k_all[:, :, :S].contiguous(), v_all[:, :, :S].contiguous()
+        gen = torch.Generator().manual_seed(920 + ql)
+        q = torch.randn(2, Hq, ql, 128, generator=gen).to(torch.bfloat16).to(torch.float32)
+        _, usa, att = reference_modules(Hq, Hkv, init, recent, heavy, eval_mode=mode, depth=d)
+        r = run_reference_rows(att, usa, q, k, v)
+        span = r["span"]
+        assert float((span - span.round()).abs().max()) == 0.0
+        arrays.update({name + "/q": bf16_bits(q), name + "/span": span.to(torch.int8).numpy(),
+                       name + "/mask": np.packbits(r["mask"].numpy(), axis=-1),
+                       name + "/out": r["out"].numpy().astype(np.float32)})
+    np.savez_compressed(os.path.join(HERE, "rows.npz"), **arrays)
+
+
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["case_a", "edge", "config0", "depth"]
+    which = sys.argv[1:] or ["case_a", "edge", "config0", "depth", "rows"]
     for name in which:
-        {"case_a": case_a, "edge": edge, "config0": config0, "depth": depth}[name]()
+        {"case_a": case_a, "edge": edge, "config0": config0, "depth": depth, "rows": rows}[name]()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

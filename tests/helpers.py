@@ -71,6 +71,30 @@ def load_depth() -> dict[str, DepthCase]:
     return out
 
 
+class RowsCase:
+    """Multi-token decode recorded from the reference: q [B,Hq,ql,D], k/v [B,Hkv,S,D] (the chunk's
+    tokens last), span / mask [B,Hq,ql,S], out [B,Hq,ql,D]."""
+
+    def __init__(self, z, name, S, ql, init, recent, depth, heavy, mode):
+        self.S, self.ql, self.init, self.recent, self.depth = int(S), int(ql), int(init), int(recent), int(depth)
+        self.heavy, self.mode = float(heavy), str(mode)
+        self.q = from_bf16_bits(z[f"{name}/q"])
+        self.k = from_bf16_bits(z["k"])[:, :, :self.S].contiguous()
+        self.v = from_bf16_bits(z["v"])[:, :, :self.S].contiguous()
+        self.span = torch.from_numpy(z[f"{name}/span"].astype(np.int64))
+        self.mask = torch.from_numpy(np.unpackbits(z[f"{name}/mask"], axis=-1)[..., :self.S].astype(bool))
+        self.out = torch.from_numpy(z[f"{name}/out"])
+
+    @property
+    def causal(self) -> torch.Tensor:
+        return torch.tril(torch.ones(self.ql, self.S), diagonal=self.S - self.ql).bool()
+
+
+def load_rows() -> dict[str, RowsCase]:
+    z = np.load(os.path.join(GOLDEN, "rows.npz"))
+    return {str(n): RowsCase(z, str(n), *p, h, m) for n, p, h, m in zip(z["names"], z["params"], z["heavy"], z["modes"])}
+
+
 def load_edge() -> dict[str, GoldenCase]:
     z = np.load(os.path.join(GOLDEN, "edge.npz"))
     q, k, v = from_bf16_bits(z["q"]), from_bf16_bits(z["k"]), from_bf16_bits(z["v"])

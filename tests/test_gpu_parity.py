@@ -265,6 +265,52 @@ def test_depth_rule_on_the_two_pass_selection(device, monkeypatch, depth):
     assert torch.equal(out0, out1) and torch.equal(ctx0.sel_cnt, ctx1.sel_cnt)
 
 
+@pytest.mark.parametrize("name", ["q5", "q16_page", "q3_short", "q4_depth"])
+def test_multi_token_decode_rows_against_reference_output(device, name):
+    """2 <= q_len <= 128 new tokens per sequence in one call (ha_decode_step_rows): every (sequence,
+    token) is a row that sees the keys up to its own, with the budget of the whole length. Against
+    the oracle on the device's codes and, when those equal the reference's, against the recorded
+    reference masks (inside the causal part) and outputs."""
+    c = helpers.load_rows()[name]
+    B, Hq, ql, S = c.q.shape[0], c.q.shape[1], c.ql, c.S
+    usa = synthetic.make_usa(Hq, 128, 0, True)
+    budget = ha.Budget(c.init, c.heavy, c.recent, c.mode, c.depth)
+    ks, vs = [c.k[b] for b in range(B)], [c.v[b] for b in range(B)]
+    cache, ctx = build(device, None, ks, vs, budget, usa, prefill_to=[S - ql] * B)
+    ctx.hash_prefill()
+    rows = ha.ChunkRows(cache, ql)
+    rctx = ha.SparseDecodeContext(rows, budget, usa.packed(device))
+    rows.advance()
+    assert cache.seq_lens.tolist() == [S] * B and rows.seq_lens.tolist() == [S - ql + i + 1 for i in range(ql)] * B
+    q_rows = c.q.permute(0, 2, 1, 3).reshape(B * ql, Hq, 128).to(device, torch.bfloat16).contiguous()
+    k_rows = c.k[:, :, S - ql:].permute(0, 2, 1, 3).reshape(B * ql, -1, 128).to(device, torch.bfloat16).contiguous()
+    v_rows = c.v[:, :, S - ql:].permute(0, 2, 1, 3).reshape(B * ql, -1, 128).to(device, torch.bfloat16).contiguous()
+    out = rctx.decode_step_rows(q_rows, k_rows, v_rows).float().cpu().reshape(B, ql, Hq, 128).permute(0, 2, 1, 3)
+    rctx.check_status()
+    q_codes = (rctx.q_codes.cpu().to(torch.int64) & ALL_BITS).reshape(B, ql, Hq).permute(0, 2, 1)   # [B,Hq,ql]
+    k_codes = torch.stack([cache.read_codes(b).cpu() for b in range(B)])                               # [B,Hq,S]
+    scores = torch.stack([orc.hamming_scores(q_codes[:, :, i], k_codes) for i in range(ql)], dim=2)   # [B,Hq,ql,S]
+    mask = orc.select_mask_rows(scores, c.init, c.recent, c.heavy, eval_mode=c.mode, retrieve_depth=c.depth)
+    mask &= c.causal
+    for b in range(B):
+        for i in range(ql):
+            S_i = S - ql + i + 1
+            lo = min(c.init, S_i)
+            hi = max(lo, S_i - c.recent)
+            for h in range(Hq):
+                want = mask[b, h, i].nonzero()[:, 0]
+                want = want[(want >= lo) & (want < hi)]
+                assert torch.equal(heavy_from_device(rctx, b * ql + i, h), want), f"b={b} token={i} h={h}"
+    ref = orc.masked_attention_rows(c.q, c.k, c.v, mask)
+    ok, max_abs, rel = helpers.att_close(out, ref)
+    assert ok, f"max_abs={max_abs:.3e} rel_l2={rel:.3e}"
+    span = 2 * scores - 32
+    if torch.equal(span, c.span):   # same codes as the reference run: its own mask and output must come out
+        assert torch.equal(mask, c.mask & c.causal)
+        ok, max_abs, rel = helpers.att_close(out, c.out)
+        assert ok, f"{name}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
+
+
 def test_ragged_batch_shuffled_pages(device):
     Hq, Hkv, lens = 8, 2, [1, 2, 31, 255, 256, 257, 1500, 4097]
     usa = synthetic.make_usa(Hq, 128, 2, True)

@@ -107,6 +107,29 @@ def test_converted_model_prefill_then_decode_matches_oracle(device):
     got = seen["out"][0].float().cpu()
     assert float((got - want).abs().max()) < 3e-2 and float((got - want).norm() / want.norm()) < 2e-2
 
+    # a chunk of 4 tokens (2 <= q_len <= 128) goes through the same library path, one row per token
+    with torch.no_grad():
+        chunk = torch.randint(0, 1000, (2, 4), generator=g).to(device)
+        out3 = model(chunk, past_key_values=cache, use_cache=True)
+    assert bool(torch.isfinite(out3.logits.float()).all())
+    assert att._ctx.cache.seq_lens.tolist() == [305, 305]
+    hs = seen["kwargs"]["hidden_states"] if "hidden_states" in seen["kwargs"] else seen["args"][0]
+    cos, sin = seen["kwargs"]["position_embeddings"]
+    with torch.no_grad():
+        q = att.q_proj(hs).view(2, 4, 4, 128).transpose(1, 2)
+        k = att.k_proj(hs).view(2, 4, 1, 128).transpose(1, 2)
+        q, k = hal._apply_rotary(q, k, cos, sin)
+    kc, vc = hal._layer_kv(cache, 0)
+    assert kc.shape[2] == 305
+    ref = orc.decode_chunk(mods[0].float().cpu(), q.to(torch.bfloat16).float().cpu(), kc.float().cpu(), vc.float().cpu(),
+                           cfg.init_budget, cfg.recent_budget, cfg.heavy_budget)
+    with torch.no_grad():
+        want = att.o_proj(ref.transpose(1, 2).reshape(2, 4, 512).to(device, torch.bfloat16)).float().cpu()
+    got = seen["out"][0].float().cpu()
+    assert float((got - want).abs().max()) < 3e-2 and float((got - want).norm() / want.norm()) < 2e-2
+    for ctx_rows in att._row_ctx.values():
+        ctx_rows.check_status()
+
     # a second prompt after reset_usa starts from an empty hash cache
     hal.reset_usa(model)
     assert att._ctx.cache.seq_lens.tolist() == [0, 0]
