@@ -333,7 +333,7 @@ def run_gpu_arm(args):
 
     def e2e_steps(n):
         for i in range(n):
-            ha.decode_step_host(ctxs[i % L], bufs[i % L], synchronize=True)
+            ha.decode_step_host(ctxs[i % L], bufs[i % L], synchronize=True, use_graph=True)
 
     e2e_steps(min(n_e2e, 3 * L))
     barrier()

@@ -305,6 +305,7 @@ class HostStepBuffers:
         self.v_dev = torch.empty(B, Hkv, HEAD_DIM, dtype=torch.bfloat16, device=dev)
         self.out_dev = torch.empty(B, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
         self._bound = None
+        self._graph = None
 
     def bound_call(self, ctx: SparseDecodeContext):
         """``ha_decode_step_host`` with every argument but (stream, synchronize) bound to the buffers
@@ -322,6 +323,22 @@ class HostStepBuffers:
             self._bound = (ctx, lambda stream, sync: fn(*fixed, vp(stream), i32(sync)))
         return self._bound[1]
 
+    def graph_for(self, ctx: SparseDecodeContext) -> torch.cuda.CUDAGraph:
+        """The CUDA graph of one ``ha_decode_step_host`` call (without the final wait) on these buffers."""
+        if self._graph is None or self._graph[0] is not ctx:
+            call = self.bound_call(ctx)
+            with torch.cuda.device(ctx.device):
+                # an eager call first: whatever the library creates at first use must not happen under capture
+                # (it writes the same cache slot and outputs the recorded call will write again)
+                _raise_on(call(torch.cuda.current_stream(ctx.device).cuda_stream, 1), "ha_decode_step_host")
+                torch.cuda.synchronize(ctx.device)
+                side, graph = torch.cuda.Stream(ctx.device), torch.cuda.CUDAGraph()
+                with torch.cuda.stream(side):
+                    with torch.cuda.graph(graph, stream=side):
+                        _raise_on(call(side.cuda_stream, 0), "ha_decode_step_host")
+            self._graph = (ctx, graph)
+        return self._graph[1]
+
     @property
     def h2d_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.q_host, self.k_host, self.v_host))
@@ -331,10 +348,25 @@ class HostStepBuffers:
         return self.out_host.numel() * self.out_host.element_size() + 4
 
 
-def decode_step_host(ctx: SparseDecodeContext, buf: HostStepBuffers, synchronize: bool = True) -> torch.Tensor:
+def decode_step_host(ctx: SparseDecodeContext, buf: HostStepBuffers, synchronize: bool = True,
+                     use_graph: bool = False) -> torch.Tensor:
     """Decode step for callers whose q / k_new / v_new / out live in host memory: the step reads
     ``buf.q_host, k_host, v_host`` (in place if page-locked, else through a copy), leaves the result
-    in ``buf.out_host`` and (if ``synchronize``) waits and checks the device status."""
+    in ``buf.out_host`` and (if ``synchronize``) waits and checks the device status.
+
+    ``use_graph``: the first call records the library call (all its kernels, the reads of the host
+    buffers and the copies back) into a CUDA graph owned by ``buf``; later calls replay it - one
+    launch per step instead of one per kernel. Everything a step reads that changes between steps
+    (the host buffers' contents, the sequence lengths) is read at replay time."""
+    if use_graph:
+        stream = torch.cuda.current_stream(ctx.device)
+        buf.graph_for(ctx).replay()
+        if synchronize:
+            stream.synchronize()
+            code = int(buf.status_host[0])
+            if code != 0:
+                raise RuntimeError(f"device status: {_lib.status_str(code)} (status {code})")
+        return buf.out_host
     call = buf.bound_call(ctx)
     stream = torch.cuda.current_stream(ctx.device).cuda_stream
     if torch.cuda.current_device() == ctx.device.index:

@@ -412,6 +412,32 @@ def test_host_buffer_entry_point_equals_device_entry_point(device):
     assert torch.equal(out_dev, out_paged)  # pageable buffers: staged through device copies
 
 
+def test_host_buffer_step_replayed_as_a_graph(device):
+    """decode_step_host(use_graph=True): the recorded call reads the host buffers and the sequence
+    lengths at replay time, so consecutive tokens with new inputs come out as from eager calls."""
+    Hq, Hkv, S0, steps = 8, 2, 400, 3
+    usa = synthetic.make_usa(Hq, 128, 0, True)
+    inp = synthetic.make_decode_inputs(98, [S0 + steps], Hq, Hkv)
+    budget = ha.Budget(16, 0.125, 16)
+    gen = torch.Generator().manual_seed(12)
+    qs = [torch.randn(1, Hq, 128, generator=gen).to(torch.bfloat16) for _ in range(steps)]
+    outs = {}
+    for mode in (False, True):
+        cache, ctx = build(device, None, inp.k, inp.v, budget, usa, prefill_to=[S0])
+        ctx.hash_prefill()
+        buf = ha.HostStepBuffers(ctx)
+        got = []
+        for t in range(steps):
+            cache.seq_lens += 1
+            buf.q_host.copy_(qs[t])
+            buf.k_host.copy_(inp.k[0][None, :, S0 + t].to(torch.bfloat16))
+            buf.v_host.copy_(inp.v[0][None, :, S0 + t].to(torch.bfloat16))
+            got.append(ha.decode_step_host(ctx, buf, use_graph=mode).clone())
+        ctx.check_status()
+        outs[mode] = torch.stack(got)
+    assert torch.equal(outs[False], outs[True])
+
+
 def test_repeated_steps_grow_the_cache(device):
     """Five consecutive tokens decoded through the same context: the appended rows and codes of
     earlier steps are what later steps score and attend to."""
