@@ -53,6 +53,10 @@ struct Row8<__nv_bfloat16> {
         s = fmaf(bf16_hi(raw.w), x[7], s);
         return s;
     }
+    __device__ __forceinline__ void unpack(float (&e)[8]) const {
+        e[0] = bf16_lo(raw.x); e[1] = bf16_hi(raw.x); e[2] = bf16_lo(raw.y); e[3] = bf16_hi(raw.y);
+        e[4] = bf16_lo(raw.z); e[5] = bf16_hi(raw.z); e[6] = bf16_lo(raw.w); e[7] = bf16_hi(raw.w);
+    }
 };
 
 template <>
@@ -72,6 +76,10 @@ struct Row8<float> {
         s = fmaf(b.z, x[6], s);
         s = fmaf(b.w, x[7], s);
         return s;
+    }
+    __device__ __forceinline__ void unpack(float (&e)[8]) const {
+        e[0] = a.x; e[1] = a.y; e[2] = a.z; e[3] = a.w;
+        e[4] = b.x; e[5] = b.y; e[6] = b.z; e[7] = b.w;
     }
 };
 
@@ -261,6 +269,184 @@ hash_decode_kernel(const HashDecodeParams p) {
             uint4* d = lane < 16 ? reinterpret_cast<uint4*>(p.k_pages + slot * kHeadDim) + lane
                                  : reinterpret_cast<uint4*>(p.v_pages + slot * kHeadDim) + (lane - 16);
             *d = *s;
+        }
+    }
+    HA_TL(kTlHashDecode, kTlExit);
+}
+
+// ------------------------------------------------------------------------------------------
+// Batched variant for large batches: a CTA evaluates up to 16 sequences of its (head, side) at
+// once as three small GEMMs instead of one sequence after the other. The head's weights are
+// converted to fp32 and stored transposed ([in][out]) in shared memory (144 KB); in a hidden layer
+// warp w owns rows 4 (w % 4) .. +3 and the input slice 32 (w / 4) .. +31, lane l the outputs
+// 4 l .. 4 l + 3: one 16-byte weight load feeds 16 FMAs (4 rows x 4 outputs). The four partial
+// sums of an output are added, biased and passed through SiLU in a second sweep. In the last
+// layer warp = row, lane = output bit, and the warp's ballot is the row's code, so the 16 rows
+// finish (store / append) in parallel. Same arithmetic type (fp32 FMA) as the kernel above; the
+// summation order differs, which only matters inside the |x| < 1e-5 band of the sign.
+// ------------------------------------------------------------------------------------------
+constexpr int kHdbRows = 16;   // sequences per CTA and pass
+constexpr int kHdbKSplit = 4;  // input slices of a hidden layer
+constexpr int kHdbMinRows = 4;  // sequences per CTA from which the batched kernel is used
+struct HdbSmem {
+    float wt0[kHeadDim][kHidden];    // layer 0, [in][out]
+    float wt1[kHidden][kHidden];     // layer 1
+    float wt2[kHidden][kCodeBits];   // layer 2
+    float bias[kMlpBias];
+    float x[2][kHdbRows][kHidden];   // activations, ping-pong
+    float part[kHdbKSplit][kHdbRows][kHidden];
+};
+constexpr size_t kHdbSmemBytes = sizeof(HdbSmem);
+
+template <typename WT>
+__device__ __forceinline__ void hdb_load_weights(HdbSmem& sm, const WT* W, const float* bias, int tid) {
+    // A load is 8 consecutive inputs of one output row; consecutive threads take consecutive output
+    // rows of the same input chunk, so a warp's transposed stores hit 32 different banks. All nine
+    // loads of a thread are issued before the first store.
+    constexpr int kPer = kHidden * (kHeadDim / 8) / kHashDecodeThreads;  // 4 loads per thread and hidden layer
+    static_assert(kPer * kHashDecodeThreads == kHidden * (kHeadDim / 8) && kCodeBits * (kHidden / 8) == kHashDecodeThreads,
+                  "thread mapping of the weight transposition");
+    const WT* W1 = W + kHidden * kHeadDim;
+    const WT* W2 = W1 + kHidden * kHidden;
+    Row8<WT> r0[kPer], r1[kPer], r2;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        const int idx = tid + j * kHashDecodeThreads, o = idx % kHidden, chunk = idx / kHidden;
+        r0[j].load(W + (size_t)o * kHeadDim + chunk * 8);
+        r1[j].load(W1 + (size_t)o * kHidden + chunk * 8);
+    }
+    r2.load(W2 + (size_t)(tid % kCodeBits) * kHidden + (tid / kCodeBits) * 8);
+    for (int i = tid; i < kMlpBias; i += kHashDecodeThreads) sm.bias[i] = __ldg(bias + i);
+    float e[8];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        const int idx = tid + j * kHashDecodeThreads, o = idx % kHidden, chunk = idx / kHidden;
+        r0[j].unpack(e);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sm.wt0[chunk * 8 + k][o] = e[k];
+        r1[j].unpack(e);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sm.wt1[chunk * 8 + k][o] = e[k];
+    }
+    r2.unpack(e);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sm.wt2[(tid / kCodeBits) * 8 + k][tid % kCodeBits] = e[k];
+}
+
+// One hidden layer for 16 rows: partial sums by (row group, input slice), then bias + SiLU.
+__device__ __forceinline__ void hdb_hidden(HdbSmem& sm, const float (*wt)[kHidden], const float* bias, int cur,
+                                           int tid) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int rg = warp & 3, ks = warp >> 2;
+    float acc[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+#pragma unroll 8
+    for (int ii = 0; ii < kHidden / kHdbKSplit; ++ii) {
+        const int i = ks * (kHidden / kHdbKSplit) + ii;
+        const float4 w4 = *reinterpret_cast<const float4*>(&wt[i][lane * 4]);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const float xv = sm.x[cur][rg * 4 + r][i];  // broadcast
+            acc[r][0] = fmaf(xv, w4.x, acc[r][0]);
+            acc[r][1] = fmaf(xv, w4.y, acc[r][1]);
+            acc[r][2] = fmaf(xv, w4.z, acc[r][2]);
+            acc[r][3] = fmaf(xv, w4.w, acc[r][3]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+        *reinterpret_cast<float4*>(&sm.part[ks][rg * 4 + r][lane * 4]) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+    __syncthreads();
+    {
+        const int row = warp;  // 16 warps, 16 rows; lane l finishes outputs 4 l .. 4 l + 3
+        float4 sum = *reinterpret_cast<const float4*>(&bias[lane * 4]);
+#pragma unroll
+        for (int k = 0; k < kHdbKSplit; ++k) {
+            const float4 p4 = *reinterpret_cast<const float4*>(&sm.part[k][row][lane * 4]);
+            sum.x += p4.x; sum.y += p4.y; sum.z += p4.z; sum.w += p4.w;
+        }
+        *reinterpret_cast<float4*>(&sm.x[cur ^ 1][row][lane * 4]) = make_float4(silu(sum.x), silu(sum.y), silu(sum.z), silu(sum.w));
+    }
+    __syncthreads();
+}
+
+template <typename WT>
+__global__ void __launch_bounds__(kHashDecodeThreads, 1)
+hash_decode_batched_kernel(const HashDecodeParams p) {
+    HA_TL(kTlHashDecode, kTlEntry);
+    extern __shared__ __align__(16) unsigned char hdb_raw[];
+    HdbSmem& sm = *reinterpret_cast<HdbSmem*>(hdb_raw);
+    const int h = blockIdx.x, side = blockIdx.y;
+    const int Hq = p.Hkv * kGroup;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int kvh = h / kGroup, g = h % kGroup;
+
+    hdb_load_weights(sm, static_cast<const WT*>(p.w[side]) + (size_t)h * kMlpElems, p.bias[side] + (size_t)h * kMlpBias, tid);
+
+    pdl_wait();
+    HA_TL(kTlHashDecode, kTlAfterWait);
+    pdl_launch_dependents();
+
+    const int b_begin = blockIdx.z * p.batch_per_cta;
+    const int b_end = min(p.B, b_begin + p.batch_per_cta);
+    for (int b0 = b_begin; b0 < b_end; b0 += kHdbRows) {
+        // ---- this warp's row: the sequence's input row (4 elements per lane) and, key side, its append slot
+        const int b = b0 + warp;
+        const bool live = b < b_end;
+        int S = 1, page = 0;
+        {
+            float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live) {
+                const __nv_bfloat16* xrow = side == 0 ? p.q + ((size_t)b * Hq + h) * kHeadDim
+                                                      : p.k_new + ((size_t)b * p.Hkv + kvh) * kHeadDim;
+                const uint2 raw = *reinterpret_cast<const uint2*>(xrow + lane * 4);
+                xv = make_float4(bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y));
+                if (side == 0 && p.q_stage != nullptr)
+                    *reinterpret_cast<uint2*>(p.q_stage + ((size_t)b * Hq + h) * kHeadDim + lane * 4) = raw;
+                if (side == 1) {
+                    S = p.seq_lens[b];
+                    page = p.page_table[(size_t)b * p.max_pages + min(max(S - 1, 0) / kPage, p.max_pages - 1)];
+                }
+            }
+            *reinterpret_cast<float4*>(&sm.x[0][warp][lane * 4]) = xv;
+        }
+        __syncthreads();  // inputs (and, in the first pass, the weights) are in shared memory
+        hdb_hidden(sm, sm.wt0, sm.bias, 0, tid);
+        hdb_hidden(sm, sm.wt1, sm.bias + kHidden, 1, tid);
+        // ---- last layer: warp = row, lane = output bit; activations of layer 1 are in x[0]
+        float pre = sm.bias[2 * kHidden + lane];
+#pragma unroll 16
+        for (int i = 0; i < kHidden; ++i) pre = fmaf(sm.x[0][warp][i], sm.wt2[i][lane], pre);
+        // bit i = 1 iff output i > 0 (efficiency/kernels/torchatt.py:35-36: relu(sign(x)))
+        const uint32_t code = __ballot_sync(0xffffffffu, pre > 0.0f);
+        __syncthreads();  // x[0] is rewritten by the next pass
+        if (!live) continue;
+        if (p.preact_dbg != nullptr)
+            p.preact_dbg[(((size_t)b * 2 + side) * Hq + h) * kCodeBits + lane] = pre;
+        if (side == 0) {
+            if (lane == 0) p.q_codes[(size_t)b * Hq + h] = code;
+            continue;
+        }
+        if (S < 1 || S > p.max_pages * kPage) {
+            if (lane == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+            continue;
+        }
+        if (page < 0 || page >= p.num_pages) {
+            if (lane == 0) report(p.status, HA_ERR_BAD_PAGE);
+            continue;
+        }
+        const size_t slot = ((size_t)page * p.Hkv + kvh) * kPage + (S - 1) % kPage;
+        if (lane == 0) p.hash_pages[slot * kGroup + g] = code;
+        if (g == 0 && p.v_new != nullptr) {  // the group's first head also appends the K and V rows (256 B each)
+            const size_t src = ((size_t)b * p.Hkv + kvh) * kHeadDim;
+            const uint4* sp = lane < 16 ? reinterpret_cast<const uint4*>(p.k_new + src) + lane
+                                        : reinterpret_cast<const uint4*>(p.v_new + src) + (lane - 16);
+            uint4* dp = lane < 16 ? reinterpret_cast<uint4*>(p.k_pages + slot * kHeadDim) + lane
+                                  : reinterpret_cast<uint4*>(p.v_pages + slot * kHeadDim) + (lane - 16);
+            *dp = *sp;
         }
     }
     HA_TL(kTlHashDecode, kTlExit);

@@ -520,6 +520,28 @@ static int hash_decode_impl(const ha_shape_t* shape, const ha_hash_weights_t* we
     const dim3 grid(shape->num_kv_heads * kGroup, key_side ? 2 : 1,
                     (shape->batch + p.batch_per_cta - 1) / p.batch_per_cta);
     cudaError_t e;
+    if (p.batch_per_cta >= kHdbMinRows) {
+        // several sequences per CTA: evaluate them together from shared-memory weights
+        const bool bf16 = weights->dtype == HA_WEIGHTS_BF16;
+        e = bf16 ? cudaFuncSetAttribute(hash_decode_batched_kernel<__nv_bfloat16>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHdbSmemBytes)
+                 : cudaFuncSetAttribute(hash_decode_batched_kernel<float>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kHdbSmemBytes);
+        if (e != cudaSuccess) return HA_ERR_LAUNCH;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kHashDecodeThreads);
+        cfg.dynamicSmemBytes = kHdbSmemBytes;
+        cfg.stream = static_cast<cudaStream_t>(stream);
+        cudaLaunchAttribute attr1[1];
+        attr1[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr1[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
+        cfg.attrs = attr1;
+        cfg.numAttrs = 1;
+        e = bf16 ? cudaLaunchKernelEx(&cfg, hash_decode_batched_kernel<__nv_bfloat16>, p)
+                 : cudaLaunchKernelEx(&cfg, hash_decode_batched_kernel<float>, p);
+        return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    }
     if (weights->dtype == HA_WEIGHTS_BF16)
         e = launch(hash_decode_kernel<__nv_bfloat16>, grid, dim3(kHashDecodeThreads),
                    static_cast<cudaStream_t>(stream), 1, p);

@@ -311,6 +311,17 @@ def test_multi_token_decode_rows_against_reference_output(device, name):
         assert ok, f"{name}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
 
 
+def test_large_batch_takes_the_batched_encoder(device):
+    """40 sequences x 32 query heads: 20 sequences per encoder CTA, i.e. the shared-memory GEMM variant of
+    the hash encoder in two passes (16 + 4 rows), key and query side; every stage against the oracle."""
+    Hq, Hkv = 32, 8
+    g = torch.Generator().manual_seed(77)
+    lens = [int(x) for x in torch.randint(40, 330, (40,), generator=g)]
+    usa = synthetic.make_usa(Hq, 128, 7, True)
+    inp = synthetic.make_decode_inputs(107, lens, Hq, Hkv)
+    run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(8, 1.0 / 8, 8), shuffle_seed=4)
+
+
 def test_ragged_batch_shuffled_pages(device):
     Hq, Hkv, lens = 8, 2, [1, 2, 31, 255, 256, 257, 1500, 4097]
     usa = synthetic.make_usa(Hq, 128, 2, True)
