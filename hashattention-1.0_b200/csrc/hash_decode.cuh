@@ -287,7 +287,9 @@ hash_decode_kernel(const HashDecodeParams p) {
 // ------------------------------------------------------------------------------------------
 constexpr int kHdbRows = 16;   // sequences per CTA and pass
 constexpr int kHdbKSplit = 4;  // input slices of a hidden layer
-constexpr int kHdbMinRows = 4;  // sequences per CTA from which the batched kernel is used
+// Sequences per CTA from which the batched kernel is used: a pass costs about 8.5 us whatever the number of
+// rows (weights to shared memory + three full GEMM sweeps), the register kernel 3.3 us + 1.5 us per further row.
+constexpr int kHdbMinRows = 6;
 struct HdbSmem {
     float wt0[kHeadDim][kHidden];    // layer 0, [in][out]
     float wt1[kHidden][kHidden];     // layer 1

@@ -520,9 +520,7 @@ static int hash_decode_impl(const ha_shape_t* shape, const ha_hash_weights_t* we
     const dim3 grid(shape->num_kv_heads * kGroup, key_side ? 2 : 1,
                     (shape->batch + p.batch_per_cta - 1) / p.batch_per_cta);
     cudaError_t e;
-    int min_rows = kHdbMinRows;
-    if (const char* env = std::getenv("HA_HDB_MIN_ROWS")) min_rows = std::atoi(env);  // experiment knob
-    if (p.batch_per_cta >= min_rows) {
+    if (p.batch_per_cta >= kHdbMinRows) {
         // several sequences per CTA: evaluate them together from shared-memory weights
         const bool bf16 = weights->dtype == HA_WEIGHTS_BF16;
         e = bf16 ? cudaFuncSetAttribute(hash_decode_batched_kernel<__nv_bfloat16>,
