@@ -1,6 +1,7 @@
 // extern "C" entry points of libhashattn.so (declared in include/hashattn.h): argument checks,
-// workspace carving and kernel launches. No allocation, no host synchronisation (except where
-// ha_decode_step_host is asked for it), no exceptions.
+// workspace carving and kernel launches. No device memory is allocated, nothing synchronises with
+// the host (except where ha_decode_step_host is asked to), nothing throws. The only resources the
+// library creates are a stream and events per device for the staggered decode step, at its first use.
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
@@ -575,9 +576,10 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
     if (weights->dtype == HA_WEIGHTS_BF16) {
         // bf16 weights: tcgen05 GEMM chain. One CTA per SM (its shared memory holds a head's weights),
         // heads in grid.y, token tiles dealt round-robin over grid.x.
-        static const cudaError_t attr = cudaFuncSetAttribute(hash_prefill_tc_kernel,
-                                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTcSmemBytes);
-        if (attr != cudaSuccess) return HA_ERR_LAUNCH;
+        // (a per-device function attribute: set at every call, so that a process driving several GPUs is served)
+        if (cudaFuncSetAttribute(hash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kTcSmemBytes) != cudaSuccess)
+            return HA_ERR_LAUNCH;
         HashPrefillTcParams t;
         t.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
         t.hash_pages = hash_pages;

@@ -608,3 +608,29 @@ def test_bad_page_id_and_bad_length_are_reported_through_the_status_word(device)
     out = ctx.decode_step(q, kn, kn)
     ctx.check_status()
     assert bool(torch.isfinite(out.float()).all())
+
+
+@pytest.mark.parametrize("mode", ["simple", "depth"])
+def test_heavy_list_shorter_than_the_budget_is_reported_not_overrun(device, mode):
+    """sel_stride (here 8 entries) smaller than what the budget selects (75 of 600 tokens, more under the
+    depth rule): the list is cut at sel_stride, every slot holds a real candidate, and the status word
+    says so - nothing faults."""
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(109, [600], 8, 2)
+    cache = ha.PagedHashKVCache(1, 2, 600, device, shuffle_seed=3)
+    cache.write_kv(0, inp.k[0], inp.v[0])
+    ctx = ha.SparseDecodeContext(cache, ha.Budget(16, 8.0, 16), usa.packed(device))   # absolute budget 8: sel_stride = 8
+    assert ctx.sel_stride == 8
+    budget = ha.Budget(16, 0.125, 16, mode, 8)       # what is then asked for does not fit
+    ctx.budget, ctx.c_budget = budget, budget.c_struct()
+    ctx.hash_prefill()
+    ctx.sel_idx.fill_(-7)
+    q = inp.q.to(device, torch.bfloat16)
+    kn = inp.k[0][None, :, -1].to(device, torch.bfloat16)
+    out = ctx.decode_step(q, kn, kn)
+    with pytest.raises(RuntimeError, match="sel_stride"):
+        ctx.check_status()
+    assert bool(torch.isfinite(out.float()).all())
+    assert int(ctx.sel_cnt.max()) <= 8
+    idx = ctx.sel_idx.cpu()
+    assert bool(((idx >= 16) & (idx < 600 - 16)).all())
