@@ -213,19 +213,17 @@ def _llama_attention_class():
     return LlamaAttention
 
 
-def convert_usa(model, config, usa_modules, collect_stats, train_usa):
-    """Swaps every ``LlamaAttention`` of ``model`` for ``LlamaAttention_heavy_hitter`` (bf16, same
-    device, same projection weights), attaches that layer's hash module and keeps the replaced
-    module's forward for prefill (hashattention/hashattention_llama.py:650-667)."""
+def _convert(model, config, usa_modules, collect_stats, train_usa, attention_cls, heavy_cls):
+    """convert_usa for one host model family: ``attention_cls`` modules become ``heavy_cls``."""
     if collect_stats or train_usa:
         raise NotImplementedError("collect_stats / train_usa are not implemented")
-    attention_cls = _llama_attention_class()
     for name, module in reversed(list(model._modules.items())):
         if len(list(module.children())) > 0:
-            model._modules[name] = convert_usa(module, config, usa_modules, collect_stats, train_usa)
+            model._modules[name] = _convert(module, config, usa_modules, collect_stats, train_usa, attention_cls,
+                                            heavy_cls)
         if isinstance(module, attention_cls):
             device = next(module.parameters()).device
-            new_module = LlamaAttention_heavy_hitter(config, module.layer_idx).bfloat16().to(device)
+            new_module = heavy_cls(config, module.layer_idx).bfloat16().to(device)
             new_module.load_state_dict(module.state_dict())
             new_module.usa_module = usa_modules[module.layer_idx]
             new_module.usa_module_dtype = usa_modules[module.layer_idx].learning_to_hash_transformation_k[0][-1].weight.dtype
@@ -234,6 +232,14 @@ def convert_usa(model, config, usa_modules, collect_stats, train_usa):
             new_module.train_usa = train_usa
             model._modules[name] = new_module
     return model
+
+
+def convert_usa(model, config, usa_modules, collect_stats, train_usa):
+    """Swaps every ``LlamaAttention`` of ``model`` for ``LlamaAttention_heavy_hitter`` (bf16, same
+    device, same projection weights), attaches that layer's hash module and keeps the replaced
+    module's forward for prefill (hashattention/hashattention_llama.py:650-667)."""
+    return _convert(model, config, usa_modules, collect_stats, train_usa, _llama_attention_class(),
+                    LlamaAttention_heavy_hitter)
 
 
 def reset_usa(model):

@@ -634,3 +634,30 @@ def test_heavy_list_shorter_than_the_budget_is_reported_not_overrun(device, mode
     assert int(ctx.sel_cnt.max()) <= 8
     idx = ctx.sel_idx.cpu()
     assert bool(((idx >= 16) & (idx < 600 - 16)).all())
+
+
+def test_recall_diagnostic_counts_the_true_top_keys_inside_the_heavy_set(device):
+    """diagnostics/recall.py (the reference's overlap statistic, hashattention_llama.py:359-395) against the
+    same count done on the CPU from the oracle's mask."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(ha.__file__), "diagnostics", "recall.py")
+    spec = importlib.util.spec_from_file_location("ha_recall", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    Hq, Hkv, lens = 8, 2, [900, 300]
+    usa = synthetic.make_usa(Hq, 128, 0, True)
+    inp = synthetic.make_decode_inputs(111, lens, Hq, Hkv)
+    budget = ha.Budget(16, 0.125, 16)
+    _, _, ctx, cache = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget)
+    got = mod.topk_recall(ctx, inp.q.to(device, torch.bfloat16)).cpu()
+    q_codes = ctx.q_codes.cpu().to(torch.int64) & ALL_BITS
+    for b, S in enumerate(lens):
+        scores = orc.hamming_scores(q_codes[b][None], cache.read_codes(b).cpu()[None])
+        mask = orc.select_mask(scores, 16, 16, 0.125)[0]                              # [Hq, S]
+        k = inp.k[b].to(torch.bfloat16).float().repeat_interleave(4, dim=0)           # [Hq, S, D]
+        logits = torch.einsum("hd,hsd->hs", inp.q[b].to(torch.bfloat16).float(), k) / 128 ** 0.5
+        top = logits[:, 16:S - 16].topk(32, dim=-1).indices + 16
+        want = mask.gather(1, top).float().mean(-1)
+        # the device and the CPU may order two near-equal logits at the edge of the top-32 differently: one key
+        assert float((got[b] - want).abs().max()) <= 1.0 / 32 + 1e-6, (got[b], want)

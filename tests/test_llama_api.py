@@ -136,3 +136,58 @@ def test_converted_model_prefill_then_decode_matches_oracle(device):
     with torch.no_grad():
         model(prompt[:, :200], use_cache=True)
     assert att._ctx.cache.seq_lens.tolist() == [200, 200]
+
+
+def test_mistral_host_converts_and_resets_like_the_llama_host():
+    """hashattention_mistral mirrors the reference's second host file: same API names, MistralAttention
+    modules swapped for MistralAttention_heavy_hitter with the projection weights kept."""
+    from transformers import MistralConfig, MistralForCausalLM
+
+    from hashattention_b200 import hashattention_mistral as ham
+
+    cfg = MistralConfig(hidden_size=512, num_attention_heads=4, num_key_value_heads=1, num_hidden_layers=2,
+                        intermediate_size=1024, vocab_size=1000, max_position_embeddings=2048, head_dim=128,
+                        sliding_window=None)
+    for k, v in dict(lth_init_dim=128, lth_final_dim=32, lth_thold=0, lth_num_layers=3, init_budget=16,
+                     heavy_budget=0.125, recent_budget=16, usa_eval_mode="simple", usa_retrieve_depth=-1).items():
+        setattr(cfg, k, v)
+    torch.manual_seed(0)
+    model = MistralForCausalLM(cfg)
+    before = {n: p.clone() for n, p in model.named_parameters() if "self_attn" in n}
+    mods = ham.load_usa(cfg, None, device="cpu")
+    model = ham.convert_usa(model, cfg, mods, collect_stats=False, train_usa=False)
+    for i, layer in enumerate(model.model.layers):
+        att = layer.self_attn
+        assert isinstance(att, ham.MistralAttention_heavy_hitter) and att.usa_module is mods[i]
+        assert att.flash_forward is not None and att.layer_idx == i
+    for n, p in before.items():
+        assert torch.equal(dict(model.named_parameters())[n], p.to(torch.bfloat16))
+    assert ham.reset_usa(model) is model and ham.set_eval_usa_mode(model) is model
+
+
+@pytest.mark.gpu
+def test_mistral_model_prefill_then_decode_on_the_gpu(device):
+    from transformers import MistralConfig, MistralForCausalLM
+
+    from hashattention_b200 import hashattention_mistral as ham
+
+    cfg = MistralConfig(hidden_size=512, num_attention_heads=4, num_key_value_heads=1, num_hidden_layers=2,
+                        intermediate_size=1024, vocab_size=1000, max_position_embeddings=2048, head_dim=128,
+                        sliding_window=None)
+    for k, v in dict(lth_init_dim=128, lth_final_dim=32, lth_thold=0, lth_num_layers=3, init_budget=16,
+                     heavy_budget=0.125, recent_budget=16, usa_eval_mode="simple", usa_retrieve_depth=-1).items():
+        setattr(cfg, k, v)
+    torch.manual_seed(1)
+    model = MistralForCausalLM(cfg).to(device).bfloat16()
+    mods = ham.load_usa(cfg, None, device=device).bfloat16()
+    model = ham.convert_usa(model, cfg, mods, collect_stats=False, train_usa=False)
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, 1000, (2, 300), generator=g).to(device)
+    with torch.no_grad():
+        out = model(prompt, use_cache=True)
+        nxt = torch.randint(0, 1000, (2, 1), generator=g).to(device)
+        out2 = model(nxt, past_key_values=out.past_key_values, use_cache=True)
+    att = model.model.layers[0].self_attn
+    att._ctx.check_status()
+    assert att._ctx.cache.seq_lens.tolist() == [301, 301]
+    assert bool(torch.isfinite(out2.logits.float()).all())
