@@ -1,9 +1,9 @@
 """Generates the golden fixtures in this directory by running the REFERENCE implementation.
 
-Needs the reference checkout (default /root/reference, override with HASHATTN_REFERENCE) and
-runs on CPU:
+Needs a checkout of the reference project (environment variable HASHATTN_REFERENCE points at
+its root) and runs on CPU:
 
-    python tests/golden/make_golden.py
+    HASHATTN_REFERENCE=<reference checkout> python tests/golden/make_golden.py [case_a|edge|config0|depth|rows ...]
 
 For every case it imports hashattention/hashattention_llama.py unmodified, builds the
 reference's USA module and LlamaAttention_heavy_hitter, and records
@@ -34,7 +34,9 @@ from torch import nn
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("HASHATTN_REFERENCE", "/root/reference")
+REF = os.environ.get("HASHATTN_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    sys.exit("set HASHATTN_REFERENCE to the root of a checkout of the reference project")
 sys.path.insert(0, ROOT)
 sys.path.insert(0, REF)
 
