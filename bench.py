@@ -205,8 +205,8 @@ def run_gpu_arm(args):
 
     w = WORKLOADS[args.workload]
     lens = workload_lens(args.workload)
-    if args.batch:
-        lens = lens[:args.batch]
+    if args.batch:  # fewer sequences, or the workload's sequences repeated
+        lens = (lens * ((args.batch + len(lens) - 1) // len(lens)))[:args.batch]
     B, L = len(lens), args.layers or w["layers"]
     budget = ha.Budget(INIT, w["heavy"], RECENT)
     nbytes = synthetic.algorithmic_bytes(lens, HQ, HKV, INIT, RECENT, w["heavy"])

@@ -58,6 +58,7 @@ int check_weights(const ha_hash_weights_t* w, bool need_q, bool need_k) {
 // grows with the total so that big problems do not drown in partials.
 struct AttSplit {
     int rounds, nsplits;
+    bool cluster;  // the splits of a (sequence, head) are the 8 CTAs of a cluster that merge among themselves
 };
 
 AttSplit att_split(const ha_shape_t* s, const ha_budget_t* b) {
@@ -71,6 +72,30 @@ AttSplit att_split(const ha_shape_t* s, const ha_budget_t* b) {
     AttSplit a;
     a.rounds = (int)rounds;
     a.nsplits = (int)((rows + kAttRoundRows * rounds - 1) / (kAttRoundRows * rounds));
+    a.cluster = false;
+    return a;
+}
+
+// Small steps (config-1-like: the gather of 41 K rows takes about as long as the hand-over to a merge kernel
+// and the merge together) run the gather as clusters of 8 CTAs x 256 threads per (sequence, head), which merge
+// through distributed shared memory: no partials, no merge kernel.
+AttSplit att_split_launch(const ha_shape_t* s, const ha_budget_t* b) {
+    AttSplit a = att_split(s, b);
+    long long rows = (long long)s->sel_stride + b->init_budget + b->recent_budget;
+    const long long cap = (long long)s->max_pages * kPage;
+    if (rows > cap) rows = cap;
+    const long long total = rows * s->batch * s->num_kv_heads * kGroup;
+    const int cluster_round_rows = kAttClusterThreads / 16 * kAttRowsPerWorker;  // 64
+    const long long per_cta = (rows + kAttClusterCtas - 1) / kAttClusterCtas;
+    const long long rounds = (per_cta + cluster_round_rows - 1) / cluster_round_rows;
+    const char* env = std::getenv("HA_CLUSTER_GATHER");  // "0" / "1" force the choice (experiments, tests)
+    const bool fits = rounds <= kAttMaxRounds && a.nsplits > 1;
+    const bool want = env != nullptr ? env[0] == '1' : total <= 65536;
+    if (fits && want) {
+        a.cluster = true;
+        a.rounds = (int)(rounds < 1 ? 1 : rounds);
+        a.nsplits = kAttClusterCtas;
+    }
     return a;
 }
 
@@ -181,14 +206,15 @@ cudaError_t launch_two_pass_select(const ha_shape_t* shape, const SelectParams& 
     return e != cudaSuccess ? e : launch_plan_select(shape, p, nkvh, s);
 }
 
-// One cluster kernel scores and selects in a single pass when the sequences are short and the
-// (sequence, kv-head) units few: all clusters resident at once, at most two rounds each (measured
-// 6.7 us against 8.5 us at B=1, S=32K). Longer or more numerous sequences are bandwidth- rather
-// than latency-bound and run faster as the two-pass pair (45 us against 62 us at B=4, S=128K).
+// One cluster kernel scores and selects in a single pass when the sequences are short and there are at
+// most 8 (sequence, kv-head) units, one cluster of 8 CTAs x 1024 threads per GPC: at most two rounds each
+// (measured 6.9 us against 9.4 us for the two-pass kernels at B=1, S=32K). With 16 units the clusters no
+// longer run side by side (13.7 us against 11.6 us for the two-pass kernels at B=2), and longer sequences
+// are bandwidth- rather than latency-bound (45 us against 62 us at B=4, S=128K).
 bool use_cluster_select(const ha_shape_t* shape) {
     const long long max_tokens = (long long)shape->max_pages * kPage;
     const long long units = (long long)shape->batch * shape->num_kv_heads;
-    return max_tokens <= 2LL * kClRoundTokens && units * kClCtas <= 148;
+    return max_tokens <= 2LL * kClRoundTokens && units <= 8;
 }
 
 }  // namespace
@@ -272,15 +298,23 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     p.recent_budget = budget->recent_budget;
     p.heavy_budget = budget->heavy_budget;
     p.scale_log2e = sm_scale * 1.4426950408889634f;
-    const AttSplit split = att_split(shape, budget);
+    const AttSplit split = att_split_launch(shape, budget);
     p.partials = w.partials;
     p.nsplits = split.nsplits;
     p.rounds = split.rounds;
+    p.round_rows = split.cluster ? kAttClusterThreads / 16 * kAttRowsPerWorker : kAttRoundRows;
     p.h0 = kvh0 * kGroup;
     const dim3 grid(split.nsplits, nheads, shape->batch);
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
-    cudaError_t e = physical ? launch(sparse_gather_kernel<true>, grid, dim3(kAttThreads), s, 1, p)
-                             : launch(sparse_gather_kernel<false>, grid, dim3(kAttThreads), s, 1, p);
+    if (split.cluster) {
+        const cudaError_t ec = physical ? launch(sparse_gather_kernel<true, kAttClusterThreads, true>, grid,
+                                                 dim3(kAttClusterThreads), s, kAttClusterCtas, p)
+                                        : launch(sparse_gather_kernel<false, kAttClusterThreads, true>, grid,
+                                                 dim3(kAttClusterThreads), s, kAttClusterCtas, p);
+        return ec == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    }
+    cudaError_t e = physical ? launch(sparse_gather_kernel<true, kAttThreads, false>, grid, dim3(kAttThreads), s, 1, p)
+                             : launch(sparse_gather_kernel<false, kAttThreads, false>, grid, dim3(kAttThreads), s, 1, p);
     if (e == cudaSuccess && split.nsplits > 1) {
         PriorityScope light(merge_priority);
         e = launch(sparse_merge_kernel, dim3(nheads, shape->batch), dim3(kHeadDim), s, 1, p);
@@ -735,7 +769,8 @@ int ha_decode_step_rows(const ha_shape_t* shape, const ha_budget_t* budget,
 
 int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget) {
     if (check_shape(shape) != HA_OK || check_budget(budget) != HA_OK) return 0;
-    const int merge = att_split(shape, budget).nsplits > 1 ? 1 : 0;
+    const AttSplit as = att_split_launch(shape, budget);
+    const int merge = as.nsplits > 1 && !as.cluster ? 1 : 0;
     if (use_cluster_select(shape)) return 3 + merge;  // encoder, cluster selection, gather (+ merge)
     const int parts = use_stagger(shape) ? stagger_parts(shape) : 1;
     return 1 + parts * (4 + merge);  // encoder; per part: histograms, plan, compaction, gather (+ merge)

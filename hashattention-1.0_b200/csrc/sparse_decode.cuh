@@ -21,9 +21,14 @@
 // valid row and masked afterwards.
 #pragma once
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace ha {
+
+constexpr int kAttClusterCtas = 8;      // splits of one (b, h) in the cluster variant of the gather (portable cluster size)
+constexpr int kAttClusterThreads = 256;
 
 struct SparseDecodeParams {
     const __nv_bfloat16* q;        // [B][Hq][128]
@@ -39,6 +44,7 @@ struct SparseDecodeParams {
     float* partials;               // workspace: [B][Hq][nsplits][130]
     int32_t* status;
     int B, Hkv, max_pages, num_pages, sel_stride, nsplits, rounds;
+    int round_rows;                // rows a CTA takes per round: 2 per thread / 16 (32 for 128 threads, 64 for 256)
     int h0;                        // first query head of this launch (a launch may cover a slice of the heads)
     int init_budget, recent_budget;
     double heavy_budget;
@@ -89,21 +95,28 @@ __device__ __forceinline__ AttPlan att_plan(const SparseDecodeParams& p, int b, 
                     p.budget_lens != nullptr ? p.budget_lens[b] : -1);
     a.cnt = listed >= 0 ? min(listed, min(a.r.hi - a.r.lo, p.sel_stride)) : min(a.r.hb, p.sel_stride);
     a.n_total = a.ok ? a.r.lo + a.cnt + (a.r.S - a.r.hi) : 0;
-    const int rows_per_cta = kAttRoundRows * p.rounds;
+    const int rows_per_cta = p.round_rows * p.rounds;
     a.nsplits = (a.n_total + rows_per_cta - 1) / rows_per_cta;
     return a;
 }
 
 // kPhysical: `sel` holds page * 256 + slot of each heavy token (written by select_kernel), so a
 // heavy row needs no page-table lookup; otherwise it holds token indices.
-template <bool kPhysical>
-__global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const SparseDecodeParams p) {
+//
+// kCluster: the splits of one (b, h) are the 8 CTAs (256 threads each) of a thread-block cluster, which merge
+// their partials through distributed shared memory and write the output themselves - no partials in global
+// memory, no merge kernel, one kernel hand-over less. Used when the whole step is small (latency-bound).
+template <bool kPhysical, int kThreads, bool kCluster>
+__global__ void __launch_bounds__(kThreads, kCluster ? 2 : 6) sparse_gather_kernel(const SparseDecodeParams p) {
+    static_assert(kCluster ? kThreads == kAttClusterThreads : kThreads == kHeadDim, "flat CTAs: thread = output dimension");
     HA_TL(kTlGather, kTlEntry);
+    constexpr int kWorkers = kThreads / 16;                          // half-warps
+    constexpr int kRoundRows = kWorkers * kAttRowsPerWorker;      // rows per CTA and round
     const int split = blockIdx.x, h = p.h0 + blockIdx.y, b = blockIdx.z;
     const int Hq = p.Hkv * kGroup, kvh = h / kGroup;
     const int tid = threadIdx.x;
     const int worker = tid >> 4, sl = tid & 15, warp = tid >> 5;
-    constexpr int kWarps = kAttThreads / 32;
+    constexpr int kWarps = kThreads / 32;
 
     __shared__ float s_m[kWarps], s_l[kWarps];
     __shared__ __align__(16) float s_acc[kWarps][kHeadDim];
@@ -115,7 +128,7 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
     int edge_shift = a.r.hi - lo - cnt;  // recent token = position + edge_shift
     const int32_t* sel = p.sel + ((size_t)b * Hq + h) * p.sel_stride;
     const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
-    const int base = split * kAttRoundRows * p.rounds + worker;
+    const int base = split * kRoundRows * p.rounds + worker;
     const unsigned pool_rows = (unsigned)p.num_pages * kPage;
 
     // page lookups of the first round's sink / recent rows, issued before the dependency wait
@@ -123,7 +136,7 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
     auto first_round_pages = [&] {
 #pragma unroll
         for (int i = 0; i < kAttRowsPerWorker; ++i) {
-            const int pos = base + i * kAttWorkers;
+            const int pos = base + i * kWorkers;
             const bool edge = pos < a.n_total && (unsigned)(pos - lo) >= (unsigned)cnt;
             const int tok = edge ? (pos < lo ? pos : pos + edge_shift) : 0;
             pre_page[i] = __ldg(pt + tok / kPage);
@@ -147,7 +160,7 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
         edge_shift = a.r.hi - lo - cnt;
         first_round_pages();
     }
-    if (split >= a.nsplits) return;
+    if (!kCluster && split >= a.nsplits) return;  // (a cluster CTA without rows still takes part in the merge)
 
     const __nv_bfloat16* kbase = p.k_pages + (size_t)kvh * kPage * kHeadDim + sl * 8;
     const __nv_bfloat16* vbase = p.v_pages + (size_t)kvh * kPage * kHeadDim + sl * 8;
@@ -192,16 +205,32 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
         }
     };
 
+    // A round whose rows are all heavy rows takes their physical ids straight from the list. In the cluster
+    // variant, where a CTA's rounds are the critical path of the step, the ids of the next such round are
+    // requested before this round's K / V rows are waited for (a round then costs one memory round trip, not
+    // two). The flat variant does not: the extra registers cost it a CTA per SM and, measured, the overlap of
+    // the staggered halves.
+    auto all_heavy = [&](int cta_first) { return kPhysical && cta_first >= lo && cta_first + kRoundRows <= lo + cnt; };
+    unsigned next_row[kAttRowsPerWorker];
+    bool have_next = false;
     for (int round = 0; round < p.rounds; ++round) {
-        const int rbase = base + round * kAttRoundRows;
+        const int rbase = base + round * kRoundRows;
         const int cta_first = rbase - worker;  // first position of the CTA in this round
         if (cta_first >= a.n_total) break;
         unsigned row[kAttRowsPerWorker];
-        if (kPhysical && cta_first >= lo && cta_first + kAttRoundRows <= lo + cnt) {
-            // ---- all 32 rows of the round are heavy rows: their physical ids come straight from the list
+        if (all_heavy(cta_first)) {
             uint32_t valid = (1u << kAttRowsPerWorker) - 1u;
 #pragma unroll
-            for (int i = 0; i < kAttRowsPerWorker; ++i) row[i] = (unsigned)__ldcg(sel + (rbase + i * kAttWorkers - lo));
+            for (int i = 0; i < kAttRowsPerWorker; ++i)
+                row[i] = (kCluster && have_next) ? next_row[i] : (unsigned)__ldcg(sel + (rbase + i * kWorkers - lo));
+            if constexpr (kCluster) {
+                have_next = round + 1 < p.rounds && all_heavy(cta_first + kRoundRows);
+                if (have_next) {
+#pragma unroll
+                    for (int i = 0; i < kAttRowsPerWorker; ++i)
+                        next_row[i] = (unsigned)__ldcg(sel + (rbase + kRoundRows + i * kWorkers - lo));
+                }
+            }
 #pragma unroll
             for (int i = 0; i < kAttRowsPerWorker; ++i) {
                 if (row[i] >= pool_rows) {
@@ -214,11 +243,12 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
             continue;
         }
         // ---- mixed round: one lookup per row, the heavy list entry or the page of a sink / recent token
+        have_next = false;
         int look[kAttRowsPerWorker], tokv[kAttRowsPerWorker];
         uint32_t valid = 0, heavy = 0;
 #pragma unroll
         for (int i = 0; i < kAttRowsPerWorker; ++i) {
-            const int pos = rbase + i * kAttWorkers;
+            const int pos = rbase + i * kWorkers;
             const bool ok = pos < a.n_total;
             const bool is_heavy = ok && (unsigned)(pos - lo) < (unsigned)cnt;
             const int tok = (ok && !is_heavy) ? (pos < lo ? pos : pos + edge_shift) : 0;
@@ -273,6 +303,7 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
         *reinterpret_cast<float4*>(&s_acc[warp][sl * 8 + 4]) = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
     __syncthreads();
+    const int dim = tid & (kHeadDim - 1);  // threads beyond 128 (256-thread CTAs) repeat the first 128
     float M = -INFINITY, L = 0.f, A = 0.f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) M = fmaxf(M, s_m[w]);
@@ -280,7 +311,43 @@ __global__ void __launch_bounds__(kAttThreads, 6) sparse_gather_kernel(const Spa
     for (int w = 0; w < kWarps; ++w) {
         const float f = s_m[w] == -INFINITY ? 0.f : exp2f(s_m[w] - M);
         L = fmaf(s_l[w], f, L);
-        A = fmaf(s_acc[w][tid], f, A);
+        A = fmaf(s_acc[w][dim], f, A);
+    }
+    if constexpr (kCluster) {
+        // ---- the 8 CTAs of the cluster hold the 8 partials of (b, h): CTA r finishes dimensions [16 r, 16 r + 16)
+        namespace cg = cooperative_groups;
+        cg::cluster_group cluster = cg::this_cluster();
+        __shared__ float c_part[2 + kHeadDim];
+        if (tid < kHeadDim) c_part[2 + tid] = A;
+        if (tid == 0) {
+            c_part[0] = M;
+            c_part[1] = L;
+        }
+        cluster.sync();
+        if (tid < kHeadDim / kAttClusterCtas) {
+            const int d = split * (kHeadDim / kAttClusterCtas) + tid;
+            float mk[kAttClusterCtas], lk[kAttClusterCtas], ak[kAttClusterCtas];
+#pragma unroll
+            for (int k = 0; k < kAttClusterCtas; ++k) {  // all remote loads issued together
+                const float* rp = cluster.map_shared_rank(c_part, k);
+                mk[k] = rp[0];
+                lk[k] = rp[1];
+                ak[k] = rp[2 + d];
+            }
+            float Mg = -INFINITY, Lg = 0.f, Ag = 0.f;
+#pragma unroll
+            for (int k = 0; k < kAttClusterCtas; ++k) Mg = fmaxf(Mg, mk[k]);
+#pragma unroll
+            for (int k = 0; k < kAttClusterCtas; ++k) {
+                const float f = mk[k] == -INFINITY ? 0.f : exp2f(mk[k] - Mg);
+                Lg = fmaf(lk[k], f, Lg);
+                Ag = fmaf(ak[k], f, Ag);
+            }
+            if (Lg > 0.f) p.out[((size_t)b * Hq + h) * kHeadDim + d] = __float2bfloat16_rn(Ag / Lg);
+        }
+        HA_TL(kTlGather, kTlExit);
+        cluster.sync();  // the partial of this CTA may be read by the others until they are done
+        return;
     }
     if (a.nsplits == 1) {  // nothing to merge with
         p.out[((size_t)b * Hq + h) * kHeadDim + tid] = __float2bfloat16_rn(A / L);
