@@ -44,7 +44,7 @@ METRIC, UNIT = "sparse_decode_attn_hbm_gbs", "GB/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # capture summarised in profiles/ (None until a capture of that workload exists)
-NCU_TRAFFIC = {"config1": 17137664}  # sparse_gather_kernel, profiles/decode_kernels_config1_ncu_full.md
+NCU_TRAFFIC = {"config1": 17146880}  # sparse_gather_kernel, profiles/decode_kernels_config1_ncu_full.md
 
 
 def peaks():
@@ -304,7 +304,10 @@ def run_gpu_arm(args):
     att_bytes = nbytes["kv"] + nbytes["qo"]
     peak, peak_src = peaks()
     att_gbs = att_bytes / (stage_us["sparse_decode"] * 1e-6) / 1e9
-    roofline = {"bound": "hbm", "kernel": "sparse_gather_kernel + sparse_merge_kernel", "achieved": att_gbs, "peak": peak, "unit": "GB/s",
+    # small steps run the gather as clusters that merge among themselves: 3 kernels per step, no merge kernel
+    clustered = int(ctxs[0].lib.ha_decode_step_launches(ctxs[0].shape, ctxs[0].c_budget)) == 3
+    roofline = {"bound": "hbm", "kernel": "sparse_gather_kernel (cluster variant, merges in the cluster)" if clustered
+                else "sparse_gather_kernel + sparse_merge_kernel", "achieved": att_gbs, "peak": peak, "unit": "GB/s",
                 "frac": att_gbs / peak, "traffic": NCU_TRAFFIC.get(args.workload), "peak_source": peak_src,
                 "algorithmic_bytes_per_launch": att_bytes, "us_per_launch": stage_us["sparse_decode"]}
     pipeline = {"bytes_per_step": nbytes, "achieved": nbytes["total"] / per_step / 1e9, "peak": peak,
