@@ -4,30 +4,32 @@
 // kv-head carries the codes of all 4 query heads of the group, so one coalesced pass scores
 // the 4 heads together; score = popcount(~(q_code ^ k_code)) in 0..32. Each CTA publishes a
 // 4 x 33 histogram of the scores of the candidate tokens of its chunk, stored bin-major
-// ([bin][chunk]) so that pass B reads the counts of one bin over all chunks as one line.
+// ([bin][chunk]) so that the counts of one bin over all chunks are one line, and the packed scores
+// of its tokens (4 bytes per token and kv-head: score + 1 per head, 0 = not a candidate).
 //
 // A small kernel in between (select_plan_kernel, one CTA per (sequence, kv-head)) derives from the
-// chunk histograms the global threshold T of each head, how many tokens tied at T still fit and how
-// many selected / tied tokens precede each chunk.
+// chunk histograms the threshold T of each head, how many tokens tied at T still fit and how many
+// selected / tied tokens precede each chunk (pick_threshold: both selection rules of the reference).
 //
-// Pass B (select_kernel) re-reads its chunk (L2-resident by then), classifies its tokens against T
-// and writes the selected token indices with a
-// packed warp-scan compaction - no sort, no atomics, nothing to reset. The list of a head is
-// ordered by the token range of the emitting warp (128 ROUNDS tokens); inside it by lane, i.e.
-// not strictly ascending.
+// Pass B (select_kernel) reads the packed scores of its chunk (L2-resident by then), classifies
+// them against T and writes the selected token indices with a packed warp-scan compaction - no
+// sort, no atomics, nothing to reset. The list of a head is ordered by the token range of the
+// emitting warp (256 ROUNDS tokens); inside it by lane, i.e. not strictly ascending.
 //
-// Together they replace the +-1 dot product of USA.forward and the sort/scatter of
-// compute_mask_multi in 'simple' mode (hashattention/hashattention_llama.py:171-187, 423-438).
+// score_select_cluster_kernel does all of this in one kernel for short sequences.
+//
+// Together they replace the +-1 dot product of USA.forward and the sort/scatter (or threshold) of
+// compute_mask_multi (hashattention/hashattention_llama.py:171-187, 423-443).
 // A stable descending sort picks, among tokens tied at the threshold, the lowest indices;
 // the tie fill below reproduces exactly that set.
 //
-// Tiling: a CTA of 256 threads owns a chunk of 4 * ROUNDS pages of one (sequence, kv-head) and
-// walks it in rounds of 1024 tokens; in a round warp w owns tokens [128 w, 128 w + 128) (half a
-// page), four per lane. Only four 16-byte loads are in flight per lane, so many CTAs fit on an
-// SM; the loads of a round are issued together without branches between them (indices are
+// Tiling of pass A: a CTA of 256 threads owns a chunk of 4 * ROUNDS pages of one (sequence,
+// kv-head) and walks it in rounds of 1024 tokens; in a round warp w owns tokens [128 w, 128 w + 128)
+// (half a page), four per lane. Only four 16-byte loads are in flight per lane, so many CTAs fit on
+// an SM; the loads of a round are issued together without branches between them (indices are
 // clamped into range instead of guarded). Everything that does not depend on the preceding
 // kernel - the sequence length, page ids and the first round's hash words - is fetched before
-// the grid-dependency wait.
+// the grid-dependency wait. Pass B: see select_kernel.
 #pragma once
 
 #include <cooperative_groups.h>
