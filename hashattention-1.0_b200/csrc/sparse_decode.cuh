@@ -9,7 +9,8 @@
 // by shuffles, online softmax in registers, CTA reduction by shuffle and shared memory, one
 // (max, sum, acc[128]) partial per CTA. A second, tiny kernel merges the partials of each
 // (b, h) with a log-sum-exp and writes the bf16 output; a (b, h) that fits one split is
-// finished by the gather kernel itself.
+// finished by the gather kernel itself. Small steps use a cluster variant of the gather instead
+// (8 CTAs of 256 threads per (b, h) that merge through distributed shared memory; see the kernel).
 //
 // Replaces hashattention/hashattention_llama.py:578-623: there every masked position is set
 // to finfo.min before an fp32 softmax, i.e. contributes exactly 0, so the softmax runs

@@ -147,8 +147,9 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
  * equals (span + 32) / 2 of the reference. Candidates are tokens [lo, hi) with
  * lo = min(init, S), hi = max(lo, S - recent); the heavy set is the min(hb, hi - lo) best
  * candidates, ties at the threshold broken by lowest token index.
- *   - sel_idx[b][h][0 .. sel_cnt[b][h]) <- heavy token indices, each once; ordered by 128-token
- *     block of the sequence, not strictly ascending inside a block
+ *   - sel_idx[b][h][0 .. sel_cnt[b][h]) <- heavy token indices, each once; ordered by blocks of
+ *     the sequence (128 to 1024 tokens, depending on the kernel that ran), not strictly
+ *     ascending inside a block: the set is the contract, not the order
  *   - scores_dbg (optional, may be NULL): [batch][num_q_heads][max_pages*page_size] u8      */
 int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
                     const uint32_t* q_codes, const uint32_t* hash_pages,
