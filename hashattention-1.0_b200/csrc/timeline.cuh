@@ -13,7 +13,9 @@ enum TimelineKernel { kTlHashDecode = 0, kTlScoreHist, kTlSelect, kTlGather, kTl
 enum TimelineEvent { kTlEntry = 0, kTlAfterWait, kTlExit, kTlMarkA, kTlMarkB, kTlMarkC, kTlEvents };
 
 #ifdef HA_TIMELINE
-__device__ unsigned long long* g_timeline = nullptr;
+// in constant memory: the pointer is read at every stamp, and a global-memory load there would put an L2 round
+// trip (about half a microsecond) into the very path that is being timed
+__constant__ unsigned long long* g_timeline = nullptr;
 
 __device__ __forceinline__ void tl_mark(int kernel, int event) {
     if (g_timeline == nullptr || threadIdx.x != 0) return;
