@@ -728,10 +728,22 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
         const int g = warp;
         const int n = s_tot[g * kBins + 32 - lane];  // lane l holds bin 32 - l; bin 0 apart
         int cum = n;
+        // tokens per bin in the (round, rank) pairs before (rd, this CTA); scanned together with the totals
+        // (independent shuffle chains interleave, this section being a serial stretch of the kernel)
+        int nbv[ROUNDS], cumbv[ROUNDS];
+#pragma unroll
+        for (int rd = 0; rd < ROUNDS; ++rd) nbv[rd] = cumbv[rd] = s_bef[rd][g * kBins + 32 - lane];
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const int u = __shfl_up_sync(0xffffffffu, cum, d);
-            if (lane >= d) cum += u;
+            int ub[ROUNDS];
+#pragma unroll
+            for (int rd = 0; rd < ROUNDS; ++rd) ub[rd] = __shfl_up_sync(0xffffffffu, cumbv[rd], d);
+            if (lane >= d) {
+                cum += u;
+#pragma unroll
+                for (int rd = 0; rd < ROUNDS; ++rd) cumbv[rd] += ub[rd];
+            }
         }
         bool overflow;
         const Threshold th = pick_threshold(p, n, cum, s_tot[g * kBins], s_ok ? r.hb : 0, overflow);
@@ -739,14 +751,7 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
         if (overflow && lane == 0 && rank == 0) report(p.status, HA_ERR_SEL_OVERFLOW);
 #pragma unroll
         for (int rd = 0; rd < ROUNDS; ++rd) {
-            // tokens above T / at T in the (round, rank) pairs before (rd, this CTA)
-            const int nb = s_bef[rd][g * kBins + 32 - lane];
-            int cumb = nb;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const int u = __shfl_up_sync(0xffffffffu, cumb, d);
-                if (lane >= d) cumb += u;
-            }
+            const int nb = nbv[rd], cumb = cumbv[rd];
             const int lt = min(max(32 - T, 0), 31);
             const int gt_l = __shfl_sync(0xffffffffu, cumb - nb, lt), eq_l = __shfl_sync(0xffffffffu, nb, lt);
             const int all31 = __shfl_sync(0xffffffffu, cumb, 31);
