@@ -24,7 +24,7 @@ HA_ERR_SEL_OVERFLOW = 8
 HA_ERR_SCRATCH_LIMIT = 9
 HA_WEIGHTS_BF16 = 0
 HA_WEIGHTS_F32 = 1
-HA_ABI_VERSION = 2
+HA_ABI_VERSION = 3
 HA_EVAL_SIMPLE = 0
 HA_EVAL_DEPTH = 1
 
@@ -42,7 +42,8 @@ class HaBudget(ctypes.Structure):
 
 
 class HaHashWeights(ctypes.Structure):
-    _fields_ = [("wq", c_void_p), ("bq", c_void_p), ("wk", c_void_p), ("bk", c_void_p), ("dtype", c_int32)]
+    _fields_ = [("wq", c_void_p), ("bq", c_void_p), ("wk", c_void_p), ("bk", c_void_p), ("dtype", c_int32),
+                ("num_layers", c_int32)]
 
 
 _P = c_void_p

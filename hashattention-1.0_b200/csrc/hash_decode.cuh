@@ -30,6 +30,7 @@ struct HashDecodeParams {
                              // q itself lives in mapped host memory (read once here instead of by every gather CTA)
     int32_t* status;
     int B, Hkv, max_pages, num_pages, batch_per_cta;
+    int layers;          // 3, 2 or 1 Linear layers (see ha_hash_weights_t.num_layers)
 };
 
 // Eight consecutive weights of one row, as stored, and their dot product with eight inputs.
@@ -159,9 +160,12 @@ __device__ __forceinline__ void hidden_layer(const Row8<WT> (&w)[kRowLoads], con
 // that was requested before the call). The caller may call mlp_eval again without a further
 // barrier: each buffer is rewritten only after barriers that every reader of the previous
 // round has passed.
+//
+// layers: 3 = all of W0, W1, W2; 2 = W0 then W2 (Linear-SiLU-Linear, hashattention_llama.py:112-120);
+// 1 = W2 alone (:121-127).
 template <typename WT, typename F>
 __device__ __forceinline__ void mlp_eval(const MlpRegs<WT>& r, const uint4 raw,
-                                         MlpSmem& sm, int warp, int lane, F&& between) {
+                                         MlpSmem& sm, int warp, int lane, F&& between, int layers = 3) {
     const int half = lane >> 4, col = (lane & 15) * 8;
     float x[8];
     {
@@ -170,13 +174,19 @@ __device__ __forceinline__ void mlp_eval(const MlpRegs<WT>& r, const uint4 raw,
         x[4] = bf16_lo(raw.z); x[5] = bf16_hi(raw.z);
         x[6] = bf16_lo(raw.w); x[7] = bf16_hi(raw.w);
     }
-    hidden_layer(r.w0, r.b0, x, sm.h0, warp, lane);
+    if (layers >= 2) hidden_layer(r.w0, r.b0, x, sm.h0, warp, lane);
     between();
-    __syncthreads();
-    load_x8(sm.h0 + col, x);
-    hidden_layer(r.w1, r.b1, x, sm.h1, warp, lane);
-    __syncthreads();
-    load_x8(sm.h1 + col, x);
+    if (layers >= 2) {
+        __syncthreads();
+        load_x8(sm.h0 + col, x);
+    } else {
+        __syncthreads();  // no hidden layer separates this call's write of `out` from the previous call's readers
+    }
+    if (layers == 3) {
+        hidden_layer(r.w1, r.b1, x, sm.h1, warp, lane);
+        __syncthreads();
+        load_x8(sm.h1 + col, x);
+    }
     {
         const float s = half_warp_sum(r.w2.dot(x)) + r.b2;
         if ((lane & 15) == 0) sm.out[warp * 2 + half] = s;
@@ -238,7 +248,7 @@ hash_decode_kernel(const HashDecodeParams p) {
                 const int pidx = min(max(S - 1, 0) / kPage, p.max_pages - 1);
                 page = p.page_table[(size_t)b * p.max_pages + pidx];
             }
-        });
+        }, p.layers);
         if (warp != 0) continue;
 
         const float pre = sm.out[lane];
@@ -416,15 +426,22 @@ hash_decode_batched_kernel(const HashDecodeParams p) {
             *reinterpret_cast<float4*>(&sm.x[0][warp][lane * 4]) = xv;
         }
         __syncthreads();  // inputs (and, in the first pass, the weights) are in shared memory
-        hdb_hidden(sm, sm.wt0, sm.bias, 0, tid);
-        hdb_hidden(sm, sm.wt1, sm.bias + kHidden, 1, tid);
-        // ---- last layer: warp = row, lane = output bit; activations of layer 1 are in x[0]
+        int cur = 0;  // which of the two activation buffers holds the input of the next layer
+        if (p.layers >= 2) {
+            hdb_hidden(sm, sm.wt0, sm.bias, cur, tid);
+            cur ^= 1;
+        }
+        if (p.layers == 3) {
+            hdb_hidden(sm, sm.wt1, sm.bias + kHidden, cur, tid);
+            cur ^= 1;
+        }
+        // ---- last layer: warp = row, lane = output bit
         float pre = sm.bias[2 * kHidden + lane];
 #pragma unroll 16
-        for (int i = 0; i < kHidden; ++i) pre = fmaf(sm.x[0][warp][i], sm.wt2[i][lane], pre);
+        for (int i = 0; i < kHidden; ++i) pre = fmaf(sm.x[cur][warp][i], sm.wt2[i][lane], pre);
         // bit i = 1 iff output i > 0 (efficiency/kernels/torchatt.py:35-36: relu(sign(x)))
         const uint32_t code = __ballot_sync(0xffffffffu, pre > 0.0f);
-        __syncthreads();  // x[0] is rewritten by the next pass
+        __syncthreads();  // the activation buffers are rewritten by the next pass
         if (!live) continue;
         if (p.preact_dbg != nullptr)
             p.preact_dbg[(((size_t)b * 2 + side) * Hq + h) * kCodeBits + lane] = pre;
@@ -468,6 +485,7 @@ struct HashPrefillParams {
     const int32_t* first_token;  // [B] or null
     int32_t* status;
     int B, Hkv, max_pages, num_pages;
+    int layers;  // 3, 2 or 1 Linear layers
 };
 
 template <typename WT>
@@ -503,7 +521,7 @@ hash_prefill_simt_kernel(const HashPrefillParams p) {
         const size_t slot = slot0 + t % kPage;
         const uint4 raw = raw_next;  // the next token's row is requested while this one is evaluated
         if (t + 1 < t_end) raw_next = load_x_row(p.k_pages + (slot + 1) * kHeadDim, lane);
-        mlp_eval(regs, raw, sm, warp, lane, [] {});
+        mlp_eval(regs, raw, sm, warp, lane, [] {}, p.layers);
         if (warp == 0) {
             const float pre = sm.out[lane];
             const uint32_t code = __ballot_sync(0xffffffffu, pre > 0.0f);

@@ -48,6 +48,7 @@ int check_budget(const ha_budget_t* b) {
 int check_weights(const ha_hash_weights_t* w, bool need_q, bool need_k) {
     if (w == nullptr) return HA_ERR_BAD_ARG;
     if (w->dtype != HA_WEIGHTS_BF16 && w->dtype != HA_WEIGHTS_F32) return HA_ERR_BAD_ARG;
+    if (w->num_layers < 0 || w->num_layers > 3) return HA_ERR_BAD_ARG;
     if (need_q && (w->wq == nullptr || w->bq == nullptr)) return HA_ERR_BAD_ARG;
     if (need_k && (w->wk == nullptr || w->bk == nullptr)) return HA_ERR_BAD_ARG;
     return HA_OK;
@@ -535,6 +536,7 @@ static int hash_decode_impl(const ha_shape_t* shape, const ha_hash_weights_t* we
     p.q_codes = q_codes;
     p.preact_dbg = preact_dbg;
     p.q_stage = static_cast<__nv_bfloat16*>(q_stage);
+    p.layers = weights->num_layers == 0 ? 3 : weights->num_layers;
     p.status = status;
     p.B = shape->batch;
     p.Hkv = shape->num_kv_heads;
@@ -607,8 +609,9 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         status == nullptr)
         return HA_ERR_BAD_ARG;
 
-    if (weights->dtype == HA_WEIGHTS_BF16) {
-        // bf16 weights: tcgen05 GEMM chain. One CTA per SM (its shared memory holds a head's weights),
+    const int layers = weights->num_layers == 0 ? 3 : weights->num_layers;
+    if (weights->dtype == HA_WEIGHTS_BF16 && layers == 3) {
+        // bf16 weights, the 3-layer MLP: tcgen05 GEMM chain. One CTA per SM (its shared memory holds a head's weights),
         // heads in grid.y, token tiles dealt round-robin over grid.x.
         // (a per-device function attribute: set at every call, so that a process driving several GPUs is served)
         if (cudaFuncSetAttribute(hash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -644,7 +647,7 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         cfg.numAttrs = 1;
         return cudaLaunchKernelEx(&cfg, hash_prefill_tc_kernel, t) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
     }
-    // fp32 weights: exact fp32 arithmetic on the CUDA cores
+    // fp32 weights, or the 1- and 2-layer hash functions: fp32 arithmetic on the CUDA cores
     HashPrefillParams p;
     p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
     p.hash_pages = hash_pages;
@@ -659,8 +662,12 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
     p.max_pages = shape->max_pages;
     p.num_pages = shape->num_pages;
     const dim3 grid(shape->num_kv_heads * kGroup, shape->max_pages, shape->batch);
-    const cudaError_t e = launch(hash_prefill_simt_kernel<float>, grid, dim3(kHashDecodeThreads),
-                                 static_cast<cudaStream_t>(stream), 1, p);
+    p.layers = layers;
+    const cudaError_t e = weights->dtype == HA_WEIGHTS_BF16
+        ? launch(hash_prefill_simt_kernel<__nv_bfloat16>, grid, dim3(kHashDecodeThreads),
+                 static_cast<cudaStream_t>(stream), 1, p)
+        : launch(hash_prefill_simt_kernel<float>, grid, dim3(kHashDecodeThreads),
+                 static_cast<cudaStream_t>(stream), 1, p);
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 

@@ -19,14 +19,15 @@ OUTLIER_CHANNELS = (3, 40, 77, 101)
 OUTLIER_SCALE = 8.0
 
 
-def make_usa(num_heads: int = 32, head_dim: int = 128, seed: int = 0, bf16: bool = True) -> USA:
+def make_usa(num_heads: int = 32, head_dim: int = 128, seed: int = 0, bf16: bool = True, num_layers: int = 3) -> USA:
     """Hash weights with torch's default Linear init under ``torch.manual_seed(seed)``: the values
     the reference's ``load_usa(config, None)`` holds under the same seed
     (hashattention/hashattention_llama.py:633-646). ``bf16=True`` rounds them once to bf16."""
     state = torch.random.get_rng_state()
     try:
         torch.manual_seed(seed)
-        usa = USA(num_heads, head_dim, {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 3})
+        usa = USA(num_heads, head_dim, {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0,
+                                        "lth_num_layers": num_layers})
     finally:
         torch.random.set_rng_state(state)
     return usa.bfloat16() if bf16 else usa

@@ -39,7 +39,7 @@ def decode_step(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
                 q_codes: torch.Tensor, sel_idx: torch.Tensor, sel_cnt: torch.Tensor,
                 workspace: torch.Tensor, status: torch.Tensor, out: torch.Tensor,
                 init_budget: int, recent_budget: int, heavy_budget: float, sm_scale: float,
-                eval_mode: int = 0, retrieve_depth: int = 0) -> None:
+                eval_mode: int = 0, retrieve_depth: int = 0, num_hash_layers: int = 3) -> None:
     lib = _lib.load()
     tensors = dict(q=q, k_new=k_new, v_new=v_new, k_pages=k_pages, v_pages=v_pages, hash_pages=hash_pages,
                    page_table=page_table, seq_lens=seq_lens, wq=wq, bq=bq, wk=wk, bk=bk, q_codes=q_codes,
@@ -58,7 +58,8 @@ def decode_step(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
     budget = _lib.HaBudget(int(init_budget), int(recent_budget), float(heavy_budget), int(eval_mode),
                            int(retrieve_depth))
     weights = _lib.HaHashWeights(wq.data_ptr(), bq.data_ptr(), wk.data_ptr(), bk.data_ptr(),
-                                 _lib.HA_WEIGHTS_BF16 if wq.dtype == torch.bfloat16 else _lib.HA_WEIGHTS_F32)
+                                 _lib.HA_WEIGHTS_BF16 if wq.dtype == torch.bfloat16 else _lib.HA_WEIGHTS_F32,
+                                 int(num_hash_layers))
     need = int(lib.ha_workspace_bytes(shape, budget))
     if need == 0 or workspace.numel() * workspace.element_size() < need:
         raise ValueError(f"workspace holds {workspace.numel() * workspace.element_size()} bytes, the step needs {need}")
@@ -76,7 +77,8 @@ def decode_step(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
 @decode_step.register_fake
 def _decode_step_fake(q, k_new, v_new, k_pages, v_pages, hash_pages, page_table, seq_lens, wq, bq, wk, bk,
                       q_codes, sel_idx, sel_cnt, workspace, status, out,
-                      init_budget, recent_budget, heavy_budget, sm_scale, eval_mode=0, retrieve_depth=0) -> None:
+                      init_budget, recent_budget, heavy_budget, sm_scale, eval_mode=0, retrieve_depth=0,
+                      num_hash_layers=3) -> None:
     return None
 
 
@@ -88,5 +90,5 @@ def decode_step_op(ctx, q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tenso
     torch.ops.hashattn.decode_step(q, k_new, v_new, c.k_pages, c.v_pages, c.hash_pages, c.page_table, c.seq_lens,
                                    w.wq, w.bq, w.wk, w.bk, ctx.q_codes, ctx.sel_idx, ctx.sel_cnt, ctx.workspace,
                                    ctx.status, out, b.init_budget, b.recent_budget, b.heavy_budget, ctx.sm_scale,
-                                   ctx.c_budget.eval_mode, ctx.c_budget.retrieve_depth)
+                                   ctx.c_budget.eval_mode, ctx.c_budget.retrieve_depth, w.num_layers)
     return out

@@ -36,28 +36,38 @@ class PackedHashWeights:
     wk: torch.Tensor
     bk: torch.Tensor
     dtype_code: int
+    num_layers: int = 3   # Linear layers of the hash function; unused slots of the layout hold zeros
 
     def c_struct(self) -> _lib.HaHashWeights:
         return _lib.HaHashWeights(self.wq.data_ptr(), self.bq.data_ptr(), self.wk.data_ptr(),
-                                  self.bk.data_ptr(), self.dtype_code)
+                                  self.bk.data_ptr(), self.dtype_code, self.num_layers)
 
     def slice_heads(self, h0: int, h1: int) -> "PackedHashWeights":
         """The weights of query heads [h0, h1): what one GPU of a kv-head partition holds."""
         return PackedHashWeights(self.wq[h0:h1].contiguous(), self.bq[h0:h1].contiguous(),
-                                 self.wk[h0:h1].contiguous(), self.bk[h0:h1].contiguous(), self.dtype_code)
+                                 self.wk[h0:h1].contiguous(), self.bk[h0:h1].contiguous(), self.dtype_code,
+                                 self.num_layers)
 
 
-def _mlp(head_dim: int, int_dim: int, final_dim: int) -> nn.Sequential:
-    return nn.Sequential(nn.Linear(head_dim, int_dim), nn.SiLU(), nn.Linear(int_dim, int_dim), nn.SiLU(),
-                         nn.Linear(int_dim, final_dim))
+def _mlp(head_dim: int, int_dim: int, final_dim: int, num_layers: int = 3) -> nn.Sequential:
+    """The hash function of one head with the reference's module structure for 3, 2 or 1 layers
+    (hashattention/hashattention_llama.py:99-127)."""
+    if num_layers == 3:
+        return nn.Sequential(nn.Linear(head_dim, int_dim), nn.SiLU(), nn.Linear(int_dim, int_dim), nn.SiLU(),
+                             nn.Linear(int_dim, final_dim))
+    if num_layers == 2:
+        return nn.Sequential(nn.Linear(head_dim, int_dim), nn.SiLU(), nn.Linear(int_dim, final_dim))
+    return nn.Sequential(nn.Linear(head_dim, final_dim))
 
 
 class USA(nn.Module):
     """Parameter container with the reference's constructor signature
     (hashattention/hashattention_llama.py:87-139).
 
-    Only the configuration the kernels implement is accepted: 3 layers, hidden width 128,
-    32 output bits, head_dim 128. Other ``lth_*`` settings raise ``NotImplementedError``.
+    Only the configurations the kernels implement are accepted: 3, 2 or 1 layers, hidden width 128,
+    32 output bits, head_dim 128. Other ``lth_*`` settings (the LSH baseline ``lth_num_layers=0`` among
+    them: its extra input coordinate depends on the largest key norm of the whole call, :75-84, so cached
+    codes would go stale) raise ``NotImplementedError``.
     """
 
     def __init__(self, num_heads: int, head_dim: int, usa_params: dict = DEFAULT_USA_CFG):
@@ -68,25 +78,39 @@ class USA(nn.Module):
         self.lth_final_dim = usa_params["lth_final_dim"]
         self.lth_thold = usa_params["lth_thold"]
         self.num_layers = usa_params.get("lth_num_layers", 3)
-        if (self.num_layers, self.int_dim, self.lth_final_dim, head_dim) != (3, HIDDEN, CODE_BITS, 128):
+        if self.num_layers not in (1, 2, 3) or (self.int_dim, self.lth_final_dim, head_dim) != (HIDDEN, CODE_BITS, 128):
             raise NotImplementedError(
-                "the sm_100a kernels implement lth_num_layers=3, lth_init_dim=128, lth_final_dim=32, "
+                "the sm_100a kernels implement lth_num_layers=1..3, lth_init_dim=128, lth_final_dim=32, "
                 f"head_dim=128; got layers={self.num_layers}, int_dim={self.int_dim}, "
                 f"final_dim={self.lth_final_dim}, head_dim={head_dim}"
             )
         self.learning_to_hash_transformation_k = nn.ModuleList(
-            [_mlp(head_dim, self.int_dim, self.lth_final_dim) for _ in range(num_heads)])
+            [_mlp(head_dim, self.int_dim, self.lth_final_dim, self.num_layers) for _ in range(num_heads)])
         self.learning_to_hash_transformation_q = nn.ModuleList(
-            [_mlp(head_dim, self.int_dim, self.lth_final_dim) for _ in range(num_heads)])
+            [_mlp(head_dim, self.int_dim, self.lth_final_dim, self.num_layers) for _ in range(num_heads)])
         self._packed: PackedHashWeights | None = None
         # a state dict loaded through this module or any parent invalidates the packed copy
         self.register_load_state_dict_post_hook(lambda module, _incompatible: setattr(module, "_packed", None))
 
     # -- packing ---------------------------------------------------------------------------
     def _pack_side(self, nets: nn.ModuleList, dtype: torch.dtype, device) -> tuple[torch.Tensor, torch.Tensor]:
-        w = torch.stack([torch.cat([net[0].weight.reshape(-1), net[2].weight.reshape(-1),
-                                    net[4].weight.reshape(-1)]) for net in nets])
-        b = torch.stack([torch.cat([net[0].bias, net[2].bias, net[4].bias]) for net in nets])
+        # the kernels' layout always has the three slots [W0 | W1 | W2]: a 2-layer function fills W0 and W2,
+        # a 1-layer function W2 only; the rest stays zero
+        def slots(net):
+            lin = [m for m in net if isinstance(m, nn.Linear)]
+            z = lambda *shape: torch.zeros(*shape, dtype=lin[0].weight.dtype, device=lin[0].weight.device)  # noqa: E731
+            first = lin[0] if len(lin) >= 2 else None
+            second = lin[1] if len(lin) == 3 else None
+            last = lin[-1]
+            ws = [first.weight if first is not None else z(HIDDEN, self.head_dim),
+                  second.weight if second is not None else z(HIDDEN, HIDDEN), last.weight]
+            bs = [first.bias if first is not None else z(HIDDEN), second.bias if second is not None else z(HIDDEN),
+                  last.bias]
+            return torch.cat([w.reshape(-1) for w in ws]), torch.cat(bs)
+
+        packed = [slots(net) for net in nets]
+        w = torch.stack([p[0] for p in packed])
+        b = torch.stack([p[1] for p in packed])
         return (w.detach().to(device=device, dtype=dtype).contiguous(),
                 b.detach().to(device=device, dtype=torch.float32).contiguous())
 
@@ -96,14 +120,14 @@ class USA(nn.Module):
         device = torch.device(device) if device is not None else self.learning_to_hash_transformation_k[0][0].weight.device
         if self._packed is not None and not refresh and self._packed.wq.device == device:
             return self._packed
-        pdtype = self.learning_to_hash_transformation_k[0][0].weight.dtype
+        pdtype = self.learning_to_hash_transformation_k[0][0].weight.dtype  # (index 0 is a Linear for every layer count)
         if pdtype == torch.bfloat16:
             wdtype, code = torch.bfloat16, _lib.HA_WEIGHTS_BF16
         else:
             wdtype, code = torch.float32, _lib.HA_WEIGHTS_F32
         wq, bq = self._pack_side(self.learning_to_hash_transformation_q, wdtype, device)
         wk, bk = self._pack_side(self.learning_to_hash_transformation_k, wdtype, device)
-        self._packed = PackedHashWeights(wq, bq, wk, bk, code)
+        self._packed = PackedHashWeights(wq, bq, wk, bk, code, self.num_layers)
         return self._packed
 
     def _apply(self, fn, *args, **kwargs):  # .cuda() / .bfloat16() / .to() invalidate the packed copy

@@ -47,7 +47,7 @@
 extern "C" {
 #endif
 
-#define HA_ABI_VERSION 2
+#define HA_ABI_VERSION 3
 
 /* status codes (return values and contents of the device status word) */
 #define HA_OK 0
@@ -102,6 +102,11 @@ typedef struct ha_hash_weights {
     const void* wk;    /* key-side weights                                                   */
     const float* bk;   /* key-side biases                                                    */
     int32_t dtype;     /* HA_WEIGHTS_BF16 or HA_WEIGHTS_F32                                  */
+    int32_t num_layers; /* lth_num_layers of the reference (hashattention_llama.py:99-127): 3 (or 0,
+                         * meaning 3): Linear-SiLU-Linear-SiLU-Linear; 2: Linear(128,128)-SiLU-
+                         * Linear(128,32), stored in the W0 and W2 slots; 1: Linear(128,32), stored in
+                         * the W2 slot. Unused slots are ignored. The layout per head stays
+                         * [W0 | W1 | W2] and [b0 | b1 | b2].                                 */
 } ha_hash_weights_t;
 
 int ha_abi_version(void);

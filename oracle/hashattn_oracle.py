@@ -48,10 +48,11 @@ def mlp_preact(nets, x: torch.Tensor) -> torch.Tensor:
 
 def nets_from_usa(usa, side: str):
     """Extracts ``[(W,b)...]`` per head, up-cast to fp32, from a module with the reference's
-    attribute layout (``learning_to_hash_transformation_{k,q}[h][0|2|4]``; :100-111)."""
+    attribute layout (``learning_to_hash_transformation_{k,q}[h]``: a Sequential of 3, 2 or 1 Linear layers
+    with SiLU between them; :99-127)."""
     mods = getattr(usa, f"learning_to_hash_transformation_{side}")
-    return [[(m[i].weight.detach().to(torch.float32), m[i].bias.detach().to(torch.float32)) for i in (0, 2, 4)]
-            for m in mods]
+    return [[(layer.weight.detach().to(torch.float32), layer.bias.detach().to(torch.float32))
+             for layer in m if hasattr(layer, "weight")] for m in mods]
 
 
 def pack_codes(preact: torch.Tensor) -> torch.Tensor:

@@ -80,17 +80,17 @@ class ListCache:
         return self.key_cache[layer_idx], self.value_cache[layer_idx]
 
 
-def reference_modules(Hq, Hkv, init, recent, heavy, seed=0, bf16_weights=True, eval_mode="simple", depth=-1):
+def reference_modules(Hq, Hkv, init, recent, heavy, seed=0, bf16_weights=True, eval_mode="simple", depth=-1, layers=3):
     cfg = LlamaConfig(hidden_size=Hq * 128, num_attention_heads=Hq, num_key_value_heads=Hkv, num_hidden_layers=1,
                       intermediate_size=256, vocab_size=128, max_position_embeddings=131072,
                       rope_parameters={"rope_theta": 500000.0, "rope_type": "default"})
     cfg.rope_theta = 500000.0
-    for k, v in dict(lth_init_dim=128, lth_final_dim=32, lth_thold=0, lth_num_layers=3, init_budget=init,
+    for k, v in dict(lth_init_dim=128, lth_final_dim=32, lth_thold=0, lth_num_layers=layers, init_budget=init,
                      heavy_budget=heavy, recent_budget=recent, usa_eval_mode=eval_mode, usa_retrieve_depth=depth).items():
         setattr(cfg, k, v)
     torch.manual_seed(seed)
-    usa = H.USA(Hq, 128, {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 3})
-    mine = synthetic.make_usa(Hq, 128, seed=seed, bf16=False)
+    usa = H.USA(Hq, 128, {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": layers})
+    mine = synthetic.make_usa(Hq, 128, seed=seed, bf16=False, num_layers=layers)
     for (n1, p1), (n2, p2) in zip(usa.state_dict().items(), mine.state_dict().items()):
         assert n1 == n2 and torch.equal(p1, p2), f"USA mirror differs from the reference at {n1}"
     if bf16_weights:
@@ -297,10 +297,24 @@ def rows():
     np.savez_compressed(os.path.join(HERE, "rows.npz"), **arrays)
 
 
+def layers():
+    """The 2-layer and 1-layer hash functions (lth_num_layers 2 and 1, :112-127) on the inputs of edge.npz
+    (S = 300, 4 query heads, 1 kv head; the inputs are stored there)."""
+    Hq, Hkv, S, init, recent, heavy = 4, 1, 300, 16, 16, 1.0 / 8
+    inp = synthetic.make_decode_inputs(91, [S], Hq, Hkv, bf16=True)
+    q, k, v = inp.q, torch.stack(inp.k), torch.stack(inp.v)
+    arrays = dict(meta=np.array([Hq, Hkv, S, init, recent], dtype=np.int64), heavy=np.float64(heavy),
+                  input_sha256=np.array(digest(q, k, v)))
+    for n in (1, 2):
+        _, usa, att = reference_modules(Hq, Hkv, init, recent, heavy, layers=n)
+        arrays.update(outputs_to_arrays(run_reference(att, usa, q, k, v), prefix=f"l{n}/"))
+    np.savez_compressed(os.path.join(HERE, "layers.npz"), **arrays)
+
+
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["case_a", "edge", "config0", "depth", "rows"]
+    which = sys.argv[1:] or ["case_a", "edge", "config0", "depth", "rows", "layers"]
     for name in which:
-        {"case_a": case_a, "edge": edge, "config0": config0, "depth": depth, "rows": rows}[name]()
+        {"case_a": case_a, "edge": edge, "config0": config0, "depth": depth, "rows": rows, "layers": layers}[name]()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -106,6 +106,16 @@ def load_edge() -> dict[str, GoldenCase]:
     return out
 
 
+def load_layers() -> dict[int, GoldenCase]:
+    """The 1- and 2-layer hash functions on the inputs stored in edge.npz."""
+    z = np.load(os.path.join(GOLDEN, "layers.npz"))
+    e = np.load(os.path.join(GOLDEN, "edge.npz"))
+    Hq, Hkv, S, init, recent = (int(x) for x in z["meta"])
+    q, k, v = from_bf16_bits(e["q"]), from_bf16_bits(e["k"]), from_bf16_bits(e["v"])
+    assert k.shape[2] == S and q.shape[1] == Hq
+    return {n: GoldenCase(z, f"l{n}/", q, k, v, init, recent, float(z["heavy"])) for n in (1, 2)}
+
+
 def load_config0(synthetic):
     """Returns (case, inputs_match): inputs are regenerated from the seed and compared with the
     recorded SHA-256; inputs_match is False if this machine's generator gives other bits."""

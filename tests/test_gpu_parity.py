@@ -322,6 +322,33 @@ def test_large_batch_takes_the_batched_encoder(device):
     run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(8, 1.0 / 8, 8), shuffle_seed=4)
 
 
+@pytest.mark.parametrize("n", [1, 2])
+def test_one_and_two_layer_hash_functions_step(device, n):
+    """lth_num_layers 1 and 2: the register encoder (decode), the CUDA-core prefill (the tcgen05 chain is
+    3-layer only) and everything downstream, against the oracle and the recorded reference run."""
+    case = helpers.load_layers()[n]
+    usa = synthetic.make_usa(case.q.shape[1], 128, 0, True, num_layers=n)
+    ks, vs = [case.k[b] for b in range(case.k.shape[0])], [case.v[b] for b in range(case.v.shape[0])]
+    identical, out, ctx, cache = run_step_and_check(device, usa, case.q, ks, vs, budget_of(case))
+    if bool((cache.read_codes(0).cpu() == case.k_codes[0]).all()) and \
+            bool(((ctx.q_codes.cpu().to(torch.int64) & ALL_BITS) == case.q_codes).all()):
+        want = orc.heavy_sets(case.mask, case.init, case.recent)
+        for h in range(case.q.shape[1]):
+            assert torch.equal(heavy_from_device(ctx, 0, h), want[0][h])
+        ok, max_abs, rel = helpers.att_close(out, case.out)
+        assert ok, f"layers={n}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
+
+
+def test_two_layer_hash_function_in_the_batched_encoder(device):
+    """40 sequences x 32 heads with the 2-layer function: the shared-memory GEMM encoder skips the unused slot."""
+    Hq, Hkv = 32, 8
+    g = torch.Generator().manual_seed(78)
+    lens = [int(x) for x in torch.randint(40, 330, (40,), generator=g)]
+    usa = synthetic.make_usa(Hq, 128, 8, True, num_layers=2)
+    inp = synthetic.make_decode_inputs(108, lens, Hq, Hkv)
+    run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(8, 1.0 / 8, 8), shuffle_seed=4)
+
+
 def test_ragged_batch_shuffled_pages(device):
     Hq, Hkv, lens = 8, 2, [1, 2, 31, 255, 256, 257, 1500, 4097]
     usa = synthetic.make_usa(Hq, 128, 2, True)

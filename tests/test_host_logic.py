@@ -21,7 +21,7 @@ def test_usa_state_dict_layout():
 
 
 @pytest.mark.parametrize("params", [
-    {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 2},
+    {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 0},
     {"lth_int_dim": 64, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 3},
     {"lth_int_dim": 128, "lth_final_dim": 64, "lth_thold": 0, "lth_num_layers": 3},
 ])

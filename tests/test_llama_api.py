@@ -30,7 +30,14 @@ def test_load_usa_builds_one_module_per_layer_and_loads_reference_state_dicts(tm
     again = hal.load_usa(cfg, str(path), device="cpu")
     for a, b in zip(mods.state_dict().values(), again.state_dict().values()):
         assert torch.equal(a, b)
-    cfg.lth_num_layers = 2
+    cfg.lth_num_layers = 2     # Linear-SiLU-Linear (hashattention_llama.py:112-120): reference keys 0 and 2
+    two = hal.load_usa(cfg, None, device="cpu")
+    assert [k for k in two.state_dict() if k.startswith("0.learning_to_hash_transformation_k.0.")] == [
+        "0.learning_to_hash_transformation_k.0.0.weight", "0.learning_to_hash_transformation_k.0.0.bias",
+        "0.learning_to_hash_transformation_k.0.2.weight", "0.learning_to_hash_transformation_k.0.2.bias"]
+    packed = two[0].packed("cpu")
+    assert packed.num_layers == 2 and packed.wk.shape == (4, 36864) and float(packed.wk[:, 16384:32768].abs().max()) == 0.0
+    cfg.lth_num_layers = 0     # the LSH baseline is not implemented
     with pytest.raises(NotImplementedError):
         hal.load_usa(cfg, None, device="cpu")
 
