@@ -37,7 +37,8 @@ from .ops import Budget, ChunkRows, SparseDecodeContext
 from .torch_ops import decode_step_op
 from .usa import USA
 
-__all__ = ["USA", "LlamaAttention_heavy_hitter", "load_usa", "convert_usa", "reset_usa", "set_eval_usa_mode"]
+__all__ = ["USA", "LlamaAttention_heavy_hitter", "load_usa", "convert_usa", "reset_usa", "set_eval_usa_mode",
+           "set_train_usa_mode", "print_stats"]
 
 
 def _rotate_half(x):
@@ -262,3 +263,16 @@ def set_eval_usa_mode(model):
         if isinstance(module, LlamaAttention_heavy_hitter):
             module.train_usa = False
     return model
+
+
+def set_train_usa_mode(model, loss_func=None, optimizer=None):
+    """The reference's switch into hash training (:683-697). Training the hash functions is outside this
+    library (it evaluates trained ones), so this refuses instead of silently decoding untrained."""
+    raise NotImplementedError("hash training (train_usa) is not implemented: train with the reference, load with load_usa")
+
+
+def print_stats(model):
+    """The reference prints the overlap statistics it collected during prefill (:713-726). Statistics are not
+    collected inside forward here; diagnostics/recall.py computes the same statistic on demand."""
+    raise NotImplementedError("collect_stats is not implemented: see diagnostics/recall.py for the overlap statistic")
+

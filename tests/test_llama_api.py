@@ -63,6 +63,12 @@ def test_convert_usa_swaps_attention_and_keeps_weights():
         hal.convert_usa(LlamaForCausalLM(cfg), cfg, mods, collect_stats=True, train_usa=False)
 
 
+def test_training_and_statistics_entry_points_exist_and_refuse():
+    for fn in (hal.set_train_usa_mode, hal.print_stats):
+        with pytest.raises(NotImplementedError):
+            fn(torch.nn.Linear(2, 2))
+
+
 def test_unsupported_modes_raise():
     cfg = tiny_config(1)
     cfg.usa_eval_mode, cfg.usa_retrieve_depth = "depth", 3   # the depth rule is supported
