@@ -265,12 +265,15 @@ def test_depth_rule_on_the_two_pass_selection(device, monkeypatch, depth):
     assert torch.equal(out0, out1) and torch.equal(ctx0.sel_cnt, ctx1.sel_cnt)
 
 
+@pytest.mark.parametrize("stagger", ["0", "1"])
 @pytest.mark.parametrize("name", ["q5", "q16_page", "q3_short", "q4_depth"])
-def test_multi_token_decode_rows_against_reference_output(device, name):
+def test_multi_token_decode_rows_against_reference_output(device, monkeypatch, name, stagger):
     """2 <= q_len <= 128 new tokens per sequence in one call (ha_decode_step_rows): every (sequence,
     token) is a row that sees the keys up to its own, with the budget of the whole length. Against
     the oracle on the device's codes and, when those equal the reference's, against the recorded
-    reference masks (inside the causal part) and outputs."""
+    reference masks (inside the causal part) and outputs. Plain, and (where the two-pass selection
+    runs) as two staggered halves of the kv-heads."""
+    monkeypatch.setenv("HA_STAGGER", stagger)
     c = helpers.load_rows()[name]
     B, Hq, ql, S = c.q.shape[0], c.q.shape[1], c.ql, c.S
     usa = synthetic.make_usa(Hq, 128, 0, True)
