@@ -229,6 +229,16 @@ def run_gpu_arm(args):
     torch.cuda.synchronize()
     for ctx in ctxs:
         ctx.check_status()
+    # what was fed in, so that a result can be tied to its inputs: the seeds and a digest of layer instance 0
+    # (step inputs, the first page of keys and its hash codes as the prefill kernel wrote them)
+    import hashlib
+    digest = hashlib.sha256()
+    for t in (qs[0], kns[0], vns[0], ctxs[0].cache.k_pages[int(ctxs[0].cache.page_table[0, 0])],
+              ctxs[0].cache.hash_pages[int(ctxs[0].cache.page_table[0, 0])]):
+        digest.update(t.contiguous().view(torch.uint8).cpu().numpy().tobytes())
+    inputs = {"seeds": {"step_inputs": 7 + rank, "cache_of_instance_l": f"{1000 * rank} + l", "page_shuffle": f"{100 * rank} + l",
+                        "hash_weights_of_instance_l": "l (torch default Linear init, rounded to bf16)"},
+              "sha256_instance0": digest.hexdigest()}
 
     def capture(fn, layers):
         g = torch.cuda.CUDAGraph()
@@ -371,7 +381,7 @@ def run_gpu_arm(args):
                        "l2": f"inputs larger than L2: {L} layer instances x {nbytes['total'] / 1e6:.1f} MB touched per "
                              f"step, visited round-robin", "launch": "CUDA graph of one step per layer instance",
                        "partition": "each GPU decodes its own sequences (all 8 kv heads); no collective on the path"},
-            "launches_per_step": launches_per_step, "roofline": roofline, "pipeline": pipeline, "prefill_hash": prefill, "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks,
+            "launches_per_step": launches_per_step, "inputs": inputs, "roofline": roofline, "pipeline": pipeline, "prefill_hash": prefill, "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks,
             "gpu_launches": launches_per_step * args.steps,
         }
         print(json.dumps(line), flush=True)
