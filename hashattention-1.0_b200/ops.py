@@ -300,6 +300,7 @@ class HostStepBuffers:
         self.v_host = torch.empty(B, Hkv, HEAD_DIM, **pin)
         self.out_host = torch.empty(B, Hq, HEAD_DIM, **pin)
         self.status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pinned)
+        self.status_view = self.status_host.numpy()  # shares the memory
         self.q_dev = torch.empty(B, Hq, HEAD_DIM, dtype=torch.bfloat16, device=dev)
         self.k_dev = torch.empty(B, Hkv, HEAD_DIM, dtype=torch.bfloat16, device=dev)
         self.v_dev = torch.empty(B, Hkv, HEAD_DIM, dtype=torch.bfloat16, device=dev)
@@ -363,7 +364,7 @@ def decode_step_host(ctx: SparseDecodeContext, buf: HostStepBuffers, synchronize
         buf.graph_for(ctx).replay()
         if synchronize:
             stream.synchronize()
-            code = int(buf.status_host[0])
+            code = int(buf.status_view[0])  # (a numpy view of the pinned word: no tensor indexing per step)
             if code != 0:
                 raise RuntimeError(f"device status: {_lib.status_str(code)} (status {code})")
         return buf.out_host
