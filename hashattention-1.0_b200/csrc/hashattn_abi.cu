@@ -378,11 +378,21 @@ StaggerResources* stagger_resources() {
     if (!r.ready) {
         int least = 0, greatest = 0;
         if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return nullptr;
-        for (int i = 0; i < kMaxParts - 1; ++i)
-            if (cudaStreamCreateWithFlags(&r.aux[i], cudaStreamNonBlocking) != cudaSuccess ||
-                cudaEventCreateWithFlags(&r.fork[i], cudaEventDisableTiming) != cudaSuccess ||
-                cudaEventCreateWithFlags(&r.join[i], cudaEventDisableTiming) != cudaSuccess)
-                return nullptr;
+        bool ok = true;
+        for (int i = 0; i < kMaxParts - 1 && ok; ++i)
+            ok = cudaStreamCreateWithFlags(&r.aux[i], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&r.fork[i], cudaEventDisableTiming) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&r.join[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) {  // give back whatever was created, so that a later call starts from nothing
+            for (int i = 0; i < kMaxParts - 1; ++i) {
+                if (r.aux[i] != nullptr) cudaStreamDestroy(r.aux[i]);
+                if (r.fork[i] != nullptr) cudaEventDestroy(r.fork[i]);
+                if (r.join[i] != nullptr) cudaEventDestroy(r.join[i]);
+                r.aux[i] = nullptr;
+                r.fork[i] = r.join[i] = nullptr;
+            }
+            return nullptr;
+        }
         r.light_priority = greatest;
         r.ready = true;
     }
