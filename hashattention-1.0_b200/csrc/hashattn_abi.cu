@@ -265,7 +265,7 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                        const int32_t* sel, const int32_t* sel_cnt, bool physical, float sm_scale,
                        void* out, void* workspace, size_t workspace_bytes,
                        int32_t* status, void* stream, int kvh0 = 0, int nkvh = -1, int merge_priority = 0,
-                       const int32_t* budget_lens = nullptr) {
+                       const int32_t* budget_lens = nullptr, int32_t* status_out = nullptr) {
     int rc = check_shape(shape);
     if (rc != HA_OK) return rc;
     rc = check_budget(budget);
@@ -290,6 +290,7 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     p.sel_cnt = budget->eval_mode == HA_EVAL_SIMPLE ? nullptr : sel_cnt;  // simple: the count follows from the budget
     p.out = static_cast<__nv_bfloat16*>(out);
     p.status = status;
+    p.status_out = nullptr;
     p.B = shape->batch;
     p.Hkv = shape->num_kv_heads;
     p.max_pages = shape->max_pages;
@@ -308,15 +309,19 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     const dim3 grid(split.nsplits, nheads, shape->batch);
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (split.cluster) {
+        p.status_out = status_out;
         const cudaError_t ec = physical ? launch(sparse_gather_kernel<true, kAttClusterThreads, true>, grid,
                                                  dim3(kAttClusterThreads), s, kAttClusterCtas, p)
                                         : launch(sparse_gather_kernel<false, kAttClusterThreads, true>, grid,
                                                  dim3(kAttClusterThreads), s, kAttClusterCtas, p);
         return ec == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
     }
+    const bool merge_follows = split.nsplits > 1;
+    p.status_out = merge_follows ? nullptr : status_out;  // the status is published by the last kernel
     cudaError_t e = physical ? launch(sparse_gather_kernel<true, kAttThreads, false>, grid, dim3(kAttThreads), s, 1, p)
                              : launch(sparse_gather_kernel<false, kAttThreads, false>, grid, dim3(kAttThreads), s, 1, p);
-    if (e == cudaSuccess && split.nsplits > 1) {
+    if (e == cudaSuccess && merge_follows) {
+        p.status_out = status_out;
         PriorityScope light(merge_priority);
         e = launch(sparse_merge_kernel, dim3(nheads, shape->batch), dim3(kHeadDim), s, 1, p);
     }
@@ -740,7 +745,9 @@ static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                             const int32_t* page_table, const int32_t* seq_lens, const int32_t* budget_lens,
                             uint32_t* q_codes, int32_t* sel_idx, int32_t* sel_cnt, float sm_scale,
                             void* out, void* workspace, size_t workspace_bytes,
-                            int32_t* status, void* stream) {
+                            int32_t* status, void* stream, int32_t* status_out = nullptr,
+                            bool* status_delivered = nullptr) {
+    if (status_delivered != nullptr) *status_delivered = false;
     int rc = hash_decode_impl(shape, weights, q, k_new, v_new, k_pages, v_pages, hash_pages, page_table,
                               seq_lens, q_codes, nullptr, q_stage, status, stream);
     if (rc != HA_OK) return rc;
@@ -752,9 +759,13 @@ static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     rc = score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, budget_lens, sel_idx, sel_cnt,
                            nullptr, workspace, workspace_bytes, status, stream);
     if (rc != HA_OK) return rc;
-    // the selection kernel left the physical rows of the heavy tokens in the workspace
+    // the selection kernel left the physical rows of the heavy tokens in the workspace; the step's last kernel
+    // also leaves the status word in status_out, if given (the staggered step above, whose last kernels run on
+    // two streams, does not)
+    if (status_delivered != nullptr) *status_delivered = status_out != nullptr;
     return sparse_decode_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, nullptr, sel_cnt, true,
-                              sm_scale, out, workspace, workspace_bytes, status, stream, 0, -1, 0, budget_lens);
+                              sm_scale, out, workspace, workspace_bytes, status, stream, 0, -1, 0, budget_lens,
+                              status_out);
 }
 
 int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -823,10 +834,14 @@ int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
     void* out_map = mapped_host_pointer(out_host);
     const bool in_place = q_map != nullptr && out_map != nullptr && (k_new_host == nullptr || k_map != nullptr) &&
                           (v_new_host == nullptr || v_map != nullptr);
+    bool status_delivered = false;
     if (in_place) {
+        // the status word, too, is stored into the caller's page-locked word by the step's last kernel when a
+        // single kernel ends the step: a copy operation after the kernels costs 5-8 us on a 19 us step
         rc = decode_step_impl(shape, budget, weights, q_map, k_map, v_map, q_dev, k_pages, v_pages, hash_pages,
                               page_table, seq_lens, nullptr, q_codes, sel_idx, sel_cnt, sm_scale, out_map, workspace,
-                              workspace_bytes, status, stream);
+                              workspace_bytes, status, stream,
+                              static_cast<int32_t*>(mapped_host_pointer(status_host)), &status_delivered);
         if (rc != HA_OK) return rc;
     } else {
         if (cudaMemcpyAsync(q_dev, q_host, q_bytes, cudaMemcpyHostToDevice, s) != cudaSuccess) return HA_ERR_LAUNCH;
@@ -842,7 +857,8 @@ int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
         if (rc != HA_OK) return rc;
         if (cudaMemcpyAsync(out_host, out_dev, q_bytes, cudaMemcpyDeviceToHost, s) != cudaSuccess) return HA_ERR_LAUNCH;
     }
-    if (cudaMemcpyAsync(status_host, status, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    if (!status_delivered &&
+        cudaMemcpyAsync(status_host, status, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess)
         return HA_ERR_LAUNCH;
     if (synchronize) {
         if (cudaStreamSynchronize(s) != cudaSuccess) return HA_ERR_LAUNCH;

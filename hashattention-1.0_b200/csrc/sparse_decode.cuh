@@ -44,6 +44,8 @@ struct SparseDecodeParams {
     __nv_bfloat16* out;            // [B][Hq][128]
     float* partials;               // workspace: [B][Hq][nsplits][130]
     int32_t* status;
+    int32_t* status_out;           // null, or where the step's last kernel leaves a copy of *status once every kernel
+                                   // before it has completed (a word of mapped host memory: saves a copy operation)
     int B, Hkv, max_pages, num_pages, sel_stride, nsplits, rounds;
     int round_rows;                // rows a CTA takes per round: 2 per thread / 16 (32 for 128 threads, 64 for 256)
     int h0;                        // first query head of this launch (a launch may cover a slice of the heads)
@@ -51,6 +53,14 @@ struct SparseDecodeParams {
     double heavy_budget;
     float scale_log2e;             // sm_scale * log2(e)
 };
+
+// Called after the dependency wait of the step's last kernel: every earlier kernel of the step has completed, so
+// the status word holds whatever they reported (a bad page this kernel itself may meet was already reported by the
+// selection, which visits every page of the sequence).
+__device__ __forceinline__ void publish_status(const SparseDecodeParams& p) {
+    if (p.status_out != nullptr && (blockIdx.x | blockIdx.y | blockIdx.z | threadIdx.x) == 0)
+        *p.status_out = __ldcg(p.status);
+}
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float (&x)[8]) {
     x[0] = bf16_lo(raw.x); x[1] = bf16_hi(raw.x);
@@ -155,6 +165,7 @@ __global__ void __launch_bounds__(kThreads, kCluster ? 2 : 6) sparse_gather_kern
     pdl_wait();
     HA_TL(kTlGather, kTlAfterWait);
     pdl_launch_dependents();
+    publish_status(p);
     if (p.sel_cnt != nullptr) {  // the length of the heavy list is a product of the selection kernels
         a = att_plan(p, b, __ldcg(p.sel_cnt + (size_t)b * Hq + h));
         cnt = a.cnt;
@@ -380,6 +391,7 @@ __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDeco
     pdl_wait();
     HA_TL(kTlMerge, kTlAfterWait);
     pdl_launch_dependents();
+    publish_status(p);
     if (p.sel_cnt != nullptr) a = att_plan(p, b, __ldcg(p.sel_cnt + (size_t)b * Hq + h));
     if (a.nsplits <= 1) return;  // written by the gather kernel (or nothing to write)
 

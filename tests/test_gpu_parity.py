@@ -640,6 +640,31 @@ def test_bad_page_id_and_bad_length_are_reported_through_the_status_word(device)
     assert bool(torch.isfinite(out.float()).all())
 
 
+@pytest.mark.parametrize("use_graph", [False, True])
+@pytest.mark.parametrize("pinned", [True, False])
+def test_host_buffer_step_delivers_the_status_word(device, use_graph, pinned):
+    """Page-locked buffers: the step's last kernel stores the status into the caller's word; pageable
+    ones: a copy after the kernels. Either way a bad page id reaches the host call, and a clean step
+    afterwards reports success again."""
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(102, [600], 8, 2)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, ha.Budget(16, 0.125, 16), usa)
+    ctx.hash_prefill()
+    buf = ha.HostStepBuffers(ctx, pinned=pinned)
+    buf.q_host.copy_(inp.q.to(torch.bfloat16))
+    buf.k_host.copy_(inp.k[0][None, :, -1].to(torch.bfloat16))
+    buf.v_host.copy_(inp.v[0][None, :, -1].to(torch.bfloat16))
+    want = ha.decode_step_host(ctx, buf, use_graph=use_graph).clone()
+    good_table = cache.page_table.clone()
+    cache.page_table[0, 1] = cache.num_pages + 5
+    with pytest.raises(RuntimeError, match="page id"):
+        ha.decode_step_host(ctx, buf, use_graph=use_graph)
+    cache.page_table.copy_(good_table)
+    ctx.status.zero_()
+    assert torch.equal(ha.decode_step_host(ctx, buf, use_graph=use_graph), want)
+    ctx.check_status()
+
+
 @pytest.mark.parametrize("mode", ["simple", "depth"])
 def test_heavy_list_shorter_than_the_budget_is_reported_not_overrun(device, mode):
     """sel_stride (here 8 entries) smaller than what the budget selects (75 of 600 tokens, more under the
