@@ -227,17 +227,26 @@ hash_decode_kernel(const HashDecodeParams p) {
     auto x_row = [&](int b) {
         return side == 0 ? p.q + ((size_t)b * Hq + h) * kHeadDim : p.k_new + ((size_t)b * p.Hkv + kvh) * kHeadDim;
     };
-    uint4 raw_next = make_uint4(0u, 0u, 0u, 0u);
+    // The group's first key head also appends the K and V rows: lanes 0-15 of warp 0 hold the K row already (it
+    // is the MLP's input), lanes 16-31 request the V row together with it - the inputs may live in mapped
+    // host memory, where a second read at the end of the kernel would cost another trip over the bus.
+    const bool appends = side == 1 && g == 0 && p.v_new != nullptr && warp == 0;
+    auto v_part = [&](int b) {
+        return *(reinterpret_cast<const uint4*>(p.v_new + ((size_t)b * p.Hkv + kvh) * kHeadDim) + (lane - 16));
+    };
+    uint4 raw_next = make_uint4(0u, 0u, 0u, 0u), v_next = make_uint4(0u, 0u, 0u, 0u);
     int S_next = 1;
     if (b_begin < b_end) {
         raw_next = load_x_row(x_row(b_begin), lane);
+        if (appends && lane >= 16) v_next = v_part(b_begin);
         if (side == 1) S_next = p.seq_lens[b_begin];
     }
     for (int b = b_begin; b < b_end; ++b) {
-        const uint4 raw = raw_next;
+        const uint4 raw = raw_next, v_raw = v_next;
         const int S = S_next;
         if (b + 1 < b_end) {
             raw_next = load_x_row(x_row(b + 1), lane);
+            if (appends && lane >= 16) v_next = v_part(b + 1);
             if (side == 1) S_next = p.seq_lens[b + 1];
         }
         if (side == 0 && p.q_stage != nullptr && warp == 0 && lane < 16)
@@ -272,13 +281,10 @@ hash_decode_kernel(const HashDecodeParams p) {
         const size_t slot = ((size_t)page * p.Hkv + kvh) * kPage + tok % kPage;
         if (lane == 0) p.hash_pages[slot * kGroup + g] = code;
         // the group's first head also appends the K and V rows (256 B each)
-        if (g == 0 && p.v_new != nullptr) {
-            const size_t src = ((size_t)b * p.Hkv + kvh) * kHeadDim;
-            const uint4* s = lane < 16 ? reinterpret_cast<const uint4*>(p.k_new + src) + lane
-                                       : reinterpret_cast<const uint4*>(p.v_new + src) + (lane - 16);
+        if (appends) {
             uint4* d = lane < 16 ? reinterpret_cast<uint4*>(p.k_pages + slot * kHeadDim) + lane
                                  : reinterpret_cast<uint4*>(p.v_pages + slot * kHeadDim) + (lane - 16);
-            *d = *s;
+            *d = lane < 16 ? raw : v_raw;
         }
     }
     HA_TL(kTlHashDecode, kTlExit);
