@@ -415,6 +415,14 @@ hash_decode_batched_kernel(const HashDecodeParams p) {
         const int b = b0 + warp;
         const bool live = b < b_end;
         int S = 1, page = 0;
+        // the rows the group's first key head appends (lanes 0-15: K, 16-31: V), requested with the inputs
+        const bool appends = live && side == 1 && g == 0 && p.v_new != nullptr;
+        uint4 app = make_uint4(0u, 0u, 0u, 0u);
+        if (appends) {
+            const size_t src = ((size_t)b * p.Hkv + kvh) * kHeadDim;
+            app = lane < 16 ? *(reinterpret_cast<const uint4*>(p.k_new + src) + lane)
+                            : *(reinterpret_cast<const uint4*>(p.v_new + src) + (lane - 16));
+        }
         {
             float4 xv = make_float4(0.f, 0.f, 0.f, 0.f);
             if (live) {
@@ -465,13 +473,10 @@ hash_decode_batched_kernel(const HashDecodeParams p) {
         }
         const size_t slot = ((size_t)page * p.Hkv + kvh) * kPage + (S - 1) % kPage;
         if (lane == 0) p.hash_pages[slot * kGroup + g] = code;
-        if (g == 0 && p.v_new != nullptr) {  // the group's first head also appends the K and V rows (256 B each)
-            const size_t src = ((size_t)b * p.Hkv + kvh) * kHeadDim;
-            const uint4* sp = lane < 16 ? reinterpret_cast<const uint4*>(p.k_new + src) + lane
-                                        : reinterpret_cast<const uint4*>(p.v_new + src) + (lane - 16);
+        if (appends) {  // 256 B each
             uint4* dp = lane < 16 ? reinterpret_cast<uint4*>(p.k_pages + slot * kHeadDim) + lane
                                   : reinterpret_cast<uint4*>(p.v_pages + slot * kHeadDim) + (lane - 16);
-            *dp = *sp;
+            *dp = app;
         }
     }
     HA_TL(kTlHashDecode, kTlExit);
