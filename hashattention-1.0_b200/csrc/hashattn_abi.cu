@@ -752,16 +752,24 @@ static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                               seq_lens, q_codes, nullptr, q_stage, status, stream);
     if (rc != HA_OK) return rc;
     const void* q_att = q_stage != nullptr ? q_stage : q;
-    if (use_stagger(shape))
-        return staggered_select_attend(shape, budget, q_att, k_pages, v_pages, hash_pages, page_table, seq_lens,
-                                       q_codes, sel_idx, sel_cnt, sm_scale, out, workspace, workspace_bytes, status,
-                                       static_cast<cudaStream_t>(stream), budget_lens);
+    if (use_stagger(shape)) {
+        rc = staggered_select_attend(shape, budget, q_att, k_pages, v_pages, hash_pages, page_table, seq_lens,
+                                     q_codes, sel_idx, sel_cnt, sm_scale, out, workspace, workspace_bytes, status,
+                                     static_cast<cudaStream_t>(stream), budget_lens);
+        if (rc == HA_OK && status_out != nullptr) {
+            // the step ended on several streams, all joined by now: a one-warp kernel stores the status word
+            // (cheaper than a copy operation between the last kernel and the end of the step)
+            publish_status_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, status_out);
+            if (cudaGetLastError() != cudaSuccess) return HA_ERR_LAUNCH;
+            if (status_delivered != nullptr) *status_delivered = true;
+        }
+        return rc;
+    }
     rc = score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, budget_lens, sel_idx, sel_cnt,
                            nullptr, workspace, workspace_bytes, status, stream);
     if (rc != HA_OK) return rc;
     // the selection kernel left the physical rows of the heavy tokens in the workspace; the step's last kernel
-    // also leaves the status word in status_out, if given (the staggered step above, whose last kernels run on
-    // two streams, does not)
+    // also leaves the status word in status_out, if given
     if (status_delivered != nullptr) *status_delivered = status_out != nullptr;
     return sparse_decode_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, nullptr, sel_cnt, true,
                               sm_scale, out, workspace, workspace_bytes, status, stream, 0, -1, 0, budget_lens,

@@ -239,8 +239,9 @@ int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget);
  * If all host buffers are page-locked and device-addressable (cudaHostAlloc / cudaHostRegister,
  * torch pin_memory) the kernels use them in place: the encoder kernel reads the inputs over the
  * bus once (keeping a device copy of q in q_dev), the last kernel stores the result into
- * out_host and, if status_host is page-locked too and one kernel ends the step, a copy of the
- * status word into status_host (else that word is copied). Otherwise the inputs are copied to the staging
+ * out_host and, if status_host is page-locked too, the step's last kernel (or, where the step ends
+ * on two streams, a one-warp kernel after their join) stores the status word into status_host;
+ * else that word is copied. Otherwise the inputs are copied to the staging
  * buffers, ha_decode_step runs on those, and `out` is copied back. Either way the host buffers
  * must stay untouched until the stream has reached the end of the call. If `synchronize` is
  * non-zero the call waits for the stream and returns the device status word (HA_OK if clean).

@@ -665,6 +665,33 @@ def test_host_buffer_step_delivers_the_status_word(device, use_graph, pinned):
     ctx.check_status()
 
 
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_staggered_host_buffer_step_delivers_result_and_status(device, monkeypatch, use_graph):
+    """A step that runs as staggered halves on two streams ends with a one-warp kernel that stores the
+    status word into the caller's page-locked word, after both streams have been joined."""
+    Hq, Hkv = 16, 4
+    lens = [300, 1025, 64, 2000, 513, 777, 1300, 256, 900, 1500]
+    usa = synthetic.make_usa(Hq, 128, 3, True)
+    inp = synthetic.make_decode_inputs(103, lens, Hq, Hkv)
+    budget = ha.Budget(32, 1.0 / 8, 32)
+    monkeypatch.setenv("HA_STAGGER", "1")
+    _, want, _, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, budget, usa, shuffle_seed=9)
+    ctx.hash_prefill()
+    buf = ha.HostStepBuffers(ctx)
+    buf.q_host.copy_(inp.q.to(torch.bfloat16))
+    buf.k_host.copy_(torch.stack([k[:, -1] for k in inp.k]).to(torch.bfloat16))
+    buf.v_host.copy_(torch.stack([v[:, -1] for v in inp.v]).to(torch.bfloat16))
+    assert torch.equal(ha.decode_step_host(ctx, buf, use_graph=use_graph).float(), want)
+    good_table = cache.page_table.clone()
+    cache.page_table[7, 0] = -3
+    with pytest.raises(RuntimeError, match="page id"):
+        ha.decode_step_host(ctx, buf, use_graph=use_graph)
+    cache.page_table.copy_(good_table)
+    ctx.status.zero_()
+    assert torch.equal(ha.decode_step_host(ctx, buf, use_graph=use_graph).float(), want)
+
+
 @pytest.mark.parametrize("mode", ["simple", "depth"])
 def test_heavy_list_shorter_than_the_budget_is_reported_not_overrun(device, mode):
     """sel_stride (here 8 entries) smaller than what the budget selects (75 of 600 tokens, more under the
