@@ -154,9 +154,8 @@ __device__ __forceinline__ void tc_hidden_epilogue(uint32_t taddr, const float* 
                 // 2^-17 that the hi/lo split itself leaves)
                 a[j] = __fdividef(x, 1.0f + __expf(-x));
             }
-            const float h0 = __bfloat162float(__float2bfloat16_rn(a[0]));
-            const float h1 = __bfloat162float(__float2bfloat16_rn(a[1]));
-            hi[e] = tc_pack_bf16(h0, h1);
+            hi[e] = tc_pack_bf16(a[0], a[1]);  // one paired conversion; the rounded values are read back by shifts
+            const float h0 = __uint_as_float(hi[e] << 16), h1 = __uint_as_float(hi[e] & 0xffff0000u);
             lo[e] = tc_pack_bf16(a[0] - h0, a[1] - h1);
         }
         const uint32_t off = tc_swizzled(row, chunk0 + c);
