@@ -2,9 +2,11 @@
 //
 // For every cached key x (128 bf16) and every query head h of its kv-head the hash MLP
 //     code = signbits( W2 . silu( W1 . silu( W0 x + b0 ) + b1 ) + b2 )
-// is a chain of three GEMMs over a tile of 128 tokens. A CTA owns one head: the head's three
-// weight matrices (72 KB bf16) stay in shared memory in the K-major 128-byte-swizzled layout the
-// UMMA shared-memory descriptors describe, and the CTA walks over token tiles:
+// is a chain of three GEMMs over a tile of 128 tokens. The (head, tile) pairs of a call, head-major, are cut
+// into one contiguous range per CTA (one CTA per SM, equal tile counts); a CTA keeps the three weight
+// matrices of its current head (72 KB bf16) in shared memory in the K-major 128-byte-swizzled layout the
+// UMMA shared-memory descriptors describe, reloads them where its range crosses into the next head, and
+// walks over its token tiles:
 //   1. the 128 x 128 key tile is copied into swizzled shared memory (it is contiguous in a page) by
 //      cp.async, one tile ahead of the arithmetic (two buffers),
 //   2. one thread issues tcgen05.mma (M = 128, N = 128, K = 16 per instruction, bf16 x bf16 -> fp32)
@@ -178,17 +180,25 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int h = blockIdx.y, kvh = h / kGroup, g = h % kGroup;
+    const int Hq = p.Hkv * kGroup;
     float* s_bias = reinterpret_cast<float*>(smem + kTcOffBias);
     unsigned long long* s_bar = reinterpret_cast<unsigned long long*>(smem + kTcOffBar);
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kTcOffBar + 16);
 
-    // ---- one-time set-up: weights and biases of this head, mbarrier, tensor memory -------------
-    const __nv_bfloat16* W = p.wk + (size_t)h * kMlpElems;
-    tc_load_operand(smem + kTcOffW0, W, 128, kTcBlockBytes, tid);
-    tc_load_operand(smem + kTcOffW1, W + kHidden * kHeadDim, 128, kTcBlockBytes, tid);
-    tc_load_operand(smem + kTcOffW2, W + kHidden * kHeadDim + kHidden * kHidden, 32, kTcW2BlockBytes, tid);
-    for (int i = tid; i < kMlpBias; i += kTcThreads) s_bias[i] = p.bk[(size_t)h * kMlpBias + i];
+    // The (head, token tile) pairs of the whole call, head-major and counting only tiles that hold tokens to
+    // encode, are cut into gridDim.x equal contiguous ranges: every SM gets the same number of tiles whatever the
+    // number of heads, and a CTA changes head (reloads the 72 KB of weights) at most once per head boundary it
+    // spans. The first head of a CTA follows from its index alone, so its weights are fetched before the
+    // dependency wait.
+    auto load_head = [&](int h) {
+        const __nv_bfloat16* W = p.wk + (size_t)h * kMlpElems;
+        tc_load_operand(smem + kTcOffW0, W, 128, kTcBlockBytes, tid);
+        tc_load_operand(smem + kTcOffW1, W + kHidden * kHeadDim, 128, kTcBlockBytes, tid);
+        tc_load_operand(smem + kTcOffW2, W + kHidden * kHeadDim + kHidden * kHidden, 32, kTcW2BlockBytes, tid);
+        for (int i = tid; i < kMlpBias; i += kTcThreads) s_bias[i] = p.bk[(size_t)h * kMlpBias + i];
+    };
+    int loaded_h = (int)(((long long)blockIdx.x * Hq) / gridDim.x);
+    load_head(loaded_h);
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(s_bar)));
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -234,39 +244,83 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
     bool aborted = false;
     pdl_wait();  // the weights above are constants; everything below may depend on the previous kernel
 
-    // Work items are (sequence, 128-token tile) pairs dealt round-robin over grid.x. next_item() skips
-    // the pairs with nothing to encode; all of its inputs are CTA-uniform.
-    struct Item { int item, S, first, t0; size_t slot0; };
-    const int tiles_per_seq = p.max_pages * (kPage / kTcTile);
-    auto next_item = [&](int item) {
+    // A sequence's tiles to encode: [first_token / 128, ceil(S / 128)); none if its length is out of range.
+    struct Item { int valid, h, S, first, t0; size_t slot0; };
+    struct Cursor { int h, b, tile, hi, S, first; long long left; };
+    auto seq_tiles = [&](int b, int& S, int& first, int& lo, int& hi) {
+        S = __ldg(p.seq_lens + b);
+        first = p.first_token != nullptr ? max(0, __ldg(p.first_token + b)) : 0;
+        if (S < 0 || S > p.max_pages * kPage) {
+            if (tid == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+            S = 0;
+        }
+        lo = first / kTcTile;
+        hi = max(lo, (S + kTcTile - 1) / kTcTile);
+    };
+    Cursor cs;
+    {
+        long long per_head = 0;  // tiles to encode per head
+        for (int b = 0; b < p.B; ++b) {
+            int S, first, lo, hi;
+            seq_tiles(b, S, first, lo, hi);
+            per_head += hi - lo;
+        }
+        const long long total = per_head * Hq;
+        const long long g0 = total * blockIdx.x / gridDim.x, g1 = total * (blockIdx.x + 1) / gridDim.x;
+        cs.left = g1 - g0;
+        cs.h = per_head > 0 ? (int)(g0 / per_head) : 0;
+        long long skip = per_head > 0 ? g0 % per_head : 0;  // tiles of head cs.h in front of this CTA's range
+        cs.b = 0;
+        cs.tile = cs.hi = cs.S = cs.first = 0;
+        for (int b = 0; b < p.B && cs.left > 0; ++b) {
+            int S, first, lo, hi;
+            seq_tiles(b, S, first, lo, hi);
+            if (skip < hi - lo) {
+                cs.b = b; cs.S = S; cs.first = first; cs.tile = lo + (int)skip; cs.hi = hi;
+                break;
+            }
+            skip -= hi - lo;
+        }
+    }
+    // The next tile of this CTA's range (all inputs are CTA-uniform). A tile on a bad page is reported and skipped.
+    auto next_item = [&]() {
         Item it;
-        for (; item < p.B * tiles_per_seq; item += gridDim.x) {
-            const int b = item / tiles_per_seq, tile = item % tiles_per_seq;
-            const int S = p.seq_lens[b];
-            if (S < 0 || S > p.max_pages * kPage) {
-                if (tid == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+        it.valid = 0; it.h = 0; it.S = 0; it.first = 0; it.t0 = 0; it.slot0 = 0;
+        while (cs.left > 0) {
+            if (cs.tile >= cs.hi) {  // on to the next sequence, or to the first one of the next head
+                if (++cs.b >= p.B) {
+                    cs.b = 0;
+                    ++cs.h;
+                }
+                int lo;
+                seq_tiles(cs.b, cs.S, cs.first, lo, cs.hi);
+                cs.tile = lo;
                 continue;
             }
-            const int first = p.first_token != nullptr ? max(0, p.first_token[b]) : 0;
-            const int t0 = tile * kTcTile;
-            if (t0 >= S || t0 + kTcTile <= first) continue;
-            const int page = p.page_table[(size_t)b * p.max_pages + t0 / kPage];
+            const int t0 = cs.tile * kTcTile;
+            const int page = __ldg(p.page_table + (size_t)cs.b * p.max_pages + t0 / kPage);
+            ++cs.tile;
+            --cs.left;
             if (page < 0 || page >= p.num_pages) {
                 if (tid == 0) report(p.status, HA_ERR_BAD_PAGE);
                 continue;
             }
-            it.item = item; it.S = S; it.first = first; it.t0 = t0;
-            it.slot0 = ((size_t)page * p.Hkv + kvh) * kPage + t0 % kPage;
+            it.valid = 1; it.h = cs.h; it.S = cs.S; it.first = cs.first; it.t0 = t0;
+            it.slot0 = ((size_t)page * p.Hkv + cs.h / kGroup) * kPage + t0 % kPage;
             return it;
         }
-        it.item = -1; it.S = 0; it.first = 0; it.t0 = 0; it.slot0 = 0;
         return it;
     };
 
-    Item cur = next_item(blockIdx.x);
-    if (cur.item >= 0) tc_prefetch_tile(smem + kTcOffX, p.k_pages + cur.slot0 * kHeadDim, tid);
-    for (uint32_t n = 0; cur.item >= 0; ++n) {
+    Item cur = next_item();
+    if (cur.valid) tc_prefetch_tile(smem + kTcOffX, p.k_pages + cur.slot0 * kHeadDim, tid);
+    for (uint32_t n = 0; cur.valid; ++n) {
         const uint32_t off_x = kTcOffX + (n & 1) * 2 * kTcBlockBytes;
+        // a new head: its weights replace the old ones (no GEMM is in flight between two tiles)
+        if (cur.h != loaded_h) {
+            loaded_h = cur.h;
+            load_head(loaded_h);
+        }
         // ---- this tile's keys have landed (cp.async); make them visible to the tensor core
         asm volatile("cp.async.wait_all;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -279,8 +333,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
             gemm(kTcColD1, off_x, kTcOffW0, kTcBlockBytes, idesc128, true);
             tc_commit(bar);
         }
-        const Item nxt = next_item(cur.item + gridDim.x);
-        if (nxt.item >= 0)
+        const Item nxt = next_item();
+        if (nxt.valid)
             tc_prefetch_tile(smem + kTcOffX + ((n + 1) & 1) * 2 * kTcBlockBytes, p.k_pages + nxt.slot0 * kHeadDim, tid);
         if (!wait_commit()) { aborted = true; break; }
         tc_hidden_epilogue(tmem + t_lane + kTcColD1 + cq * 32, s_bias + cq * 32, smem + kTcOffHi + kb * kTcBlockBytes,
@@ -318,7 +372,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
 #pragma unroll
             for (int i = 0; i < 32; ++i) code |= (v[i] + s_bias[2 * kHidden + i] > 0.0f ? 1u : 0u) << i;
             const int t = cur.t0 + (int)row;
-            if (t < cur.S && t >= cur.first) p.hash_pages[(cur.slot0 + row) * kGroup + g] = code;
+            if (t < cur.S && t >= cur.first) p.hash_pages[(cur.slot0 + row) * kGroup + cur.h % kGroup] = code;
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();  // the accumulators may be overwritten by the next tile

@@ -626,8 +626,7 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
 
     const int layers = weights->num_layers == 0 ? 3 : weights->num_layers;
     if (weights->dtype == HA_WEIGHTS_BF16 && layers == 3) {
-        // bf16 weights, the 3-layer MLP: tcgen05 GEMM chain. One CTA per SM (its shared memory holds a head's weights),
-        // heads in grid.y, token tiles dealt round-robin over grid.x.
+        // bf16 weights, the 3-layer MLP: tcgen05 GEMM chain. One CTA per SM (its shared memory holds a head's weights).
         // (a per-device function attribute: set at every call, so that a process driving several GPUs is served)
         if (cudaFuncSetAttribute(hash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kTcSmemBytes) != cudaSuccess)
@@ -645,13 +644,17 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         t.Hkv = shape->num_kv_heads;
         t.max_pages = shape->max_pages;
         t.num_pages = shape->num_pages;
+        // one CTA per SM; the kernel cuts the (head, tile) pairs into that many equal ranges
         const int Hq = shape->num_kv_heads * kGroup;
-        const long long tiles = (long long)shape->batch * shape->max_pages * (kPage / kTcTile);
-        long long gx = 148 / Hq;
-        if (gx < 1) gx = 1;
+        const long long tiles = (long long)Hq * shape->batch * shape->max_pages * (kPage / kTcTile);
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1)
+            return HA_ERR_LAUNCH;
+        long long gx = sms;
         if (gx > tiles) gx = tiles;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)gx, Hq, 1);
+        cfg.gridDim = dim3((unsigned)gx, 1, 1);
         cfg.blockDim = dim3(kTcThreads);
         cfg.dynamicSmemBytes = kTcSmemBytes;
         cfg.stream = static_cast<cudaStream_t>(stream);
