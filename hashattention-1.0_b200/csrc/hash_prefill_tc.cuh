@@ -312,36 +312,52 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
         return it;
     };
 
-    Item cur = next_item();
-    if (cur.valid) tc_prefetch_tile(smem + kTcOffX, p.k_pages + cur.slot0 * kHeadDim, tid);
-    for (uint32_t n = 0; cur.valid; ++n) {
-        const uint32_t off_x = kTcOffX + (n & 1) * 2 * kTcBlockBytes;
-        // a new head: its weights replace the old ones (no GEMM is in flight between two tiles)
-        if (cur.h != loaded_h) {
-            loaded_h = cur.h;
-            load_head(loaded_h);
-        }
-        // ---- this tile's keys have landed (cp.async); make them visible to the tensor core
-        asm volatile("cp.async.wait_all;" ::: "memory");
+    // what the epilogue (or cp.async) wrote becomes visible to the tensor core; the accumulator reads are done
+    auto publish = [&]() {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncthreads();
-
-        // ---- layer 0: D1 = X W0^T; meanwhile the next tile's keys start streaming in
+    };
+    // layer 0 of a tile whose keys sit in key buffer `buf`: D1 = X W0^T (waits for the keys first)
+    auto start_tile = [&](uint32_t buf) {
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        publish();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            gemm(kTcColD1, off_x, kTcOffW0, kTcBlockBytes, idesc128, true);
+            gemm(kTcColD1, kTcOffX + buf * 2 * kTcBlockBytes, kTcOffW0, kTcBlockBytes, idesc128, true);
             tc_commit(bar);
         }
+    };
+    auto codes = [&](const Item& it) {  // thread = token row: 32 pre-activations -> one packed code
+        if (warp >= 4) return;
+        float v[32];
+        tc_ld32(tmem + t_lane + kTcColD3, v);
+        uint32_t code = 0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) code |= (v[i] + s_bias[2 * kHidden + i] > 0.0f ? 1u : 0u) << i;
+        const int t = it.t0 + (int)row;
+        if (t < it.S && t >= it.first) p.hash_pages[(it.slot0 + row) * kGroup + it.h % kGroup] = code;
+    };
+
+    Item cur = next_item();
+    if (cur.valid) {
+        tc_prefetch_tile(smem + kTcOffX, p.k_pages + cur.slot0 * kHeadDim, tid);
+        if (cur.h != loaded_h) {  // (cannot happen for the first tile of a range; kept for safety)
+            __syncthreads();
+            loaded_h = cur.h;
+            load_head(loaded_h);
+        }
+        start_tile(0);
+    }
+    for (uint32_t n = 0; cur.valid; ++n) {
+        // ---- layer 0 is running; meanwhile the next tile's keys start streaming in
         const Item nxt = next_item();
         if (nxt.valid)
             tc_prefetch_tile(smem + kTcOffX + ((n + 1) & 1) * 2 * kTcBlockBytes, p.k_pages + nxt.slot0 * kHeadDim, tid);
         if (!wait_commit()) { aborted = true; break; }
         tc_hidden_epilogue(tmem + t_lane + kTcColD1 + cq * 32, s_bias + cq * 32, smem + kTcOffHi + kb * kTcBlockBytes,
                            smem + kTcOffLo + kb * kTcBlockBytes, row, chunk0);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
+        publish();
 
         // ---- layer 1: D2 = (Hhi + Hlo) W1^T
         if (tid == 0) {
@@ -353,9 +369,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
         if (!wait_commit()) { aborted = true; break; }
         tc_hidden_epilogue(tmem + t_lane + kTcColD2 + cq * 32, s_bias + kHidden + cq * 32,
                            smem + kTcOffHi + kb * kTcBlockBytes, smem + kTcOffLo + kb * kTcBlockBytes, row, chunk0);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
+        publish();
 
         // ---- layer 2: D3 = (Hhi + Hlo) W2^T, N = 32
         if (tid == 0) {
@@ -365,17 +379,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
             tc_commit(bar);
         }
         if (!wait_commit()) { aborted = true; break; }
-        if (warp < 4) {  // thread = token row: 32 pre-activations -> one packed code
-            float v[32];
-            tc_ld32(tmem + t_lane + kTcColD3, v);
-            uint32_t code = 0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) code |= (v[i] + s_bias[2 * kHidden + i] > 0.0f ? 1u : 0u) << i;
-            const int t = cur.t0 + (int)row;
-            if (t < cur.S && t >= cur.first) p.hash_pages[(cur.slot0 + row) * kGroup + cur.h % kGroup] = code;
+        // ---- the codes of this tile are packed while layer 0 of the next tile runs (D1 and D3 are different
+        //      columns; D3 is written again only after two more barriers). A change of head rewrites the biases the
+        //      codes need, so there the codes come first.
+        if (nxt.valid && nxt.h != loaded_h) {
+            codes(cur);
+            __syncthreads();
+            loaded_h = nxt.h;
+            load_head(loaded_h);
+            start_tile((n + 1) & 1);
+        } else {
+            if (nxt.valid) start_tile((n + 1) & 1);
+            codes(cur);
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();  // the accumulators may be overwritten by the next tile
         cur = nxt;
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
