@@ -11,7 +11,9 @@
 //      cp.async, one tile ahead of the arithmetic (two buffers),
 //   2. one thread issues tcgen05.mma (M = 128, N = 128, K = 16 per instruction, bf16 x bf16 -> fp32)
 //      into tensor memory and commits to an mbarrier,
-//   3. the 16 warps read the accumulator with tcgen05.ld (thread = token row, 32 columns each), add
+//   3. the 16 warps read the accumulator with tcgen05.ld (thread = token row, 16 columns at a time: first the
+//      columns 0..63, then 64..127, and the K-half of the next GEMM that reads the first half's activations is
+//      issued in between, so that it runs under the second half of the epilogue), add
 //      the bias, apply SiLU in fp32 and split the activation into a hi and a lo bf16 (hi + lo
 //      carries 16 mantissa bits), written back to swizzled shared memory as the next A operand,
 //   4. layer 2 runs two MMAs per k-step (hi and lo against the same weights), layer 3 likewise
@@ -105,6 +107,19 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t r[32];
     asm volatile(
@@ -137,13 +152,13 @@ __device__ __forceinline__ void tc_load_operand(unsigned char* dst, const __nv_b
     }
 }
 
-// bias + SiLU + hi/lo split of 32 accumulator columns (chunks 4*q4 .. 4*q4+3 of K-half block kb).
+// bias + SiLU + hi/lo split of 16 accumulator columns (chunks chunk0, chunk0 + 1 of one K-half block).
 __device__ __forceinline__ void tc_hidden_epilogue(uint32_t taddr, const float* bias, unsigned char* hi_blk,
                                                    unsigned char* lo_blk, uint32_t row, uint32_t chunk0) {
-    float v[32];
-    tc_ld32(taddr, v);
+    float v[16];
+    tc_ld16(taddr, v);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {  // 4 chunks of 8 columns
+    for (int c = 0; c < 2; ++c) {  // 2 chunks of 8 columns
         uint32_t hi[4], lo[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -216,8 +231,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
     const uint32_t sbase = tc_smem_u32(smem);
     const uint32_t idesc128 = tc_idesc(128), idesc32 = tc_idesc(32);
     // this thread's accumulator slice: TMEM lanes 32 (warp % 4) .. +31, columns 32 (warp / 4) .. +31
-    const uint32_t row = (warp & 3) * 32 + lane, cq = warp >> 2;  // cq: column quarter 0..3
-    const uint32_t kb = cq >> 1, chunk0 = (cq & 1) * 4;           // K-half block and first chunk of the next A operand
+    // in each half of a hidden epilogue: TMEM lanes 32 (warp % 4) .. +31, columns 64 half + 16 (warp / 4) .. +15
+    const uint32_t row = (warp & 3) * 32 + lane, cq = warp >> 2;  // cq: group of 16 columns inside a half, 0..3
+    const uint32_t chunk0 = cq * 2;                                // first 16-byte chunk inside the K-half block
     const uint32_t t_lane = ((warp & 3) * 32u) << 16;
     uint32_t phase = 0;
 
@@ -227,6 +243,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
         for (uint32_t ks = 0; ks < 8; ++ks) {
             const uint32_t a = sbase + off_a + (ks >> 2) * kTcBlockBytes + (ks & 3) * 32;
             const uint32_t bb = sbase + off_b + (ks >> 2) * b_block_bytes + (ks & 3) * 32;
+            tc_mma(tmem + col_d, tc_smem_desc(a), tc_smem_desc(bb), idesc, (first && ks == 0) ? 0u : 1u);
+        }
+    };
+    // the k-steps of one K-half (half = 0: inputs 0..63, 1: inputs 64..127) of such a GEMM
+    auto gemm_half = [&](uint32_t col_d, uint32_t off_a, uint32_t off_b, uint32_t b_block_bytes, uint32_t idesc,
+                         uint32_t half, bool first) {
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks) {
+            const uint32_t a = sbase + off_a + half * kTcBlockBytes + ks * 32;
+            const uint32_t bb = sbase + off_b + half * b_block_bytes + ks * 32;
             tc_mma(tmem + col_d, tc_smem_desc(a), tc_smem_desc(bb), idesc, (first && ks == 0) ? 0u : 1u);
         }
     };
@@ -328,6 +354,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
             tc_commit(bar);
         }
     };
+    // bias + SiLU + hi/lo split of this thread's 16 columns in half `half` of accumulator col_d
+    auto hidden = [&](uint32_t col_d, const float* bias, uint32_t half) {
+        const uint32_t c0 = half * 64 + cq * 16;
+        tc_hidden_epilogue(tmem + t_lane + col_d + c0, bias + c0, smem + kTcOffHi + half * kTcBlockBytes,
+                           smem + kTcOffLo + half * kTcBlockBytes, row, chunk0);
+    };
     auto codes = [&](const Item& it) {  // thread = token row: 32 pre-activations -> one packed code
         if (warp >= 4) return;
         float v[32];
@@ -355,27 +387,37 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
         if (nxt.valid)
             tc_prefetch_tile(smem + kTcOffX + ((n + 1) & 1) * 2 * kTcBlockBytes, p.k_pages + nxt.slot0 * kHeadDim, tid);
         if (!wait_commit()) { aborted = true; break; }
-        tc_hidden_epilogue(tmem + t_lane + kTcColD1 + cq * 32, s_bias + cq * 32, smem + kTcOffHi + kb * kTcBlockBytes,
-                           smem + kTcOffLo + kb * kTcBlockBytes, row, chunk0);
+        // ---- hidden layers: the epilogue runs in two halves of 64 columns; the half of the next GEMM that reads
+        //      the first half's activations (its K-half 0, hi and lo) is issued before the second half is worked on
+        hidden(kTcColD1, s_bias, 0);
         publish();
-
-        // ---- layer 1: D2 = (Hhi + Hlo) W1^T
+        if (tid == 0) {  // layer 1, K-half 0: D2 = (Hhi + Hlo) W1^T
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            gemm_half(kTcColD2, kTcOffHi, kTcOffW1, kTcBlockBytes, idesc128, 0, true);
+            gemm_half(kTcColD2, kTcOffLo, kTcOffW1, kTcBlockBytes, idesc128, 0, false);
+        }
+        hidden(kTcColD1, s_bias, 1);
+        publish();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            gemm(kTcColD2, kTcOffHi, kTcOffW1, kTcBlockBytes, idesc128, true);
-            gemm(kTcColD2, kTcOffLo, kTcOffW1, kTcBlockBytes, idesc128, false);
+            gemm_half(kTcColD2, kTcOffHi, kTcOffW1, kTcBlockBytes, idesc128, 1, false);
+            gemm_half(kTcColD2, kTcOffLo, kTcOffW1, kTcBlockBytes, idesc128, 1, false);
             tc_commit(bar);
         }
         if (!wait_commit()) { aborted = true; break; }
-        tc_hidden_epilogue(tmem + t_lane + kTcColD2 + cq * 32, s_bias + kHidden + cq * 32,
-                           smem + kTcOffHi + kb * kTcBlockBytes, smem + kTcOffLo + kb * kTcBlockBytes, row, chunk0);
+        hidden(kTcColD2, s_bias + kHidden, 0);
         publish();
-
-        // ---- layer 2: D3 = (Hhi + Hlo) W2^T, N = 32
+        if (tid == 0) {  // layer 2, K-half 0: D3 = (Hhi + Hlo) W2^T, N = 32
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            gemm_half(kTcColD3, kTcOffHi, kTcOffW2, kTcW2BlockBytes, idesc32, 0, true);
+            gemm_half(kTcColD3, kTcOffLo, kTcOffW2, kTcW2BlockBytes, idesc32, 0, false);
+        }
+        hidden(kTcColD2, s_bias + kHidden, 1);
+        publish();
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            gemm(kTcColD3, kTcOffHi, kTcOffW2, kTcW2BlockBytes, idesc32, true);
-            gemm(kTcColD3, kTcOffLo, kTcOffW2, kTcW2BlockBytes, idesc32, false);
+            gemm_half(kTcColD3, kTcOffHi, kTcOffW2, kTcW2BlockBytes, idesc32, 1, false);
+            gemm_half(kTcColD3, kTcOffLo, kTcOffW2, kTcW2BlockBytes, idesc32, 1, false);
             tc_commit(bar);
         }
         if (!wait_commit()) { aborted = true; break; }
