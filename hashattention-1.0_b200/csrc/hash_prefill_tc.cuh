@@ -169,7 +169,10 @@ __device__ __forceinline__ void tc_hidden_epilogue(uint32_t taddr, const float* 
                 const float x = v[col] + bias[col];
                 // SiLU with the hardware exp2 / reciprocal (relative error ~1e-6, well below the
                 // 2^-17 that the hi/lo split itself leaves)
-                a[j] = __fdividef(x, 1.0f + __expf(-x));
+                float e, r;  // exactly one exp2 and one reciprocal instruction per activation
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+                a[j] = x * r;
             }
             hi[e] = tc_pack_bf16(a[0], a[1]);  // one paired conversion; the rounded values are read back by shifts
             const float h0 = __uint_as_float(hi[e] << 16), h1 = __uint_as_float(hi[e] & 0xffff0000u);
