@@ -145,19 +145,23 @@ def ragged_lengths(config_index: int, batch: int, low: int, high: int) -> list[i
     return torch.randint(low, high + 1, (batch,), generator=g).tolist()
 
 
-def fill_cache_on_device(cache, seq_lens, seed: int) -> None:
+def fill_cache_on_device(cache, seq_lens, seed: int, kv_head0: int = 0) -> None:
     """Fills a paged cache directly on its device with keys / values of the same distribution as
-    :func:`make_decode_inputs` (N(0,1), outlier channels x8, RoPE, bf16), drawn from the device
-    generator. For benchmarks, where the tensors are too large to draw on the host; parity tests
-    use the host generators above."""
+    :func:`make_decode_inputs` (N(0,1), outlier channels x8, RoPE, bf16), drawn from device
+    generators. For benchmarks, where the tensors are too large to draw on the host; parity tests
+    use the host generators above.
+
+    Every kv-head has its own generator, seeded by ``(seed, global head index)``: the cache's head
+    ``j`` holds global head ``kv_head0 + j``, so a GPU that owns a slice of the kv-heads gets exactly
+    the rows the unsharded cache holds for those heads."""
     dev = cache.device
-    g = torch.Generator(device=dev).manual_seed(seed)
+    gens = [torch.Generator(device=dev).manual_seed(seed * 64 + kv_head0 + j) for j in range(cache.num_kv_heads)]
     inv_freq = 1.0 / (ROPE_THETA ** (torch.arange(0, 128, 2, dtype=torch.float32, device=dev) / 128))
     for b, S in enumerate(int(s) for s in seq_lens):
         for start in range(0, S, 32768):
             n = min(32768, S - start)
-            k = torch.randn(cache.num_kv_heads, n, 128, generator=g, device=dev)
-            v = torch.randn(cache.num_kv_heads, n, 128, generator=g, device=dev)
+            k = torch.stack([torch.randn(n, 128, generator=g, device=dev) for g in gens])
+            v = torch.stack([torch.randn(n, 128, generator=g, device=dev) for g in gens])
             k[..., list(OUTLIER_CHANNELS)] *= OUTLIER_SCALE
             freqs = torch.arange(start, start + n, device=dev, dtype=torch.float32)[:, None] * inv_freq[None, :]
             emb = torch.cat([freqs, freqs], dim=-1)

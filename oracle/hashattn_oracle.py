@@ -224,6 +224,22 @@ def decode_chunk(usa, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, init_bu
     return masked_attention_rows(q, k, v, mask)
 
 
+def cached_span(usa, q: torch.Tensor, k_new: torch.Tensor, past_signs: torch.Tensor, group: int) -> torch.Tensor:
+    """The reference's cached-signature branch of compute_mask_multi (hashattention_llama.py:409-420),
+    which it keeps disabled (:407-408): q_embedding of the query (:411), k_embedding of only the keys
+    that are not cached yet (:412), concatenation with the stored signs (:413-414), one baddbmm (:415-420).
+    ``q [B,Hq,D]``, ``k_new [B,Hkv,n,D]`` (the keys beyond the cached ones), ``past_signs [B,Hq,S-n,32]``
+    (+-1) -> span ``[B,Hq,S]``."""
+    q_sign = torch.sign(mlp_preact(nets_from_usa(usa, "q"), q[:, :, None, :]))                   # (:216-226)
+    k_rep = k_new.to(torch.float32).repeat_interleave(group, dim=1)
+    k_sign = torch.sign(mlp_preact(nets_from_usa(usa, "k"), k_rep))                              # (:204-214)
+    total = torch.cat([past_signs, k_sign], dim=-2)                                              # (:413)
+    B, H, S, W = total.shape
+    span = torch.baddbmm(torch.empty(B * H, 1, S), q_sign.reshape(B * H, 1, W),
+                         total.reshape(B * H, S, W).transpose(1, 2), beta=0, alpha=1.0)          # (:415-420)
+    return span.reshape(B, H, S)
+
+
 # ------------------------------------------------------------------------------------------
 # the whole step, structured like the reference (re-hashes every key, full sort, dense softmax)
 # ------------------------------------------------------------------------------------------

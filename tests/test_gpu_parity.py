@@ -510,34 +510,42 @@ def test_repeated_steps_grow_the_cache(device):
 
 
 def test_kv_head_partition_is_bit_identical(device):
-    """Sharding by kv-head (what multi-GPU runs do) changes no bit: each shard run alone gives the
-    same codes, sets and output as the unsharded run."""
-    Hq, Hkv = 16, 4
+    """Sharding by kv-head (what multi-GPU runs do) changes no bit: each shard, cut with the partition
+    module's own functions and run alone, gives the same codes, sets and output as the unsharded run, and
+    the shards' outputs concatenated in rank order are the unsharded output."""
+    from hashattention_b200 import partition
+    Hq, Hkv, world = 16, 4, 2
     usa = synthetic.make_usa(Hq, 128, 0, True)
     inp = synthetic.make_decode_inputs(99, [1300, 700], Hq, Hkv)
     budget = ha.Budget(16, 1.0 / 16, 16)
     _, out_full, ctx_full, cache_full = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget)
     packed = usa.packed(device)
-    for shard in range(2):
-        j0, j1 = shard * 2, shard * 2 + 2
+    q_full = inp.q.to(torch.bfloat16)
+    k_new = torch.stack([k[:, -1] for k in inp.k]).to(torch.bfloat16)
+    v_new = torch.stack([v[:, -1] for v in inp.v]).to(torch.bfloat16)
+    outs = []
+    for shard in range(world):
+        j0, j1 = partition.kv_head_range(Hkv, world, shard)
+        q_l, k_l, v_l = partition.shard_step_inputs(q_full, k_new, v_new, world, shard)
         ks, vs = [k[j0:j1] for k in inp.k], [v[j0:j1] for v in inp.v]
         lens = inp.seq_lens
-        cache = ha.PagedHashKVCache(2, 2, max(lens), device, shuffle_seed=21 + shard)
+        cache = ha.PagedHashKVCache(2, j1 - j0, max(lens), device, shuffle_seed=21 + shard)
         for b, S in enumerate(lens):
             cache.write_kv(b, ks[b][:, :S - 1], vs[b][:, :S - 1])
         ctx = ha.SparseDecodeContext(cache, budget, packed.slice_heads(j0 * 4, j1 * 4))
         ctx.hash_prefill()
         cache.seq_lens += 1
-        out = ctx.decode_step(inp.q[:, j0 * 4:j1 * 4].contiguous().to(device, torch.bfloat16),
-                              torch.stack([k[:, -1] for k in ks]).to(device, torch.bfloat16),
-                              torch.stack([v[:, -1] for v in vs]).to(device, torch.bfloat16)).float().cpu()
+        out = ctx.decode_step(q_l.to(device), k_l.to(device), v_l.to(device))
         ctx.check_status()
-        assert torch.equal(out, out_full[:, j0 * 4:j1 * 4])
+        outs.append(out)
+        assert torch.equal(out.float().cpu(), out_full[:, j0 * 4:j1 * 4])
         assert torch.equal(ctx.sel_cnt.cpu(), ctx_full.sel_cnt[:, j0 * 4:j1 * 4].cpu())
         for b in range(2):
             assert torch.equal(cache.read_codes(b), cache_full.read_codes(b)[j0 * 4:j1 * 4])
-            for h in range(8):
+            for h in range((j1 - j0) * 4):
                 assert torch.equal(heavy_from_device(ctx, b, h), heavy_from_device(ctx_full, b, j0 * 4 + h))
+    # rank order == kv-head order: what partition.gather_output concatenates on every rank
+    assert torch.equal(torch.cat(outs, dim=1).float().cpu(), out_full)
 
 
 @pytest.mark.gpu
