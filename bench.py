@@ -384,13 +384,14 @@ class Bench:
                 "min": min(per), "max": max(per), "repeats": repeats}
 
     def measure_stages(self, steps):
-        """Device time of the step's stages, each as its own graph over the same L instances (the stages are
-        separate library calls here; inside ha_decode_step they overlap through programmatic launches)."""
+        """Device time of the step's stages, each as its own graph over the same L instances: the encoder, scoring +
+        plan, selection + attention (separate library calls here; inside ha_decode_step they overlap through
+        programmatic launches, and small shapes run a single-pass cluster selection instead: `step_kernels`)."""
         L = self.L
         fns = {
             "hash_decode": lambda l: self.ctxs[l].hash_decode(self.qs[l], self.kns[l], self.vns[l]),
-            "score_select": lambda l: self.ctxs[l].score_select(),
-            "sparse_decode": lambda l: self.ctxs[l].sparse_decode(self.qs[l], out=self.outs[l]),
+            "score_plan": lambda l: self.ctxs[l].score_plan(),
+            "select_attend": lambda l: self.ctxs[l].select_attend(self.qs[l], out=self.outs[l]),
         }
         reps = max(4, min(200, steps // L))
         out = {}
@@ -507,13 +508,15 @@ def run_gpu_arm(args):
 
     stage_us = b.measure_stages(args.steps)
     att_bytes = b.nbytes_gpu["kv"] + b.nbytes_gpu["qo"]
-    att_gbs = att_bytes / (stage_us["sparse_decode"] * 1e-6) / 1e9
-    kernel = "sparse_gather_kernel (cluster variant)" if b.launches_per_step == 3 else "sparse_gather_kernel + sparse_merge_kernel"
+    att_gbs = att_bytes / (stage_us["select_attend"] * 1e-6) / 1e9
+    kernel = "select_attend_kernel + select_attend_merge_kernel"
     traffic, traffic_src = ncu_traffic(args.workload if world == 1 else f"{args.workload}/gpus{world}", kernel)
     roofline = {"bound": "hbm", "kernel": kernel, "achieved": att_gbs, "peak": peak, "unit": "GB/s",
                 "frac": att_gbs / peak, "frac_of_8tbs": att_gbs / 8000.0, "traffic": traffic, "traffic_source": traffic_src,
                 "peak_source": peak_src, "algorithmic_bytes_per_launch": att_bytes,
-                "us_per_launch": stage_us["sparse_decode"], "per": "GPU (this rank's kv-heads)"}
+                "us_per_launch": stage_us["select_attend"], "per": "GPU (this rank's kv-heads)",
+                "note": "the selection + attention stage of the step timed as its own graph over the same layer instances "
+                        "(ha_select_attend on the plan ha_score_plan left); bytes: the K/V rows it attends + q/out"}
     pipeline = pipeline_block(b, per_step, stage_us, peak * world)
     pipeline["peak_note"] = f"{world} x {peak} GB/s" if world > 1 else peak_src
 
@@ -530,7 +533,7 @@ def run_gpu_arm(args):
            "how": "ha_decode_step_host per step, q/k/v in pinned host memory, result + status back, stream wait; "
                   "value: the call replayed as a CUDA graph; eager: one C-ABI call per step",
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
-    L_primary, launches = b.L, b.launches_per_step
+    L_primary, launches, step_path = b.L, b.launches_per_step, b.ctxs[0].step_path()
     per_gpu_batch, hkv_local = b.B, b.hkv
     nbytes_primary = b.nbytes
     b.free()
@@ -548,7 +551,7 @@ def run_gpu_arm(args):
             blk = pipeline_block(s, ts["median"], st, peak)
             blk.update({"workload": f"{name}: {WORKLOADS[name]['desc']}", "us_per_layer": ts["median"] * 1e6,
                         "us_per_layer_p10_p90": [ts["p10"] * 1e6, ts["p90"] * 1e6], "layer_instances": s.L,
-                        "launches_per_step": s.launches_per_step})
+                        "launches_per_step": s.launches_per_step, "step_kernels": s.ctxs[0].step_path()})
             secondary[name] = blk
             s.free()
 
@@ -578,7 +581,7 @@ def run_gpu_arm(args):
                       "partition": f"kv-heads cut over {world} GPU(s): {hkv_local} per GPU; no collective on the path, "
                                    f"one all-gather of the outputs at the end (final_gather_us)"},
             "final_gather_us": t_gather * 1e6, "out_sha256_instance0": out_digest,
-            "launches_per_step": launches, "inputs": inputs, "roofline": roofline, "pipeline": pipeline,
+            "launches_per_step": launches, "step_kernels": step_path, "inputs": inputs, "roofline": roofline, "pipeline": pipeline,
             "secondary": secondary, "prefill_hash": prefill, "e2e": e2e, "cpu_baseline": cpu, "clocks": clocks,
             "gpu_launches": launches * args.steps,
         }

@@ -24,9 +24,11 @@ HA_ERR_SEL_OVERFLOW = 8
 HA_ERR_SCRATCH_LIMIT = 9
 HA_WEIGHTS_BF16 = 0
 HA_WEIGHTS_F32 = 1
-HA_ABI_VERSION = 3
+HA_ABI_VERSION = 4
 HA_EVAL_SIMPLE = 0
 HA_EVAL_DEPTH = 1
+HA_OPT_CLUSTER_GATHER = 0
+HA_OPT_CLUSTER_SELECT = 1
 
 
 class HaShape(ctypes.Structure):
@@ -53,6 +55,8 @@ _S, _B, _W = POINTER(HaShape), POINTER(HaBudget), POINTER(HaHashWeights)
 PROTOTYPES = {
     "ha_abi_version": (c_int, []),
     "ha_status_str": (c_char_p, [c_int]),
+    "ha_set_option": (c_int, [c_int, c_int]),
+    "ha_get_option": (c_int, [c_int]),
     "ha_workspace_bytes": (c_size_t, [_S, _B]),
     "ha_workspace_init": (c_int, [_S, _B, _P, c_size_t, _P]),
     "ha_hash_decode": (c_int, [_S, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
@@ -60,6 +64,9 @@ PROTOTYPES = {
     "ha_score_select": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P, _P]),
     "ha_static_scratch_needed": (c_size_t, [_S]),
     "ha_decode_step_launches": (c_int, [_S, _B]),
+    "ha_decode_step_path": (c_char_p, [_S, _B]),
+    "ha_score_plan": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, c_size_t, _P, _P]),
+    "ha_select_attend": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, c_float, _P, _P, c_size_t, _P, _P]),
     "ha_score_select_static": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, _P]),
     "ha_sparse_decode": (c_int, [_S, _B, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P, c_size_t, _P, _P]),
     "ha_decode_step": (c_int, [_S, _B, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P,

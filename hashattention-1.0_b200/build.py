@@ -14,8 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libhashattn.so")
 SOURCES = ["hashattn_abi.cu"]
-HEADERS = ["common.cuh", "hash_decode.cuh", "score_select.cuh", "sparse_decode.cuh",
-           os.path.join("..", "..", "include", "hashattn.h")]
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))) + [os.path.join("..", "..", "include", "hashattn.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC",

@@ -1,10 +1,10 @@
 // extern "C" entry points of libhashattn.so (declared in include/hashattn.h): argument checks,
 // workspace carving and kernel launches. No device memory is allocated, nothing synchronises with
-// the host (except where ha_decode_step_host is asked to), nothing throws. The only resources the
-// library creates are a stream and events per device for the staggered decode step, at its first use.
+// the host (except where ha_decode_step_host is asked to), nothing throws, and the library creates no
+// streams, events or other CUDA resources of its own.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
-#include <cstdlib>
 #include <mutex>
 #include <utility>
 
@@ -12,6 +12,7 @@
 #include "hash_decode.cuh"
 #include "hash_prefill_tc.cuh"
 #include "score_select.cuh"
+#include "select_attend.cuh"
 #include "sparse_decode.cuh"
 
 #ifndef HA_USE_PDL
@@ -23,6 +24,15 @@ namespace {
 
 constexpr size_t kAlign = 256;
 inline size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+// Process-wide dispatch options (ha_set_option); -1 / 0 = the library decides.
+std::atomic<int> g_options[HA_OPT_COUNT_] = {};
+bool g_options_ready = [] {
+    g_options[HA_OPT_CLUSTER_GATHER] = -1;
+    g_options[HA_OPT_CLUSTER_SELECT] = -1;
+    return true;
+}();
+inline int option(int key) { return g_options[key].load(std::memory_order_relaxed); }
 
 int check_shape(const ha_shape_t* s) {
     if (s == nullptr) return HA_ERR_BAD_ARG;
@@ -89,9 +99,9 @@ AttSplit att_split_launch(const ha_shape_t* s, const ha_budget_t* b) {
     const int cluster_round_rows = kAttClusterThreads / 16 * kAttRowsPerWorker;  // 64
     const long long per_cta = (rows + kAttClusterCtas - 1) / kAttClusterCtas;
     const long long rounds = (per_cta + cluster_round_rows - 1) / cluster_round_rows;
-    const char* env = std::getenv("HA_CLUSTER_GATHER");  // "0" / "1" force the choice (experiments, tests)
+    const int forced = option(HA_OPT_CLUSTER_GATHER);  // 0 / 1 force the choice (experiments, tests)
     const bool fits = rounds <= kAttMaxRounds && a.nsplits > 1;
-    const bool want = env != nullptr ? env[0] == '1' : total <= 65536;
+    const bool want = forced >= 0 ? forced == 1 : total <= 65536;
     if (fits && want) {
         a.cluster = true;
         a.rounds = (int)(rounds < 1 ? 1 : rounds);
@@ -100,49 +110,65 @@ AttSplit att_split_launch(const ha_shape_t* s, const ha_budget_t* b) {
     return a;
 }
 
+// How a sequence is cut into chunks for scoring and selection: 4, 8 or 16 pages per chunk (the kernels are
+// compiled for these), about 32 chunks per sequence; small problems take smaller chunks (up to 64 per
+// sequence) until the scoring grid has two CTAs per SM.
+struct Geometry {
+    int chunk_pages, nchunks;
+    int nslots;  // CTAs per (sequence, head) of select_attend_kernel: the chunks plus the two edge CTAs
+};
+
+Geometry geometry(const ha_shape_t* s) {
+    Geometry g;
+    const int want = (s->max_pages + 31) / 32;
+    g.chunk_pages = want <= 4 ? 4 : (want <= 8 ? 8 : kMaxChunkPages);
+    const long long units = (long long)s->batch * s->num_kv_heads;
+    auto chunks = [&](int cp) { return (s->max_pages + cp - 1) / cp; };
+    while (g.chunk_pages > 4 && units * chunks(g.chunk_pages) < 2 * 148 && chunks(g.chunk_pages / 2) <= 64)
+        g.chunk_pages /= 2;
+#ifdef HA_CHUNK_DIV
+    for (int d = HA_CHUNK_DIV; d > 1 && g.chunk_pages > 4; d /= 2) g.chunk_pages /= 2;
+#endif
+    g.nchunks = chunks(g.chunk_pages);
+    g.nslots = g.nchunks + kSaEdgeSlots;
+    return g;
+}
+
 struct Workspace {
     uint32_t* hist;     // [B][Hkv][4*33][nchunks] per-chunk score histograms
-    int32_t* sel_rows;  // [B][Hq][sel_stride] physical rows of the selected tokens
-    float* partials;    // [B][Hq][nsplits][130] attention partials
+    int32_t* sel_rows;  // [B][Hq][sel_stride] physical rows of the selected tokens (single-pass cluster selection)
+    float* partials;    // [B][Hq][max(nsplits, nslots)][130] attention partials
     int32_t* plan;      // [B][Hkv][8 + 8 * nchunks] thresholds, tie quotas and per-chunk output bases
-    uint32_t* scores;   // [B][Hkv][nchunks * chunk tokens] packed scores of the 4 heads of a group, one byte each
+    uint8_t* scores;    // [B][Hq][nchunks * chunk tokens] one score byte per token and query head
+    uint32_t* arrive;   // [B][Hkv] arrival counters of the scoring kernel (zero between calls)
     size_t bytes;
 };
 
-size_t scores_bytes(const ha_shape_t* s) {
-    return (size_t)s->batch * s->num_kv_heads * num_chunks_for(s->max_pages) * chunk_pages_for(s->max_pages) * kPage *
-           sizeof(uint32_t);
+size_t scores_bytes(const ha_shape_t* s, const Geometry& g) {
+    return (size_t)s->batch * s->num_kv_heads * kGroup * g.nchunks * g.chunk_pages * kPage;
 }
 
 Workspace carve(const ha_shape_t* s, const ha_budget_t* b, void* base) {
-    const size_t Hq = (size_t)s->num_kv_heads * kGroup;
-    const size_t n_hist = (size_t)s->batch * s->num_kv_heads * num_chunks_for(s->max_pages) * kGroup * kBins;
+    const Geometry g = geometry(s);
+    const size_t Hq = (size_t)s->num_kv_heads * kGroup, units = (size_t)s->batch * s->num_kv_heads;
     char* p = static_cast<char*>(base);
     Workspace w;
     size_t off = 0;
     w.hist = reinterpret_cast<uint32_t*>(p + off);
-    off += align_up(n_hist * sizeof(uint32_t));
+    off += align_up(units * g.nchunks * kGroup * kBins * sizeof(uint32_t));
     w.sel_rows = reinterpret_cast<int32_t*>(p + off);
     off += align_up((size_t)s->batch * Hq * s->sel_stride * sizeof(int32_t));
     w.partials = reinterpret_cast<float*>(p + off);
-    off += align_up((size_t)s->batch * Hq * att_split(s, b).nsplits * kPartStride * sizeof(float));
+    off += align_up((size_t)s->batch * Hq * std::max(att_split(s, b).nsplits, g.nslots) * kPartStride * sizeof(float));
     w.plan = reinterpret_cast<int32_t*>(p + off);
-    off += align_up((size_t)s->batch * s->num_kv_heads * (8 + 8 * (size_t)num_chunks_for(s->max_pages)) * sizeof(int32_t));
-    w.scores = reinterpret_cast<uint32_t*>(p + off);
-    off += align_up(scores_bytes(s));
+    off += align_up(units * (8 + 8 * (size_t)g.nchunks) * sizeof(int32_t));
+    w.scores = reinterpret_cast<uint8_t*>(p + off);
+    off += align_up(scores_bytes(s, g));
+    w.arrive = reinterpret_cast<uint32_t*>(p + off);
+    off += align_up(units * sizeof(uint32_t));
     w.bytes = off;
     return w;
 }
-
-// Priority given to the kernels launched inside a PriorityScope (0 = the stream's own). Used only
-// by the staggered decode step, where the short latency-bound kernels of one half must get SM
-// slots ahead of the queued CTAs of the other half's streaming kernels.
-thread_local int t_launch_priority = 0;
-struct PriorityScope {
-    int saved;
-    explicit PriorityScope(int p) : saved(t_launch_priority) { t_launch_priority = p; }
-    ~PriorityScope() { t_launch_priority = saved; }
-};
 
 // Every kernel is launched with programmatic stream serialization (it may start while its
 // predecessor drains and synchronises itself with griddepcontrol.wait); cluster_x > 1 adds a
@@ -155,7 +181,7 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[3];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
     cfg.numAttrs = 1;
@@ -166,45 +192,76 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t
         attr[cfg.numAttrs].val.clusterDim.z = 1;
         ++cfg.numAttrs;
     }
-    if (t_launch_priority != 0) {
-        attr[cfg.numAttrs].id = cudaLaunchAttributePriority;
-        attr[cfg.numAttrs].val.priority = t_launch_priority;
-        ++cfg.numAttrs;
-    }
     cfg.attrs = attr;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-// The two-pass selection on the kv-heads [p.kvh0, p.kvh0 + nkvh): chunk histograms and packed
-// scores (launch_score_hist), then the plan (thresholds and output bases, derived from the
-// histograms once per (sequence, kv-head)) and the compaction (launch_plan_select).
+// Kernels that keep more than a few KB of shared memory per CTA ask for a carve-out that holds a full SM's worth
+// of their CTAs (the default split may size it for fewer); set once per device and kernel.
+std::atomic<unsigned> g_carveout_set[64] = {};
+
+template <typename K>
+void prefer_carveout(K kernel, int kernel_id, int percent) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return;
+    const unsigned bit = 1u << kernel_id;
+    if (g_carveout_set[dev].load(std::memory_order_relaxed) & bit) return;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, percent) != cudaSuccess)
+        (void)cudaGetLastError();  // only a hint
+    g_carveout_set[dev].fetch_or(bit, std::memory_order_relaxed);
+}
+
+// Scoring, histograms and the plan (score_hist_kernel) on the kv-heads [p.kvh0, p.kvh0 + nkvh).
 cudaError_t launch_score_hist(const ha_shape_t* shape, const SelectParams& p, int nkvh, cudaStream_t s) {
     const dim3 grid(p.nchunks, nkvh, shape->batch);
-    switch (chunk_pages_for(shape->max_pages)) {
+    prefer_carveout(score_hist_kernel<1>, 0, 40);  // 5 CTAs x 13 KB
+    prefer_carveout(score_hist_kernel<2>, 1, 40);
+    prefer_carveout(score_hist_kernel<4>, 2, 40);
+    switch (geometry(shape).chunk_pages) {
         case 4: return launch(score_hist_kernel<1>, grid, dim3(kSelThreads), s, 1, p);
         case 8: return launch(score_hist_kernel<2>, grid, dim3(kSelThreads), s, 1, p);
         default: return launch(score_hist_kernel<4>, grid, dim3(kSelThreads), s, 1, p);
     }
 }
 
-cudaError_t launch_plan_select(const ha_shape_t* shape, const SelectParams& p, int nkvh, cudaStream_t s,
-                               int priority = 0) {
-    const dim3 grid(p.nchunks, nkvh, shape->batch);
-    const int chunk_pages = chunk_pages_for(shape->max_pages);
-    PriorityScope scope(priority);
-    const cudaError_t e = launch(select_plan_kernel, dim3(nkvh, shape->batch), dim3(kSelThreads), s, 1, p,
-                                 chunk_pages * kPage);
-    if (e != cudaSuccess) return e;
-    switch (chunk_pages) {
-        case 4: return launch(select_kernel<1>, grid, dim3(kSelBThreads), s, 1, p);
-        case 8: return launch(select_kernel<2>, grid, dim3(kSelBThreads), s, 1, p);
-        default: return launch(select_kernel<4>, grid, dim3(kSelBThreads), s, 1, p);
+// Selection + attention (select_attend_kernel and the merge of its partials), or the selection alone, on the
+// query heads [p.h0, p.h0 + nheads).
+cudaError_t launch_select_attend(const ha_shape_t* shape, const SelectAttendParams& p, int nheads, bool gather,
+                                 cudaStream_t s) {
+    const dim3 grid(p.nslots, nheads, shape->batch);
+    const int chunk_pages = geometry(shape).chunk_pages;
+    if (!gather) {
+        switch (chunk_pages) {
+            case 4: return launch(select_attend_kernel<1, false, 8>, grid, dim3(kSaThreads), s, 1, p);
+            case 8: return launch(select_attend_kernel<2, false, 8>, grid, dim3(kSaThreads), s, 1, p);
+            default: return launch(select_attend_kernel<4, false, 8>, grid, dim3(kSaThreads), s, 1, p);
+        }
     }
-}
-
-cudaError_t launch_two_pass_select(const ha_shape_t* shape, const SelectParams& p, int nkvh, cudaStream_t s) {
-    const cudaError_t e = launch_score_hist(shape, p, nkvh, s);
-    return e != cudaSuccess ? e : launch_plan_select(shape, p, nkvh, s);
+    // a grid that fits the GPU at 8 CTAs per SM runs as one wave of the 64-register build; larger grids run faster
+    // on the 72-register build at 7 CTAs per SM
+    const bool one_wave = (long long)p.nslots * nheads * shape->batch <= 8LL * 148;
+    cudaError_t e;
+    if (one_wave) {
+        prefer_carveout(select_attend_kernel<1, true, 8>, 3, 75);  // 8 CTAs x 6 - 18.5 KB
+        prefer_carveout(select_attend_kernel<2, true, 8>, 4, 75);
+        prefer_carveout(select_attend_kernel<4, true, 8>, 5, 75);
+        switch (chunk_pages) {
+            case 4: e = launch(select_attend_kernel<1, true, 8>, grid, dim3(kSaThreads), s, 1, p); break;
+            case 8: e = launch(select_attend_kernel<2, true, 8>, grid, dim3(kSaThreads), s, 1, p); break;
+            default: e = launch(select_attend_kernel<4, true, 8>, grid, dim3(kSaThreads), s, 1, p); break;
+        }
+    } else {
+        prefer_carveout(select_attend_kernel<1, true, 7>, 6, 75);
+        prefer_carveout(select_attend_kernel<2, true, 7>, 7, 75);
+        prefer_carveout(select_attend_kernel<4, true, 7>, 8, 75);
+        switch (chunk_pages) {
+            case 4: e = launch(select_attend_kernel<1, true, 7>, grid, dim3(kSaThreads), s, 1, p); break;
+            case 8: e = launch(select_attend_kernel<2, true, 7>, grid, dim3(kSaThreads), s, 1, p); break;
+            default: e = launch(select_attend_kernel<4, true, 7>, grid, dim3(kSaThreads), s, 1, p); break;
+        }
+    }
+    if (e != cudaSuccess) return e;
+    return launch(select_attend_merge_kernel, dim3(nheads, shape->batch), dim3(kMergeThreads), s, 1, p, chunk_pages * kPage);
 }
 
 // One cluster kernel scores and selects in a single pass when the sequences are short and there are at
@@ -215,7 +272,9 @@ cudaError_t launch_two_pass_select(const ha_shape_t* shape, const SelectParams& 
 bool use_cluster_select(const ha_shape_t* shape) {
     const long long max_tokens = (long long)shape->max_pages * kPage;
     const long long units = (long long)shape->batch * shape->num_kv_heads;
-    return max_tokens <= 2LL * kClRoundTokens && units <= 8;
+    const int forced = option(HA_OPT_CLUSTER_SELECT);  // 0 never, 1 whenever the sequences fit the kernel
+    if (forced == 0 || max_tokens > 2LL * kClRoundTokens) return false;
+    return forced == 1 || units <= 8;
 }
 
 }  // namespace
@@ -227,7 +286,7 @@ namespace {
 SelectParams select_params(const ha_shape_t* shape, const ha_budget_t* budget, const uint32_t* q_codes,
                            const uint32_t* hash_pages, const int32_t* page_table, const int32_t* seq_lens,
                            int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg, int32_t* status,
-                           uint32_t* hist, int32_t* plan, uint32_t* scores, int32_t* sel_rows,
+                           uint32_t* hist, int32_t* plan, uint8_t* scores, uint32_t* arrive, int32_t* sel_rows,
                            const int32_t* budget_lens = nullptr) {
     SelectParams p;
     p.q_codes = q_codes;
@@ -236,6 +295,7 @@ SelectParams select_params(const ha_shape_t* shape, const ha_budget_t* budget, c
     p.seq_lens = seq_lens;
     p.budget_lens = budget_lens;
     p.hist = hist;
+    p.arrive = arrive;
     p.plan = plan;
     p.scores = scores;
     p.sel_idx = sel_idx;
@@ -248,7 +308,7 @@ SelectParams select_params(const ha_shape_t* shape, const ha_budget_t* budget, c
     p.max_pages = shape->max_pages;
     p.num_pages = shape->num_pages;
     p.sel_stride = shape->sel_stride;
-    p.nchunks = num_chunks_for(shape->max_pages);
+    p.nchunks = geometry(shape).nchunks;
     p.kvh0 = 0;
     p.init_budget = budget->init_budget;
     p.recent_budget = budget->recent_budget;
@@ -258,14 +318,50 @@ SelectParams select_params(const ha_shape_t* shape, const ha_budget_t* budget, c
     return p;
 }
 
+// The attention side (q, pools, out) may be null when only the selection is run.
+SelectAttendParams select_attend_params(const ha_shape_t* shape, const ha_budget_t* budget, const int32_t* plan,
+                                        const uint8_t* scores, float* partials, int32_t* sel_idx, const void* q,
+                                        const void* k_pages, const void* v_pages, const int32_t* page_table,
+                                        const int32_t* seq_lens, const int32_t* budget_lens, float sm_scale, void* out,
+                                        int32_t* status, int32_t* status_out) {
+    const Geometry g = geometry(shape);
+    SelectAttendParams p;
+    p.plan = plan;
+    p.scores = scores;
+    p.sel_idx = sel_idx;
+    p.q = static_cast<const __nv_bfloat16*>(q);
+    p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
+    p.v_pages = static_cast<const __nv_bfloat16*>(v_pages);
+    p.page_table = page_table;
+    p.seq_lens = seq_lens;
+    p.budget_lens = budget_lens;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.partials = partials;
+    p.status = status;
+    p.status_out = status_out;
+    p.B = shape->batch;
+    p.Hkv = shape->num_kv_heads;
+    p.max_pages = shape->max_pages;
+    p.num_pages = shape->num_pages;
+    p.sel_stride = shape->sel_stride;
+    p.nchunks = g.nchunks;
+    p.nslots = g.nslots;
+    p.h0 = 0;
+    p.init_budget = budget->init_budget;
+    p.recent_budget = budget->recent_budget;
+    p.heavy_budget = budget->heavy_budget;
+    p.scale_log2e = sm_scale * 1.4426950408889634f;
+    return p;
+}
+
 // sel == nullptr with physical == true: use the physical rows select_kernel left in the workspace.
 int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                        const void* q, const void* k_pages, const void* v_pages,
                        const int32_t* page_table, const int32_t* seq_lens,
                        const int32_t* sel, const int32_t* sel_cnt, bool physical, float sm_scale,
                        void* out, void* workspace, size_t workspace_bytes,
-                       int32_t* status, void* stream, int kvh0 = 0, int nkvh = -1, int merge_priority = 0,
-                       const int32_t* budget_lens = nullptr, int32_t* status_out = nullptr) {
+                       int32_t* status, void* stream, const int32_t* budget_lens = nullptr,
+                       int32_t* status_out = nullptr) {
     int rc = check_shape(shape);
     if (rc != HA_OK) return rc;
     rc = check_budget(budget);
@@ -274,7 +370,7 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
         seq_lens == nullptr || out == nullptr || status == nullptr || !std::isfinite(sm_scale))
         return HA_ERR_BAD_ARG;
     if (budget->eval_mode != HA_EVAL_SIMPLE && sel_cnt == nullptr) return HA_ERR_BAD_ARG;  // variable-size sets
-    const int nheads = (nkvh < 0 ? shape->num_kv_heads : nkvh) * kGroup;  // heads [4 kvh0, 4 kvh0 + nheads)
+    const int nheads = shape->num_kv_heads * kGroup;
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
     const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
@@ -305,7 +401,7 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     p.nsplits = split.nsplits;
     p.rounds = split.rounds;
     p.round_rows = split.cluster ? kAttClusterThreads / 16 * kAttRowsPerWorker : kAttRoundRows;
-    p.h0 = kvh0 * kGroup;
+    p.h0 = 0;
     const dim3 grid(split.nsplits, nheads, shape->batch);
     const cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (split.cluster) {
@@ -322,7 +418,6 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                              : launch(sparse_gather_kernel<false, kAttThreads, false>, grid, dim3(kAttThreads), s, 1, p);
     if (e == cudaSuccess && merge_follows) {
         p.status_out = status_out;
-        PriorityScope light(merge_priority);
         e = launch(sparse_merge_kernel, dim3(nheads, shape->batch), dim3(kHeadDim), s, 1, p);
     }
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
@@ -331,78 +426,10 @@ int sparse_decode_impl(const ha_shape_t* shape, const ha_budget_t* budget,
 }  // namespace
 }  // namespace ha
 
-// ------------------------------------------------------------------------------------------
-// Staggered decode step. Between the histogram pass and the gather of one set of kv-heads lie
-// the plan and the compaction, short kernels that leave HBM idle. For large problems the step is
-// therefore run as two halves of the kv-heads, the second one a histogram pass behind the
-// first, so that one half's short kernels overlap the other half's streaming kernels. The second
-// half runs on a stream that belongs to the library (one per device, created at the first such
-// call) and is forked from / joined to the caller's stream with events, which also works under
-// stream capture. Every (sequence, kv-head) is independent, so the result is bit-identical.
-// ------------------------------------------------------------------------------------------
 namespace ha {
 namespace {
 
 constexpr int kMaxDevices = 64;
-
-constexpr int kMaxParts = 4;
-
-struct StaggerResources {
-    cudaStream_t aux[kMaxParts - 1] = {};           // parts 1.. run here; part 0 on the caller's stream
-    cudaEvent_t fork[kMaxParts - 1] = {}, join[kMaxParts - 1] = {};
-    int light_priority = 0;  // for the short kernels: the most urgent priority the device offers
-    bool ready = false;
-};
-std::mutex g_stagger_mutex;  // held while a staggered step is enqueued: the events are shared
-StaggerResources g_stagger[kMaxDevices];
-
-// Environment override HA_STAGGER: "0" never, "1" whenever the two-pass selection runs on at
-// least two kv-heads; otherwise only when the hash pages of the step exceed 32 MB.
-bool use_stagger(const ha_shape_t* shape) {
-    if (use_cluster_select(shape) || shape->num_kv_heads < 2) return false;
-    const char* env = std::getenv("HA_STAGGER");
-    if (env != nullptr && env[0] == '0') return false;
-    if (env != nullptr && env[0] == '1') return true;
-    const long long hash_bytes = (long long)shape->batch * shape->num_kv_heads * shape->max_pages * kPage * 16;
-    return hash_bytes >= (32LL << 20);
-}
-
-// Two parts measured best (B=4, S=128K: 82.9 us per step against 83.8 with three and 91.5 with four
-// parts, 88.2 without staggering); HA_STAGGER_PARTS is an experiment knob.
-int stagger_parts(const ha_shape_t* shape) {
-    int parts = 2;
-    if (const char* env = std::getenv("HA_STAGGER_PARTS")) parts = std::atoi(env);
-    return std::max(2, std::min(parts, std::min(kMaxParts, shape->num_kv_heads)));
-}
-
-// Caller holds g_stagger_mutex.
-StaggerResources* stagger_resources() {
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-    StaggerResources& r = g_stagger[dev];
-    if (!r.ready) {
-        int least = 0, greatest = 0;
-        if (cudaDeviceGetStreamPriorityRange(&least, &greatest) != cudaSuccess) return nullptr;
-        bool ok = true;
-        for (int i = 0; i < kMaxParts - 1 && ok; ++i)
-            ok = cudaStreamCreateWithFlags(&r.aux[i], cudaStreamNonBlocking) == cudaSuccess &&
-                 cudaEventCreateWithFlags(&r.fork[i], cudaEventDisableTiming) == cudaSuccess &&
-                 cudaEventCreateWithFlags(&r.join[i], cudaEventDisableTiming) == cudaSuccess;
-        if (!ok) {  // give back whatever was created, so that a later call starts from nothing
-            for (int i = 0; i < kMaxParts - 1; ++i) {
-                if (r.aux[i] != nullptr) cudaStreamDestroy(r.aux[i]);
-                if (r.fork[i] != nullptr) cudaEventDestroy(r.fork[i]);
-                if (r.join[i] != nullptr) cudaEventDestroy(r.join[i]);
-                r.aux[i] = nullptr;
-                r.fork[i] = r.join[i] = nullptr;
-            }
-            return nullptr;
-        }
-        r.light_priority = greatest;
-        r.ready = true;
-    }
-    return &r;
-}
 
 // The device-side address of a page-locked, device-addressable host buffer; null for anything else
 // (pageable memory, device memory).
@@ -413,56 +440,6 @@ void* mapped_host_pointer(const void* host) {
         return nullptr;
     }
     return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
-}
-
-int staggered_select_attend(const ha_shape_t* shape, const ha_budget_t* budget, const void* q,
-                            const void* k_pages, const void* v_pages, const uint32_t* hash_pages,
-                            const int32_t* page_table, const int32_t* seq_lens, const uint32_t* q_codes,
-                            int32_t* sel_idx, int32_t* sel_cnt, float sm_scale, void* out, void* workspace,
-                            size_t workspace_bytes, int32_t* status, cudaStream_t s, const int32_t* budget_lens) {
-    int rc = check_budget(budget);
-    if (rc != HA_OK) return rc;
-    if (q_codes == nullptr || hash_pages == nullptr || page_table == nullptr || seq_lens == nullptr ||
-        sel_idx == nullptr || sel_cnt == nullptr || status == nullptr)
-        return HA_ERR_BAD_ARG;
-    if (workspace == nullptr) return HA_ERR_WORKSPACE;
-    const Workspace w = carve(shape, budget, workspace);
-    if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
-    const int parts = stagger_parts(shape);
-    const SelectParams base = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx,
-                                            sel_cnt, nullptr, status, w.hist, w.plan, w.scores, w.sel_rows,
-                                            budget_lens);
-
-    std::lock_guard<std::mutex> lock(g_stagger_mutex);
-    StaggerResources* r = stagger_resources();
-    if (r == nullptr) return HA_ERR_LAUNCH;
-    const int light = r->light_priority;
-    // Part i covers kv-heads [first, first + n) (the larger parts first) on stream i (0 = the caller's) and
-    // starts when the histogram pass of part i - 1 is done.
-    bool ok = true;
-    int first = 0;
-    for (int i = 0; i < parts; ++i) {
-        const int n = shape->num_kv_heads / parts + (i < shape->num_kv_heads % parts ? 1 : 0);
-        cudaStream_t si = i == 0 ? s : r->aux[i - 1];
-        SelectParams p = base;
-        p.kvh0 = first;
-        ok = ok && launch_score_hist(shape, p, n, si) == cudaSuccess;
-        if (i + 1 < parts) {  // even after a failed launch: every stream that forks is also joined below
-            if (cudaEventRecord(r->fork[i], si) != cudaSuccess ||
-                cudaStreamWaitEvent(r->aux[i], r->fork[i], 0) != cudaSuccess)
-                return HA_ERR_LAUNCH;
-        }
-        ok = ok && launch_plan_select(shape, p, n, si, light) == cudaSuccess;
-        ok = ok && sparse_decode_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, nullptr, sel_cnt, true,
-                                      sm_scale, out, workspace, workspace_bytes, status, si, first, n, light,
-                                      budget_lens) == HA_OK;
-        first += n;
-    }
-    for (int i = 1; i < parts; ++i)
-        if (cudaEventRecord(r->join[i - 1], r->aux[i - 1]) != cudaSuccess ||
-            cudaStreamWaitEvent(s, r->join[i - 1], 0) != cudaSuccess)
-            return HA_ERR_LAUNCH;
-    return ok ? HA_OK : HA_ERR_LAUNCH;
 }
 
 }  // namespace
@@ -481,6 +458,16 @@ int ha_debug_set_timeline(unsigned long long* buffer) {
 #endif
 
 int ha_abi_version(void) { return HA_ABI_VERSION; }
+
+int ha_set_option(int option_key, int value) {
+    if (option_key < 0 || option_key >= HA_OPT_COUNT_) return HA_ERR_BAD_ARG;
+    g_options[option_key].store(value, std::memory_order_relaxed);
+    return HA_OK;
+}
+
+int ha_get_option(int option_key) {
+    return option_key < 0 || option_key >= HA_OPT_COUNT_ ? 0 : option(option_key);
+}
 
 const char* ha_status_str(int status) {
     switch (status) {
@@ -512,8 +499,8 @@ int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* 
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
     const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
-    // the kernels keep no state in the workspace between calls; clearing it only makes runs
-    // that read it before writing (a misuse) reproducible
+    // the arrival counters of the scoring kernel must start at zero (the kernel leaves them at zero);
+    // nothing else in the workspace carries state between calls
     if (cudaMemsetAsync(workspace, 0, w.bytes, static_cast<cudaStream_t>(stream)) != cudaSuccess)
         return HA_ERR_LAUNCH;
     return HA_OK;
@@ -693,30 +680,75 @@ static int score_select_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                              const uint32_t* q_codes, const uint32_t* hash_pages,
                              const int32_t* page_table, const int32_t* seq_lens, const int32_t* budget_lens,
                              int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg,
-                             void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+                             void* workspace, size_t workspace_bytes, int32_t* status, void* stream,
+                             bool plan_only = false) {
     int rc = check_shape(shape);
     if (rc != HA_OK) return rc;
     rc = check_budget(budget);
     if (rc != HA_OK) return rc;
     if (q_codes == nullptr || hash_pages == nullptr || page_table == nullptr || seq_lens == nullptr ||
-        sel_idx == nullptr || sel_cnt == nullptr || status == nullptr)
+        (sel_idx == nullptr && !plan_only) || sel_cnt == nullptr || status == nullptr)
         return HA_ERR_BAD_ARG;
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
     const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
 
     const SelectParams p = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
-                                         scores_dbg, status, w.hist, w.plan, w.scores, w.sel_rows, budget_lens);
+                                         scores_dbg, status, w.hist, w.plan, w.scores, w.arrive, w.sel_rows, budget_lens);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const long long max_tokens = (long long)shape->max_pages * kPage;
-    if (use_cluster_select(shape)) {
+    if (!plan_only && use_cluster_select(shape)) {
         const dim3 cgrid(kClCtas, shape->num_kv_heads, shape->batch);
         const cudaError_t e = max_tokens <= kClRoundTokens
             ? launch(score_select_cluster_kernel<1>, cgrid, dim3(kClThreads), s, kClCtas, p)
             : launch(score_select_cluster_kernel<2>, cgrid, dim3(kClThreads), s, kClCtas, p);
         return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
     }
-    return launch_two_pass_select(shape, p, shape->num_kv_heads, s) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    if (launch_score_hist(shape, p, shape->num_kv_heads, s) != cudaSuccess) return HA_ERR_LAUNCH;
+    if (plan_only) return HA_OK;
+    const SelectAttendParams sa = select_attend_params(shape, budget, w.plan, w.scores, w.partials, sel_idx, nullptr,
+                                                       nullptr, nullptr, page_table, seq_lens, budget_lens, 1.0f,
+                                                       nullptr, status, nullptr);
+    return launch_select_attend(shape, sa, shape->num_kv_heads * kGroup, false, s) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+}
+
+// The selection + attention stage on the plan and score bytes a scoring call left in the workspace.
+static int select_attend_impl(const ha_shape_t* shape, const ha_budget_t* budget, const void* q, const void* k_pages,
+                              const void* v_pages, const int32_t* page_table, const int32_t* seq_lens,
+                              const int32_t* budget_lens, int32_t* sel_idx, float sm_scale, void* out, void* workspace,
+                              size_t workspace_bytes, int32_t* status, void* stream, int32_t* status_out) {
+    int rc = check_shape(shape);
+    if (rc != HA_OK) return rc;
+    rc = check_budget(budget);
+    if (rc != HA_OK) return rc;
+    if (q == nullptr || k_pages == nullptr || v_pages == nullptr || page_table == nullptr || seq_lens == nullptr ||
+        sel_idx == nullptr || out == nullptr || status == nullptr || !std::isfinite(sm_scale))
+        return HA_ERR_BAD_ARG;
+    if (workspace == nullptr) return HA_ERR_WORKSPACE;
+    const Workspace w = carve(shape, budget, workspace);
+    if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
+    const SelectAttendParams sa = select_attend_params(shape, budget, w.plan, w.scores, w.partials, sel_idx, q, k_pages,
+                                                       v_pages, page_table, seq_lens, budget_lens, sm_scale, out,
+                                                       status, status_out);
+    return launch_select_attend(shape, sa, shape->num_kv_heads * kGroup, true, static_cast<cudaStream_t>(stream)) ==
+                   cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+}
+
+int ha_score_plan(const ha_shape_t* shape, const ha_budget_t* budget,
+                  const uint32_t* q_codes, const uint32_t* hash_pages,
+                  const int32_t* page_table, const int32_t* seq_lens, int32_t* sel_cnt,
+                  void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+    return score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, nullptr, nullptr, sel_cnt,
+                             nullptr, workspace, workspace_bytes, status, stream, true);
+}
+
+int ha_select_attend(const ha_shape_t* shape, const ha_budget_t* budget,
+                     const void* q, const void* k_pages, const void* v_pages,
+                     const int32_t* page_table, const int32_t* seq_lens,
+                     int32_t* sel_idx, float sm_scale, void* out,
+                     void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+    return select_attend_impl(shape, budget, q, k_pages, v_pages, page_table, seq_lens, nullptr, sel_idx, sm_scale, out,
+                              workspace, workspace_bytes, status, stream, nullptr);
 }
 
 int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -755,28 +787,24 @@ static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                               seq_lens, q_codes, nullptr, q_stage, status, stream);
     if (rc != HA_OK) return rc;
     const void* q_att = q_stage != nullptr ? q_stage : q;
-    if (use_stagger(shape)) {
-        rc = staggered_select_attend(shape, budget, q_att, k_pages, v_pages, hash_pages, page_table, seq_lens,
-                                     q_codes, sel_idx, sel_cnt, sm_scale, out, workspace, workspace_bytes, status,
-                                     static_cast<cudaStream_t>(stream), budget_lens);
-        if (rc == HA_OK && status_out != nullptr) {
-            // the step ended on several streams, all joined by now: a one-warp kernel stores the status word
-            // (cheaper than a copy operation between the last kernel and the end of the step)
-            publish_status_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, status_out);
-            if (cudaGetLastError() != cudaSuccess) return HA_ERR_LAUNCH;
-            if (status_delivered != nullptr) *status_delivered = true;
-        }
-        return rc;
+    if (!use_cluster_select(shape)) {
+        // scoring + plan, then selection + attention; the merge kernel, last of the step, also leaves the status
+        // word in status_out, if given
+        rc = score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, budget_lens, sel_idx, sel_cnt,
+                               nullptr, workspace, workspace_bytes, status, stream, true);
+        if (rc != HA_OK) return rc;
+        if (status_delivered != nullptr) *status_delivered = status_out != nullptr;
+        return select_attend_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, budget_lens, sel_idx,
+                                  sm_scale, out, workspace, workspace_bytes, status, stream, status_out);
     }
     rc = score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, budget_lens, sel_idx, sel_cnt,
                            nullptr, workspace, workspace_bytes, status, stream);
     if (rc != HA_OK) return rc;
-    // the selection kernel left the physical rows of the heavy tokens in the workspace; the step's last kernel
+    // the cluster selection left the physical rows of the heavy tokens in the workspace; the step's last kernel
     // also leaves the status word in status_out, if given
     if (status_delivered != nullptr) *status_delivered = status_out != nullptr;
     return sparse_decode_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, nullptr, sel_cnt, true,
-                              sm_scale, out, workspace, workspace_bytes, status, stream, 0, -1, 0, budget_lens,
-                              status_out);
+                              sm_scale, out, workspace, workspace_bytes, status, stream, budget_lens, status_out);
 }
 
 int ha_decode_step(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -808,11 +836,20 @@ int ha_decode_step_rows(const ha_shape_t* shape, const ha_budget_t* budget,
 
 int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget) {
     if (check_shape(shape) != HA_OK || check_budget(budget) != HA_OK) return 0;
-    const AttSplit as = att_split_launch(shape, budget);
-    const int merge = as.nsplits > 1 && !as.cluster ? 1 : 0;
-    if (use_cluster_select(shape)) return 3 + merge;  // encoder, cluster selection, gather (+ merge)
-    const int parts = use_stagger(shape) ? stagger_parts(shape) : 1;
-    return 1 + parts * (4 + merge);  // encoder; per part: histograms, plan, compaction, gather (+ merge)
+    if (use_cluster_select(shape)) {  // encoder, cluster selection, gather (+ merge)
+        const AttSplit as = att_split_launch(shape, budget);
+        return 3 + (as.nsplits > 1 && !as.cluster ? 1 : 0);
+    }
+    return 4;  // encoder, scoring + plan, selection + attention, merge
+}
+
+const char* ha_decode_step_path(const ha_shape_t* shape, const ha_budget_t* budget) {
+    if (check_shape(shape) != HA_OK || check_budget(budget) != HA_OK) return "invalid";
+    if (use_cluster_select(shape))
+        return att_split_launch(shape, budget).cluster
+            ? "hash_decode | score_select_cluster | sparse_gather (cluster)"
+            : "hash_decode | score_select_cluster | sparse_gather | sparse_merge";
+    return "hash_decode | score_hist | select_attend | select_attend_merge";
 }
 
 int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
@@ -896,25 +933,28 @@ void* g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_sc
 
 struct StaticScratch {
     uint32_t* hist;     // [B][Hkv][4*33][nchunks]
-    int32_t* sel_rows;  // [B][Hq][sel_stride]
     int32_t* plan;      // [B][Hkv][8 + 8 * nchunks]
-    uint32_t* scores;   // [B][Hkv][nchunks * chunk tokens]
-    size_t bytes;
+    uint8_t* scores;    // [B][Hq][nchunks * chunk tokens]
+    uint32_t* arrive;   // [B][Hkv]
+    size_t arrive_bytes, bytes;
 };
 
 StaticScratch carve_static(const ha_shape_t* s, void* base) {
-    const size_t n_hist = (size_t)s->batch * s->num_kv_heads * num_chunks_for(s->max_pages) * kGroup * kBins;
-    const size_t n_rows = (size_t)s->batch * s->num_kv_heads * kGroup * s->sel_stride;
+    const ha::Geometry g = ha::geometry(s);
+    const size_t units = (size_t)s->batch * s->num_kv_heads;
     char* p = static_cast<char*>(base);
     StaticScratch w;
-    w.hist = reinterpret_cast<uint32_t*>(p);
-    const size_t off = align_up(n_hist * sizeof(uint32_t));
-    w.sel_rows = reinterpret_cast<int32_t*>(p + off);
-    const size_t off2 = off + align_up(n_rows * sizeof(int32_t));
-    w.plan = reinterpret_cast<int32_t*>(p + off2);
-    const size_t off3 = off2 + align_up((size_t)s->batch * s->num_kv_heads * (8 + 8 * (size_t)num_chunks_for(s->max_pages)) * sizeof(int32_t));
-    w.scores = reinterpret_cast<uint32_t*>(p + off3);
-    w.bytes = off3 + align_up(ha::scores_bytes(s));
+    size_t off = 0;
+    w.hist = reinterpret_cast<uint32_t*>(p + off);
+    off += align_up(units * g.nchunks * kGroup * kBins * sizeof(uint32_t));
+    w.plan = reinterpret_cast<int32_t*>(p + off);
+    off += align_up(units * (8 + 8 * (size_t)g.nchunks) * sizeof(int32_t));
+    w.scores = reinterpret_cast<uint8_t*>(p + off);
+    off += align_up(ha::scores_bytes(s, g));
+    w.arrive = reinterpret_cast<uint32_t*>(p + off);
+    w.arrive_bytes = units * sizeof(uint32_t);
+    off += align_up(w.arrive_bytes);
+    w.bytes = off;
     return w;
 }
 
@@ -958,11 +998,18 @@ int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
     if (rc != HA_OK) return rc;
     const StaticScratch w = carve_static(shape, base);
 
-    // Every word of hist / plan / scores / sel_rows that a kernel reads was written earlier in the same
-    // call, so nothing left over from the previous call needs clearing.
+    // The arrival counters must be zero when the scoring kernel starts; the buffer keeps whatever the last call
+    // (possibly one of another shape, with the counters elsewhere) left, so they are cleared on the stream first.
+    // Every other word a kernel reads was written earlier in the same call.
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(w.arrive, 0, w.arrive_bytes, s) != cudaSuccess) return HA_ERR_LAUNCH;
     const SelectParams p = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
-                                         nullptr, status, w.hist, w.plan, w.scores, w.sel_rows);
-    return launch_two_pass_select(shape, p, shape->num_kv_heads, static_cast<cudaStream_t>(stream)) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+                                         nullptr, status, w.hist, w.plan, w.scores, w.arrive, nullptr);
+    if (launch_score_hist(shape, p, shape->num_kv_heads, s) != cudaSuccess) return HA_ERR_LAUNCH;
+    const SelectAttendParams sa = select_attend_params(shape, budget, w.plan, w.scores, nullptr, sel_idx, nullptr,
+                                                       nullptr, nullptr, page_table, seq_lens, nullptr, 1.0f, nullptr,
+                                                       status, nullptr);
+    return launch_select_attend(shape, sa, shape->num_kv_heads * kGroup, false, s) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
 }  // extern "C"

@@ -1,35 +1,38 @@
-// Hamming scoring and budget selection.
+// Hamming scoring and the selection plan.
 //
-// Pass A (score_hist_kernel) streams the key-hash pages once: one 16-byte word per token per
-// kv-head carries the codes of all 4 query heads of the group, so one coalesced pass scores
-// the 4 heads together; score = popcount(~(q_code ^ k_code)) in 0..32. Each CTA publishes a
-// 4 x 33 histogram of the scores of the candidate tokens of its chunk, stored bin-major
-// ([bin][chunk]) so that the counts of one bin over all chunks are one line, and the packed scores
-// of its tokens (4 bytes per token and kv-head: score + 1 per head, 0 = not a candidate).
+// score_hist_kernel streams the key-hash pages once: one 16-byte word per token per kv-head carries
+// the codes of all 4 query heads of the group, so one coalesced pass scores the 4 heads together;
+// score = popcount(~(q_code ^ k_code)) in 0..32. Each CTA publishes a 4 x 33 histogram of the scores
+// of the candidate tokens of its chunk, stored bin-major ([bin][chunk]) so that the counts of one bin
+// over all chunks are one line, and the scores of its tokens, one byte per token and query head
+// (score + 1, 0 = not a candidate), in one plane per head.
 //
-// A small kernel in between (select_plan_kernel, one CTA per (sequence, kv-head)) derives from the
-// chunk histograms the threshold T of each head, how many tokens tied at T still fit and how many
-// selected / tied tokens precede each chunk (pick_threshold: both selection rules of the reference).
+// The CTA that finishes last for a (sequence, kv-head) - an arrival counter, no waiting - derives from
+// the chunk histograms the plan of that unit (select_plan): the threshold T of each head, how many
+// tokens tied at T still fit, and how many selected / tied tokens precede each chunk (pick_threshold:
+// both selection rules of the reference).
 //
-// Pass B (select_kernel) reads the packed scores of its chunk (L2-resident by then), classifies
-// them against T and writes the selected token indices with a packed warp-scan compaction - no
-// sort, no atomics, nothing to reset. The list of a head is ordered by the token range of the
-// emitting warp (256 ROUNDS tokens); inside it by lane, i.e. not strictly ascending.
+// select_attend_kernel (select_attend.cuh) then classifies each chunk's score bytes against T, compacts
+// the selected tokens and attends them - no sort, no atomics in the output path.
 //
-// score_select_cluster_kernel does all of this in one kernel for short sequences.
+// score_select_cluster_kernel does scoring and selection in one kernel for short sequences.
 //
 // Together they replace the +-1 dot product of USA.forward and the sort/scatter (or threshold) of
 // compute_mask_multi (hashattention/hashattention_llama.py:171-187, 423-443).
 // A stable descending sort picks, among tokens tied at the threshold, the lowest indices;
-// the tie fill below reproduces exactly that set.
+// the tie fill reproduces exactly that set.
 //
-// Tiling of pass A: a CTA of 256 threads owns a chunk of 4 * ROUNDS pages of one (sequence,
+// Tiling of score_hist_kernel: a CTA of 256 threads owns a chunk of 4 * ROUNDS pages of one (sequence,
 // kv-head) and walks it in rounds of 1024 tokens; in a round warp w owns tokens [128 w, 128 w + 128)
 // (half a page), four per lane. Only four 16-byte loads are in flight per lane, so many CTAs fit on
 // an SM; the loads of a round are issued together without branches between them (indices are
 // clamped into range instead of guarded). Everything that does not depend on the preceding
 // kernel - the sequence length, page ids and the first round's hash words - is fetched before
-// the grid-dependency wait. Pass B: see select_kernel.
+// the grid-dependency wait.
+//
+// Layout of a score plane: inside every block of 128 tokens the byte of token 32 it + lane (the it-th
+// token of a lane in the warp's round) sits at offset 4 lane + it, so that a lane stores its four
+// tokens of one head as one 32-bit word and a warp 128 contiguous bytes per head.
 #pragma once
 
 #include <cooperative_groups.h>
@@ -40,6 +43,9 @@ namespace ha {
 
 namespace cg = cooperative_groups;
 
+#ifndef HA_SH_MIN_CTAS
+#define HA_SH_MIN_CTAS 4
+#endif
 constexpr int kRoundPages = 4;                        // pages per round
 constexpr int kRoundTokens = kRoundPages * kPage;     // 1024
 constexpr int kLaneTokens = kRoundTokens / kSelThreads;  // 4 tokens per lane and round
@@ -51,11 +57,12 @@ struct SelectParams {
     const int32_t* seq_lens;
     const int32_t* budget_lens;  // [B] or null: the length the heavy budget is a fraction of, if not seq_lens
     uint32_t* hist;            // workspace: [B][Hkv][4*33][nchunks]
+    uint32_t* arrive;          // workspace: [B][Hkv] chunks of the unit that have published their histogram (0 between calls)
     int32_t* sel_idx;          // [B][Hq][sel_stride] token indices
     int32_t* sel_rows;         // workspace: [B][Hq][sel_stride] page * 256 + slot of the same tokens
     int32_t* sel_cnt;          // [B][Hq]
     int32_t* plan;             // workspace: [B][Hkv][8 + 8 * nchunks]: T[4], need[4], then per chunk base[4], eqb[4]
-    uint32_t* scores;          // workspace: [B][Hkv][nchunks * chunk tokens]: byte g = score of head g + 1, 0 = not a candidate
+    uint8_t* scores;           // workspace: [B][Hq][nchunks * chunk tokens]: score + 1, 0 = not a candidate (layout above)
     uint8_t* scores_dbg;       // [B][Hq][max_pages*256] or null
     int32_t* status;
     int B, Hkv, max_pages, num_pages, sel_stride, nchunks;
@@ -81,9 +88,17 @@ struct RoundWords {
         return chunk_start + rd * kRoundTokens + warp * (kLaneTokens * 32);
     }
 
+    // page id (unchecked) of the page that holds token t0
+    static __device__ __forceinline__ int page_of(const SelectParams& p, int b, int t0) {
+        return __ldg(p.page_table + (size_t)b * p.max_pages + min(t0 / kPage, p.max_pages - 1));
+    }
+
     __device__ __forceinline__ void load(const SelectParams& p, int b, int kvh, int t0, int lane, const SeqRange& r) {
-        const int pidx = min(t0 / kPage, p.max_pages - 1);
-        const int pg = __ldg(p.page_table + (size_t)b * p.max_pages + pidx);
+        load(p, kvh, t0, lane, r, page_of(p, b, t0));
+    }
+
+    // pg: what page_of() returned for t0 (fetched ahead of time, so that the hash words are the only loads on the way)
+    __device__ __forceinline__ void load(const SelectParams& p, int kvh, int t0, int lane, const SeqRange& r, int pg) {
         const bool page_ok = pg >= 0 && pg < p.num_pages;
         page = page_ok ? pg : 0;
         const uint4* src = p.hash_pages + ((size_t)page * p.Hkv + kvh) * kPage;
@@ -188,122 +203,148 @@ __device__ __forceinline__ Threshold pick_threshold(const SelectParams& p, int n
     return t;
 }
 
-// The plan of one (sequence, kv-head), worked out by one CTA of 256 threads between the two passes.
-// From the per-chunk histograms it derives, once instead of in every CTA of pass B, the global
-// threshold T and the tie quota of each head, and for every chunk the number of selected tokens
-// and of tied tokens that precede it. The counts of 32 chunks at a time are staged
-// in shared memory ([head][bin][chunk], all 8 warps load: warp w the bins of head w % 4, lower or
-// upper half), then warp g works head g out with lane = chunk.
-constexpr int kPlanHalf = (kBins + 1) / 2;  // 17 bins per loading warp
+// The plan of one (sequence, kv-head), worked out by one CTA of 256 threads (the one that published the unit's
+// last histogram). From the per-chunk histograms it derives the global threshold T and the tie quota of each
+// head, and for every chunk the number of selected tokens and of tied tokens that precede it.
+// The counts of up to 64 chunks are staged in shared memory in one trip (33 independent loads per thread);
+// thread (head, bin) adds a row up, warp g picks head g's threshold from the 33 totals, thread (head, chunk)
+// counts what its chunk holds above and at the threshold, and a scan over the chunks gives the offsets.
+// Sequences of more than 64 chunks take two sweeps over blocks of 64 (totals first, then offsets).
+constexpr int kPlanChunks = 64;            // chunks staged at a time
+constexpr int kPlanPitch = kPlanChunks + 2;  // row pitch (16-bit words): rows start in different banks
+constexpr int kPlanRows = kGroup * kBins;    // 132 (head, bin) rows
+
+struct PlanSmem {
+    uint16_t stage[kPlanRows][kPlanPitch];  // a chunk holds at most 4096 tokens
+    int tot[kPlanRows];
+    int T[kGroup], need[kGroup];
+    int warp_gt[kSelWarps], warp_eq[kSelWarps];
+};
 
 __device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kvh, const SeqRange& r, int nchunks_b,
-                                            uint32_t (*stage)[kBins][32], int tid) {
-    const int lane = tid & 31, warp = tid >> 5, g = warp & 3;
+                                            PlanSmem& sm, int tid) {
+    const int lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
-    const uint32_t* hbase = p.hist + (((size_t)b * p.Hkv + kvh) * (kGroup * kBins) + g * kBins) * p.nchunks;
+    const uint32_t* hbase = p.hist + ((size_t)b * p.Hkv + kvh) * kPlanRows * p.nchunks;
     int32_t* plan = p.plan + ((size_t)b * p.Hkv + kvh) * (8 + 8 * p.nchunks);
-    auto stage_pass = [&](int cc0) {
-        const int s0 = (warp >> 2) * kPlanHalf, cc = cc0 + lane;
-        uint32_t v[kPlanHalf];
-#pragma unroll
-        for (int k = 0; k < kPlanHalf; ++k)
-            v[k] = cc < nchunks_b ? __ldcg(hbase + (size_t)min(s0 + k, kBins - 1) * p.nchunks + cc) : 0u;
-#pragma unroll
-        for (int k = 0; k < kPlanHalf; ++k)
-            if (s0 + k < kBins) stage[g][s0 + k][lane] = v[k];
-    };
-    const bool one_pass = nchunks_b <= 32;
+    // chunks staged at a time: 32 for sequences of up to 32 chunks (one batch of loads, half the adding up), else 64
+    const int pc_shift = nchunks_b <= 32 ? 5 : 6, pc = 1 << pc_shift;
+    constexpr int kPerThread = (kPlanRows * kPlanChunks + kSelThreads - 1) / kSelThreads;  // 33
+    constexpr int kBatch = (kPerThread + 1) / 2;  // independent loads per batch (33 values at once would spill)
 
-    // totals per bin over all chunks -> T and the tie quota (lane l holds bin 32 - l)
-    int tot_hi = 0, tot0 = 0;
-    for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
-        if (cc0 > 0) __syncthreads();
-        stage_pass(cc0);
-        __syncthreads();
-        if (warp < kGroup) {
-            tot0 += __reduce_add_sync(0xffffffffu, (int)stage[g][0][lane]);
-#pragma unroll 8
-            for (int s = 1; s < kBins; ++s) {
-                const int t = __reduce_add_sync(0xffffffffu, (int)stage[g][s][lane]);
-                if (lane == 32 - s) tot_hi += t;
+    // counts of chunks [c0, c0 + pc) -> sm.stage; element e = row * pc + chunk, thread t takes e = t + 256 i
+    auto stage_block = [&](int c0) {
+#pragma unroll
+        for (int h0 = 0; h0 < kPerThread; h0 += kBatch) {
+            if (h0 * kSelThreads >= kPlanRows * pc) break;
+            uint32_t v[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const int e = tid + (h0 + i) * kSelThreads, row = e >> pc_shift, cc = c0 + (e & (pc - 1));
+                v[i] = (row < kPlanRows && cc < nchunks_b) ? __ldcg(hbase + (size_t)row * p.nchunks + cc) : 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+                const int e = tid + (h0 + i) * kSelThreads, row = e >> pc_shift;
+                if (row < kPlanRows) sm.stage[row][e & (pc - 1)] = (uint16_t)v[i];
             }
         }
+    };
+    auto row_total = [&] {
+        int t = 0;
+        if (tid < kPlanRows) {
+#pragma unroll 16
+            for (int c = 0; c < pc; ++c) t += sm.stage[tid][c];
+        }
+        return t;
+    };
+
+    // ---- totals per (head, bin) over all chunks
+    int tot = 0;
+    for (int c0 = 0; c0 < nchunks_b; c0 += pc) {
+        if (c0 > 0) __syncthreads();
+        stage_block(c0);
+        __syncthreads();
+        tot += row_total();
     }
-    int T = kBins, need = 0;
+    if (tid < kPlanRows) sm.tot[tid] = tot;
+    __syncthreads();
+
+    // ---- T and the tie quota: warp g for head g, lane l holds bin 32 - l
     if (warp < kGroup) {
-        int cum = tot_hi;
+        const int g = warp;
+        const int n = sm.tot[g * kBins + 32 - lane];
+        int cum = n;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const int u = __shfl_up_sync(0xffffffffu, cum, d);
             if (lane >= d) cum += u;
         }
         bool overflow;
-        const Threshold th = pick_threshold(p, tot_hi, cum, tot0, r.hb, overflow);
-        T = th.T;
-        need = th.need;
+        const Threshold th = pick_threshold(p, n, cum, sm.tot[g * kBins], r.hb, overflow);
         if (lane == 0) {
             if (overflow) report(p.status, HA_ERR_SEL_OVERFLOW);
-            plan[g] = T;
-            plan[4 + g] = need;
+            sm.T[g] = th.T;
+            sm.need[g] = th.need;
+            plan[g] = th.T;
+            plan[4 + g] = th.need;
             p.sel_cnt[(size_t)b * Hq + kvh * kGroup + g] = th.count;
         }
     }
+    __syncthreads();
 
-    // per chunk: tokens above T and tokens at T, then exclusive prefixes over the chunks
+    // ---- per chunk: tokens above T and tokens at T, then exclusive prefixes over the chunks.
+    //      thread = (head g, chunk cl of the block): 4 x pc threads, a head's chunks are pc / 32 warps
+    const int g = (tid >> pc_shift) & (kGroup - 1), cl = tid & (pc - 1);
+    const bool works = tid < kGroup * pc;  // warp-uniform
+    const int T = sm.T[g], need = sm.need[g];
+    const int wpg = pc >> 5;  // warps per head: 1 or 2
     int gt_carry = 0, eq_carry = 0;
-    for (int cc0 = 0; cc0 < nchunks_b; cc0 += 32) {
-        if (!one_pass) {  // otherwise the counts of the only pass are still staged
+    for (int c0 = 0; c0 < nchunks_b; c0 += pc) {
+        if (nchunks_b > pc) {  // otherwise the counts of the only block are still staged
             __syncthreads();
-            stage_pass(cc0);
+            stage_block(c0);
             __syncthreads();
         }
-        if (warp < kGroup) {
-            const int cc = cc0 + lane;
-            int gt = 0, eq = 0;
-#pragma unroll 8
-            for (int s = 0; s < kBins; ++s) {
-                const int v = (int)stage[g][s][lane];
-                gt += s > T ? v : 0;
-                eq += s == T ? v : 0;
-            }
-            int pg = gt, pe = eq;
+        int gt = 0, eq = 0;
+        if (works) {
+#pragma unroll 11
+            for (int sbin = 0; sbin < kBins; ++sbin) gt += sbin > T ? (int)sm.stage[g * kBins + sbin][cl] : 0;
+            eq = T < kBins ? (int)sm.stage[g * kBins + T][cl] : 0;
+        }
+        int pg = gt, pe = eq;
 #pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const int u0 = __shfl_up_sync(0xffffffffu, pg, d), u1 = __shfl_up_sync(0xffffffffu, pe, d);
-                if (lane >= d) {
-                    pg += u0;
-                    pe += u1;
-                }
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u0 = __shfl_up_sync(0xffffffffu, pg, d), u1 = __shfl_up_sync(0xffffffffu, pe, d);
+            if (lane >= d) {
+                pg += u0;
+                pe += u1;
             }
-            const int gt_before = gt_carry + pg - gt, eq_before = eq_carry + pe - eq;
+        }
+        if (lane == 31) {
+            sm.warp_gt[warp] = pg;
+            sm.warp_eq[warp] = pe;
+        }
+        __syncthreads();
+        if (works) {
+            // with two warps per head the upper one adds the lower one's total
+            const int w0 = g * wpg;
+            const bool upper = wpg == 2 && warp == w0 + 1;
+            const int gt_before = gt_carry + (upper ? sm.warp_gt[w0] : 0) + pg - gt;
+            const int eq_before = eq_carry + (upper ? sm.warp_eq[w0] : 0) + pe - eq;
+            const int cc = c0 + cl;
             if (cc < nchunks_b) {
                 plan[8 + 8 * cc + g] = gt_before + min(eq_before, need);
                 plan[8 + 8 * cc + 4 + g] = eq_before;
             }
-            gt_carry += __shfl_sync(0xffffffffu, pg, 31);
-            eq_carry += __shfl_sync(0xffffffffu, pe, 31);
+            gt_carry += sm.warp_gt[w0] + (wpg == 2 ? sm.warp_gt[w0 + 1] : 0);
+            eq_carry += sm.warp_eq[w0] + (wpg == 2 ? sm.warp_eq[w0 + 1] : 0);
         }
     }
 }
 
-__global__ void __launch_bounds__(kSelThreads) select_plan_kernel(const SelectParams p, int chunk_tokens) {
-    HA_TL(kTlSelectPlan, kTlEntry);
-    __shared__ uint32_t s_stage[kGroup][kBins][32];
-    const int kvh = p.kvh0 + blockIdx.x, b = blockIdx.y;
-    const int S = p.seq_lens[b];
-    const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
-    const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget,
-                                 p.budget_lens != nullptr ? p.budget_lens[b] : -1);
-    pdl_wait();
-    HA_TL(kTlSelectPlan, kTlAfterWait);
-    pdl_launch_dependents();
-    if (!s_ok) return;
-    select_plan(p, b, kvh, r, (r.S + chunk_tokens - 1) / chunk_tokens, s_stage, threadIdx.x);
-    HA_TL(kTlSelectPlan, kTlExit);
-}
-
 template <int ROUNDS>
-__global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(kSelThreads, HA_SH_MIN_CTAS) score_hist_kernel(const SelectParams p) {
     HA_TL(kTlScoreHist, kTlEntry);
     const int c = blockIdx.x, kvh = p.kvh0 + blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -311,6 +352,8 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     constexpr int chunk_tokens = ROUNDS * kRoundTokens;
 
     __shared__ uint32_t s_hist[kSelWarps][kGroup * kBins];
+    __shared__ PlanSmem s_plan;  // the plan's staging area (last CTA of the unit only)
+    __shared__ int s_last;
     for (int i = tid; i < kSelWarps * kGroup * kBins; i += kSelThreads) (&s_hist[0][0])[i] = 0;
 
     const int S = p.seq_lens[b];
@@ -319,8 +362,16 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     const bool active = s_ok && chunk_start < S;
     const SeqRange r = seq_range(s_ok ? S : 1, p.init_budget, p.recent_budget, p.heavy_budget,
                                  p.budget_lens != nullptr ? p.budget_lens[b] : -1);
-    RoundWords rw;
-    if (active) rw.load(p, b, kvh, RoundWords::first_token(chunk_start, 0, warp), lane, r);
+    // two rounds of hash words are kept in flight: while one is scored the next is on its way
+    RoundWords rw[2];
+    int pgs[ROUNDS];  // page ids of this warp's half pages, all requested up front
+    if (active) {
+#pragma unroll
+        for (int rd = 0; rd < ROUNDS; ++rd) pgs[rd] = RoundWords::page_of(p, b, RoundWords::first_token(chunk_start, rd, warp));
+        rw[0].load(p, kvh, RoundWords::first_token(chunk_start, 0, warp), lane, r, pgs[0]);
+        if (ROUNDS > 1 && chunk_start + kRoundTokens < S)
+            rw[1].load(p, kvh, RoundWords::first_token(chunk_start, 1, warp), lane, r, pgs[1]);
+    }
 
     pdl_wait();
     HA_TL(kTlScoreHist, kTlAfterWait);
@@ -335,39 +386,48 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
     __syncthreads();  // s_hist is zero
 
     uint32_t* h0 = &s_hist[warp][0];
-    uint32_t* srow = p.scores + ((size_t)b * p.Hkv + kvh) * ((size_t)p.nchunks * chunk_tokens);
+    const size_t pitch = (size_t)p.nchunks * chunk_tokens;
+    uint8_t* plane0 = p.scores + ((size_t)b * Hq + kvh * kGroup) * pitch;
     bool bad_page = false;
-#pragma unroll 1
+#pragma unroll
     for (int rd = 0; rd < ROUNDS; ++rd) {
+        if (chunk_start + rd * kRoundTokens >= S) break;
+        RoundWords& cur = rw[rd & 1];
         const int t0 = RoundWords::first_token(chunk_start, rd, warp);
-        if (rd > 0) {
-            if (chunk_start + rd * kRoundTokens >= S) break;
-            rw.load(p, b, kvh, t0, lane, r);
-        }
-        rw.refresh_newest(p, kvh, t0, lane, r);
-        bad_page |= rw.bad_page;
+        cur.refresh_newest(p, kvh, t0, lane, r);
+        bad_page |= cur.bad_page;
+        uint32_t plane[kGroup] = {0u, 0u, 0u, 0u};  // per head: byte it = score + 1 of this lane's it-th token
 #pragma unroll
         for (int it = 0; it < kLaneTokens; ++it) {
-            const uint32_t s0 = __popc(qn.x ^ rw.w[it].x), s1 = __popc(qn.y ^ rw.w[it].y);
-            const uint32_t s2 = __popc(qn.z ^ rw.w[it].z), s3 = __popc(qn.w ^ rw.w[it].w);
-            const bool is_cand = rw.interior || ((rw.cand >> it) & 1u);
+            const uint32_t s0 = __popc(qn.x ^ cur.w[it].x), s1 = __popc(qn.y ^ cur.w[it].y);
+            const uint32_t s2 = __popc(qn.z ^ cur.w[it].z), s3 = __popc(qn.w ^ cur.w[it].w);
+            const bool is_cand = cur.interior || ((cur.cand >> it) & 1u);
             if (is_cand) {
                 atomicAdd(h0 + s0, 1u);
                 atomicAdd(h0 + kBins + s1, 1u);
                 atomicAdd(h0 + 2 * kBins + s2, 1u);
                 atomicAdd(h0 + 3 * kBins + s3, 1u);
+                plane[0] |= (s0 + 1u) << (8 * it);
+                plane[1] |= (s1 + 1u) << (8 * it);
+                plane[2] |= (s2 + 1u) << (8 * it);
+                plane[3] |= (s3 + 1u) << (8 * it);
             }
-            // pass B works from these 4 bytes per token instead of the 16-byte hash word
-            srow[t0 + it * 32 + lane] = is_cand ? (s0 | (s1 << 8) | (s2 << 16) | (s3 << 24)) + 0x01010101u : 0u;
-            if (p.scores_dbg != nullptr && ((rw.valid >> it) & 1u)) {
-                const size_t pitch = (size_t)p.max_pages * kPage;
-                uint8_t* d = p.scores_dbg + ((size_t)b * Hq + kvh * kGroup) * pitch + t0 + it * 32 + lane;
+            if (p.scores_dbg != nullptr && ((cur.valid >> it) & 1u)) {
+                const size_t dpitch = (size_t)p.max_pages * kPage;
+                uint8_t* d = p.scores_dbg + ((size_t)b * Hq + kvh * kGroup) * dpitch + t0 + it * 32 + lane;
                 d[0] = (uint8_t)s0;
-                d[pitch] = (uint8_t)s1;
-                d[2 * pitch] = (uint8_t)s2;
-                d[3 * pitch] = (uint8_t)s3;
+                d[dpitch] = (uint8_t)s1;
+                d[2 * dpitch] = (uint8_t)s2;
+                d[3 * dpitch] = (uint8_t)s3;
             }
         }
+        // the round after next takes this round's registers
+        if (rd + 2 < ROUNDS && chunk_start + (rd + 2) * kRoundTokens < S)
+            cur.load(p, kvh, RoundWords::first_token(chunk_start, rd + 2, warp), lane, r, pgs[rd + 2 < ROUNDS ? rd + 2 : 0]);
+        // the selection works from these bytes instead of the 16-byte hash words
+#pragma unroll
+        for (int g = 0; g < kGroup; ++g)
+            *reinterpret_cast<uint32_t*>(plane0 + g * pitch + t0 + lane * 4) = plane[g];
     }
     if (bad_page) report(p.status, HA_ERR_BAD_PAGE);
     __syncthreads();
@@ -376,230 +436,29 @@ __global__ void __launch_bounds__(kSelThreads) score_hist_kernel(const SelectPar
 #pragma unroll
         for (int w = 0; w < kSelWarps; ++w) v += s_hist[w][tid];
         p.hist[(((size_t)b * p.Hkv + kvh) * (kGroup * kBins) + tid) * p.nchunks + c] = v;
+        __threadfence();  // the histogram is visible device-wide before this CTA counts itself in
     }
+
+    HA_TL(kTlScoreHist, kTlMarkA);
+    // ---- the CTA that publishes last for this (sequence, kv-head) works the unit's plan out. Nobody waits:
+    //      every CTA makes its histogram visible, then counts itself in; the one that finds all the others
+    //      counted reads their histograms and leaves the counter at zero for the next call.
+    __syncthreads();
+    const int nchunks_b = (S + chunk_tokens - 1) / chunk_tokens;
+    if (tid == 0) {
+        uint32_t* counter = p.arrive + (size_t)b * p.Hkv + kvh;
+        const uint32_t before = atomicAdd(counter, 1u);
+        s_last = before + 1u == (uint32_t)nchunks_b;
+        if (s_last) *counter = 0u;
+    }
+    __syncthreads();
+    HA_TL(kTlScoreHist, kTlMarkB);
+    if (!s_last) return;
+    __threadfence();
+    HA_TL(kTlSelectPlan, kTlEntry);
+    select_plan(p, b, kvh, r, nchunks_b, s_plan, tid);
+    HA_TL(kTlSelectPlan, kTlExit);
     HA_TL(kTlScoreHist, kTlExit);
-}
-
-// Pass B. A CTA of 128 threads owns the chunk of pass A; warp w owns the 256 ROUNDS contiguous
-// tokens [chunk_start + 256 ROUNDS w, ...), lane l the tokens 128 j + 4 l + k of it (j = 0 ..
-// 2 ROUNDS - 1 one 16-byte load each, k = 0..3 its components), 8 ROUNDS tokens in all, numbered
-// n = 4 j + k in ascending token order.
-constexpr int kSelBThreads = 128;
-constexpr int kSelBWarps = kSelBThreads / 32;
-
-// byte g of each of the NW words, gathered into one word (byte w of the result = byte g of a[w])
-template <int NW>
-__device__ __forceinline__ uint32_t gather_byte(const uint32_t (&a)[NW], int g) {
-    if constexpr (NW == 4) {
-        const uint32_t sel = 0x0040u + 0x11u * g;  // bytes g of x (index g) and of y (index 4 + g)
-        return __byte_perm(__byte_perm(a[0], a[1], sel), __byte_perm(a[2], a[3], sel), 0x5410u);
-    } else if constexpr (NW == 2) {
-        return __byte_perm(a[0], a[1], 0x4440u + 0x11u * g) & 0xffffu;
-    } else {
-        return (a[0] >> (8 * g)) & 0xffu;
-    }
-}
-
-template <int ROUNDS>
-__global__ void __launch_bounds__(kSelBThreads, 8) select_kernel(const SelectParams p) {
-    HA_TL(kTlSelect, kTlEntry);
-    const int c = blockIdx.x, kvh = p.kvh0 + blockIdx.y, b = blockIdx.z;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int Hq = p.Hkv * kGroup;
-    constexpr int chunk_tokens = ROUNDS * kRoundTokens;
-    constexpr int kWarpTokens = chunk_tokens / kSelBWarps;  // 256 ROUNDS
-    constexpr int kLoads = kWarpTokens / 128;                // 2 ROUNDS 16-byte loads per lane
-    constexpr int kWords = ROUNDS;                           // flag words: 8 tokens x 4 heads each
-    __shared__ int s_plan[16];  // T[4], need[4], base[4], eqb[4]
-    __shared__ uint32_t s_wg[kSelBWarps][2], s_we[kSelBWarps][2];  // per warp: counts of heads (0,1) / (2,3), 16 bits each
-
-    // --- before the dependency wait: the sequence length, the page ids of this warp's tokens
-    //     (ROUNDS pages) and its packed scores
-    const int S = p.seq_lens[b];
-    const bool s_ok = S >= 1 && S <= p.max_pages * kPage;  // a bad length was reported by pass A
-    const int chunk_start = c * chunk_tokens;
-    const bool active = s_ok && chunk_start < S;
-    const int wbase = chunk_start + warp * kWarpTokens;
-    int pg[ROUNDS];
-    {
-        const int32_t* pt = p.page_table + (size_t)b * p.max_pages;
-#pragma unroll
-        for (int i = 0; i < ROUNDS; ++i) {
-            const int v = __ldg(pt + min(wbase / kPage + i, p.max_pages - 1));
-            pg[i] = v >= 0 && v < p.num_pages ? v : 0;  // tokens of a bad page are no candidates: never emitted
-        }
-    }
-
-    // this warp's packed scores. They were written by score_hist, two kernels ahead in the stream:
-    // select_plan, the kernel directly in front, could only pass its dependency wait after score_hist
-    // had completed, and this kernel's CTAs start after that. Pass A wrote whole rounds of 1024
-    // tokens up to the one that contains S - 1.
-    uint4 sc[kLoads];
-    {
-        const uint32_t* srow = p.scores + ((size_t)b * p.Hkv + kvh) * ((size_t)p.nchunks * chunk_tokens);
-        const int written_end = s_ok ? (S + kRoundTokens - 1) / kRoundTokens * kRoundTokens : 0;
-        // loaded whatever S is (always inside the buffer), so that the loads do not wait for seq_lens
-#pragma unroll
-        for (int j = 0; j < kLoads; ++j) sc[j] = __ldcg(reinterpret_cast<const uint4*>(srow + wbase + j * 128 + lane * 4));
-#pragma unroll
-        for (int j = 0; j < kLoads; ++j)
-            if (wbase + j * 128 + lane * 4 >= written_end) sc[j] = make_uint4(0u, 0u, 0u, 0u);  // stale words of an earlier call
-    }
-
-    pdl_wait();
-    HA_TL(kTlSelect, kTlAfterWait);
-    pdl_launch_dependents();
-    if (!active) return;
-
-    // --- the plan of this (sequence, kv-head): thresholds, tie quotas, and for this chunk where its
-    //     output starts and how many tied tokens precede it
-    if (tid < 16) {
-        const int32_t* plan = p.plan + ((size_t)b * p.Hkv + kvh) * (8 + 8 * p.nchunks);
-        s_plan[tid] = __ldcg(plan + (tid < 8 ? tid : 8 + 8 * c + (tid - 8)));
-    }
-    __syncthreads();
-    HA_TL(kTlSelect, kTlMarkB);
-    const int* s_T = s_plan;
-    const int* s_need = s_plan + 4;
-    const int* s_base = s_plan + 8;
-    const int* s_eqb = s_plan + 12;
-
-    // --- classify: stored bytes are score + 1 (0 for a token that is no candidate) and are compared
-    //     with T + 1 >= 1, so non-candidates never match. a + (127 - T') carries into bit 7 of a byte
-    //     iff a > T', a + (128 - T') iff a >= T' (bytes <= 33: no carry between bytes). Flag words: bit
-    //     8 g + (n & 7) of word n / 8 for token n of this lane and head g.
-    const uint32_t t4 = ((uint32_t)s_T[0] | ((uint32_t)s_T[1] << 8) | ((uint32_t)s_T[2] << 16) | ((uint32_t)s_T[3] << 24)) + 0x01010101u;
-    const uint32_t gt_add = 0x7F7F7F7Fu - t4, ge_add = 0x80808080u - t4;
-    uint32_t gtw[kWords], gew[kWords];
-#pragma unroll
-    for (int i = 0; i < kWords; ++i) gtw[i] = gew[i] = 0;
-#pragma unroll
-    for (int j = 0; j < kLoads; ++j) {
-        const uint32_t a[4] = {sc[j].x, sc[j].y, sc[j].z, sc[j].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int pos = (j & 1) * 4 + k;
-            gtw[j >> 1] |= ((a[k] + gt_add) >> (7 - pos)) & (0x01010101u << pos);
-            gew[j >> 1] |= ((a[k] + ge_add) >> (7 - pos)) & (0x01010101u << pos);
-        }
-    }
-    // per head: bit n = token n of this lane
-    uint32_t gt[kGroup], eq[kGroup];
-#pragma unroll
-    for (int g = 0; g < kGroup; ++g) {
-        gt[g] = gather_byte<kWords>(gtw, g);
-        eq[g] = gather_byte<kWords>(gew, g) & ~gt[g];
-    }
-    {
-        uint32_t g01 = __popc(gt[0]) | (__popc(gt[1]) << 16), g23 = __popc(gt[2]) | (__popc(gt[3]) << 16);
-        uint32_t e01 = __popc(eq[0]) | (__popc(eq[1]) << 16), e23 = __popc(eq[2]) | (__popc(eq[3]) << 16);
-        g01 = __reduce_add_sync(0xffffffffu, g01);  // a warp holds up to 1024 tokens: 16-bit fields do not overflow
-        g23 = __reduce_add_sync(0xffffffffu, g23);
-        e01 = __reduce_add_sync(0xffffffffu, e01);
-        e23 = __reduce_add_sync(0xffffffffu, e23);
-        if (lane == 0) {
-            s_wg[warp][0] = g01; s_wg[warp][1] = g23;
-            s_we[warp][0] = e01; s_we[warp][1] = e23;
-        }
-    }
-    __syncthreads();
-    HA_TL(kTlSelect, kTlMarkC);
-
-    // --- where this warp's output starts and how it treats ties, per head (lane g works head g out):
-    //     0 = takes no tied token, 1 = takes all, 2 = the tie quota ends inside this warp's tokens
-    int my_base = 0, my_eqb = 0, my_mode = 0;
-    {
-        const int g = lane & 3;
-        int gt_b = 0, eq_b = 0;
-#pragma unroll
-        for (int w = 0; w < kSelBWarps - 1; ++w) {
-            const int cg = (int)((s_wg[w][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
-            const int ce = (int)((s_we[w][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
-            gt_b += w < warp ? cg : 0;
-            eq_b += w < warp ? ce : 0;
-        }
-        const int eq_in = (int)((s_we[warp][g >> 1] >> ((g & 1) * 16)) & 0xffffu);
-        const int need = s_need[g];
-        my_eqb = s_eqb[g] + eq_b;
-        my_base = s_base[g] + gt_b + (min(my_eqb, need) - min(s_eqb[g], need));
-        my_mode = my_eqb + eq_in <= need ? 1 : (my_eqb < need ? 2 : 0);
-    }
-    if ((s_wg[warp][0] | s_wg[warp][1] | s_we[warp][0] | s_we[warp][1]) == 0) return;  // nothing of any head here
-
-    // --- per head: the selected tokens of this lane, their positions from a packed warp scan, emission
-    uint32_t sel[kGroup];
-    uint32_t cnt01 = 0, cnt23 = 0;
-    int base_pos[kGroup];
-#pragma unroll
-    for (int g = 0; g < kGroup; ++g) {
-        base_pos[g] = __shfl_sync(0xffffffffu, my_base, g);
-        const int mode = __shfl_sync(0xffffffffu, my_mode, g);
-        sel[g] = gt[g] | (mode == 1 ? eq[g] : 0u);
-        if (mode == 2) {  // warp-uniform, at most once per (sequence, head): rank the tied tokens by token index
-            const uint32_t lt_mask = (1u << lane) - 1u;
-            int eq_run = __shfl_sync(0xffffffffu, my_eqb, g);
-            const int need = s_need[g];
-#pragma unroll
-            for (int j = 0; j < kLoads; ++j) {
-                // token order inside a block of 128 tokens is (lane, k): ties in lower lanes come first
-                const uint32_t nib = (eq[g] >> (4 * j)) & 0xFu;
-                int before = 0, total = 0;
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const uint32_t m_eq = __ballot_sync(0xffffffffu, (nib >> k) & 1u);
-                    before += __popc(m_eq & lt_mask);
-                    total += __popc(m_eq);
-                }
-                int own = 0;
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-                    if ((nib >> k) & 1u) {
-                        if (eq_run + before + own < need) sel[g] |= 1u << (4 * j + k);
-                        ++own;
-                    }
-                eq_run += total;
-            }
-        }
-        if (g < 2) cnt01 |= __popc(sel[g]) << (16 * g);
-        else cnt23 |= __popc(sel[g]) << (16 * (g - 2));
-    }
-    uint32_t ex01 = cnt01, ex23 = cnt23;  // exclusive prefix over lanes of the per-head counts
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const uint32_t u0 = __shfl_up_sync(0xffffffffu, ex01, d), u1 = __shfl_up_sync(0xffffffffu, ex23, d);
-        if (lane >= d) {
-            ex01 += u0;
-            ex23 += u1;
-        }
-    }
-    ex01 -= cnt01;
-    ex23 -= cnt23;
-    const int pos0[kGroup] = {base_pos[0] + (int)(ex01 & 0xffffu), base_pos[1] + (int)(ex01 >> 16),
-                              base_pos[2] + (int)(ex23 & 0xffffu), base_pos[3] + (int)(ex23 >> 16)};
-    // order inside a warp's piece of a head's list is lane-major; a lane visits only its selected tokens
-    const int tok0 = wbase + lane * 4;          // token n of this lane = tok0 + 128 (n / 4) + n % 4
-    const int slot0 = (lane * 4) & (kPage - 1);  // wbase is page aligned
-#pragma unroll
-    for (int g = 0; g < kGroup; ++g) {
-        uint32_t m = sel[g];
-        int o = pos0[g];
-        int32_t* idx = p.sel_idx + ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride;
-        int32_t* rows = p.sel_rows + ((size_t)b * Hq + kvh * kGroup + g) * p.sel_stride;
-        while (m != 0) {
-            const int n = __ffs(m) - 1;
-            m &= m - 1;
-            const int off = (n >> 2) * 128 + (n & 3);  // offset inside the warp's tokens, minus 4 lane
-            int page = pg[0];
-#pragma unroll
-            for (int i = 1; i < ROUNDS; ++i) page = (n >> 3) == i ? pg[i] : page;
-            if (o < p.sel_stride) {
-                idx[o] = tok0 + off;
-                rows[o] = page * kPage + ((slot0 + off) & (kPage - 1));
-            }
-            ++o;
-        }
-    }
-    HA_TL(kTlSelect, kTlExit);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -62,12 +62,6 @@ __device__ __forceinline__ void publish_status(const SparseDecodeParams& p) {
         *p.status_out = __ldcg(p.status);
 }
 
-// The same for a step that ends on several streams: launched (without the programmatic-launch attribute) on the
-// caller's stream after the other streams have been joined, so everything the step launched has completed.
-__global__ void publish_status_kernel(const int32_t* status, int32_t* status_out) {
-    if (threadIdx.x == 0) *status_out = __ldcg(status);
-}
-
 __device__ __forceinline__ void unpack8(const uint4& raw, float (&x)[8]) {
     x[0] = bf16_lo(raw.x); x[1] = bf16_hi(raw.x);
     x[2] = bf16_lo(raw.y); x[3] = bf16_hi(raw.y);

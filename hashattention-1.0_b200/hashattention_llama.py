@@ -23,6 +23,15 @@ What runs where
     (sequence, new token); needs ``recent_budget >= q_len - 1``.
   * Training (``train_usa``) and statistics (``collect_stats``) are not implemented and raise
     ``NotImplementedError``.
+  * Padded batches: the paged cache stores whole sequences from token 0, so an ``attention_mask`` that
+    hides keys (left- or right-padding of a batch of prompts) is refused with ``NotImplementedError``
+    at prefill instead of silently attending the pad tokens (the reference adds the mask to the
+    attention weights, :593-603). Decode one sequence, or equal-length prompts, per batch.
+
+Memory: this module keeps its own paged copy of the layer's K / V (bf16, 512 B per token and kv-head) next to
+the caller's cache object, sized for the prompt plus ``config.usa_decode_headroom`` new tokens (default 4096)
+and never beyond ``config.usa_max_seq_len`` (default ``max_position_embeddings``). The number of cached tokens
+is tracked on the host; a step that would not fit raises ``ValueError`` before anything is launched.
 """
 from __future__ import annotations
 
@@ -97,10 +106,13 @@ class LlamaAttention_heavy_hitter(nn.Module):
         self.collect_stats = False
         self.train_usa = False
         self.flash_forward = None  # the replaced module's forward, used for prefill
-        # longest sequence the paged cache is sized for; set config.usa_max_seq_len to change it
+        # longest sequence the paged cache may be sized for; set config.usa_max_seq_len to change it
         self.max_seq_len = int(getattr(config, "usa_max_seq_len", self.max_position_embeddings))
+        # tokens of room the cache gets beyond the prompt it was created for
+        self.decode_headroom = int(getattr(config, "usa_decode_headroom", 4096))
         self._ctx: Optional[SparseDecodeContext] = None
-        self._row_ctx: dict = {}  # (id of the decode context, q_len) -> context over ChunkRows
+        self._cached_tokens = 0  # host-side copy of the cache's sequence length (all sequences advance together)
+        self._steps_since_status_check = 0
 
     def __repr__(self):
         return (f"{super().__repr__()}\nSparsification Setting(topk:{self.heavy_budget}  edge:{self.init_budget, self.recent_budget} \n"
@@ -110,38 +122,60 @@ class LlamaAttention_heavy_hitter(nn.Module):
     # hash pages of the paged cache
     def _reset_state(self):
         if self._ctx is not None:
+            self._ctx.check_status()  # a problem a kernel reported since the last check surfaces here at the latest
             self._ctx.cache.reset()
+        self._cached_tokens = 0
 
-    def _context(self, batch: int, device) -> SparseDecodeContext:
-        if self._ctx is None or self._ctx.batch != batch or self._ctx.device != device:
+    def _context(self, batch: int, device, need_tokens: int = 0) -> SparseDecodeContext:
+        """The decode context for ``batch`` sequences; (re)built when the batch, the device or the room
+        needed (``need_tokens``, at prefill) changes."""
+        ctx = self._ctx
+        if ctx is None or ctx.batch != batch or ctx.device != device or need_tokens > ctx.cache.max_pages * PAGE:
             if self.usa_module is None:
                 raise RuntimeError("no usa_module attached: build the model with convert_usa")
-            cache = PagedHashKVCache(batch, self.num_key_value_heads, self.max_seq_len, device)
+            capacity = min(self.max_seq_len, max(need_tokens, 1) + self.decode_headroom) if need_tokens else self.max_seq_len
+            cache = PagedHashKVCache(batch, self.num_key_value_heads, capacity, device)
             budget = Budget(self.init_budget, self.heavy_budget, self.recent_budget,
                             "simple" if self.usa_eval_mode == "simple" else "depth", int(self.usa_retrieve_depth))
-            self._ctx = SparseDecodeContext(cache, budget, self.usa_module.packed(device))
-        return self._ctx
+            self._ctx = ctx = SparseDecodeContext(cache, budget, self.usa_module.packed(device))
+            ctx.row_contexts = {}  # q_len -> context over ChunkRows of this cache; dies with the context
+            self._cached_tokens = 0
+        return ctx
 
     def _rows_context(self, ctx: SparseDecodeContext, q_len: int) -> SparseDecodeContext:
         """The context of a multi-token step of ``q_len`` tokens per sequence: rows over the same cache."""
-        key = (id(ctx), q_len)
-        if key not in self._row_ctx:
-            self._row_ctx = {k: v for k, v in self._row_ctx.items() if k[0] == id(ctx)}  # drop rows of an old cache
-            self._row_ctx[key] = SparseDecodeContext(ChunkRows(ctx.cache, q_len), ctx.budget, ctx.weights)
-        return self._row_ctx[key]
+        if q_len not in ctx.row_contexts:
+            ctx.row_contexts[q_len] = SparseDecodeContext(ChunkRows(ctx.cache, q_len), ctx.budget, ctx.weights)
+        return ctx.row_contexts[q_len]
+
+    @staticmethod
+    def _hides_keys(attention_mask) -> bool:
+        """Whether the mask hides a key from the last query (padding), in the forms a decoder passes:
+        [B, S] of 0 / 1, or [B, 1, q, S] either boolean (True = visible) or additive (0 = visible)."""
+        if attention_mask is None:
+            return False
+        if attention_mask.dim() == 2:
+            return bool((attention_mask == 0).any())
+        last = attention_mask[..., -1, :]
+        return bool((~last).any()) if last.dtype == torch.bool else bool((last != 0).any())
 
     def _prefill(self, hidden_states, past, kwargs, new_style):
         if self.flash_forward is None:
             raise RuntimeError("prefill needs the original attention forward (set by convert_usa)")
+        if hidden_states.shape[0] > 1 and self._hides_keys(kwargs.get("attention_mask")):
+            raise NotImplementedError(
+                "padded batches are not supported: the paged cache stores whole sequences, so pad tokens would be "
+                "attended (the reference masks them, hashattention_llama.py:593-603); use equal-length prompts")
         out = self.flash_forward(hidden_states=hidden_states, **kwargs)
         if past is not None:
             k, v = _layer_kv(past, self.layer_idx)  # post-RoPE keys, all tokens so far
-            ctx = self._context(k.shape[0], k.device)
-            if k.shape[2] > ctx.cache.max_pages * PAGE:
+            if k.shape[2] > self.max_seq_len:
                 raise ValueError(f"sequence of {k.shape[2]} tokens exceeds usa_max_seq_len={self.max_seq_len}")
+            ctx = self._context(k.shape[0], k.device, need_tokens=k.shape[2])
             for b in range(k.shape[0]):
                 ctx.cache.write_kv(b, k[b], v[b])
             ctx.hash_prefill()
+            self._cached_tokens = k.shape[2]
         return out
 
     def forward(self, hidden_states: torch.Tensor, attention_mask: Optional[torch.Tensor] = None,
@@ -177,10 +211,20 @@ class LlamaAttention_heavy_hitter(nn.Module):
             past.update(k, v, self.layer_idx, {"sin": sin, "cos": cos, "cache_position": cache_position})
 
         ctx = self._context(bsz, hidden_states.device)
+        room = ctx.cache.max_pages * PAGE
+        if self._cached_tokens + q_len > room:  # (the kernels would report it and write nothing)
+            raise ValueError(f"the sequence would grow to {self._cached_tokens + q_len} tokens, the cache holds {room}: "
+                             f"raise config.usa_decode_headroom (now {self.decode_headroom}) or config.usa_max_seq_len")
+        self._cached_tokens += q_len
+        self._steps_since_status_check += 1
+        if self._steps_since_status_check >= 256:  # an occasional look at the device status word (synchronises)
+            self._steps_since_status_check = 0
+            ctx.check_status()
         if q_len == 1:
             ctx.cache.seq_lens += 1
-            out = decode_step_op(ctx, q[:, :, 0].to(torch.bfloat16).contiguous(),
-                                 k[:, :, 0].to(torch.bfloat16).contiguous(), v[:, :, 0].to(torch.bfloat16).contiguous())
+            out = torch.zeros(bsz, self.num_heads, self.head_dim, dtype=torch.bfloat16, device=hidden_states.device)
+            decode_step_op(ctx, q[:, :, 0].to(torch.bfloat16).contiguous(), k[:, :, 0].to(torch.bfloat16).contiguous(),
+                           v[:, :, 0].to(torch.bfloat16).contiguous(), out=out)
         else:
             # 2 <= q_len <= 128 (:529): one row per (sequence, new token), each a single-token problem on
             # the keys up to its own with the budget of the whole length (:423-434)

@@ -179,6 +179,40 @@ class SparseDecodeContext:
         _raise_on(rc, "ha_score_select")
         return self.sel_idx, self.sel_cnt
 
+    def score_plan(self, q_codes: torch.Tensor | None = None) -> torch.Tensor:
+        """First half of the step after the encoder (``ha_score_plan``): streams the hash pages and leaves the
+        score bytes and the selection plan in the workspace. Returns ``sel_cnt [B, Hq]``."""
+        q_codes = self.q_codes if q_codes is None else q_codes
+        _check(q_codes, "q_codes", torch.int32, (self.batch, self.num_q_heads), self.device)
+        c = self.cache
+        with torch.cuda.device(self.device):
+            rc = self.lib.ha_score_plan(
+                self.shape, self.c_budget, q_codes.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
+                c.seq_lens.data_ptr(), self.sel_cnt.data_ptr(), self.workspace.data_ptr(), self.workspace_bytes,
+                self.status.data_ptr(), _stream_ptr(self.device))
+        _raise_on(rc, "ha_score_plan")
+        return self.sel_cnt
+
+    def select_attend(self, q, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Second half (``ha_select_attend``), on the plan :meth:`score_plan` left in the workspace: selects
+        (``sel_idx``) and attends in one kernel. Returns ``out [B, Hq, 128]`` bf16."""
+        self._check_q(q)
+        out = torch.empty_like(q) if out is None else out
+        _check(out, "out", torch.bfloat16, (self.batch, self.num_q_heads, HEAD_DIM), self.device)
+        c = self.cache
+        with torch.cuda.device(self.device):
+            rc = self.lib.ha_select_attend(
+                self.shape, self.c_budget, q.data_ptr(), c.k_pages.data_ptr(), c.v_pages.data_ptr(),
+                c.page_table.data_ptr(), c.seq_lens.data_ptr(), self.sel_idx.data_ptr(), self.sm_scale,
+                out.data_ptr(), self.workspace.data_ptr(), self.workspace_bytes, self.status.data_ptr(),
+                _stream_ptr(self.device))
+        _raise_on(rc, "ha_select_attend")
+        return out
+
+    def step_path(self) -> str:
+        """The kernels one :meth:`decode_step` launches for this shape, by name."""
+        return self.lib.ha_decode_step_path(self.shape, self.c_budget).decode()
+
     def score_select_static(self, q_codes: torch.Tensor | None = None):
         """:meth:`score_select` through ``ha_score_select_static``: no workspace is handed over, the
         kernels use the scratch buffer built into the library. Meant for hosts that are not allowed to

@@ -14,9 +14,9 @@
  *   - Unless a parameter is documented as a host pointer, every pointer is a DEVICE pointer.
  *   - Nothing is allocated or freed inside the library; temporaries live in a caller-provided
  *     workspace of ha_workspace_bytes() bytes that was prepared once by ha_workspace_init().
- *   - All work is ordered on the given CUDA stream (large decode steps fork part of it onto a
- *     library-owned stream and join it back before returning); no entry point synchronises
- *     with the host except ha_decode_step_host (documented there).
+ *   - All work is ordered on the given CUDA stream; the library creates no streams or events of
+ *     its own, and no entry point synchronises with the host except ha_decode_step_host
+ *     (documented there).
  *   - Kernels validate page ids and sizes before touching memory; a violation is reported
  *     through the 4-byte device word `status` (0 == clean) instead of a fault.
  *
@@ -47,7 +47,7 @@
 extern "C" {
 #endif
 
-#define HA_ABI_VERSION 3
+#define HA_ABI_VERSION 4
 
 /* status codes (return values and contents of the device status word) */
 #define HA_OK 0
@@ -112,12 +112,25 @@ typedef struct ha_hash_weights {
 int ha_abi_version(void);
 const char* ha_status_str(int status);
 
+/* Process-wide dispatch options (no reference counterpart; the library reads no environment
+ * variables). For experiments and tests: results never depend on them, only which kernels run.
+ *   HA_OPT_CLUSTER_GATHER  -1 library decides, 0 / 1: thread-block-cluster variant of the gather
+ *   HA_OPT_CLUSTER_SELECT  -1 library decides (at most 8 (sequence, kv-head) units of at most 65536
+ *                          tokens), 0 never, 1 whenever the sequences fit: single-pass cluster kernel
+ *                          for scoring + selection                                                */
+#define HA_OPT_CLUSTER_GATHER 0
+#define HA_OPT_CLUSTER_SELECT 1
+#define HA_OPT_COUNT_ 2
+int ha_set_option(int option_key, int value); /* HA_ERR_BAD_ARG for an unknown key */
+int ha_get_option(int option_key);
+
 /* Bytes of workspace needed by any entry point below for this shape and these budgets
  * (0 if either is invalid). Host-only arithmetic. */
 size_t ha_workspace_bytes(const ha_shape_t* shape, const ha_budget_t* budget);
 
-/* Zeroes the workspace's arrival counters. Call once after allocating the workspace (and
- * again only if a kernel was aborted); the kernels leave the counters at zero themselves. */
+/* Zeroes the workspace, in particular the arrival counters of the scoring kernel. REQUIRED once
+ * after allocating the workspace (and again only if a kernel was aborted): the kernels leave the
+ * counters at zero themselves and keep no other state in the workspace between calls.          */
 int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* workspace,
                       size_t workspace_bytes, void* stream);
 
@@ -152,9 +165,9 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
  * equals (span + 32) / 2 of the reference. Candidates are tokens [lo, hi) with
  * lo = min(init, S), hi = max(lo, S - recent); the heavy set is the min(hb, hi - lo) best
  * candidates, ties at the threshold broken by lowest token index.
- *   - sel_idx[b][h][0 .. sel_cnt[b][h]) <- heavy token indices, each once; ordered by blocks of
- *     the sequence (128 to 1024 tokens, depending on the kernel that ran), not strictly
- *     ascending inside a block: the set is the contract, not the order
+ *   - sel_idx[b][h][0 .. sel_cnt[b][h]) <- heavy token indices, each once; ordered by chunks of
+ *     the sequence (1024 to 32768 tokens, depending on the kernel that ran), not ascending
+ *     inside a chunk: the set is the contract, not the order
  *   - scores_dbg (optional, may be NULL): [batch][num_q_heads][max_pages*page_size] u8      */
 int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
                     const uint32_t* q_codes, const uint32_t* hash_pages,
@@ -167,22 +180,41 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
  * inference-server plugin whose enqueue hook may not allocate, or a process whose memory pool
  * already owns the whole device, where a cudaMalloc for the workspace is either forbidden or
  * fails.) Same inputs, outputs, results and status codes as ha_score_select; the per-chunk
- * score histograms and the row list live in a buffer of HA_STATIC_SCRATCH_BYTES that is part
- * of the library image: every GPU that loads libhashattn.so carries it until the process ends.
+ * score histograms, the plan and the score bytes live in a buffer of HA_STATIC_SCRATCH_BYTES that
+ * is part of the library image: every GPU that loads libhashattn.so carries it until the process ends.
  *   - Returns HA_ERR_SCRATCH_LIMIT, launching nothing, when this shape needs more than that
  *     (ha_static_scratch_needed() tells how much a shape needs).
  *   - Calls no allocator of any kind. The first call on each device looks the buffer's device
  *     address up (cudaGetSymbolAddress) and keeps it; make that first call outside any stream
  *     capture.
- *   - All calls on a device share the one buffer. Nothing in it has to be zero on entry (each
- *     call writes every word before reading it), but two calls whose kernels may overlap on
- *     the GPU - different streams, no ordering between them - overwrite each other: order them. */
+ *   - All calls on a device share the one buffer, which keeps whatever the last call left. The
+ *     one part that must start at zero (the scoring kernel's arrival counters) is cleared by
+ *     every call on `stream` before its kernels; every other word is written before it is read.
+ *     Two calls whose kernels may overlap on the GPU - different streams, no ordering between
+ *     them - overwrite each other: order them.                                                  */
 #define HA_STATIC_SCRATCH_BYTES (4u << 20)
 size_t ha_static_scratch_needed(const ha_shape_t* shape);
 int ha_score_select_static(const ha_shape_t* shape, const ha_budget_t* budget,
                            const uint32_t* q_codes, const uint32_t* hash_pages,
                            const int32_t* page_table, const int32_t* seq_lens,
                            int32_t* sel_idx, int32_t* sel_cnt, int32_t* status, void* stream);
+
+/* The two halves of ha_decode_step after the encoder, as stages of their own (profiling, or a
+ * host that interleaves other work): ha_score_plan streams the hash pages, leaves one score byte
+ * per token and query head, the per-chunk histograms and the selection plan (thresholds, tie
+ * quotas, per-chunk output offsets) in the workspace and writes sel_cnt; ha_select_attend, called
+ * next on the same stream with the same workspace, selects (sel_idx <- heavy token indices, as
+ * ha_score_select) and attends (out, as ha_sparse_decode) chunk by chunk in one kernel.
+ * References: hashattention/hashattention_llama.py:171-187, 423-443 and :578-623.            */
+int ha_score_plan(const ha_shape_t* shape, const ha_budget_t* budget,
+                  const uint32_t* q_codes, const uint32_t* hash_pages,
+                  const int32_t* page_table, const int32_t* seq_lens, int32_t* sel_cnt,
+                  void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+int ha_select_attend(const ha_shape_t* shape, const ha_budget_t* budget,
+                     const void* q, const void* k_pages, const void* v_pages,
+                     const int32_t* page_table, const int32_t* seq_lens,
+                     int32_t* sel_idx, float sm_scale, void* out,
+                     void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
 /* Sparse GQA flash-decode over sink + heavy + recent tokens.
  * Replaces hashattention/hashattention_llama.py:578-623 (repeat_kv, QK^T/sqrt(d), mask fill,
@@ -229,9 +261,11 @@ int ha_decode_step_rows(const ha_shape_t* shape, const ha_budget_t* budget,
                         int32_t* status, void* stream);
 
 /* Number of kernels one ha_decode_step call enqueues for this shape and budget (the library picks
- * between a single-pass and a two-pass selection, and may run large steps as two staggered halves
- * of the kv-heads); 0 for an invalid shape. For launch accounting; no reference counterpart.     */
+ * between a single-pass cluster selection and scoring + fused selection/attention); 0 for an
+ * invalid shape. For launch accounting; no reference counterpart.     */
 int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget);
+/* The kernels of that step by name, in launch order, as a static string (for labelling measurements). */
+const char* ha_decode_step_path(const ha_shape_t* shape, const ha_budget_t* budget);
 
 /* ha_decode_step for a caller whose per-step tensors live in HOST memory.
  * q_host, k_new_host, v_new_host (inputs) and out_host (result) are HOST pointers; q_dev,
@@ -239,17 +273,12 @@ int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget);
  * If all host buffers are page-locked and device-addressable (cudaHostAlloc / cudaHostRegister,
  * torch pin_memory) the kernels use them in place: the encoder kernel reads the inputs over the
  * bus once (keeping a device copy of q in q_dev), the last kernel stores the result into
- * out_host and, if status_host is page-locked too, the step's last kernel (or, where the step ends
- * on two streams, a one-warp kernel after their join) stores the status word into status_host;
- * else that word is copied. Otherwise the inputs are copied to the staging
+ * out_host and, if status_host is page-locked too, the step's last kernel stores the status word
+ * into status_host; else that word is copied. Otherwise the inputs are copied to the staging
  * buffers, ha_decode_step runs on those, and `out` is copied back. Either way the host buffers
  * must stay untouched until the stream has reached the end of the call. If `synchronize` is
  * non-zero the call waits for the stream and returns the device status word (HA_OK if clean).
- * status_host is a host int32 receiving that word.
- * Besides the caller's stream, steps with more than 32 MB of hash pages use streams and events
- * that belong to the library (created at the first such call on a device, never during the
- * caller's stream capture if an eager call came first) and are joined back before the call
- * returns; this holds for ha_decode_step too.                                               */
+ * status_host is a host int32 receiving that word.                                          */
 int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
                         const ha_hash_weights_t* weights,
                         const void* q_host, const void* k_new_host, const void* v_new_host,

@@ -28,3 +28,21 @@ def device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture
+def lib_option(pkg):
+    """Sets dispatch options of the library (ha_set_option) for one test and puts the old values back."""
+    from hashattention_b200 import _lib
+    keys = {"cluster_gather": _lib.HA_OPT_CLUSTER_GATHER, "cluster_select": _lib.HA_OPT_CLUSTER_SELECT}
+    lib = _lib.load()
+    saved = {}
+
+    def set_option(name, value):
+        key = keys[name]
+        saved.setdefault(key, lib.ha_get_option(key))
+        assert lib.ha_set_option(key, int(value)) == _lib.HA_OK
+
+    yield set_option
+    for key, value in saved.items():
+        lib.ha_set_option(key, value)

@@ -251,29 +251,29 @@ def test_depth_rule_step_against_reference_output(device, name):
 
 
 @pytest.mark.parametrize("depth", [1, 4])
-def test_depth_rule_on_the_two_pass_selection(device, monkeypatch, depth):
-    """40 units (two-pass selection, plan kernel) under the depth rule, plain and as staggered halves."""
+def test_depth_rule_on_the_scoring_plus_fused_selection_path(device, depth):
+    """40 units (scoring kernel with the plan, then selection + attention in one kernel) under the depth rule,
+    against the oracle; a second run gives the same bits."""
     Hq, Hkv = 16, 4
     lens = [300, 1025, 64, 2000, 513, 777, 1300, 256, 900, 1500]
     usa = synthetic.make_usa(Hq, 128, 3, True)
     inp = synthetic.make_decode_inputs(103, lens, Hq, Hkv)
     budget = ha.Budget(32, 1.0 / 8, 32, "depth", depth)
-    monkeypatch.setenv("HA_STAGGER", "0")
     _, out0, ctx0, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
-    monkeypatch.setenv("HA_STAGGER", "1")
+    assert "select_attend" in ctx0.step_path()
     _, out1, ctx1, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
     assert torch.equal(out0, out1) and torch.equal(ctx0.sel_cnt, ctx1.sel_cnt)
 
 
-@pytest.mark.parametrize("stagger", ["0", "1"])
+@pytest.mark.parametrize("cluster_select", [-1, 0])
 @pytest.mark.parametrize("name", ["q5", "q16_page", "q3_short", "q4_depth"])
-def test_multi_token_decode_rows_against_reference_output(device, monkeypatch, name, stagger):
+def test_multi_token_decode_rows_against_reference_output(device, lib_option, name, cluster_select):
     """2 <= q_len <= 128 new tokens per sequence in one call (ha_decode_step_rows): every (sequence,
     token) is a row that sees the keys up to its own, with the budget of the whole length. Against
     the oracle on the device's codes and, when those equal the reference's, against the recorded
-    reference masks (inside the causal part) and outputs. Plain, and (where the two-pass selection
-    runs) as two staggered halves of the kv-heads."""
-    monkeypatch.setenv("HA_STAGGER", stagger)
+    reference masks (inside the causal part) and outputs. With the kernels the library picks, and with the
+    single-pass cluster selection switched off (scoring kernel + fused selection / attention)."""
+    lib_option("cluster_select", cluster_select)
     c = helpers.load_rows()[name]
     B, Hq, ql, S = c.q.shape[0], c.q.shape[1], c.ql, c.S
     usa = synthetic.make_usa(Hq, 128, 0, True)
@@ -369,26 +369,39 @@ def test_many_units_take_the_two_pass_selection(device):
     run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(32, 1.0 / 8, 32), shuffle_seed=9)
 
 
+def test_cluster_and_fused_paths_select_the_same_sets(device, lib_option):
+    """A small step (8 units) runs the single-pass cluster selection and the cluster gather by default; with that
+    switched off it runs the scoring kernel and the fused selection + attention. Both must select exactly the same
+    sets (and pass the oracle check); the outputs agree to rounding (the partials are merged in a different order)."""
+    Hq, Hkv = 16, 4
+    lens = [2000, 1025]
+    usa = synthetic.make_usa(Hq, 128, 3, True)
+    inp = synthetic.make_decode_inputs(103, lens, Hq, Hkv)
+    budget = ha.Budget(32, 1.0 / 8, 32)
+    _, out0, ctx0, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
+    assert "cluster" in ctx0.step_path()
+    lib_option("cluster_select", 0)
+    _, out1, ctx1, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
+    assert "select_attend" in ctx1.step_path()
+    assert torch.equal(ctx0.sel_cnt, ctx1.sel_cnt)
+    for b in range(len(lens)):
+        for h in range(Hq):
+            assert torch.equal(heavy_from_device(ctx0, b, h), heavy_from_device(ctx1, b, h))
+    ok, max_abs, rel = helpers.att_close(out1, out0)
+    assert ok, (max_abs, rel)
+
+
 @pytest.mark.parametrize("Hkv", [4, 3])
-def test_staggered_step_is_bit_identical_to_the_plain_step(device, monkeypatch, Hkv):
-    """HA_STAGGER=1 runs the step as two halves of the kv-heads on two streams (what large problems
-    do by default); every (sequence, kv-head) is independent, so nothing may change - eagerly and
-    when the step is captured into a CUDA graph. Hkv = 3 splits unevenly (1 + 2)."""
+def test_fused_step_replays_bit_identically_from_a_cuda_graph(device, Hkv):
+    """The step on the scoring + fused selection / attention path (30 - 40 units, ragged lengths), eagerly against
+    the oracle and then captured into a CUDA graph: every replay gives the eager run's bits."""
     Hq = 4 * Hkv
     lens = [300, 1025, 64, 2000, 513, 777, 1300, 256, 900, 1500]
     usa = synthetic.make_usa(Hq, 128, 3, True)
     inp = synthetic.make_decode_inputs(103, lens, Hq, Hkv)
     budget = ha.Budget(32, 1.0 / 8, 32)
-    monkeypatch.setenv("HA_STAGGER", "0")
-    _, out0, ctx0, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
-    monkeypatch.setenv("HA_STAGGER", "1")
     _, out1, ctx1, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
-    assert torch.equal(out0, out1)
-    assert torch.equal(ctx0.sel_cnt, ctx1.sel_cnt)
-    for b in range(len(lens)):
-        for h in range(Hq):
-            assert torch.equal(heavy_from_device(ctx0, b, h), heavy_from_device(ctx1, b, h))
-    # captured: the second stream joins the capture through the fork event and leaves it at the join
+    assert "select_attend" in ctx1.step_path()
     q = inp.q.to(device, torch.bfloat16)
     k_new = torch.stack([k[:, -1] for k in inp.k]).to(device, torch.bfloat16)
     v_new = torch.stack([v[:, -1] for v in inp.v]).to(device, torch.bfloat16)
@@ -409,17 +422,18 @@ def test_staggered_step_is_bit_identical_to_the_plain_step(device, monkeypatch, 
 
 @pytest.mark.parametrize("S", [40000, 70000])
 def test_long_sequence_selection(device, S):
-    """S = 40,000 runs the cluster kernel with two rounds; S = 70,000 (chunks of 8 pages, two rounds
-    per CTA) the two-pass pair. Both against the oracle."""
+    """S = 40,000 runs the cluster kernel with two rounds; S = 70,000 the scoring kernel + fused selection /
+    attention. Both against the oracle."""
     Hq, Hkv = 8, 2
     usa = synthetic.make_usa(Hq, 128, 4, True)
     inp = synthetic.make_decode_inputs(104, [S], Hq, Hkv)
     run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(128, 1.0 / 32, 128), shuffle_seed=2)
 
 
-def test_two_pass_selection_with_two_rounds_per_cta(device):
-    """S = 40,000 through the workspace-free entry point, which always runs the score_hist + select
-    pair (8-page chunks, two rounds per CTA here), against the oracle on the device's own codes."""
+def test_selection_alone_through_the_scoring_kernel_and_the_select_only_kernel(device):
+    """S = 40,000 through the workspace-free entry point, which always runs the scoring kernel and the
+    selection-only build of the fused kernel (two rounds per scoring CTA here), against the oracle on the
+    device's own codes."""
     Hq, Hkv, S = 8, 2, 40000
     usa = synthetic.make_usa(Hq, 128, 6, True)
     inp = synthetic.make_decode_inputs(105, [S], Hq, Hkv)
@@ -674,15 +688,14 @@ def test_host_buffer_step_delivers_the_status_word(device, use_graph, pinned):
 
 
 @pytest.mark.parametrize("use_graph", [False, True])
-def test_staggered_host_buffer_step_delivers_result_and_status(device, monkeypatch, use_graph):
-    """A step that runs as staggered halves on two streams ends with a one-warp kernel that stores the
-    status word into the caller's page-locked word, after both streams have been joined."""
+def test_host_buffer_step_on_the_fused_path_delivers_result_and_status(device, use_graph):
+    """A step of 40 units (scoring + fused selection / attention; the merge kernel ends it) from host buffers: the
+    last kernel stores the result and the status word into the caller's page-locked memory."""
     Hq, Hkv = 16, 4
     lens = [300, 1025, 64, 2000, 513, 777, 1300, 256, 900, 1500]
     usa = synthetic.make_usa(Hq, 128, 3, True)
     inp = synthetic.make_decode_inputs(103, lens, Hq, Hkv)
     budget = ha.Budget(32, 1.0 / 8, 32)
-    monkeypatch.setenv("HA_STAGGER", "1")
     _, want, _, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget, shuffle_seed=9)
     cache, ctx = build(device, inp.q, inp.k, inp.v, budget, usa, shuffle_seed=9)
     ctx.hash_prefill()

@@ -140,7 +140,7 @@ def test_converted_model_prefill_then_decode_matches_oracle(device):
         want = att.o_proj(ref.transpose(1, 2).reshape(2, 4, 512).to(device, torch.bfloat16)).float().cpu()
     got = seen["out"][0].float().cpu()
     assert float((got - want).abs().max()) < 3e-2 and float((got - want).norm() / want.norm()) < 2e-2
-    for ctx_rows in att._row_ctx.values():
+    for ctx_rows in att._ctx.row_contexts.values():
         ctx_rows.check_status()
 
     # a second prompt after reset_usa starts from an empty hash cache
@@ -176,6 +176,39 @@ def test_mistral_host_converts_and_resets_like_the_llama_host():
     for n, p in before.items():
         assert torch.equal(dict(model.named_parameters())[n], p.to(torch.bfloat16))
     assert ham.reset_usa(model) is model and ham.set_eval_usa_mode(model) is model
+
+
+@pytest.mark.gpu
+def test_cache_room_is_checked_on_the_host_and_padded_batches_are_refused(device):
+    """The module tracks the cached length on the host: a step that would not fit the paged cache raises before
+    anything is launched (the kernels would only report it and leave `out` unwritten), and a prefill whose
+    attention mask hides keys (a padded batch) is refused instead of attending the pad tokens."""
+    cfg = tiny_config(1)
+    cfg.usa_decode_headroom = 2
+    torch.manual_seed(1)
+    model = LlamaForCausalLM(cfg).to(torch.bfloat16).to(device).eval()
+    mods = hal.load_usa(cfg, None, device=device).bfloat16()
+    model = hal.convert_usa(model, cfg, mods, collect_stats=False, train_usa=False)
+    att = model.model.layers[0].self_attn
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, 1000, (2, 254), generator=g).to(device)
+    with torch.no_grad():
+        cache = model(prompt, use_cache=True).past_key_values
+        room = att._ctx.cache.max_pages * 256
+        assert room == 256  # 254 + 2 of headroom, one page
+        for _ in range(2):
+            out = model(torch.randint(0, 1000, (2, 1), generator=g).to(device), past_key_values=cache, use_cache=True)
+            assert bool(torch.isfinite(out.logits.float()).all())
+        with pytest.raises(ValueError, match="usa_decode_headroom"):
+            model(torch.randint(0, 1000, (2, 1), generator=g).to(device), past_key_values=cache, use_cache=True)
+    att._ctx.check_status()  # nothing was launched for the refused step
+    assert att._ctx.cache.seq_lens.tolist() == [256, 256]
+
+    hal.reset_usa(model)
+    mask = torch.ones(2, 200, dtype=torch.long, device=device)
+    mask[1, :7] = 0  # left padding of the second prompt
+    with torch.no_grad(), pytest.raises(NotImplementedError, match="padded"):
+        model(prompt[:, :200], attention_mask=mask, use_cache=True)
 
 
 @pytest.mark.gpu
