@@ -590,19 +590,145 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------
+# BASELINE configs[4]: the whole Llama-3.1-8B-architecture model, tensor-parallel, greedy decode
+# --------------------------------------------------------------------------------------------
+CONFIG4_DESC = ("BASELINE configs[4]: Llama-3.1-8B architecture (32 layers, hidden 4096, 32q/8kv heads, d=128, FFN 14336, "
+                "vocab 128256), random bf16 weights, HashAttention on every layer (init 128 / recent 128 / heavy 1/32), "
+                "batch 8, prefill 32768 random token ids, greedy decode, tensor-parallel with an all-reduce after "
+                "attention and after the MLP")
+
+
+def run_config4(args):
+    """`--steps` greedy decode steps of the whole model (every layer, batch 8) after a prefill of `--prefill`
+    tokens; one process per GPU, q/k/v/w1/w3 column-parallel, wo/w2 row-parallel, NCCL all-reduce after
+    attention and MLP. Prints decode tokens/s (whole batch, all GPUs together)."""
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    ha = entry.load_package()
+    from hashattention_b200 import llama_tp
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    batch = args.batch or 8
+    cfg = llama_tp.LlamaTPConfig(max_seq_len=args.prefill + args.steps + args.warmup + 8)
+    if args.layers:
+        cfg.n_layers = args.layers
+    model = llama_tp.TPLlama(cfg, world, rank, dev, batch, seed=0)
+    tokens = llama_tp.tokens_for(cfg, batch, args.prefill).to(dev)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sync()
+    t0 = time.perf_counter()
+    cur = model.prefill(tokens)
+    sync()
+    prefill_s = time.perf_counter() - t0
+    model.check_status()
+
+    nxt = torch.empty_like(cur)
+    for _ in range(2):  # eager steps first (lazy initialisation of the libraries involved)
+        model.decode_step(cur, nxt)
+        cur.copy_(nxt)
+    sync()
+    launch = "CUDA graph of one decode step (all layers, both all-reduces per layer)"
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                model.decode_step(cur, nxt)
+                cur.copy_(nxt)
+        torch.cuda.current_stream().wait_stream(side)
+    except Exception as e:  # a collective that cannot be captured: run the steps eagerly
+        graph, launch = None, f"eager (graph capture failed: {type(e).__name__})"
+        torch.cuda.synchronize()
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        else:
+            model.decode_step(cur, nxt)
+            cur.copy_(nxt)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    seconds = float(t.item()) * 1e-3
+    clocks = sampler.stop() if sampler is not None else None
+    model.check_status()
+    seq_len = int(model.ctxs[0].cache.seq_lens[0])
+    launches = int(model.ctxs[0].lib.ha_decode_step_launches(model.ctxs[0].shape, model.ctxs[0].c_budget))
+    if rank == 0:
+        line = {
+            "metric": "decode_tokens_per_s", "value": batch * args.steps / seconds, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"config4: {CONFIG4_DESC}", "batch": batch, "prefill_tokens": args.prefill,
+                       "layers": cfg.n_layers, "parallelism": f"tp{world}"},
+            "prefill_s": prefill_s, "context_at_end": seq_len, "launch": launch,
+            "attention_kernels_per_layer": model.ctxs[0].step_path(), "sample_tokens": cur[:4].tolist(),
+            "gpu_launches": launches * cfg.n_layers * args.steps, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    # A captured graph that holds NCCL kernels must be gone before the communicator is torn down (a teardown in
+    # the other order has been seen to block); the ranks leave together, without waiting for destructors.
+    graph = None
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=600)
     ap.add_argument("--warmup", type=int, default=60)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="config3")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["config4"], default="config3")
+    ap.add_argument("--prefill", type=int, default=32768, help="config4: prompt length")
     ap.add_argument("--layers", type=int, default=0, help="layer instances kept resident (0 = sized to exceed L2)")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the configs[1] / configs[2] blocks")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "config4":
+        if args.impl == "reference":
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the reference's full-model host (efficiency/model.py, "
+                                  "generate.py) imports modules that are not in its repository; no CPU arm for config4"}))
+            return
+        if args.steps == 600 and args.warmup == 60:  # the defaults of the layer-step workloads
+            args.steps, args.warmup = 256, 8
+        run_config4(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

@@ -73,6 +73,7 @@ PROTOTYPES = {
                                c_size_t, _P, _P]),
     "ha_decode_step_rows": (c_int, [_S, _B, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, _P, _P,
                                     c_size_t, _P, _P]),
+    "ha_rope_split": (c_int, [_P, _P, c_int32, c_int32, c_int32, c_float, _P, _P, _P, _P]),
     "ha_decode_step_host": (c_int, [_S, _B, _W, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                     _P, _P, _P, c_float, _P, c_size_t, _P, _P, c_int]),
 }

@@ -918,6 +918,53 @@ int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
 }  // extern "C"
 
 // ------------------------------------------------------------------------------------------
+// ha_rope_split: helper of a host model's decode step - splits the fused q|k|v projection of one new token per
+// sequence into the contiguous q, k_new, v_new tensors the decode step takes and applies the rotary position
+// embedding to q and k on the way (one launch instead of a dozen elementwise ones).
+// ------------------------------------------------------------------------------------------
+namespace ha {
+namespace {
+
+// grid (heads, B), 64 threads: thread t owns dimensions t and t + 64 of one head (the rotate-half pair).
+__global__ void __launch_bounds__(64) rope_split_kernel(const __nv_bfloat16* __restrict__ qkv, const long long* __restrict__ pos,
+                                                        __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k,
+                                                        __nv_bfloat16* __restrict__ v, int hq, int hkv, float log2_theta) {
+    const int head = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+    const int heads = hq + 2 * hkv;
+    const __nv_bfloat16* src = qkv + ((size_t)b * heads + head) * kHeadDim;
+    const float x1 = __bfloat162float(src[t]), x2 = __bfloat162float(src[t + 64]);
+    __nv_bfloat16* dst;
+    if (head < hq) dst = q + ((size_t)b * hq + head) * kHeadDim;
+    else if (head < hq + hkv) dst = k + ((size_t)b * hkv + (head - hq)) * kHeadDim;
+    else {  // a value head: copied as it is
+        dst = v + ((size_t)b * hkv + (head - hq - hkv)) * kHeadDim;
+        dst[t] = src[t];
+        dst[t + 64] = src[t + 64];
+        return;
+    }
+    // angle = position * theta^(-2 t / 128), cos / sin in fp32 as the reference's rotary tables are
+    const float inv_freq = exp2f(-log2_theta * (float)(2 * t) / (float)kHeadDim);
+    float sn, cs;
+    sincosf((float)pos[b] * inv_freq, &sn, &cs);
+    dst[t] = __float2bfloat16_rn(x1 * cs - x2 * sn);
+    dst[t + 64] = __float2bfloat16_rn(x2 * cs + x1 * sn);
+}
+
+}  // namespace
+}  // namespace ha
+
+extern "C" int ha_rope_split(const void* qkv, const int64_t* positions, int32_t batch, int32_t num_q_heads,
+                             int32_t num_kv_heads, float rope_theta, void* q, void* k_new, void* v_new, void* stream) {
+    if (qkv == nullptr || positions == nullptr || q == nullptr || k_new == nullptr || v_new == nullptr) return HA_ERR_BAD_ARG;
+    if (batch < 1 || batch > 65535 || num_q_heads < 1 || num_kv_heads < 1 || !(rope_theta > 1.0f)) return HA_ERR_BAD_ARG;
+    rope_split_kernel<<<dim3(num_q_heads + 2 * num_kv_heads, batch), 64, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const long long*>(positions),
+        static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k_new), static_cast<__nv_bfloat16*>(v_new),
+        num_q_heads, num_kv_heads, log2f(rope_theta));
+    return cudaGetLastError() == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+}
+
+// ------------------------------------------------------------------------------------------
 // ha_score_select_static: the selection kernels on scratch memory that is part of the library
 // image, for callers that may not allocate (see include/hashattn.h).
 // ------------------------------------------------------------------------------------------

@@ -293,6 +293,23 @@ class SparseDecodeContext:
         return out
 
 
+def rope_split(qkv: torch.Tensor, positions: torch.Tensor, num_q_heads: int, num_kv_heads: int, rope_theta: float):
+    """``ha_rope_split``: the fused projection ``qkv [B, (Hq + 2 Hkv) * 128]`` bf16 of one new token per sequence ->
+    contiguous ``q [B, Hq, 128]``, ``k_new``, ``v_new [B, Hkv, 128]`` with the rotary embedding applied to q and k
+    for ``positions [B]`` (int64, on the device)."""
+    B = qkv.shape[0]
+    _check(qkv, "qkv", torch.bfloat16, (B, (num_q_heads + 2 * num_kv_heads) * HEAD_DIM), qkv.device)
+    _check(positions, "positions", torch.int64, (B,), qkv.device)
+    q = torch.empty(B, num_q_heads, HEAD_DIM, dtype=torch.bfloat16, device=qkv.device)
+    k = torch.empty(B, num_kv_heads, HEAD_DIM, dtype=torch.bfloat16, device=qkv.device)
+    v = torch.empty_like(k)
+    with torch.cuda.device(qkv.device):
+        rc = _lib.load().ha_rope_split(qkv.data_ptr(), positions.data_ptr(), B, num_q_heads, num_kv_heads, float(rope_theta),
+                                       q.data_ptr(), k.data_ptr(), v.data_ptr(), _stream_ptr(qkv.device))
+    _raise_on(rc, "ha_rope_split")
+    return q, k, v
+
+
 class ChunkRows:
     """A multi-token decode step laid out as rows for ``ha_decode_step_rows``: ``q_len`` new tokens
     for each of the ``B`` sequences of ``cache`` become ``B * q_len`` rows (sequence-major) that share

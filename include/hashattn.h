@@ -290,6 +290,16 @@ int ha_decode_step_host(const ha_shape_t* shape, const ha_budget_t* budget,
                         void* workspace, size_t workspace_bytes,
                         int32_t* status, void* stream, int synchronize);
 
+/* Helper for a host model's decode step (one new token per sequence): splits the fused projection
+ * qkv [batch][num_q_heads + 2 * num_kv_heads][128] bf16 (query heads, then key heads, then value
+ * heads) into the contiguous q [batch][num_q_heads][128], k_new and v_new [batch][num_kv_heads][128]
+ * that ha_decode_step takes, applying the rotary position embedding (rotate-half convention,
+ * angle = positions[b] * rope_theta^(-2i/128), fp32) to q and k on the way. Replaces
+ * apply_rotary_pos_emb + the view / transpose of hashattention/hashattention_llama.py:551-571 for
+ * q_len == 1. positions: [batch] int64 on the device.                                          */
+int ha_rope_split(const void* qkv, const int64_t* positions, int32_t batch, int32_t num_q_heads,
+                  int32_t num_kv_heads, float rope_theta, void* q, void* k_new, void* v_new, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
