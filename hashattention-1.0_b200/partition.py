@@ -41,9 +41,16 @@ def shard_step_inputs(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
 
 def gather_output(out_local: torch.Tensor, group=None) -> torch.Tensor:
     """Concatenates the per-rank outputs [B, Hq/world, D] along the head axis, on every rank.
-    The only communication of the path; rank order equals kv-head order."""
+    The only communication of the path; rank order equals kv-head order. One collective into one buffer
+    (``all_gather_into_tensor``) where the backend has it (NCCL), the list form otherwise (gloo)."""
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return out_local
-    parts = [torch.empty_like(out_local) for _ in range(dist.get_world_size(group))]
-    dist.all_gather(parts, out_local.contiguous(), group=group)
+    world = dist.get_world_size(group)
+    local = out_local.contiguous()
+    if dist.get_backend(group) == "nccl":
+        flat = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(flat, local, group=group)
+        return flat.transpose(0, 1).reshape(local.shape[0], world * local.shape[1], *local.shape[2:])
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local, group=group)
     return torch.cat(parts, dim=1)
