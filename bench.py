@@ -492,8 +492,8 @@ def run_gpu_arm(args):
     b.prepare_step_graphs()
 
     # ---- the timed regions ---------------------------------------------------------------------
-    sampler = ClockSampler(local) if rank == 0 else None
-    t = b.measure_steps(args.steps, args.warmup)
+    sampler = ClockSampler(local) if rank == 0 and not args.steps_only else None
+    t = b.measure_steps(args.steps, args.warmup, repeats=1 if args.steps_only else REPEATS)
     # keep the same workload running a little longer so the clock samples are under load
     t_end = time.perf_counter() + 1.5
     while sampler is not None and time.perf_counter() < t_end:
@@ -502,6 +502,15 @@ def run_gpu_arm(args):
     clocks = sampler.stop() if sampler is not None else None
     per_step = t["median"]
     value = b.nbytes["total"] / per_step / 1e9
+    if args.steps_only:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "us_per_layer": per_step * 1e6, "config": config_block(args.workload),
+                              "batch": b.B, "layer_instances": b.L, "step_kernels": b.ctxs[0].step_path(),
+                              "note": "--steps-only: no stage, prefill, end-to-end or CPU measurements"}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     out_full, t_gather = b.final_gather()
     out_digest = hashlib.sha256(out_full.contiguous().view(torch.uint8).cpu().numpy().tobytes()).hexdigest()
@@ -718,6 +727,8 @@ def main():
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (profiling small cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="skip the configs[1] / configs[2] blocks")
+    ap.add_argument("--steps-only", action="store_true",
+                    help="warm up, time the steps, print a short line and stop (for profiler captures of small cases)")
     args = ap.parse_args()
     if args.workload == "config4":
         if args.impl == "reference":
