@@ -194,12 +194,73 @@ __device__ __forceinline__ void mlp_eval(const MlpRegs<WT>& r, const uint4 raw,
     __syncthreads();
 }
 
+// mlp_eval for two rows at once (`sm[0]`, `sm[1]`): the same weights in registers feed both rows, and the two
+// dependent chains (dot, shuffle reduction, SiLU, barrier) interleave, so the pair costs little more than one row.
+template <typename WT>
+__device__ __forceinline__ void hidden_layer2(const Row8<WT> (&w)[kRowLoads], const float (&bias)[kRowLoads],
+                                              const float (&xa)[8], const float (&xb)[8], float* da, float* db,
+                                              int warp, int lane) {
+    const int half = lane >> 4, sub = lane & 15;
+    float ma = 0.f, mb = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRowLoads; ++j) {
+        const float sa = half_warp_sum(w[j].dot(xa)) + bias[j];
+        const float sb = half_warp_sum(w[j].dot(xb)) + bias[j];
+        ma = sub == j ? sa : ma;
+        mb = sub == j ? sb : mb;
+    }
+    if (sub < kRowLoads) {
+        da[warp * (2 * kRowLoads) + 2 * sub + half] = silu(ma);
+        db[warp * (2 * kRowLoads) + 2 * sub + half] = silu(mb);
+    }
+}
+
+__device__ __forceinline__ void unpack_x8(const uint4 raw, float (&x)[8]) {
+    x[0] = bf16_lo(raw.x); x[1] = bf16_hi(raw.x);
+    x[2] = bf16_lo(raw.y); x[3] = bf16_hi(raw.y);
+    x[4] = bf16_lo(raw.z); x[5] = bf16_hi(raw.z);
+    x[6] = bf16_lo(raw.w); x[7] = bf16_hi(raw.w);
+}
+
+template <typename WT, typename F>
+__device__ __forceinline__ void mlp_eval2(const MlpRegs<WT>& r, const uint4 raw_a, const uint4 raw_b,
+                                          MlpSmem (&sm)[2], int warp, int lane, F&& between, int layers = 3) {
+    const int half = lane >> 4, col = (lane & 15) * 8;
+    float xa[8], xb[8];
+    unpack_x8(raw_a, xa);
+    unpack_x8(raw_b, xb);
+    if (layers >= 2) hidden_layer2(r.w0, r.b0, xa, xb, sm[0].h0, sm[1].h0, warp, lane);
+    between();
+    __syncthreads();
+    if (layers >= 2) {
+        load_x8(sm[0].h0 + col, xa);
+        load_x8(sm[1].h0 + col, xb);
+    }
+    if (layers == 3) {
+        hidden_layer2(r.w1, r.b1, xa, xb, sm[0].h1, sm[1].h1, warp, lane);
+        __syncthreads();
+        load_x8(sm[0].h1 + col, xa);
+        load_x8(sm[1].h1 + col, xb);
+    }
+    {
+        const float sa = half_warp_sum(r.w2.dot(xa)) + r.b2;
+        const float sb = half_warp_sum(r.w2.dot(xb)) + r.b2;
+        if ((lane & 15) == 0) {
+            sm[0].out[warp * 2 + half] = sa;
+            sm[1].out[warp * 2 + half] = sb;
+        }
+    }
+    __syncthreads();
+}
+
 // This lane's 8 consecutive elements (columns 8 * (lane % 16) ...) of a 128-element bf16 row.
 __device__ __forceinline__ uint4 load_x_row(const __nv_bfloat16* xrow, int lane) {
     return *reinterpret_cast<const uint4*>(xrow + (lane & 15) * 8);
 }
 
-template <typename WT>
+// kPairs: a CTA with two or more sequences evaluates them two at a time; with one sequence per CTA the
+// single-row loop is a little leaner.
+template <typename WT, bool kPairs>
 __global__ void __launch_bounds__(kHashDecodeThreads)
 hash_decode_kernel(const HashDecodeParams p) {
     HA_TL(kTlHashDecode, kTlEntry);
@@ -211,7 +272,7 @@ hash_decode_kernel(const HashDecodeParams p) {
     MlpRegs<WT> regs;
     regs.load(static_cast<const WT*>(p.w[side]) + (size_t)h * kMlpElems,
               p.bias[side] + (size_t)h * kMlpBias, warp, lane >> 4, (lane & 15) * 8);
-    __shared__ MlpSmem sm;
+    __shared__ MlpSmem sm[2];
 
     pdl_wait();
     HA_TL(kTlHashDecode, kTlAfterWait);
@@ -221,70 +282,151 @@ hash_decode_kernel(const HashDecodeParams p) {
     const int b_end = min(p.B, b_begin + p.batch_per_cta);
     const int kvh = h / kGroup, g = h % kGroup;
 
-    // The input row and (key side) the sequence length of the next sequence are requested while the
-    // current one is evaluated; the page-table entry of the append slot, whose address depends on
-    // the length, is fetched underneath the MLP arithmetic.
-    auto x_row = [&](int b) {
-        return side == 0 ? p.q + ((size_t)b * Hq + h) * kHeadDim : p.k_new + ((size_t)b * p.Hkv + kvh) * kHeadDim;
-    };
-    // The group's first key head also appends the K and V rows: lanes 0-15 of warp 0 hold the K row already (it
-    // is the MLP's input), lanes 16-31 request the V row together with it - the inputs may live in mapped
-    // host memory, where a second read at the end of the kernel would cost another trip over the bus.
-    const bool appends = side == 1 && g == 0 && p.v_new != nullptr && warp == 0;
-    auto v_part = [&](int b) {
-        return *(reinterpret_cast<const uint4*>(p.v_new + ((size_t)b * p.Hkv + kvh) * kHeadDim) + (lane - 16));
-    };
-    uint4 raw_next = make_uint4(0u, 0u, 0u, 0u), v_next = make_uint4(0u, 0u, 0u, 0u);
-    int S_next = 1;
-    if (b_begin < b_end) {
-        raw_next = load_x_row(x_row(b_begin), lane);
-        if (appends && lane >= 16) v_next = v_part(b_begin);
-        if (side == 1) S_next = p.seq_lens[b_begin];
-    }
-    for (int b = b_begin; b < b_end; ++b) {
-        const uint4 raw = raw_next, v_raw = v_next;
-        const int S = S_next;
-        if (b + 1 < b_end) {
-            raw_next = load_x_row(x_row(b + 1), lane);
-            if (appends && lane >= 16) v_next = v_part(b + 1);
-            if (side == 1) S_next = p.seq_lens[b + 1];
-        }
-        if (side == 0 && p.q_stage != nullptr && warp == 0 && lane < 16)
-            *reinterpret_cast<uint4*>(p.q_stage + ((size_t)b * Hq + h) * kHeadDim + lane * 8) = raw;
-        int page = 0;
-        mlp_eval(regs, raw, sm, warp, lane, [&] {
-            if (side == 1) {
-                const int pidx = min(max(S - 1, 0) / kPage, p.max_pages - 1);
-                page = p.page_table[(size_t)b * p.max_pages + pidx];
+    if constexpr (kPairs) {
+        // The sequences of this CTA are evaluated two at a time (the pair shares every weight register and its two
+        // dependent chains interleave); the input rows, the V rows of the append and (key side) the sequence lengths
+        // of a pair are requested together, the page-table entries of the append slots underneath the MLP arithmetic.
+        auto x_row = [&](int b) {
+            return side == 0 ? p.q + ((size_t)b * Hq + h) * kHeadDim : p.k_new + ((size_t)b * p.Hkv + kvh) * kHeadDim;
+        };
+        // The group's first key head also appends the K and V rows: lanes 0-15 of warp 0 hold the K row already (it
+        // is the MLP's input), lanes 16-31 request the V row together with it - the inputs may live in mapped
+        // host memory, where a second read at the end of the kernel would cost another trip over the bus.
+        const bool appends = side == 1 && g == 0 && p.v_new != nullptr && warp == 0;
+        auto v_part = [&](int b) {
+            return *(reinterpret_cast<const uint4*>(p.v_new + ((size_t)b * p.Hkv + kvh) * kHeadDim) + (lane - 16));
+        };
+        // what warp 0 does with a finished row: code out, and (key side) the append
+        auto finish = [&](int b, const MlpSmem& m, const uint4 raw, const uint4 v_raw, int S, int page) {
+            const float pre = m.out[lane];
+            // bit i = 1 iff output i > 0 (efficiency/kernels/torchatt.py:35-36: relu(sign(x)))
+            const uint32_t code = __ballot_sync(0xffffffffu, pre > 0.0f);
+            if (p.preact_dbg != nullptr)
+                p.preact_dbg[(((size_t)b * 2 + side) * Hq + h) * kCodeBits + lane] = pre;
+            if (side == 0) {
+                if (lane == 0) p.q_codes[(size_t)b * Hq + h] = code;
+                return;
             }
-        }, p.layers);
-        if (warp != 0) continue;
+            if (S < 1 || S > p.max_pages * kPage) {
+                if (lane == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+                return;
+            }
+            if (page < 0 || page >= p.num_pages) {
+                if (lane == 0) report(p.status, HA_ERR_BAD_PAGE);
+                return;
+            }
+            const size_t slot = ((size_t)page * p.Hkv + kvh) * kPage + (S - 1) % kPage;
+            if (lane == 0) p.hash_pages[slot * kGroup + g] = code;
+            // the group's first head also appends the K and V rows (256 B each)
+            if (appends) {
+                uint4* d = lane < 16 ? reinterpret_cast<uint4*>(p.k_pages + slot * kHeadDim) + lane
+                                     : reinterpret_cast<uint4*>(p.v_pages + slot * kHeadDim) + (lane - 16);
+                *d = lane < 16 ? raw : v_raw;
+            }
+        };
+        auto page_of = [&](int b, int S) {
+            return p.page_table[(size_t)b * p.max_pages + min(max(S - 1, 0) / kPage, p.max_pages - 1)];
+        };
+        for (int b = b_begin; b < b_end; b += 2) {
+            const bool two = b + 1 < b_end;
+            const int b1 = two ? b + 1 : b;
+            const uint4 raw0 = load_x_row(x_row(b), lane), raw1 = load_x_row(x_row(b1), lane);
+            uint4 v0 = make_uint4(0u, 0u, 0u, 0u), v1 = v0;
+            if (appends && lane >= 16) {
+                v0 = v_part(b);
+                v1 = v_part(b1);
+            }
+            int S0 = 1, S1 = 1, page0 = 0, page1 = 0;
+            if (side == 1) {
+                S0 = p.seq_lens[b];
+                S1 = p.seq_lens[b1];
+            }
+            if (side == 0 && p.q_stage != nullptr && warp == 0 && lane < 16) {
+                *reinterpret_cast<uint4*>(p.q_stage + ((size_t)b * Hq + h) * kHeadDim + lane * 8) = raw0;
+                if (two) *reinterpret_cast<uint4*>(p.q_stage + ((size_t)b1 * Hq + h) * kHeadDim + lane * 8) = raw1;
+            }
+            if (two) {
+                mlp_eval2(regs, raw0, raw1, sm, warp, lane, [&] {
+                    if (side == 1) {
+                        page0 = page_of(b, S0);
+                        page1 = page_of(b1, S1);
+                    }
+                }, p.layers);
+            } else {
+                mlp_eval(regs, raw0, sm[0], warp, lane, [&] {
+                    if (side == 1) page0 = page_of(b, S0);
+                }, p.layers);
+            }
+            if (warp != 0) continue;
+            finish(b, sm[0], raw0, v0, S0, page0);
+            if (two) finish(b1, sm[1], raw1, v1, S1, page1);
+        }
+    } else {
+        // The input row and (key side) the sequence length of the next sequence are requested while the
+        // current one is evaluated; the page-table entry of the append slot, whose address depends on
+        // the length, is fetched underneath the MLP arithmetic.
+        auto x_row = [&](int b) {
+            return side == 0 ? p.q + ((size_t)b * Hq + h) * kHeadDim : p.k_new + ((size_t)b * p.Hkv + kvh) * kHeadDim;
+        };
+        // The group's first key head also appends the K and V rows: lanes 0-15 of warp 0 hold the K row already (it
+        // is the MLP's input), lanes 16-31 request the V row together with it - the inputs may live in mapped
+        // host memory, where a second read at the end of the kernel would cost another trip over the bus.
+        const bool appends = side == 1 && g == 0 && p.v_new != nullptr && warp == 0;
+        auto v_part = [&](int b) {
+            return *(reinterpret_cast<const uint4*>(p.v_new + ((size_t)b * p.Hkv + kvh) * kHeadDim) + (lane - 16));
+        };
+        uint4 raw_next = make_uint4(0u, 0u, 0u, 0u), v_next = make_uint4(0u, 0u, 0u, 0u);
+        int S_next = 1;
+        if (b_begin < b_end) {
+            raw_next = load_x_row(x_row(b_begin), lane);
+            if (appends && lane >= 16) v_next = v_part(b_begin);
+            if (side == 1) S_next = p.seq_lens[b_begin];
+        }
+        for (int b = b_begin; b < b_end; ++b) {
+            const uint4 raw = raw_next, v_raw = v_next;
+            const int S = S_next;
+            if (b + 1 < b_end) {
+                raw_next = load_x_row(x_row(b + 1), lane);
+                if (appends && lane >= 16) v_next = v_part(b + 1);
+                if (side == 1) S_next = p.seq_lens[b + 1];
+            }
+            if (side == 0 && p.q_stage != nullptr && warp == 0 && lane < 16)
+                *reinterpret_cast<uint4*>(p.q_stage + ((size_t)b * Hq + h) * kHeadDim + lane * 8) = raw;
+            int page = 0;
+            mlp_eval(regs, raw, sm[0], warp, lane, [&] {
+                if (side == 1) {
+                    const int pidx = min(max(S - 1, 0) / kPage, p.max_pages - 1);
+                    page = p.page_table[(size_t)b * p.max_pages + pidx];
+                }
+            }, p.layers);
+            if (warp != 0) continue;
 
-        const float pre = sm.out[lane];
-        // bit i = 1 iff output i > 0 (efficiency/kernels/torchatt.py:35-36: relu(sign(x)))
-        const uint32_t code = __ballot_sync(0xffffffffu, pre > 0.0f);
-        if (p.preact_dbg != nullptr)
-            p.preact_dbg[(((size_t)b * 2 + side) * Hq + h) * kCodeBits + lane] = pre;
-        if (side == 0) {
-            if (lane == 0) p.q_codes[(size_t)b * Hq + h] = code;
-            continue;
-        }
-        if (S < 1 || S > p.max_pages * kPage) {
-            if (lane == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
-            continue;
-        }
-        const int tok = S - 1;
-        if (page < 0 || page >= p.num_pages) {
-            if (lane == 0) report(p.status, HA_ERR_BAD_PAGE);
-            continue;
-        }
-        const size_t slot = ((size_t)page * p.Hkv + kvh) * kPage + tok % kPage;
-        if (lane == 0) p.hash_pages[slot * kGroup + g] = code;
-        // the group's first head also appends the K and V rows (256 B each)
-        if (appends) {
-            uint4* d = lane < 16 ? reinterpret_cast<uint4*>(p.k_pages + slot * kHeadDim) + lane
-                                 : reinterpret_cast<uint4*>(p.v_pages + slot * kHeadDim) + (lane - 16);
-            *d = lane < 16 ? raw : v_raw;
+            const float pre = sm[0].out[lane];
+            // bit i = 1 iff output i > 0 (efficiency/kernels/torchatt.py:35-36: relu(sign(x)))
+            const uint32_t code = __ballot_sync(0xffffffffu, pre > 0.0f);
+            if (p.preact_dbg != nullptr)
+                p.preact_dbg[(((size_t)b * 2 + side) * Hq + h) * kCodeBits + lane] = pre;
+            if (side == 0) {
+                if (lane == 0) p.q_codes[(size_t)b * Hq + h] = code;
+                continue;
+            }
+            if (S < 1 || S > p.max_pages * kPage) {
+                if (lane == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
+                continue;
+            }
+            const int tok = S - 1;
+            if (page < 0 || page >= p.num_pages) {
+                if (lane == 0) report(p.status, HA_ERR_BAD_PAGE);
+                continue;
+            }
+            const size_t slot = ((size_t)page * p.Hkv + kvh) * kPage + tok % kPage;
+            if (lane == 0) p.hash_pages[slot * kGroup + g] = code;
+            // the group's first head also appends the K and V rows (256 B each)
+            if (appends) {
+                uint4* d = lane < 16 ? reinterpret_cast<uint4*>(p.k_pages + slot * kHeadDim) + lane
+                                     : reinterpret_cast<uint4*>(p.v_pages + slot * kHeadDim) + (lane - 16);
+                *d = lane < 16 ? raw : v_raw;
+            }
         }
     }
     HA_TL(kTlHashDecode, kTlExit);

@@ -581,12 +581,14 @@ static int hash_decode_impl(const ha_shape_t* shape, const ha_hash_weights_t* we
                  : cudaLaunchKernelEx(&cfg, hash_decode_batched_kernel<float>, p);
         return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
     }
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool pairs = p.batch_per_cta >= 2;  // two sequences of a CTA are evaluated together
     if (weights->dtype == HA_WEIGHTS_BF16)
-        e = launch(hash_decode_kernel<__nv_bfloat16>, grid, dim3(kHashDecodeThreads),
-                   static_cast<cudaStream_t>(stream), 1, p);
+        e = pairs ? launch(hash_decode_kernel<__nv_bfloat16, true>, grid, dim3(kHashDecodeThreads), st, 1, p)
+                  : launch(hash_decode_kernel<__nv_bfloat16, false>, grid, dim3(kHashDecodeThreads), st, 1, p);
     else
-        e = launch(hash_decode_kernel<float>, grid, dim3(kHashDecodeThreads),
-                   static_cast<cudaStream_t>(stream), 1, p);
+        e = pairs ? launch(hash_decode_kernel<float, true>, grid, dim3(kHashDecodeThreads), st, 1, p)
+                  : launch(hash_decode_kernel<float, false>, grid, dim3(kHashDecodeThreads), st, 1, p);
     return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 

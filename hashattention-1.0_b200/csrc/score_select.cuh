@@ -203,6 +203,14 @@ __device__ __forceinline__ Threshold pick_threshold(const SelectParams& p, int n
     return t;
 }
 
+// byte g of each of the 4 words, gathered into one word (byte w of the result = byte g of a[w])
+template <int NW>
+__device__ __forceinline__ uint32_t gather_byte(const uint32_t (&a)[NW], int g) {
+    static_assert(NW == 4, "four words");
+    const uint32_t sel = 0x0040u + 0x11u * g;  // bytes g of x (index g) and of y (index 4 + g)
+    return __byte_perm(__byte_perm(a[0], a[1], sel), __byte_perm(a[2], a[3], sel), 0x5410u);
+}
+
 // The plan of one (sequence, kv-head), worked out by one CTA of 256 threads (the one that published the unit's
 // last histogram). From the per-chunk histograms it derives the global threshold T and the tie quota of each
 // head, and for every chunk the number of selected tokens and of tied tokens that precede it.
@@ -397,28 +405,47 @@ __global__ void __launch_bounds__(kSelThreads, HA_SH_MIN_CTAS) score_hist_kernel
         cur.refresh_newest(p, kvh, t0, lane, r);
         bad_page |= cur.bad_page;
         uint32_t plane[kGroup] = {0u, 0u, 0u, 0u};  // per head: byte it = score + 1 of this lane's it-th token
+        if (cur.interior && p.scores_dbg == nullptr) {
+            // the common round: every token is a candidate. The four scores of a token are packed with byte
+            // permutes and the 4 x 4 bytes of the lane's tokens transposed at the end.
+            uint32_t tok[kLaneTokens];
 #pragma unroll
-        for (int it = 0; it < kLaneTokens; ++it) {
-            const uint32_t s0 = __popc(qn.x ^ cur.w[it].x), s1 = __popc(qn.y ^ cur.w[it].y);
-            const uint32_t s2 = __popc(qn.z ^ cur.w[it].z), s3 = __popc(qn.w ^ cur.w[it].w);
-            const bool is_cand = cur.interior || ((cur.cand >> it) & 1u);
-            if (is_cand) {
+            for (int it = 0; it < kLaneTokens; ++it) {
+                const uint32_t s0 = __popc(qn.x ^ cur.w[it].x), s1 = __popc(qn.y ^ cur.w[it].y);
+                const uint32_t s2 = __popc(qn.z ^ cur.w[it].z), s3 = __popc(qn.w ^ cur.w[it].w);
                 atomicAdd(h0 + s0, 1u);
                 atomicAdd(h0 + kBins + s1, 1u);
                 atomicAdd(h0 + 2 * kBins + s2, 1u);
                 atomicAdd(h0 + 3 * kBins + s3, 1u);
-                plane[0] |= (s0 + 1u) << (8 * it);
-                plane[1] |= (s1 + 1u) << (8 * it);
-                plane[2] |= (s2 + 1u) << (8 * it);
-                plane[3] |= (s3 + 1u) << (8 * it);
+                // bytes (s0, s1, s2, s3): byte 1 of a score register is zero and fills the unused positions
+                tok[it] = __byte_perm(__byte_perm(s0, s1, 0x1140u), __byte_perm(s2, s3, 0x1140u), 0x5410u) + 0x01010101u;
             }
-            if (p.scores_dbg != nullptr && ((cur.valid >> it) & 1u)) {
-                const size_t dpitch = (size_t)p.max_pages * kPage;
-                uint8_t* d = p.scores_dbg + ((size_t)b * Hq + kvh * kGroup) * dpitch + t0 + it * 32 + lane;
-                d[0] = (uint8_t)s0;
-                d[dpitch] = (uint8_t)s1;
-                d[2 * dpitch] = (uint8_t)s2;
-                d[3 * dpitch] = (uint8_t)s3;
+#pragma unroll
+            for (int g = 0; g < kGroup; ++g) plane[g] = gather_byte<kLaneTokens>(tok, g);
+        } else {
+#pragma unroll
+            for (int it = 0; it < kLaneTokens; ++it) {
+                const uint32_t s0 = __popc(qn.x ^ cur.w[it].x), s1 = __popc(qn.y ^ cur.w[it].y);
+                const uint32_t s2 = __popc(qn.z ^ cur.w[it].z), s3 = __popc(qn.w ^ cur.w[it].w);
+                const bool is_cand = cur.interior || ((cur.cand >> it) & 1u);
+                if (is_cand) {
+                    atomicAdd(h0 + s0, 1u);
+                    atomicAdd(h0 + kBins + s1, 1u);
+                    atomicAdd(h0 + 2 * kBins + s2, 1u);
+                    atomicAdd(h0 + 3 * kBins + s3, 1u);
+                    plane[0] |= (s0 + 1u) << (8 * it);
+                    plane[1] |= (s1 + 1u) << (8 * it);
+                    plane[2] |= (s2 + 1u) << (8 * it);
+                    plane[3] |= (s3 + 1u) << (8 * it);
+                }
+                if (p.scores_dbg != nullptr && ((cur.valid >> it) & 1u)) {
+                    const size_t dpitch = (size_t)p.max_pages * kPage;
+                    uint8_t* d = p.scores_dbg + ((size_t)b * Hq + kvh * kGroup) * dpitch + t0 + it * 32 + lane;
+                    d[0] = (uint8_t)s0;
+                    d[dpitch] = (uint8_t)s1;
+                    d[2 * dpitch] = (uint8_t)s2;
+                    d[3 * dpitch] = (uint8_t)s3;
+                }
             }
         }
         // the round after next takes this round's registers

@@ -211,15 +211,31 @@ def run_step_and_check(device, usa, q, ks, vs, budget, shuffle_seed=11, via_host
     return identical, out, ctx, cache
 
 
+def differing_code_bits(cache, ctx, case) -> int:
+    """Hash bits (keys and query) in which the device's codes differ from the recorded reference run. run_step_and_check
+    has already shown that every such bit lies inside the |x| < 1e-5 exclusion band; there may be a handful."""
+    n = 0
+    for b in range(case.k.shape[0]):
+        x = cache.read_codes(b).cpu() ^ case.k_codes[b]
+        n += int(sum(((x >> i) & 1).sum() for i in range(32)))
+    x = (ctx.q_codes.cpu().to(torch.int64) & ALL_BITS) ^ case.q_codes
+    return n + int(sum(((x >> i) & 1).sum() for i in range(32)))
+
+
+MAX_BAND_BITS = 32  # far more differing bits than the band can explain would mean a broken encoder, not rounding
+
+
 @pytest.mark.parametrize("name", ["case_a", "config0", "edge/short", "edge/p256", "edge/abs48"])
-def test_decode_step_end_to_end_against_reference_output(device, cases, name):
+def test_decode_step_end_to_end_against_reference_output(device, cases, name, record_property):
     case = get_case(cases, name)
     usa = synthetic.make_usa(case.q.shape[1], 128, 0, True)
     ks, vs = [case.k[b] for b in range(case.k.shape[0])], [case.v[b] for b in range(case.v.shape[0])]
     identical, out, ctx, cache = run_step_and_check(device, usa, case.q, ks, vs, budget_of(case))
-    codes_equal_ref = all(bool((cache.read_codes(b).cpu() == case.k_codes[b]).all()) for b in range(len(ks)))
-    codes_equal_ref &= bool(((ctx.q_codes.cpu().to(torch.int64) & ALL_BITS) == case.q_codes).all())
-    if codes_equal_ref:  # then everything downstream must equal the recorded reference run
+    n_diff = differing_code_bits(cache, ctx, case)
+    record_property("hash_bits_differing_from_reference", n_diff)
+    record_property("compared_with_reference_output", n_diff == 0)
+    assert n_diff <= MAX_BAND_BITS, f"{n_diff} hash bits differ from the reference run"
+    if n_diff == 0:  # then everything downstream must equal the recorded reference run
         want = orc.heavy_sets(case.mask, case.init, case.recent)
         for b in range(len(ks)):
             for h in range(case.q.shape[1]):
@@ -229,7 +245,7 @@ def test_decode_step_end_to_end_against_reference_output(device, cases, name):
 
 
 @pytest.mark.parametrize("name", ["d0", "d2", "d6", "neg", "big_hb", "abs5"])
-def test_depth_rule_step_against_reference_output(device, name):
+def test_depth_rule_step_against_reference_output(device, name, record_property):
     """usa_eval_mode != 'simple': variable-size sets with every tie kept (single-pass cluster
     selection at this size); against the oracle on the device's codes and, when those equal the
     reference's, against the recorded reference mask and output."""
@@ -239,9 +255,11 @@ def test_depth_rule_step_against_reference_output(device, name):
     ks, vs = [case.k[b] for b in range(case.k.shape[0])], [case.v[b] for b in range(case.v.shape[0])]
     budget = ha.Budget(case.init, c.heavy, case.recent, "depth", c.depth)
     _, out, ctx, cache = run_step_and_check(device, usa, case.q, ks, vs, budget)
-    codes_equal_ref = all(bool((cache.read_codes(b).cpu() == case.k_codes[b]).all()) for b in range(len(ks)))
-    codes_equal_ref &= bool(((ctx.q_codes.cpu().to(torch.int64) & ALL_BITS) == case.q_codes).all())
-    if codes_equal_ref:
+    n_diff = differing_code_bits(cache, ctx, case)
+    record_property("hash_bits_differing_from_reference", n_diff)
+    record_property("compared_with_reference_output", n_diff == 0)
+    assert n_diff <= MAX_BAND_BITS, f"{n_diff} hash bits differ from the reference run"
+    if n_diff == 0:
         want = orc.heavy_sets(c.mask, case.init, case.recent)
         for b in range(len(ks)):
             for h in range(case.q.shape[1]):
@@ -267,7 +285,7 @@ def test_depth_rule_on_the_scoring_plus_fused_selection_path(device, depth):
 
 @pytest.mark.parametrize("cluster_select", [-1, 0])
 @pytest.mark.parametrize("name", ["q5", "q16_page", "q3_short", "q4_depth"])
-def test_multi_token_decode_rows_against_reference_output(device, lib_option, name, cluster_select):
+def test_multi_token_decode_rows_against_reference_output(device, lib_option, name, cluster_select, record_property):
     """2 <= q_len <= 128 new tokens per sequence in one call (ha_decode_step_rows): every (sequence,
     token) is a row that sees the keys up to its own, with the budget of the whole length. Against
     the oracle on the device's codes and, when those equal the reference's, against the recorded
@@ -308,7 +326,12 @@ def test_multi_token_decode_rows_against_reference_output(device, lib_option, na
     ok, max_abs, rel = helpers.att_close(out, ref)
     assert ok, f"max_abs={max_abs:.3e} rel_l2={rel:.3e}"
     span = 2 * scores - 32
-    if torch.equal(span, c.span):   # same codes as the reference run: its own mask and output must come out
+    # (a key bit inside the exclusion band moves one span entry per row by 2, a query bit a whole row of them; the
+    # reference's span holds its mask value outside the causal part, which is not compared)
+    n_diff = int(((span != c.span) & c.causal).sum())
+    record_property("span_entries_differing_from_reference", n_diff)
+    record_property("compared_with_reference_output", n_diff == 0)
+    if n_diff == 0:   # same codes as the reference run: its own mask and output must come out
         assert torch.equal(mask, c.mask & c.causal)
         ok, max_abs, rel = helpers.att_close(out, c.out)
         assert ok, f"{name}: max_abs={max_abs:.3e} rel_l2={rel:.3e}"
