@@ -263,7 +263,6 @@ __device__ __forceinline__ uint4 load_x_row(const __nv_bfloat16* xrow, int lane)
 template <typename WT, bool kPairs>
 __global__ void __launch_bounds__(kHashDecodeThreads)
 hash_decode_kernel(const HashDecodeParams p) {
-    HA_TL(kTlHashDecode, kTlEntry);
     const int h = blockIdx.x;                // query head whose MLP this CTA evaluates
     const int side = blockIdx.y;             // 0 = query net, 1 = key net
     const int Hq = p.Hkv * kGroup;
@@ -275,7 +274,6 @@ hash_decode_kernel(const HashDecodeParams p) {
     __shared__ MlpSmem sm[2];
 
     pdl_wait();
-    HA_TL(kTlHashDecode, kTlAfterWait);
     pdl_launch_dependents();
 
     const int b_begin = blockIdx.z * p.batch_per_cta;
@@ -429,7 +427,6 @@ hash_decode_kernel(const HashDecodeParams p) {
             }
         }
     }
-    HA_TL(kTlHashDecode, kTlExit);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -536,7 +533,6 @@ __device__ __forceinline__ void hdb_hidden(HdbSmem& sm, const float (*wt)[kHidde
 template <typename WT>
 __global__ void __launch_bounds__(kHashDecodeThreads, 1)
 hash_decode_batched_kernel(const HashDecodeParams p) {
-    HA_TL(kTlHashDecode, kTlEntry);
     extern __shared__ __align__(16) unsigned char hdb_raw[];
     HdbSmem& sm = *reinterpret_cast<HdbSmem*>(hdb_raw);
     const int h = blockIdx.x, side = blockIdx.y;
@@ -547,7 +543,6 @@ hash_decode_batched_kernel(const HashDecodeParams p) {
     hdb_load_weights(sm, static_cast<const WT*>(p.w[side]) + (size_t)h * kMlpElems, p.bias[side] + (size_t)h * kMlpBias, tid);
 
     pdl_wait();
-    HA_TL(kTlHashDecode, kTlAfterWait);
     pdl_launch_dependents();
 
     const int b_begin = blockIdx.z * p.batch_per_cta;
@@ -621,7 +616,6 @@ hash_decode_batched_kernel(const HashDecodeParams p) {
             *dp = app;
         }
     }
-    HA_TL(kTlHashDecode, kTlExit);
 }
 
 // Prefill key-hash build on the CUDA cores, exact fp32 arithmetic: CTA (h, page, b) keeps the

@@ -1,51 +1,75 @@
-// Prefill key-hash build on the 5th-generation tensor cores (tcgen05, sm_100a only).
+// Prefill key-hash build on the 5th-generation tensor cores (tcgen05, sm_100a only), warp-specialised.
 //
 // For every cached key x (128 bf16) and every query head h of its kv-head the hash MLP
 //     code = signbits( W2 . silu( W1 . silu( W0 x + b0 ) + b1 ) + b2 )
 // is a chain of three GEMMs over a tile of 128 tokens. The (head, tile) pairs of a call, head-major, are cut
 // into one contiguous range per CTA (one CTA per SM, equal tile counts); a CTA keeps the three weight
 // matrices of its current head (72 KB bf16) in shared memory in the K-major 128-byte-swizzled layout the
-// UMMA shared-memory descriptors describe, reloads them where its range crosses into the next head, and
-// walks over its token tiles:
-//   1. the 128 x 128 key tile is copied into swizzled shared memory (it is contiguous in a page) by
-//      cp.async, one tile ahead of the arithmetic (two buffers),
-//   2. one thread issues tcgen05.mma (M = 128, N = 128, K = 16 per instruction, bf16 x bf16 -> fp32)
-//      into tensor memory and commits to an mbarrier,
-//   3. the 16 warps read the accumulator with tcgen05.ld (thread = token row, 16 columns at a time: first the
-//      columns 0..63, then 64..127, and the K-half of the next GEMM that reads the first half's activations is
-//      issued in between, so that it runs under the second half of the epilogue), add
-//      the bias, apply SiLU in fp32 and split the activation into a hi and a lo bf16 (hi + lo
-//      carries 16 mantissa bits), written back to swizzled shared memory as the next A operand,
-//   4. layer 2 runs two MMAs per k-step (hi and lo against the same weights), layer 3 likewise
-//      with N = 32, and the last epilogue packs the 32 sign bits of a token row into its code.
+// UMMA shared-memory descriptors describe, and reloads them where its range crosses into the next head.
+//
+// Roles of the 18 warps of a CTA:
+//   * warp 1, the loader: one thread copies the 128 x 128 key tile (two TMA box copies, written in the same
+//     swizzle) into a ring of four shared-memory buffers, up to four tiles ahead of the arithmetic;
+//   * warp 0, the issuer: one thread issues every tcgen05.mma of the CTA and commits to mbarriers;
+//   * warps 2-17, the epilogue: a thread owns one token row (its tensor-memory lane) and one 32-column slice of a
+//     hidden layer. It reads its accumulator columns (tcgen05.ld), adds the bias, applies SiLU in fp32, splits
+//     the activation into a hi and a lo bf16 (hi + lo carries 16 mantissa bits) and writes both back with
+//     tcgen05.st over the columns it has just read: the next GEMM takes its A operand from tensor memory (two
+//     MMAs per k-step, hi and lo against the same weights), so activations never pass through shared memory.
+//     The last epilogue packs the sign bits of a token row into its code.
+// Two tiles are in flight, one per slot of 256 tensor-memory columns (two regions of 128 that swap roles from
+// tile to tile: layer-0 accumulator and its activations in one, layer-1 accumulator and its activations in the
+// other, the 32 layer-2 columns back in the first). The epilogue warps alternate between the slots,
+//     layer 0 of a, layer 0 of b, layer 1 of a, layer 1 of b, codes of a, (next pair) layer 0 of a', codes of b, ...
+// and the issuer follows the same order, so the GEMM that a phase waits for was issued a whole phase earlier and
+// runs under the other tile's arithmetic.
+//
 // The hi/lo split keeps the pre-activations within ~3e-6 of fp32 arithmetic, which is what makes
 // the packed codes match the reference bit for bit outside the |x| < 1e-5 band.
 //
 // Follows USA.k_embedding(hard=True) (hashattention/hashattention_llama.py:204-214).
 //
-// Every wait on the mbarrier is bounded: if a commit never arrives the CTA records
-// HA_ERR_TIMEOUT, stops issuing work, frees its tensor memory and returns.
+// Every wait is bounded: if a barrier never completes, the waiting thread records HA_ERR_TIMEOUT and raises a
+// CTA-wide flag that ends every other wait; the CTA then waits (bounded) for the tensor core and its copies,
+// frees its tensor memory and returns.
 #pragma once
+
+#include <cuda.h>  // CUtensorMap (the type only: the encoder is looked up at run time)
 
 #include "common.cuh"
 
 namespace ha {
 
-constexpr int kTcThreads = 512;
+constexpr int kTcEpiWarps = 16;                       // four 32-column slices x four quarters of the 128 tensor-memory lanes
+constexpr int kTcEpiThreads = kTcEpiWarps * 32;
+constexpr int kTcMmaWarp = 0;
+constexpr int kTcLoadWarp = 1;
+constexpr int kTcEpiWarp0 = 2;                        // epilogue warps kTcEpiWarp0 .. kTcEpiWarp0 + kTcEpiWarps - 1
+constexpr int kTcThreads = (kTcEpiWarps + 2) * 32;
 constexpr int kTcTile = 128;                          // tokens per tile = TMEM lanes
+constexpr int kTcXBufs = 4;                           // key-tile ring
 constexpr uint32_t kTcBlockBytes = 128 * 128;         // one K-half of a 128-row operand: 128 rows x 128 B
 constexpr uint32_t kTcW2BlockBytes = 32 * 128;        // one K-half of W2 (32 rows)
 constexpr uint32_t kTcOffW0 = 0;
 constexpr uint32_t kTcOffW1 = kTcOffW0 + 2 * kTcBlockBytes;
 constexpr uint32_t kTcOffW2 = kTcOffW1 + 2 * kTcBlockBytes;
-constexpr uint32_t kTcOffX = kTcOffW2 + 2 * kTcW2BlockBytes;           // two key-tile buffers (double buffering)
-constexpr uint32_t kTcOffHi = kTcOffX + 4 * kTcBlockBytes;
-constexpr uint32_t kTcOffLo = kTcOffHi + 2 * kTcBlockBytes;
-constexpr uint32_t kTcOffBias = kTcOffLo + 2 * kTcBlockBytes;          // 288 floats
-constexpr uint32_t kTcOffBar = kTcOffBias + 1280;                      // mbarrier (8 B) + tmem base (4 B)
-constexpr uint32_t kTcSmemBytes = kTcOffBar + 64 + 1024;               // + slack to align the base to 1024 B
+constexpr uint32_t kTcOffX = kTcOffW2 + 2 * kTcW2BlockBytes;
+constexpr uint32_t kTcOffBias = kTcOffX + kTcXBufs * 2 * kTcBlockBytes;  // 288 floats
+constexpr uint32_t kTcOffBar = kTcOffBias + 1280;
+// mbarriers (8 bytes each), by index
+constexpr int kTcBarXFull = 0;                        // [kTcXBufs] the loader's expect-tx arrival + the bytes of the two copies
+constexpr int kTcBarXEmpty = kTcBarXFull + kTcXBufs;  // [kTcXBufs] commit: layer 0 has read the tile
+constexpr int kTcBarAcc = kTcBarXEmpty + kTcXBufs;    // [2 slots][3 layers] commit: accumulator complete
+constexpr int kTcBarAct = kTcBarAcc + 6;              // [2 slots] 16 warps: the activations of a hidden layer are written
+constexpr int kTcBarDrained = kTcBarAct + 2;          // 16 epilogue warps + issuer: no GEMM reads the old weights any more
+constexpr int kTcBarWeights = kTcBarDrained + 1;      // 16 epilogue warps: the next head's weights are in place
+constexpr int kTcBarFinal = kTcBarWeights + 1;        // commit: every GEMM of the CTA has completed
+constexpr int kTcNumBars = kTcBarFinal + 1;
+constexpr uint32_t kTcOffTmem = kTcOffBar + 8 * 32;   // tmem base (4 B), abort flag (4 B)
+constexpr uint32_t kTcSmemBytes = kTcOffTmem + 64 + 1024;  // + slack to align the base to 1024 B
+static_assert(kTcNumBars <= 32, "barrier block");
+static_assert(kTcSmemBytes <= 227 * 1024, "shared memory of one CTA");
 constexpr uint32_t kTcTmemCols = 512;
-constexpr uint32_t kTcColD1 = 0, kTcColD2 = 128, kTcColD3 = 256;
 constexpr int kTcSpinLimit = 1 << 22;
 
 struct HashPrefillTcParams {
@@ -69,17 +93,25 @@ __device__ __forceinline__ uint32_t tc_swizzled(uint32_t row, uint32_t chunk) {
     return (row >> 3) * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
 }
 
-// Shared-memory matrix descriptor: K-major, SWIZZLE_128B, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+// Shared-memory matrix descriptor (K-major, SWIZZLE_128B, 8-row groups 1024 B apart) in two parts: only the low word
+// depends on the address, and the descriptor of a later k-step of the operand follows by adding the k-step's offset in
+// 16-byte units (the sum stays inside the address field).
+__device__ __forceinline__ uint32_t tc_desc_lo(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ uint64_t tc_desc(uint32_t lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(64u | (1u << 14) | (2u << 29)));
+    return d;
 }
+// k-step ks (16 inputs = 32 bytes of the 128-byte rows, four per K-half block) of an operand, in 16-byte units
+__host__ __device__ constexpr uint32_t tc_koff(uint32_t ks, uint32_t block_bytes) { return (ks >> 2) * (block_bytes >> 4) + (ks & 3) * 2; }
 
 // Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t tc_idesc(uint32_t n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+// D (tensor memory) (+)= A (shared memory) . B (shared memory)
+__device__ __forceinline__ void tc_mma_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
@@ -89,12 +121,38 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_
         : "memory");
 }
 
+// D (tensor memory) (+)= A (tensor memory: lane = row, two bf16 per column, K = 16 in 8 columns) . B (shared memory)
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t"
+        "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// Bounded wait for phase `parity` of the mbarrier; false if it ran out.
-__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ void tc_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Has phase `parity` of the mbarrier completed? (does not block)
+__device__ __forceinline__ bool tc_test(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+
+// Bounded wait for phase `parity` of the mbarrier; false if it ran out or another thread of the CTA gave up.
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
     for (int spin = 0; spin < kTcSpinLimit; ++spin) {
         uint32_t done;
         asm volatile(
@@ -103,25 +161,16 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity) {
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) return true;
+        if (*abort_flag != 0) return false;
     }
+    report(status, HA_ERR_TIMEOUT);
+    *abort_flag = 1;
     return false;
 }
 
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
+// 32 accumulator columns of this thread's lane: issue, and the wait that makes the registers readable. The wait takes
+// the registers as operands, so that nothing that reads them can be scheduled in front of it.
+__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -131,97 +180,217 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tc_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :: "memory");
+    asm volatile(""
+                 : "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
 }
 
+// 8 columns of this thread's lane, complete on return.
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+                 :: "memory");
+}
+
+// 32 columns of this thread's lane written to tensor memory; returns when the write has completed.
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};\n"
+        :: "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+           "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// TMA: the box at element column x, row y of the key cache -> shared memory, bytes counted on the mbarrier (the
+// copy reads this GPU's memory only and is not multicast).
+__device__ __forceinline__ void tc_tma_load(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// two fp32 -> one word of two bf16 (round to nearest even): a in the low half, b in the high half
 __device__ __forceinline__ uint32_t tc_pack_bf16(float a, float b) {
-    const __nv_bfloat162 t = __floats2bfloat162_rn(a, b);  // .x = a (low half), .y = b
-    return *reinterpret_cast<const uint32_t*>(&t);
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+    return d;
 }
 
 // Copies `rows` rows of 128 bf16 (row-major, 256 B apart in global memory) into the two K-half
-// blocks of a swizzled operand; block_bytes = rows * 128.
+// blocks of a swizzled operand; block_bytes = rows * 128. Thread t of n.
 __device__ __forceinline__ void tc_load_operand(unsigned char* dst, const __nv_bfloat16* src, int rows,
-                                                uint32_t block_bytes, int tid) {
-    for (int i = tid; i < rows * 16; i += kTcThreads) {
+                                                uint32_t block_bytes, int t, int n) {
+    for (int i = t; i < rows * 16; i += n) {
         const int row = i >> 4, c16 = i & 15;  // c16: 16-byte chunk of the 256-byte row
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(src + (size_t)row * kHeadDim) + c16);
         *reinterpret_cast<uint4*>(dst + (c16 >> 3) * block_bytes + tc_swizzled(row, c16 & 7)) = v;
     }
 }
 
-// bias + SiLU + hi/lo split of 16 accumulator columns (chunks chunk0, chunk0 + 1 of one K-half block).
-__device__ __forceinline__ void tc_hidden_epilogue(uint32_t taddr, const float* bias, unsigned char* hi_blk,
-                                                   unsigned char* lo_blk, uint32_t row, uint32_t chunk0) {
-    float v[16];
-    tc_ld16(taddr, v);
+// bias + SiLU + hi/lo split of 32 accumulator columns v (bit patterns of fp32) of one row. The 32 words that take
+// their place are the A operand of two k-steps of the next GEMM: words 0..7 hold the hi halves of activations
+// 0..15 (two per word, the even one in the low half), 8..15 their lo halves, 16..23 and 24..31 those of 16..31.
+__device__ __forceinline__ void tc_activate32(const uint32_t (&v)[32], const float* bias, uint32_t (&out)[32]) {
+    const f32x2 nlog2e = pack2(-1.4426950408889634f, -1.4426950408889634f), one = pack2(1.0f, 1.0f);
+    const f32x2 minus1 = pack2(-1.0f, -1.0f);
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {  // 2 chunks of 8 columns
-        uint32_t hi[4], lo[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            float a[2];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int col = c * 8 + e * 2 + j;
-                const float x = v[col] + bias[col];
-                // SiLU with the hardware exp2 / reciprocal (relative error ~1e-6, well below the
-                // 2^-17 that the hi/lo split itself leaves)
-                float e, r;  // exactly one exp2 and one reciprocal instruction per activation
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
-                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
-                a[j] = x * r;
-            }
-            hi[e] = tc_pack_bf16(a[0], a[1]);  // one paired conversion; the rounded values are read back by shifts
-            const float h0 = __uint_as_float(hi[e] << 16), h1 = __uint_as_float(hi[e] & 0xffff0000u);
-            lo[e] = tc_pack_bf16(a[0] - h0, a[1] - h1);
+    for (int pr = 0; pr < 16; ++pr) {
+        const float2 bb = *reinterpret_cast<const float2*>(bias + 2 * pr);  // the same address in every lane: a broadcast
+        const f32x2 x = add2(pack2(__uint_as_float(v[2 * pr]), __uint_as_float(v[2 * pr + 1])), pack2(bb.x, bb.y));
+        float t0, t1;
+        unpack2(mul2(x, nlog2e), t0, t1);
+        // SiLU x / (1 + e^-x) with the hardware exp2 and ONE reciprocal for the pair: 1 / (a0 a1) times a1 and a0.
+        // e is held below 2^60 so that the product stays finite (the activation is below 1e-16 in magnitude there).
+        float e0, e1, r;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(fminf(t0, 60.0f)));
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(fminf(t1, 60.0f)));
+        float a0, a1;
+        unpack2(add2(pack2(e0, e1), one), a0, a1);
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a0 * a1));
+        const f32x2 y = mul2(x, mul2(pack2(a1, a0), pack2(r, r)));
+        float y0, y1;
+        unpack2(y, y0, y1);
+        const uint32_t hi = tc_pack_bf16(y0, y1);
+        float l0, l1;
+        unpack2(fma2(pack2(bf16_lo(hi), bf16_hi(hi)), minus1, y), l0, l1);  // y - hi, exact
+        const int w = (pr >> 3) * 16 + (pr & 7);
+        out[w] = hi;
+        out[w + 8] = tc_pack_bf16(l0, l1);
+    }
+}
+
+// The (head, token tile) pairs of the whole call, head-major and counting only tiles that hold tokens to encode,
+// are cut into gridDim.x equal contiguous ranges: every SM gets the same number of tiles whatever the number of
+// heads. A cursor walks over the tiles of this CTA's range; every value is CTA-uniform, so each role runs its own.
+struct TcItem {
+    int h, S, first, t0, store;
+    size_t slot0;  // (page * Hkv + kv head) * page size + offset of the tile's first token
+};
+struct TcCursor {
+    const HashPrefillTcParams& p;
+    long long per_head, g0, total;  // tiles to encode per head; this CTA's first tile; its number of tiles
+    int h, b, tile, hi, S, first;
+    bool reporter;
+
+    // A sequence's tiles to encode: [first_token / 128, ceil(S / 128)); none if its length is out of range.
+    __device__ void seq_tiles(int bb, int& S_, int& first_, int& lo, int& hi_) const {
+        S_ = __ldg(p.seq_lens + bb);
+        first_ = p.first_token != nullptr ? max(0, __ldg(p.first_token + bb)) : 0;
+        if (S_ < 0 || S_ > p.max_pages * kPage) {
+            if (reporter) report(p.status, HA_ERR_BAD_SEQ_LEN);
+            S_ = 0;
         }
-        const uint32_t off = tc_swizzled(row, chunk0 + c);
-        *reinterpret_cast<uint4*>(hi_blk + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4*>(lo_blk + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        lo = first_ / kTcTile;
+        hi_ = max(lo, (S_ + kTcTile - 1) / kTcTile);
     }
-}
-
-// Asynchronous copy (cp.async, 16 bytes per request) of a 128-token key tile into a swizzled buffer.
-__device__ __forceinline__ void tc_prefetch_tile(unsigned char* dst, const __nv_bfloat16* src, int tid) {
-    for (int i = tid; i < kTcTile * 16; i += kTcThreads) {
-        const int row = i >> 4, c16 = i & 15;
-        const uint32_t d = tc_smem_u32(dst + (c16 >> 3) * kTcBlockBytes + tc_swizzled(row, c16 & 7));
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + (size_t)row * kHeadDim + c16 * 8) : "memory");
+    __device__ TcCursor(const HashPrefillTcParams& p_, bool reporter_) : p(p_), reporter(reporter_) {
+        const int Hq = p.Hkv * kGroup;
+        per_head = 0;
+        for (int bb = 0; bb < p.B; ++bb) {
+            int S_, first_, lo, hi_;
+            seq_tiles(bb, S_, first_, lo, hi_);
+            per_head += hi_ - lo;
+        }
+        const long long all = per_head * Hq;
+        g0 = all * blockIdx.x / gridDim.x;
+        total = all * (blockIdx.x + 1) / gridDim.x - g0;
+        h = per_head > 0 ? (int)(g0 / per_head) : 0;
+        long long skip = per_head > 0 ? g0 % per_head : 0;  // tiles of head h in front of this CTA's range
+        b = 0;
+        tile = hi = S = first = 0;
+        for (int bb = 0; bb < p.B && total > 0; ++bb) {
+            int S_, first_, lo, hi_;
+            seq_tiles(bb, S_, first_, lo, hi_);
+            if (skip < hi_ - lo) {
+                b = bb; S = S_; first = first_; tile = lo + (int)skip; hi = hi_;
+                break;
+            }
+            skip -= hi_ - lo;
+        }
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-}
+    // Is local tile i the first one of a head (other than the CTA's first tile)? The weights change in front of it.
+    __device__ bool head_starts_at(long long i) const { return i > 0 && (g0 + i) % per_head == 0; }
+    __device__ int head_of(long long i) const { return (int)((g0 + i) / per_head); }
+    // The next tile (to be called `total` times). A tile on a bad page is reported, read from page 0 and not stored.
+    __device__ TcItem next() {
+        const int Hq = p.Hkv * kGroup;
+        for (int guard = 0; tile >= hi && guard <= p.B * Hq; ++guard) {  // on to the next sequence, or the next head
+            if (++b >= p.B) {
+                b = 0;
+                ++h;
+            }
+            int lo;
+            seq_tiles(b, S, first, lo, hi);
+            tile = lo;
+        }
+        TcItem it;
+        it.h = min(h, Hq - 1); it.S = S; it.first = first; it.t0 = tile * kTcTile; it.store = tile < hi ? 1 : 0;
+        int page = __ldg(p.page_table + (size_t)b * p.max_pages + min(it.t0 / kPage, p.max_pages - 1));
+        ++tile;
+        if (page < 0 || page >= p.num_pages) {
+            if (reporter) report(p.status, HA_ERR_BAD_PAGE);
+            page = 0;
+            it.store = 0;
+        }
+        it.slot0 = ((size_t)page * p.Hkv + it.h / kGroup) * kPage + it.t0 % kPage;
+        return it;
+    }
+};
 
-__global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const HashPrefillTcParams p) {
+__global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const HashPrefillTcParams p,
+                                                                        const __grid_constant__ CUtensorMap k_map) {
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
     float* s_bias = reinterpret_cast<float*>(smem + kTcOffBias);
-    unsigned long long* s_bar = reinterpret_cast<unsigned long long*>(smem + kTcOffBar);
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kTcOffBar + 16);
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kTcOffTmem);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kTcOffTmem + 4);
+    const uint32_t sbase = tc_smem_u32(smem);
+    const uint32_t bars = sbase + kTcOffBar;
+    auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
 
-    // The (head, token tile) pairs of the whole call, head-major and counting only tiles that hold tokens to
-    // encode, are cut into gridDim.x equal contiguous ranges: every SM gets the same number of tiles whatever the
-    // number of heads, and a CTA changes head (reloads the 72 KB of weights) at most once per head boundary it
-    // spans. The first head of a CTA follows from its index alone, so its weights are fetched before the
-    // dependency wait.
-    auto load_head = [&](int h) {
+    // The weights of head h, by thread t of n. The first head of a CTA follows from its index alone, so its weights
+    // are fetched before the dependency wait.
+    auto load_head = [&](int h, int t, int n) {
         const __nv_bfloat16* W = p.wk + (size_t)h * kMlpElems;
-        tc_load_operand(smem + kTcOffW0, W, 128, kTcBlockBytes, tid);
-        tc_load_operand(smem + kTcOffW1, W + kHidden * kHeadDim, 128, kTcBlockBytes, tid);
-        tc_load_operand(smem + kTcOffW2, W + kHidden * kHeadDim + kHidden * kHidden, 32, kTcW2BlockBytes, tid);
-        for (int i = tid; i < kMlpBias; i += kTcThreads) s_bias[i] = p.bk[(size_t)h * kMlpBias + i];
+        tc_load_operand(smem + kTcOffW0, W, 128, kTcBlockBytes, t, n);
+        tc_load_operand(smem + kTcOffW1, W + kHidden * kHeadDim, 128, kTcBlockBytes, t, n);
+        tc_load_operand(smem + kTcOffW2, W + kHidden * kHeadDim + kHidden * kHidden, 32, kTcW2BlockBytes, t, n);
+        for (int i = t; i < kMlpBias; i += n) s_bias[i] = p.bk[(size_t)h * kMlpBias + i];
     };
-    int loaded_h = (int)(((long long)blockIdx.x * Hq) / gridDim.x);
-    load_head(loaded_h);
+    load_head((int)(((long long)blockIdx.x * Hq) / gridDim.x), tid, kTcThreads);
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(s_bar)));
+        auto init = [&](int first, int n, uint32_t count) {
+            for (int i = first; i < first + n; ++i)
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar(i)), "r"(count));
+        };
+        init(kTcBarXFull, kTcXBufs, 1);
+        init(kTcBarXEmpty, kTcXBufs, 1);
+        init(kTcBarAcc, 6, 1);
+        init(kTcBarAct, 2, kTcEpiWarps);
+        init(kTcBarDrained, 1, kTcEpiWarps + 1);
+        init(kTcBarWeights, 1, kTcEpiWarps);
+        init(kTcBarFinal, 1, 1);
+        *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {
+    if (warp == kTcMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(s_tmem)), "r"(kTcTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -230,223 +399,203 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *s_tmem;
-    const uint32_t bar = tc_smem_u32(s_bar);
-    const uint32_t sbase = tc_smem_u32(smem);
-    const uint32_t idesc128 = tc_idesc(128), idesc32 = tc_idesc(32);
-    // this thread's accumulator slice: TMEM lanes 32 (warp % 4) .. +31, columns 32 (warp / 4) .. +31
-    // in each half of a hidden epilogue: TMEM lanes 32 (warp % 4) .. +31, columns 64 half + 16 (warp / 4) .. +15
-    const uint32_t row = (warp & 3) * 32 + lane, cq = warp >> 2;  // cq: group of 16 columns inside a half, 0..3
-    const uint32_t chunk0 = cq * 2;                                // first 16-byte chunk inside the K-half block
-    const uint32_t t_lane = ((warp & 3) * 32u) << 16;
-    uint32_t phase = 0;
-
-    // one K = 128 GEMM: 8 k-steps of 16 (32 bytes inside the swizzled 128-byte rows, 4 per K-half)
-    auto gemm = [&](uint32_t col_d, uint32_t off_a, uint32_t off_b, uint32_t b_block_bytes, uint32_t idesc, bool first) {
-#pragma unroll
-        for (uint32_t ks = 0; ks < 8; ++ks) {
-            const uint32_t a = sbase + off_a + (ks >> 2) * kTcBlockBytes + (ks & 3) * 32;
-            const uint32_t bb = sbase + off_b + (ks >> 2) * b_block_bytes + (ks & 3) * 32;
-            tc_mma(tmem + col_d, tc_smem_desc(a), tc_smem_desc(bb), idesc, (first && ks == 0) ? 0u : 1u);
-        }
-    };
-    // the k-steps of one K-half (half = 0: inputs 0..63, 1: inputs 64..127) of such a GEMM
-    auto gemm_half = [&](uint32_t col_d, uint32_t off_a, uint32_t off_b, uint32_t b_block_bytes, uint32_t idesc,
-                         uint32_t half, bool first) {
-#pragma unroll
-        for (uint32_t ks = 0; ks < 4; ++ks) {
-            const uint32_t a = sbase + off_a + half * kTcBlockBytes + ks * 32;
-            const uint32_t bb = sbase + off_b + half * b_block_bytes + ks * 32;
-            tc_mma(tmem + col_d, tc_smem_desc(a), tc_smem_desc(bb), idesc, (first && ks == 0) ? 0u : 1u);
-        }
-    };
-    // Waits (bounded) for the commit of the GEMMs just issued, then agrees CTA-wide on the outcome,
-    // so that the warp-synchronous tensor-memory loads that follow are never executed by a part of
-    // the CTA only. Returns false for every thread if any thread's wait ran out.
-    auto wait_commit = [&]() -> bool {
-        const bool ok = tc_wait(bar, phase);
-        if (!ok) report(p.status, HA_ERR_TIMEOUT);
-        phase ^= 1;
-        const bool all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        return all_ok;
-    };
-    bool aborted = false;
     pdl_wait();  // the weights above are constants; everything below may depend on the previous kernel
 
-    // A sequence's tiles to encode: [first_token / 128, ceil(S / 128)); none if its length is out of range.
-    struct Item { int valid, h, S, first, t0; size_t slot0; };
-    struct Cursor { int h, b, tile, hi, S, first; long long left; };
-    auto seq_tiles = [&](int b, int& S, int& first, int& lo, int& hi) {
-        S = __ldg(p.seq_lens + b);
-        first = p.first_token != nullptr ? max(0, __ldg(p.first_token + b)) : 0;
-        if (S < 0 || S > p.max_pages * kPage) {
-            if (tid == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
-            S = 0;
-        }
-        lo = first / kTcTile;
-        hi = max(lo, (S + kTcTile - 1) / kTcTile);
-    };
-    Cursor cs;
-    {
-        long long per_head = 0;  // tiles to encode per head
-        for (int b = 0; b < p.B; ++b) {
-            int S, first, lo, hi;
-            seq_tiles(b, S, first, lo, hi);
-            per_head += hi - lo;
-        }
-        const long long total = per_head * Hq;
-        const long long g0 = total * blockIdx.x / gridDim.x, g1 = total * (blockIdx.x + 1) / gridDim.x;
-        cs.left = g1 - g0;
-        cs.h = per_head > 0 ? (int)(g0 / per_head) : 0;
-        long long skip = per_head > 0 ? g0 % per_head : 0;  // tiles of head cs.h in front of this CTA's range
-        cs.b = 0;
-        cs.tile = cs.hi = cs.S = cs.first = 0;
-        for (int b = 0; b < p.B && cs.left > 0; ++b) {
-            int S, first, lo, hi;
-            seq_tiles(b, S, first, lo, hi);
-            if (skip < hi - lo) {
-                cs.b = b; cs.S = S; cs.first = first; cs.tile = lo + (int)skip; cs.hi = hi;
-                break;
-            }
-            skip -= hi - lo;
-        }
-    }
-    // The next tile of this CTA's range (all inputs are CTA-uniform). A tile on a bad page is reported and skipped.
-    auto next_item = [&]() {
-        Item it;
-        it.valid = 0; it.h = 0; it.S = 0; it.first = 0; it.t0 = 0; it.slot0 = 0;
-        while (cs.left > 0) {
-            if (cs.tile >= cs.hi) {  // on to the next sequence, or to the first one of the next head
-                if (++cs.b >= p.B) {
-                    cs.b = 0;
-                    ++cs.h;
-                }
-                int lo;
-                seq_tiles(cs.b, cs.S, cs.first, lo, cs.hi);
-                cs.tile = lo;
-                continue;
-            }
-            const int t0 = cs.tile * kTcTile;
-            const int page = __ldg(p.page_table + (size_t)cs.b * p.max_pages + t0 / kPage);
-            ++cs.tile;
-            --cs.left;
-            if (page < 0 || page >= p.num_pages) {
-                if (tid == 0) report(p.status, HA_ERR_BAD_PAGE);
-                continue;
-            }
-            it.valid = 1; it.h = cs.h; it.S = cs.S; it.first = cs.first; it.t0 = t0;
-            it.slot0 = ((size_t)page * p.Hkv + cs.h / kGroup) * kPage + t0 % kPage;
-            return it;
-        }
-        return it;
+    // every lane waits for itself; the warp then agrees, so that the warp-wide instructions that follow are never
+    // executed by a part of it
+    auto wait = [&](int b, uint32_t parity) {
+        const bool ok = tc_wait(bar(b), parity, s_abort, p.status);
+        return __all_sync(0xffffffffu, ok) != 0;
     };
 
-    // what the epilogue (or cp.async) wrote becomes visible to the tensor core; the accumulator reads are done
-    auto publish = [&]() {
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncthreads();
-    };
-    // layer 0 of a tile whose keys sit in key buffer `buf`: D1 = X W0^T (waits for the keys first)
-    auto start_tile = [&](uint32_t buf) {
-        asm volatile("cp.async.wait_all;" ::: "memory");
-        publish();
-        if (tid == 0) {
+    if (warp >= kTcEpiWarp0) {
+        // ---- epilogue warps ----------------------------------------------------------------------------------
+        // (a warp reaches the tensor-memory lanes 32 (warp % 4) .. + 31; any 16 consecutive warps cover each quarter 4 times)
+        const uint32_t sl = (uint32_t)(warp - kTcEpiWarp0) >> 2;  // this warp's 32-column slice of a hidden layer
+        const uint32_t row = (uint32_t)(warp & 3) * 32 + lane;    // token row of the tile = tensor-memory lane
+        const uint32_t t_base = tmem + (((uint32_t)(warp & 3) * 32u) << 16);
+        TcCursor cur(p, false);
+        const long long total = cur.total;
+        uint32_t cnt[2] = {0, 0}, changes = 0;  // tiles worked on per slot; head changes seen
+        bool ok = true;
+        // a hidden layer of the tile in `slot`: accumulator -> hi/lo activations in place (layer 0 works in the slot's
+        // region cnt & 1, layer 1 in the other one)
+        auto hidden = [&](uint32_t slot, uint32_t layer) {
+            if (!wait(kTcBarAcc + 3 * (int)slot + (int)layer, cnt[slot] & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            gemm(kTcColD1, kTcOffX + buf * 2 * kTcBlockBytes, kTcOffW0, kTcBlockBytes, idesc128, true);
-            tc_commit(bar);
-        }
-    };
-    // bias + SiLU + hi/lo split of this thread's 16 columns in half `half` of accumulator col_d
-    auto hidden = [&](uint32_t col_d, const float* bias, uint32_t half) {
-        const uint32_t c0 = half * 64 + cq * 16;
-        tc_hidden_epilogue(tmem + t_lane + col_d + c0, bias + c0, smem + kTcOffHi + half * kTcBlockBytes,
-                           smem + kTcOffLo + half * kTcBlockBytes, row, chunk0);
-    };
-    auto codes = [&](const Item& it) {  // thread = token row: 32 pre-activations -> one packed code
-        if (warp >= 4) return;
-        float v[32];
-        tc_ld32(tmem + t_lane + kTcColD3, v);
-        uint32_t code = 0;
+            const uint32_t col = slot * 256u + ((cnt[slot] & 1) ^ layer) * 128u + 32u * sl;
+            uint32_t r[32], out[32];
+            tc_ld32_issue(t_base + col, r);
+            tc_ld_wait(r);
+            tc_activate32(r, s_bias + layer * kHidden + 32 * sl, out);
+            tc_st32(t_base + col, out);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc_arrive(bar(kTcBarAct + (int)slot));
+            return true;
+        };
+        // the codes of the tile in `slot`: thread = token row, each of the row's four warps packs 8 of the 32 sign bits
+        auto codes = [&](uint32_t slot, const TcItem& it) {
+            if (!wait(kTcBarAcc + 3 * (int)slot + 2, cnt[slot] & 1)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t r[8];
+            tc_ld8(t_base + slot * 256u + (cnt[slot] & 1) * 128u + 8u * sl, r);
+            uint32_t code = 0;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) code |= (v[i] + s_bias[2 * kHidden + i] > 0.0f ? 1u : 0u) << i;
-        const int t = it.t0 + (int)row;
-        if (t < it.S && t >= it.first) p.hash_pages[(it.slot0 + row) * kGroup + it.h % kGroup] = code;
-    };
-
-    Item cur = next_item();
-    if (cur.valid) {
-        tc_prefetch_tile(smem + kTcOffX, p.k_pages + cur.slot0 * kHeadDim, tid);
-        if (cur.h != loaded_h) {  // (cannot happen for the first tile of a range; kept for safety)
-            __syncthreads();
-            loaded_h = cur.h;
-            load_head(loaded_h);
+            for (int k = 0; k < 8; ++k) code |= (__uint_as_float(r[k]) + s_bias[2 * kHidden + 8 * sl + k] > 0.0f ? 1u : 0u) << k;
+            const int t = it.t0 + (int)row;
+            if (it.store && t < it.S && t >= it.first)
+                reinterpret_cast<uint8_t*>(p.hash_pages)[((it.slot0 + row) * kGroup + it.h % kGroup) * 4 + sl] = (uint8_t)code;
+            ++cnt[slot];
+            return true;
+        };
+        // The tiles of a head are worked on in pairs, one tile per slot, in the order
+        //     layer 0 of a, [codes of the previous pair's b], layer 0 of b, layer 1 of a, layer 1 of b, codes of a
+        // so that the GEMM a phase waits for was issued at least one whole phase earlier.
+        for (long long s0 = 0; s0 < total && ok;) {
+            const long long s1 = min(total, s0 + cur.per_head - (cur.g0 + s0) % cur.per_head);  // end of this head's tiles
+            if (s0 > 0) {
+                // the weights change: the issuer and every epilogue warp meet (all GEMMs of the old head have completed),
+                // then the epilogue warps load together
+                __syncwarp();
+                if (lane == 0) tc_arrive(bar(kTcBarDrained));
+                if (!(ok = wait(kTcBarDrained, changes & 1))) break;
+                load_head(cur.head_of(s0), tid - kTcEpiWarp0 * 32, kTcEpiThreads);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) tc_arrive(bar(kTcBarWeights));
+                if (!(ok = wait(kTcBarWeights, changes & 1))) break;
+                ++changes;
+            }
+            TcItem it_a, it_b, it_pend;
+            bool pend = false;
+            for (long long a = s0; a < s1 && ok; a += 2) {
+                const bool has_b = a + 1 < s1;
+                it_a = cur.next();  // (the page-table reads complete under the arithmetic: the items are used by the codes)
+                if (has_b) it_b = cur.next();
+#pragma unroll 1
+                for (uint32_t ph = 0; ph < 4 && ok; ++ph) {
+                    const uint32_t slot = ph & 1;
+                    if (slot == 0 || has_b) ok = hidden(slot, ph >> 1);
+                    if (ok && ph == 0 && pend) ok = codes(1, it_pend);
+                    if (ok && ph == 3) ok = codes(0, it_a);
+                }
+                pend = has_b;
+                it_pend = it_b;
+            }
+            if (ok && pend) ok = codes(1, it_pend);
+            s0 = s1;
         }
-        start_tile(0);
+    } else if (warp == kTcMmaWarp) {
+        // ---- issuer ------------------------------------------------------------------------------------------
+        // One thread issues every tcgen05.mma of the CTA, in the order in which the epilogue warps finish their phases.
+        // The whole warp runs the loop with the same values in every lane (the operands of tcgen05.mma are warp-
+        // uniform); lane 0 alone issues.
+        const TcCursor cur0(p, false);
+        const int total = __shfl_sync(0xffffffffu, (int)cur0.total, 0);
+        const int per_head = __shfl_sync(0xffffffffu, (int)cur0.per_head, 0);
+        const int first_end = __shfl_sync(0xffffffffu, cur0.per_head > 0 ? (int)(cur0.per_head - cur0.g0 % cur0.per_head) : 0, 0);
+        const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+        const bool issue = lane == 0;
+        const uint32_t w0_lo = tc_desc_lo(sbase + kTcOffW0), w1_lo = tc_desc_lo(sbase + kTcOffW1);
+        const uint32_t w2_lo = tc_desc_lo(sbase + kTcOffW2), x_lo = tc_desc_lo(sbase + kTcOffX);
+        // accumulator regions of a slot's current tile: layer 0 (and layer 2) in d_a, layer 1 in d_b; they swap per tile
+        uint32_t d_a[2] = {tmem_u, tmem_u + 256u}, d_b[2] = {tmem_u + 128u, tmem_u + 384u};
+        uint32_t changes = 0;
+        bool ok = true;
+        // layer 0 of tile i into its slot: D1 = X W0^T
+        auto layer0 = [&](int i, int slot) {
+            const uint32_t buf = (uint32_t)i % kTcXBufs;
+            if (!wait(kTcBarXFull + (int)buf, ((uint32_t)i / kTcXBufs) & 1)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (issue) {
+                const uint32_t xb = x_lo + buf * (2 * kTcBlockBytes >> 4);
+#pragma unroll
+                for (uint32_t ks = 0; ks < 8; ++ks)
+                    tc_mma_ss(d_a[slot], tc_desc(xb + tc_koff(ks, kTcBlockBytes)), tc_desc(w0_lo + tc_koff(ks, kTcBlockBytes)),
+                              tc_idesc(128), ks == 0 ? 0u : 1u);
+                tc_commit(bar(kTcBarXEmpty + (int)buf));
+                tc_commit(bar(kTcBarAcc + 3 * slot + 0));
+            }
+            return true;
+        };
+        // layer 1 (D2 = act(D1) W1^T) or layer 2 (D3 = act(D2) W2^T, 32 columns over D1) of the slot's tile, once all
+        // 16 epilogue warps have written their activations
+        auto layer12 = [&](int slot, uint32_t layer) {
+            if (!wait(kTcBarAct + slot, layer)) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (issue) {
+                const uint32_t d = layer == 0 ? d_b[slot] : d_a[slot], a = layer == 0 ? d_a[slot] : d_b[slot];
+                const uint32_t w_lo = layer == 0 ? w1_lo : w2_lo, blk = layer == 0 ? kTcBlockBytes : kTcW2BlockBytes;
+                const uint32_t idesc = layer == 0 ? tc_idesc(128) : tc_idesc(32);
+#pragma unroll
+                for (uint32_t ks = 0; ks < 8; ++ks) {
+                    const uint64_t bdesc = tc_desc(w_lo + (ks >> 2) * (blk >> 4) + (ks & 3) * 2);
+                    tc_mma_ts(d, a + 16 * ks, bdesc, idesc, ks == 0 ? 0u : 1u);
+                    tc_mma_ts(d, a + 16 * ks + 8, bdesc, idesc, 1u);
+                }
+                tc_commit(bar(kTcBarAcc + 3 * slot + 1 + (int)layer));
+            }
+            return true;
+        };
+        for (int s0 = 0; s0 < total && ok;) {
+            const int s1 = min(total, s0 == 0 ? first_end : s0 + per_head);
+            if (s0 > 0) {  // the next head's weights
+                if (issue) tc_arrive(bar(kTcBarDrained));
+                if (!(ok = wait(kTcBarWeights, changes & 1))) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                ++changes;
+            }
+            ok = layer0(s0, 0);
+            if (ok && s0 + 1 < s1) ok = layer0(s0 + 1, 1);
+            for (int a = s0; a < s1 && ok; a += 2) {
+                const bool has_b = a + 1 < s1;
+                ok = layer12(0, 0);
+                if (ok && has_b) ok = layer12(1, 0);
+                if (ok) ok = layer12(0, 1);
+                if (ok) {  // the slot's next tile swaps the two regions (layer 0 of it follows layer 2 in the tensor core's order)
+                    const uint32_t t = d_a[0]; d_a[0] = d_b[0]; d_b[0] = t;
+                    if (a + 2 < s1) ok = layer0(a + 2, 0);
+                }
+                if (ok && has_b) {
+                    ok = layer12(1, 1);
+                    const uint32_t t = d_a[1]; d_a[1] = d_b[1]; d_b[1] = t;
+                    if (ok && a + 3 < s1) ok = layer0(a + 3, 1);
+                }
+            }
+            s0 = s1;
+        }
+        // the tensor core has finished everything issued above (after a time-out: one more bounded wait)
+        if (issue) tc_commit(bar(kTcBarFinal));
+        for (int spin = 0; spin < kTcSpinLimit && __all_sync(0xffffffffu, tc_test(bar(kTcBarFinal), 0)) == 0; ++spin) {}
+    } else {
+        // ---- loader ------------------------------------------------------------------------------------------
+        // One thread: a tile is two TMA box copies (the two K-halves, 64 elements x 128 rows each, written in the
+        // 128-byte swizzle) that complete on the buffer's mbarrier; the ring runs up to four tiles ahead.
+        if (lane == 0) {
+            TcCursor cur(p, true);
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&k_map) : "memory");
+            long long i = 0;
+            for (; i < cur.total; ++i) {
+                const uint32_t buf = (uint32_t)(i % kTcXBufs);
+                if (!tc_wait(bar(kTcBarXEmpty + (int)buf), ((uint32_t)(i / kTcXBufs) & 1) ^ 1, s_abort, p.status)) break;
+                const TcItem it = cur.next();
+                const uint32_t full = bar(kTcBarXFull + (int)buf), dst = sbase + kTcOffX + buf * 2 * kTcBlockBytes;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(2 * kTcBlockBytes) : "memory");
+                tc_tma_load(dst, &k_map, 0, (int)it.slot0, full);
+                tc_tma_load(dst + kTcBlockBytes, &k_map, 64, (int)it.slot0, full);
+            }
+            // no copy is left in flight when the CTA ends (they have all landed unless the CTA gave up early)
+            for (long long j = max(0ll, i - kTcXBufs); j < i; ++j)
+                for (int spin = 0; spin < kTcSpinLimit && !tc_test(bar(kTcBarXFull + (int)(j % kTcXBufs)), (uint32_t)(j / kTcXBufs) & 1); ++spin) {}
+        }
+        __syncwarp();
     }
-    for (uint32_t n = 0; cur.valid; ++n) {
-        // ---- layer 0 is running; meanwhile the next tile's keys start streaming in
-        const Item nxt = next_item();
-        if (nxt.valid)
-            tc_prefetch_tile(smem + kTcOffX + ((n + 1) & 1) * 2 * kTcBlockBytes, p.k_pages + nxt.slot0 * kHeadDim, tid);
-        if (!wait_commit()) { aborted = true; break; }
-        // ---- hidden layers: the epilogue runs in two halves of 64 columns; the half of the next GEMM that reads
-        //      the first half's activations (its K-half 0, hi and lo) is issued before the second half is worked on
-        hidden(kTcColD1, s_bias, 0);
-        publish();
-        if (tid == 0) {  // layer 1, K-half 0: D2 = (Hhi + Hlo) W1^T
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            gemm_half(kTcColD2, kTcOffHi, kTcOffW1, kTcBlockBytes, idesc128, 0, true);
-            gemm_half(kTcColD2, kTcOffLo, kTcOffW1, kTcBlockBytes, idesc128, 0, false);
-        }
-        hidden(kTcColD1, s_bias, 1);
-        publish();
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            gemm_half(kTcColD2, kTcOffHi, kTcOffW1, kTcBlockBytes, idesc128, 1, false);
-            gemm_half(kTcColD2, kTcOffLo, kTcOffW1, kTcBlockBytes, idesc128, 1, false);
-            tc_commit(bar);
-        }
-        if (!wait_commit()) { aborted = true; break; }
-        hidden(kTcColD2, s_bias + kHidden, 0);
-        publish();
-        if (tid == 0) {  // layer 2, K-half 0: D3 = (Hhi + Hlo) W2^T, N = 32
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            gemm_half(kTcColD3, kTcOffHi, kTcOffW2, kTcW2BlockBytes, idesc32, 0, true);
-            gemm_half(kTcColD3, kTcOffLo, kTcOffW2, kTcW2BlockBytes, idesc32, 0, false);
-        }
-        hidden(kTcColD2, s_bias + kHidden, 1);
-        publish();
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            gemm_half(kTcColD3, kTcOffHi, kTcOffW2, kTcW2BlockBytes, idesc32, 1, false);
-            gemm_half(kTcColD3, kTcOffLo, kTcOffW2, kTcW2BlockBytes, idesc32, 1, false);
-            tc_commit(bar);
-        }
-        if (!wait_commit()) { aborted = true; break; }
-        // ---- the codes of this tile are packed while layer 0 of the next tile runs (D1 and D3 are different
-        //      columns; D3 is written again only after two more barriers). A change of head rewrites the biases the
-        //      codes need, so there the codes come first.
-        if (nxt.valid && nxt.h != loaded_h) {
-            codes(cur);
-            __syncthreads();
-            loaded_h = nxt.h;
-            load_head(loaded_h);
-            start_tile((n + 1) & 1);
-        } else {
-            if (nxt.valid) start_tile((n + 1) & 1);
-            codes(cur);
-        }
-        cur = nxt;
-    }
-    asm volatile("cp.async.wait_all;" ::: "memory");
 
-    // ---- release tensor memory (after a time-out: give in-flight MMAs one more bounded wait) -------
-    __syncthreads();
-    if (aborted && tid == 0) tc_wait(bar, phase ^ 1);
+    // ---- release tensor memory ---------------------------------------------------------------------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
+    if (warp == kTcMmaWarp) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTcTmemCols) : "memory");
     }

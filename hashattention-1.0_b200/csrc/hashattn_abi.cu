@@ -449,14 +449,6 @@ using namespace ha;
 
 extern "C" {
 
-#ifdef HA_TIMELINE
-// Debug builds only: where the kernels stamp their timeline (device buffer of
-// kTlKernels * kTlEvents * 2 unsigned 64-bit words, minima preset to ~0, maxima to 0).
-int ha_debug_set_timeline(unsigned long long* buffer) {
-    return cudaMemcpyToSymbol(g_timeline, &buffer, sizeof(buffer)) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
-}
-#endif
-
 int ha_abi_version(void) { return HA_ABI_VERSION; }
 
 int ha_set_option(int option_key, int value) {
@@ -601,6 +593,30 @@ int ha_hash_decode(const ha_shape_t* shape, const ha_hash_weights_t* weights,
                             q_codes, preact_dbg, nullptr, status, stream);
 }
 
+// cuTensorMapEncodeTiled, looked up once through the runtime (the library does not link against libcuda).
+static bool encode_key_map(CUtensorMap* map, const void* k_pages, uint64_t rows) {
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static std::atomic<encode_fn> cached{nullptr};
+    encode_fn fn = cached.load();
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || sym == nullptr)
+            return false;
+        fn = reinterpret_cast<encode_fn>(sym);
+        cached.store(fn);
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)kHeadDim, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)kHeadDim * sizeof(__nv_bfloat16)};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kTcTile}, elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(k_pages), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
                     const void* k_pages, uint32_t* hash_pages,
                     const int32_t* page_table, const int32_t* seq_lens,
@@ -633,6 +649,10 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         t.Hkv = shape->num_kv_heads;
         t.max_pages = shape->max_pages;
         t.num_pages = shape->num_pages;
+        // the key cache as a 2-d tensor [rows = pages x kv heads x page size][128] for the kernel's TMA loads: boxes of
+        // 64 elements x 128 rows, 128-byte swizzle
+        CUtensorMap k_map;
+        if (!encode_key_map(&k_map, k_pages, (uint64_t)shape->num_pages * shape->num_kv_heads * kPage)) return HA_ERR_LAUNCH;
         // one CTA per SM; the kernel cuts the (head, tile) pairs into that many equal ranges
         const int Hq = shape->num_kv_heads * kGroup;
         const long long tiles = (long long)Hq * shape->batch * shape->max_pages * (kPage / kTcTile);
@@ -652,7 +672,7 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         attr1[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
         cfg.attrs = attr1;
         cfg.numAttrs = 1;
-        return cudaLaunchKernelEx(&cfg, hash_prefill_tc_kernel, t) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+        return cudaLaunchKernelEx(&cfg, hash_prefill_tc_kernel, t, k_map) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
     }
     // fp32 weights, or the 1- and 2-layer hash functions: fp32 arithmetic on the CUDA cores
     HashPrefillParams p;

@@ -353,7 +353,6 @@ __device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kv
 
 template <int ROUNDS>
 __global__ void __launch_bounds__(kSelThreads, HA_SH_MIN_CTAS) score_hist_kernel(const SelectParams p) {
-    HA_TL(kTlScoreHist, kTlEntry);
     const int c = blockIdx.x, kvh = p.kvh0 + blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;
@@ -382,7 +381,6 @@ __global__ void __launch_bounds__(kSelThreads, HA_SH_MIN_CTAS) score_hist_kernel
     }
 
     pdl_wait();
-    HA_TL(kTlScoreHist, kTlAfterWait);
     pdl_launch_dependents();
 
     if (!s_ok) {
@@ -466,7 +464,6 @@ __global__ void __launch_bounds__(kSelThreads, HA_SH_MIN_CTAS) score_hist_kernel
         __threadfence();  // the histogram is visible device-wide before this CTA counts itself in
     }
 
-    HA_TL(kTlScoreHist, kTlMarkA);
     // ---- the CTA that publishes last for this (sequence, kv-head) works the unit's plan out. Nobody waits:
     //      every CTA makes its histogram visible, then counts itself in; the one that finds all the others
     //      counted reads their histograms and leaves the counter at zero for the next call.
@@ -479,13 +476,9 @@ __global__ void __launch_bounds__(kSelThreads, HA_SH_MIN_CTAS) score_hist_kernel
         if (s_last) *counter = 0u;
     }
     __syncthreads();
-    HA_TL(kTlScoreHist, kTlMarkB);
     if (!s_last) return;
     __threadfence();
-    HA_TL(kTlSelectPlan, kTlEntry);
     select_plan(p, b, kvh, r, nchunks_b, s_plan, tid);
-    HA_TL(kTlSelectPlan, kTlExit);
-    HA_TL(kTlScoreHist, kTlExit);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -506,7 +499,6 @@ constexpr int kClHistCopies = 8;                              // warp w updates 
 
 template <int ROUNDS>
 __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(const SelectParams p) {
-    HA_TL(kTlScoreHist, kTlEntry);
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int kvh = p.kvh0 + blockIdx.y, b = blockIdx.z;
@@ -532,7 +524,6 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
     if (active0) rw.load(p, b, kvh, first_token(0), lane, r);
 
     pdl_wait();
-    HA_TL(kTlScoreHist, kTlAfterWait);
     pdl_launch_dependents();
     if (!s_ok && tid == 0 && rank == 0 && blockIdx.y == 0) report(p.status, HA_ERR_BAD_SEQ_LEN);
 
@@ -607,7 +598,6 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
         for (int rd = 0; rd < ROUNDS; ++rd) s_bef[rd][tid] = bef[rd];
     }
     __syncthreads();  // s_tot / s_bef complete (the other CTAs may still be reading s_cta_hist)
-    HA_TL(kTlSelect, kTlAfterWait);
 
     // --- threshold, tie quota and output bases per head: warp g scans the 33 bins downwards --------
     if (warp < kGroup) {
@@ -770,7 +760,6 @@ __global__ void __launch_bounds__(kClThreads, 1) score_select_cluster_kernel(con
             }
         }
     }
-    HA_TL(kTlSelect, kTlExit);
     cluster.sync();  // s_cta_hist may be read by the other CTAs until they, too, are past the exchange
 }
 

@@ -43,25 +43,8 @@ constexpr int kSaRoundRows = kSaWorkers * kSaRows;   // 32
 constexpr int kSaWarps = kSaThreads / 32;
 constexpr int kSaEdgeSlots = 2;  // CTA 0 of a head attends the sink tokens, CTA 1 the recent ones, CTA 2 + c chunk c
 
-// Packed pairs of fp32 values (sm_100: two fused multiply-adds per instruction) and the multiply-add that takes
-// bf16 operands as they are stored (exact products, fp32 accumulation, no unpacking).
-typedef unsigned long long f32x2;
-__device__ __forceinline__ f32x2 pack2(float a, float b) {
-    f32x2 r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
-__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
-    f32x2 d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
-    f32x2 d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
+// bf16 operands of the mixed-precision multiply-add are taken as they are stored (exact products, fp32
+// accumulation, no unpacking).
 __device__ __forceinline__ f32x2 bf16x2_to_f32x2(uint32_t w) { return pack2(bf16_lo(w), bf16_hi(w)); }
 // c + lo(a) * lo(b) + hi(a) * hi(b) for two words of two bf16 each
 __device__ __forceinline__ float dot_bf16x2(uint32_t a, uint32_t b, float c) {
@@ -97,7 +80,6 @@ struct SelectAttendParams {
 // lets a grid of up to 1184 CTAs run as a single wave.
 template <int ROUNDS, bool kGather, int kMinCtas>
 __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(const SelectAttendParams p) {
-    HA_TL(kTlGather, kTlEntry);
     constexpr int chunk_tokens = ROUNDS * kRoundTokens;
     constexpr int kWords = 2 * ROUNDS;             // 32-bit words of score bytes per thread: 8 ROUNDS tokens
     constexpr int kTpb = 128 / (4 * kWords);       // threads that share a block of 128 tokens: 16, 8 or 4
@@ -284,7 +266,6 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
         s_pages[tid] = v >= 0 && v < p.num_pages ? v : -1;  // tokens of a bad page are no candidates: never selected
     }
     pdl_wait();
-    HA_TL(kTlGather, kTlAfterWait);
     pdl_launch_dependents();
     if (!active) return;
 
@@ -412,10 +393,8 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
     }
     if constexpr (!kGather) return;
     __syncthreads();
-    HA_TL(kTlGather, kTlMarkA);
     attend_list(n_list);
     store_partial();
-    HA_TL(kTlGather, kTlExit);
 }
 
 // Log-sum-exp merge of the partials select_attend_kernel left for one (sequence, head): the partials of the CTAs
@@ -427,7 +406,6 @@ constexpr int kMergeThreads = kHeadDim * kMergeSlices;
 constexpr int kMergeBatch = 17;
 
 __global__ void __launch_bounds__(kMergeThreads) select_attend_merge_kernel(const SelectAttendParams p, int chunk_tokens) {
-    HA_TL(kTlMerge, kTlEntry);
     const int h = p.h0 + blockIdx.x, b = blockIdx.y;
     const int Hq = p.Hkv * kGroup;
     const int tid = threadIdx.x, d = tid % kHeadDim, slice = tid / kHeadDim;
@@ -438,7 +416,6 @@ __global__ void __launch_bounds__(kMergeThreads) select_attend_merge_kernel(cons
     const int nparts = kSaEdgeSlots + (S + chunk_tokens - 1) / chunk_tokens;
 
     pdl_wait();
-    HA_TL(kTlMerge, kTlAfterWait);
     pdl_launch_dependents();
     if (p.status_out != nullptr && (blockIdx.x | blockIdx.y | threadIdx.x) == 0) *p.status_out = __ldcg(p.status);
     if (!ok) return;
@@ -488,7 +465,6 @@ __global__ void __launch_bounds__(kMergeThreads) select_attend_merge_kernel(cons
         A = fmaf(s_a[w][d], f, A);
     }
     p.out[((size_t)b * Hq + h) * kHeadDim + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
-    HA_TL(kTlMerge, kTlExit);
 }
 
 }  // namespace ha

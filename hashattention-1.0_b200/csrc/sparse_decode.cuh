@@ -120,7 +120,6 @@ __device__ __forceinline__ AttPlan att_plan(const SparseDecodeParams& p, int b, 
 template <bool kPhysical, int kThreads, bool kCluster>
 __global__ void __launch_bounds__(kThreads, kCluster ? 2 : 6) sparse_gather_kernel(const SparseDecodeParams p) {
     static_assert(kCluster ? kThreads == kAttClusterThreads : kThreads == kHeadDim, "flat CTAs: thread = output dimension");
-    HA_TL(kTlGather, kTlEntry);
     constexpr int kWorkers = kThreads / 16;                          // half-warps
     constexpr int kRoundRows = kWorkers * kAttRowsPerWorker;      // rows per CTA and round
     const int split = blockIdx.x, h = p.h0 + blockIdx.y, b = blockIdx.z;
@@ -163,7 +162,6 @@ __global__ void __launch_bounds__(kThreads, kCluster ? 2 : 6) sparse_gather_kern
     }
 
     pdl_wait();
-    HA_TL(kTlGather, kTlAfterWait);
     pdl_launch_dependents();
     publish_status(p);
     if (p.sel_cnt != nullptr) {  // the length of the heavy list is a product of the selection kernels
@@ -357,7 +355,6 @@ __global__ void __launch_bounds__(kThreads, kCluster ? 2 : 6) sparse_gather_kern
             }
             if (Lg > 0.f) p.out[((size_t)b * Hq + h) * kHeadDim + d] = __float2bfloat16_rn(Ag / Lg);
         }
-        HA_TL(kTlGather, kTlExit);
         cluster.sync();  // the partial of this CTA may be read by the others until they are done
         return;
     }
@@ -371,7 +368,6 @@ __global__ void __launch_bounds__(kThreads, kCluster ? 2 : 6) sparse_gather_kern
         part[0] = M;
         part[1] = L;
     }
-    HA_TL(kTlGather, kTlExit);
 }
 
 // Log-sum-exp merge of the partials of one (b, h): 128 threads, thread = output dimension. Warp w
@@ -379,7 +375,6 @@ __global__ void __launch_bounds__(kThreads, kCluster ? 2 : 6) sparse_gather_kern
 // lane = split for the (max, sum) pairs, all loads of a pass issued together; the four warps'
 // results are combined in shared memory.
 __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDecodeParams p) {
-    HA_TL(kTlMerge, kTlEntry);
     const int h = p.h0 + blockIdx.x, b = blockIdx.y;
     const int Hq = p.Hkv * kGroup;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -389,7 +384,6 @@ __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDeco
     __shared__ float s_a[kWarps][kHeadDim];
 
     pdl_wait();
-    HA_TL(kTlMerge, kTlAfterWait);
     pdl_launch_dependents();
     publish_status(p);
     if (p.sel_cnt != nullptr) a = att_plan(p, b, __ldcg(p.sel_cnt + (size_t)b * Hq + h));
@@ -446,7 +440,6 @@ __global__ void __launch_bounds__(kHeadDim) sparse_merge_kernel(const SparseDeco
         A = fmaf(s_a[w][tid], f, A);
     }
     p.out[((size_t)b * Hq + h) * kHeadDim + tid] = __float2bfloat16_rn(A / L);
-    HA_TL(kTlMerge, kTlExit);
 }
 
 }  // namespace ha
