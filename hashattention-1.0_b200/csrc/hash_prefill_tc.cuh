@@ -168,27 +168,21 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
     return false;
 }
 
-// 32 accumulator columns of this thread's lane: issue, and the wait that makes the registers readable. The wait takes
-// the registers as operands, so that nothing that reads them can be scheduled in front of it.
-__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+// 16 accumulator columns of this thread's lane: issue, and the wait that makes the registers readable (it waits for
+// every read the thread has issued). The wait takes the registers as operands, so that nothing that reads them can be
+// scheduled in front of it.
+__device__ __forceinline__ void tc_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr));
 }
-__device__ __forceinline__ void tc_ld_wait(uint32_t (&r)[32]) {
+__device__ __forceinline__ void tc_ld16_wait(uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
                  : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
                    "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
-                 :: "memory");
-    asm volatile(""
-                 : "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
                  :: "memory");
 }
 
@@ -202,19 +196,15 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  :: "memory");
 }
 
-// 32 columns of this thread's lane written to tensor memory; returns when the write has completed.
-__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+// 16 columns of this thread's lane written to tensor memory (complete after tcgen05.wait::st).
+__device__ __forceinline__ void tc_st16_issue(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};\n"
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};\n"
         :: "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
            "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
            "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 // TMA: the box at element column x, row y of the key cache -> shared memory, bytes counted on the mbarrier (the
@@ -242,14 +232,14 @@ __device__ __forceinline__ void tc_load_operand(unsigned char* dst, const __nv_b
     }
 }
 
-// bias + SiLU + hi/lo split of 32 accumulator columns v (bit patterns of fp32) of one row. The 32 words that take
-// their place are the A operand of two k-steps of the next GEMM: words 0..7 hold the hi halves of activations
-// 0..15 (two per word, the even one in the low half), 8..15 their lo halves, 16..23 and 24..31 those of 16..31.
-__device__ __forceinline__ void tc_activate32(const uint32_t (&v)[32], const float* bias, uint32_t (&out)[32]) {
+// bias + SiLU + hi/lo split of 16 accumulator columns v (bit patterns of fp32) of one row. The 16 words that take their
+// place are the A operand of one k-step of the next GEMM: words 0..7 hold the hi halves of the activations (two per
+// word, the even one in the low half), words 8..15 their lo halves.
+__device__ __forceinline__ void tc_activate16(const uint32_t (&v)[16], const float* bias, uint32_t (&out)[16]) {
     const f32x2 nlog2e = pack2(-1.4426950408889634f, -1.4426950408889634f), one = pack2(1.0f, 1.0f);
     const f32x2 minus1 = pack2(-1.0f, -1.0f);
 #pragma unroll
-    for (int pr = 0; pr < 16; ++pr) {
+    for (int pr = 0; pr < 8; ++pr) {
         const float2 bb = *reinterpret_cast<const float2*>(bias + 2 * pr);  // the same address in every lane: a broadcast
         const f32x2 x = add2(pack2(__uint_as_float(v[2 * pr]), __uint_as_float(v[2 * pr + 1])), pack2(bb.x, bb.y));
         float t0, t1;
@@ -268,9 +258,8 @@ __device__ __forceinline__ void tc_activate32(const uint32_t (&v)[32], const flo
         const uint32_t hi = tc_pack_bf16(y0, y1);
         float l0, l1;
         unpack2(fma2(pack2(bf16_lo(hi), bf16_hi(hi)), minus1, y), l0, l1);  // y - hi, exact
-        const int w = (pr >> 3) * 16 + (pr & 7);
-        out[w] = hi;
-        out[w + 8] = tc_pack_bf16(l0, l1);
+        out[pr] = hi;
+        out[pr + 8] = tc_pack_bf16(l0, l1);
     }
 }
 
@@ -416,37 +405,61 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
         const uint32_t t_base = tmem + (((uint32_t)(warp & 3) * 32u) << 16);
         TcCursor cur(p, false);
         const long long total = cur.total;
-        uint32_t cnt[2] = {0, 0}, changes = 0;  // tiles worked on per slot; head changes seen
+        uint32_t cnt_e[2] = {0, 0}, cnt_c[2] = {0, 0}, changes = 0;  // tiles per slot: hidden layers done, codes done; head changes
         bool ok = true;
-        // a hidden layer of the tile in `slot`: accumulator -> hi/lo activations in place (layer 0 works in the slot's
-        // region cnt & 1, layer 1 in the other one)
-        auto hidden = [&](uint32_t slot, uint32_t layer) {
-            if (!wait(kTcBarAcc + 3 * (int)slot + (int)layer, cnt[slot] & 1)) return false;
+        // column of this warp's slice in the accumulator of hidden layer `layer` of the slot's tile number `count` (layer 0
+        // works in the slot's region count & 1, layer 1 in the other one)
+        auto slice_col = [&](uint32_t slot, uint32_t layer, uint32_t count) { return slot * 256u + ((count & 1) ^ layer) * 128u + 32u * sl; };
+        // The slice is read and worked on in two halves of 16 columns, rx and ry, and every read is requested one half
+        // ahead of its arithmetic: the second half at the start of the phase, the first half of the FOLLOWING phase between
+        // the halves (if that phase's accumulator is complete by then; otherwise the phase starts with `acquire`).
+        uint32_t rx[16], ry[16];
+        auto acquire = [&](uint32_t slot, uint32_t layer) {
+            if (!wait(kTcBarAcc + 3 * (int)slot + (int)layer, cnt_e[slot] & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t col = slot * 256u + ((cnt[slot] & 1) ^ layer) * 128u + 32u * sl;
-            uint32_t r[32], out[32];
-            tc_ld32_issue(t_base + col, r);
-            tc_ld_wait(r);
-            tc_activate32(r, s_bias + layer * kHidden + 32 * sl, out);
-            tc_st32(t_base + col, out);
+            tc_ld16_issue(t_base + slice_col(slot, layer, cnt_e[slot]), rx);
+            return true;
+        };
+        // next_count: tiles of that slot whose hidden layers will be done when the phase starts
+        auto prefetch = [&](uint32_t slot, uint32_t layer, uint32_t next_count) {
+            if (__all_sync(0xffffffffu, tc_test(bar(kTcBarAcc + 3 * (int)slot + (int)layer), next_count & 1)) == 0) return false;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            tc_ld16_issue(t_base + slice_col(slot, layer, next_count), rx);
+            return true;
+        };
+        // a hidden layer of the slot's tile (first half requested): accumulator -> hi/lo activations in place
+        auto hidden = [&](uint32_t slot, uint32_t layer, bool want_next, uint32_t next_slot, uint32_t next_layer,
+                          uint32_t next_count, bool& have_next) {
+            const uint32_t col = slice_col(slot, layer, cnt_e[slot]);
+            const float* bias = s_bias + layer * kHidden + 32 * sl;
+            uint32_t out[16];
+            tc_ld16_wait(rx);
+            tc_ld16_issue(t_base + col + 16u, ry);
+            tc_activate16(rx, bias, out);
+            tc_st16_issue(t_base + col, out);
+            tc_ld16_wait(ry);
+            have_next = want_next && prefetch(next_slot, next_layer, next_count);
+            tc_activate16(ry, bias + 16, out);
+            tc_st16_issue(t_base + col + 16u, out);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) tc_arrive(bar(kTcBarAct + (int)slot));
-            return true;
+            if (layer == 1) ++cnt_e[slot];
         };
         // the codes of the tile in `slot`: thread = token row, each of the row's four warps packs 8 of the 32 sign bits
         auto codes = [&](uint32_t slot, const TcItem& it) {
-            if (!wait(kTcBarAcc + 3 * (int)slot + 2, cnt[slot] & 1)) return false;
+            if (!wait(kTcBarAcc + 3 * (int)slot + 2, cnt_c[slot] & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t r[8];
-            tc_ld8(t_base + slot * 256u + (cnt[slot] & 1) * 128u + 8u * sl, r);
+            tc_ld8(t_base + slot * 256u + (cnt_c[slot] & 1) * 128u + 8u * sl, r);
             uint32_t code = 0;
 #pragma unroll
             for (int k = 0; k < 8; ++k) code |= (__uint_as_float(r[k]) + s_bias[2 * kHidden + 8 * sl + k] > 0.0f ? 1u : 0u) << k;
             const int t = it.t0 + (int)row;
             if (it.store && t < it.S && t >= it.first)
                 reinterpret_cast<uint8_t*>(p.hash_pages)[((it.slot0 + row) * kGroup + it.h % kGroup) * 4 + sl] = (uint8_t)code;
-            ++cnt[slot];
+            ++cnt_c[slot];
             return true;
         };
         // The tiles of a head are worked on in pairs, one tile per slot, in the order
@@ -473,12 +486,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
                 const bool has_b = a + 1 < s1;
                 it_a = cur.next();  // (the page-table reads complete under the arithmetic: the items are used by the codes)
                 if (has_b) it_b = cur.next();
+                bool have_a = false, have_b = false;
 #pragma unroll 1
-                for (uint32_t ph = 0; ph < 4 && ok; ++ph) {
-                    const uint32_t slot = ph & 1;
-                    if (slot == 0 || has_b) ok = hidden(slot, ph >> 1);
-                    if (ok && ph == 0 && pend) ok = codes(1, it_pend);
-                    if (ok && ph == 3) ok = codes(0, it_a);
+                for (uint32_t layer = 0; layer < 2 && ok; ++layer) {
+                    if (!have_a && !(ok = acquire(0, layer))) break;
+                    hidden(0, layer, has_b, 1, layer, cnt_e[1], have_b);
+                    if (layer == 0 && pend && !(ok = codes(1, it_pend))) break;
+                    if (has_b) {
+                        if (!have_b && !(ok = acquire(1, layer))) break;
+                        hidden(1, layer, layer == 0, 0, 1, cnt_e[0], have_a);
+                    } else {
+                        have_a = false;
+                    }
+                    if (layer == 1) ok = codes(0, it_a);
                 }
                 pend = has_b;
                 it_pend = it_b;
