@@ -237,7 +237,6 @@ __device__ __forceinline__ void tc_load_operand(unsigned char* dst, const __nv_b
 // word, the even one in the low half), words 8..15 their lo halves.
 __device__ __forceinline__ void tc_activate16(const uint32_t (&v)[16], const float* bias, uint32_t (&out)[16]) {
     const f32x2 nlog2e = pack2(-1.4426950408889634f, -1.4426950408889634f), one = pack2(1.0f, 1.0f);
-    const f32x2 minus1 = pack2(-1.0f, -1.0f);
 #pragma unroll
     for (int pr = 0; pr < 8; ++pr) {
         const float2 bb = *reinterpret_cast<const float2*>(bias + 2 * pr);  // the same address in every lane: a broadcast
@@ -256,8 +255,10 @@ __device__ __forceinline__ void tc_activate16(const uint32_t (&v)[16], const flo
         float y0, y1;
         unpack2(y, y0, y1);
         const uint32_t hi = tc_pack_bf16(y0, y1);
-        float l0, l1;
-        unpack2(fma2(pack2(bf16_lo(hi), bf16_hi(hi)), minus1, y), l0, l1);  // y - hi, exact
+        float l0, l1;  // y - hi, exact: the multiply-add takes the bf16 halves of hi as they are
+        asm("{\n\t.reg .b16 h0, h1;\n\tmov.b32 {h0, h1}, %2;\n\t"
+            "fma.rn.f32.bf16 %0, h0, %3, %4;\n\tfma.rn.f32.bf16 %1, h1, %3, %5;\n\t}"
+            : "=f"(l0), "=f"(l1) : "r"(hi), "h"((unsigned short)0xBF80), "f"(y0), "f"(y1));
         out[pr] = hi;
         out[pr + 8] = tc_pack_bf16(l0, l1);
     }
