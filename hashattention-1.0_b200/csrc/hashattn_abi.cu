@@ -140,7 +140,7 @@ struct Workspace {
     float* partials;    // [B][Hq][max(nsplits, nslots)][130] attention partials
     int32_t* plan;      // [B][Hkv][8 + 8 * nchunks] thresholds, tie quotas and per-chunk output bases
     uint8_t* scores;    // [B][Hq][nchunks * chunk tokens] one score byte per token and query head
-    uint32_t* arrive;   // [B][Hkv] arrival counters of the scoring kernel (zero between calls)
+    uint32_t* arrive;   // [B][Hkv][kArriveStride] arrival counter and histogram totals of the scoring kernel (zero between calls)
     size_t bytes;
 };
 
@@ -165,7 +165,7 @@ Workspace carve(const ha_shape_t* s, const ha_budget_t* b, void* base) {
     w.scores = reinterpret_cast<uint8_t*>(p + off);
     off += align_up(scores_bytes(s, g));
     w.arrive = reinterpret_cast<uint32_t*>(p + off);
-    off += align_up(units * sizeof(uint32_t));
+    off += align_up(units * kArriveStride * sizeof(uint32_t));
     w.bytes = off;
     return w;
 }
@@ -1004,7 +1004,7 @@ struct StaticScratch {
     uint32_t* hist;     // [B][Hkv][4*33][nchunks]
     int32_t* plan;      // [B][Hkv][8 + 8 * nchunks]
     uint8_t* scores;    // [B][Hq][nchunks * chunk tokens]
-    uint32_t* arrive;   // [B][Hkv]
+    uint32_t* arrive;   // [B][Hkv][kArriveStride]
     size_t arrive_bytes, bytes;
 };
 
@@ -1021,7 +1021,7 @@ StaticScratch carve_static(const ha_shape_t* s, void* base) {
     w.scores = reinterpret_cast<uint8_t*>(p + off);
     off += align_up(ha::scores_bytes(s, g));
     w.arrive = reinterpret_cast<uint32_t*>(p + off);
-    w.arrive_bytes = units * sizeof(uint32_t);
+    w.arrive_bytes = units * ha::kArriveStride * sizeof(uint32_t);
     off += align_up(w.arrive_bytes);
     w.bytes = off;
     return w;

@@ -1,16 +1,17 @@
 // Hamming scoring and the selection plan.
 //
 // score_hist_kernel streams the key-hash pages once: one 16-byte word per token per kv-head carries
-// the codes of all 4 query heads of the group, so one coalesced pass scores the 4 heads together;
-// score = popcount(~(q_code ^ k_code)) in 0..32. Each CTA publishes a 4 x 33 histogram of the scores
-// of the candidate tokens of its chunk, stored bin-major ([bin][chunk]) so that the counts of one bin
-// over all chunks are one line, and the scores of its tokens, one byte per token and query head
+// the four 32-bit codes of the kv-head's query heads, so a lane scores 4 heads per load,
+// score = popcount(~(q_code ^ k_code)) in 0..32. Each CTA builds the 4 x 33 histogram of the scores
+// of the candidate tokens of its chunk, adds it to the totals of its (sequence, kv-head) with atomic
+// adds, and publishes per score the number of its tokens AT OR ABOVE that score, bin-major
+// ([bin][chunk]); it also writes the scores of its tokens, one byte per token and query head
 // (score + 1, 0 = not a candidate), in one plane per head.
 //
-// The CTA that finishes last for a (sequence, kv-head) - an arrival counter, no waiting - derives from
-// the chunk histograms the plan of that unit (select_plan): the threshold T of each head, how many
-// tokens tied at T still fit, and how many selected / tied tokens precede each chunk (pick_threshold:
-// both selection rules of the reference).
+// The CTA that finishes last for a (sequence, kv-head) - an arrival counter, no waiting - derives
+// the plan of that unit (select_plan): the threshold T of each head and how many tokens tied at T still
+// fit from the totals (pick_threshold: both selection rules of the reference), then how many selected /
+// tied tokens precede each chunk from two published counts per chunk and head.
 //
 // select_attend_kernel (select_attend.cuh) then classifies each chunk's score bytes against T, compacts
 // the selected tokens and attends them - no sort, no atomics in the output path.
@@ -56,8 +57,9 @@ struct SelectParams {
     const int32_t* page_table;
     const int32_t* seq_lens;
     const int32_t* budget_lens;  // [B] or null: the length the heavy budget is a fraction of, if not seq_lens
-    uint32_t* hist;            // workspace: [B][Hkv][4*33][nchunks]
-    uint32_t* arrive;          // workspace: [B][Hkv] chunks of the unit that have published their histogram (0 between calls)
+    uint32_t* hist;            // workspace: [B][Hkv][4*33][nchunks] per chunk: tokens at or above each score
+    uint32_t* arrive;          // workspace: [B][Hkv][kArriveStride] chunks of the unit that have published, then the unit's
+                               // histogram totals (all 0 between calls)
     int32_t* sel_idx;          // [B][Hq][sel_stride] token indices
     int32_t* sel_rows;         // workspace: [B][Hq][sel_stride] page * 256 + slot of the same tokens
     int32_t* sel_cnt;          // [B][Hq]
@@ -212,18 +214,16 @@ __device__ __forceinline__ uint32_t gather_byte(const uint32_t (&a)[NW], int g) 
 }
 
 // The plan of one (sequence, kv-head), worked out by one CTA of 256 threads (the one that published the unit's
-// last histogram). From the per-chunk histograms it derives the global threshold T and the tie quota of each
-// head, and for every chunk the number of selected tokens and of tied tokens that precede it.
-// The counts of up to 64 chunks are staged in shared memory in one trip (33 independent loads per thread);
-// thread (head, bin) adds a row up, warp g picks head g's threshold from the 33 totals, thread (head, chunk)
-// counts what its chunk holds above and at the threshold, and a scan over the chunks gives the offsets.
-// Sequences of more than 64 chunks take two sweeps over blocks of 64 (totals first, then offsets).
-constexpr int kPlanChunks = 64;            // chunks staged at a time
-constexpr int kPlanPitch = kPlanChunks + 2;  // row pitch (16-bit words): rows start in different banks
-constexpr int kPlanRows = kGroup * kBins;    // 132 (head, bin) rows
+// last histogram). The scoring CTAs have added their histograms up in the unit's totals (33 bins x 4 heads, behind
+// the arrival counter) and stored, per chunk, the counts of tokens at or above every score: warp g picks head g's
+// threshold T and tie quota from the totals, thread (head, chunk) reads what its chunk holds at or above T and
+// above T, and a scan over the chunks gives the number of selected and of tied tokens that precede each chunk.
+// The totals are left at zero for the next call.
+constexpr int kPlanChunks = 64;            // chunks per sweep (sequences of more than 64 chunks take several)
+constexpr int kPlanRows = kGroup * kBins;  // 132 (head, bin) rows
+constexpr int kArriveStride = 136;         // words per unit behind p.arrive: the arrival counter, then the 132 totals
 
 struct PlanSmem {
-    uint16_t stage[kPlanRows][kPlanPitch];  // a chunk holds at most 4096 tokens
     int tot[kPlanRows];
     int T[kGroup], need[kGroup];
     int warp_gt[kSelWarps], warp_eq[kSelWarps];
@@ -235,47 +235,14 @@ __device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kv
     const int Hq = p.Hkv * kGroup;
     const uint32_t* hbase = p.hist + ((size_t)b * p.Hkv + kvh) * kPlanRows * p.nchunks;
     int32_t* plan = p.plan + ((size_t)b * p.Hkv + kvh) * (8 + 8 * p.nchunks);
-    // chunks staged at a time: 32 for sequences of up to 32 chunks (one batch of loads, half the adding up), else 64
-    const int pc_shift = nchunks_b <= 32 ? 5 : 6, pc = 1 << pc_shift;
-    constexpr int kPerThread = (kPlanRows * kPlanChunks + kSelThreads - 1) / kSelThreads;  // 33
-    constexpr int kBatch = (kPerThread + 1) / 2;  // independent loads per batch (33 values at once would spill)
-
-    // counts of chunks [c0, c0 + pc) -> sm.stage; element e = row * pc + chunk, thread t takes e = t + 256 i
-    auto stage_block = [&](int c0) {
-#pragma unroll
-        for (int h0 = 0; h0 < kPerThread; h0 += kBatch) {
-            if (h0 * kSelThreads >= kPlanRows * pc) break;
-            uint32_t v[kBatch];
-#pragma unroll
-            for (int i = 0; i < kBatch; ++i) {
-                const int e = tid + (h0 + i) * kSelThreads, row = e >> pc_shift, cc = c0 + (e & (pc - 1));
-                v[i] = (row < kPlanRows && cc < nchunks_b) ? __ldcg(hbase + (size_t)row * p.nchunks + cc) : 0u;
-            }
-#pragma unroll
-            for (int i = 0; i < kBatch; ++i) {
-                const int e = tid + (h0 + i) * kSelThreads, row = e >> pc_shift;
-                if (row < kPlanRows) sm.stage[row][e & (pc - 1)] = (uint16_t)v[i];
-            }
-        }
-    };
-    auto row_total = [&] {
-        int t = 0;
-        if (tid < kPlanRows) {
-#pragma unroll 16
-            for (int c = 0; c < pc; ++c) t += sm.stage[tid][c];
-        }
-        return t;
-    };
+    uint32_t* totals = p.arrive + ((size_t)b * p.Hkv + kvh) * kArriveStride + 1;
+    const int pc_shift = nchunks_b <= 32 ? 5 : 6, pc = 1 << pc_shift;  // chunks per sweep: 32 or 64
 
     // ---- totals per (head, bin) over all chunks
-    int tot = 0;
-    for (int c0 = 0; c0 < nchunks_b; c0 += pc) {
-        if (c0 > 0) __syncthreads();
-        stage_block(c0);
-        __syncthreads();
-        tot += row_total();
+    if (tid < kPlanRows) {
+        sm.tot[tid] = (int)__ldcg(totals + tid);
+        totals[tid] = 0u;
     }
-    if (tid < kPlanRows) sm.tot[tid] = tot;
     __syncthreads();
 
     // ---- T and the tie quota: warp g for head g, lane l holds bin 32 - l
@@ -302,23 +269,20 @@ __device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kv
     __syncthreads();
 
     // ---- per chunk: tokens above T and tokens at T, then exclusive prefixes over the chunks.
-    //      thread = (head g, chunk cl of the block): 4 x pc threads, a head's chunks are pc / 32 warps
+    //      thread = (head g, chunk cl of the sweep): 4 x pc threads, a head's chunks are pc / 32 warps
     const int g = (tid >> pc_shift) & (kGroup - 1), cl = tid & (pc - 1);
     const bool works = tid < kGroup * pc;  // warp-uniform
     const int T = sm.T[g], need = sm.need[g];
     const int wpg = pc >> 5;  // warps per head: 1 or 2
     int gt_carry = 0, eq_carry = 0;
     for (int c0 = 0; c0 < nchunks_b; c0 += pc) {
-        if (nchunks_b > pc) {  // otherwise the counts of the only block are still staged
-            __syncthreads();
-            stage_block(c0);
-            __syncthreads();
-        }
+        if (c0 > 0) __syncthreads();  // (warp_gt / warp_eq of the previous sweep have been read)
         int gt = 0, eq = 0;
-        if (works) {
-#pragma unroll 11
-            for (int sbin = 0; sbin < kBins; ++sbin) gt += sbin > T ? (int)sm.stage[g * kBins + sbin][cl] : 0;
-            eq = T < kBins ? (int)sm.stage[g * kBins + T][cl] : 0;
+        if (works && c0 + cl < nchunks_b) {
+            const uint32_t* col = hbase + (size_t)(g * kBins) * p.nchunks + c0 + cl;
+            const int ge = T < kBins ? (int)__ldcg(col + (size_t)T * p.nchunks) : 0;  // at or above T
+            gt = T + 1 < kBins ? (int)__ldcg(col + (size_t)(T + 1) * p.nchunks) : 0;
+            eq = ge - gt;
         }
         int pg = gt, pe = eq;
 #pragma unroll
@@ -456,12 +420,28 @@ __global__ void __launch_bounds__(kSelThreads, HA_SH_MIN_CTAS) score_hist_kernel
     }
     if (bad_page) report(p.status, HA_ERR_BAD_PAGE);
     __syncthreads();
-    if (tid < kGroup * kBins) {
-        uint32_t v = 0;
+    // the chunk's histogram: added to the unit's totals, and stored as counts of tokens at or above each score.
+    // Warp g takes head g, lane l the score 32 - l (a scan over the lanes gives "at or above"); lane 0 also score 0.
+    uint32_t* unit = p.arrive + ((size_t)b * p.Hkv + kvh) * kArriveStride;
+    if (warp < kGroup) {
+        const int row0 = warp * kBins;
+        uint32_t v = 0, v0 = 0;
 #pragma unroll
-        for (int w = 0; w < kSelWarps; ++w) v += s_hist[w][tid];
-        p.hist[(((size_t)b * p.Hkv + kvh) * (kGroup * kBins) + tid) * p.nchunks + c] = v;
-        __threadfence();  // the histogram is visible device-wide before this CTA counts itself in
+        for (int w = 0; w < kSelWarps; ++w) {
+            v += s_hist[w][row0 + 32 - lane];
+            v0 += s_hist[w][row0];
+        }
+        if (v != 0u) atomicAdd(unit + 1 + row0 + 32 - lane, v);
+        if (lane == 0 && v0 != 0u) atomicAdd(unit + 1 + row0, v0);
+        uint32_t ge = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t u = __shfl_up_sync(0xffffffffu, ge, d);
+            if (lane >= d) ge += u;
+        }
+        uint32_t* dst = p.hist + (((size_t)b * p.Hkv + kvh) * (kGroup * kBins) + row0) * p.nchunks + c;
+        dst[(size_t)(32 - lane) * p.nchunks] = ge;
+        if (lane == 31) dst[0] = ge + v0;
     }
 
     // ---- the CTA that publishes last for this (sequence, kv-head) works the unit's plan out. Nobody waits:
@@ -470,7 +450,8 @@ __global__ void __launch_bounds__(kSelThreads, HA_SH_MIN_CTAS) score_hist_kernel
     __syncthreads();
     const int nchunks_b = (S + chunk_tokens - 1) / chunk_tokens;
     if (tid == 0) {
-        uint32_t* counter = p.arrive + (size_t)b * p.Hkv + kvh;
+        __threadfence();  // what the CTA has written (ordered before this thread by the barrier) is visible device-wide
+        uint32_t* counter = unit;
         const uint32_t before = atomicAdd(counter, 1u);
         s_last = before + 1u == (uint32_t)nchunks_b;
         if (s_last) *counter = 0u;
