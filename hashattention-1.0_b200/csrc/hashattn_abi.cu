@@ -15,10 +15,6 @@
 #include "select_attend.cuh"
 #include "sparse_decode.cuh"
 
-#ifndef HA_USE_PDL
-#define HA_USE_PDL 1
-#endif
-
 namespace ha {
 namespace {
 
@@ -126,9 +122,6 @@ Geometry geometry(const ha_shape_t* s) {
     auto chunks = [&](int cp) { return (s->max_pages + cp - 1) / cp; };
     while (g.chunk_pages > 4 && units * chunks(g.chunk_pages) < 2 * 148 && chunks(g.chunk_pages / 2) <= 64)
         g.chunk_pages /= 2;
-#ifdef HA_CHUNK_DIV
-    for (int d = HA_CHUNK_DIV; d > 1 && g.chunk_pages > 4; d /= 2) g.chunk_pages /= 2;
-#endif
     g.nchunks = chunks(g.chunk_pages);
     g.nslots = g.nchunks + kSaEdgeSlots;
     return g;
@@ -183,7 +176,7 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, cudaStream_t
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = 1;
     if (cluster_x > 1) {
         attr[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
@@ -566,7 +559,7 @@ static int hash_decode_impl(const ha_shape_t* shape, const ha_hash_weights_t* we
         cfg.stream = static_cast<cudaStream_t>(stream);
         cudaLaunchAttribute attr1[1];
         attr1[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr1[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
+        attr1[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr1;
         cfg.numAttrs = 1;
         e = bf16 ? cudaLaunchKernelEx(&cfg, hash_decode_batched_kernel<__nv_bfloat16>, p)
@@ -669,7 +662,7 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         cfg.stream = static_cast<cudaStream_t>(stream);
         cudaLaunchAttribute attr1[1];
         attr1[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr1[0].val.programmaticStreamSerializationAllowed = HA_USE_PDL;
+        attr1[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr1;
         cfg.numAttrs = 1;
         return cudaLaunchKernelEx(&cfg, hash_prefill_tc_kernel, t, k_map) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;

@@ -44,9 +44,7 @@ namespace ha {
 
 namespace cg = cooperative_groups;
 
-#ifndef HA_SH_MIN_CTAS
-#define HA_SH_MIN_CTAS 4
-#endif
+constexpr int kShMinCtas = 4;                         // CTAs of score_hist_kernel per SM (64 registers per thread)
 constexpr int kRoundPages = 4;                        // pages per round
 constexpr int kRoundTokens = kRoundPages * kPage;     // 1024
 constexpr int kLaneTokens = kRoundTokens / kSelThreads;  // 4 tokens per lane and round
@@ -316,7 +314,7 @@ __device__ __forceinline__ void select_plan(const SelectParams& p, int b, int kv
 }
 
 template <int ROUNDS>
-__global__ void __launch_bounds__(kSelThreads, HA_SH_MIN_CTAS) score_hist_kernel(const SelectParams p) {
+__global__ void __launch_bounds__(kSelThreads, kShMinCtas) score_hist_kernel(const SelectParams p) {
     const int c = blockIdx.x, kvh = p.kvh0 + blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int Hq = p.Hkv * kGroup;

@@ -29,16 +29,10 @@
 
 namespace ha {
 
-#ifndef HA_SA_MIN_CTAS
-#define HA_SA_MIN_CTAS 7
-#endif
-#ifndef HA_SA_ROWS
-#define HA_SA_ROWS 2
-#endif
 constexpr int kSaThreads = 128;
 constexpr int kSaLanes = 8;                          // lanes that share a row: 16 of the 128 dimensions each
 constexpr int kSaWorkers = kSaThreads / kSaLanes;    // 16 rows are worked on side by side
-constexpr int kSaRows = HA_SA_ROWS;                  // rows a worker keeps in flight per round
+constexpr int kSaRows = 2;                           // rows a worker keeps in flight per round
 constexpr int kSaRoundRows = kSaWorkers * kSaRows;   // 32
 constexpr int kSaWarps = kSaThreads / 32;
 constexpr int kSaEdgeSlots = 2;  // CTA 0 of a head attends the sink tokens, CTA 1 the recent ones, CTA 2 + c chunk c
