@@ -128,7 +128,7 @@ int ha_get_option(int option_key);
  * (0 if either is invalid). Host-only arithmetic. */
 size_t ha_workspace_bytes(const ha_shape_t* shape, const ha_budget_t* budget);
 
-/* Zeroes the workspace, in particular the arrival counters of the scoring kernel. REQUIRED once
+/* Zeroes the workspace, in particular the arrival counters and histogram totals of the scoring kernel. REQUIRED once
  * after allocating the workspace (and again only if a kernel was aborted): the kernels leave the
  * counters at zero themselves and keep no other state in the workspace between calls.          */
 int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* workspace,
@@ -188,7 +188,7 @@ int ha_score_select(const ha_shape_t* shape, const ha_budget_t* budget,
  *     address up (cudaGetSymbolAddress) and keeps it; make that first call outside any stream
  *     capture.
  *   - All calls on a device share the one buffer, which keeps whatever the last call left. The
- *     one part that must start at zero (the scoring kernel's arrival counters) is cleared by
+ *     one part that must start at zero (the scoring kernel's arrival counters and histogram totals) is cleared by
  *     every call on `stream` before its kernels; every other word is written before it is read.
  *     Two calls whose kernels may overlap on the GPU - different streams, no ordering between
  *     them - overwrite each other: order them.                                                  */
