@@ -2,6 +2,8 @@
 recorded from the reference. Integer results (codes outside the |x|<1e-5 band, Hamming
 scores, selected sets) must match bit-exactly; the bf16 attention output must be within
 max-abs 2e-2 and rel-L2 1e-2 of the fp32 reference."""
+import copy
+
 import pytest
 import torch
 
@@ -82,6 +84,56 @@ def test_prefill_codes_match_reference(device, cases, name):
     ctx.check_status()
     for b in range(case.k.shape[0]):
         assert helpers.codes_match(cache.read_codes(b).cpu(), case.k_codes[b], case.k_must[b])
+
+
+PREFILL_SHAPES = [
+    # (kv heads, sequence lengths, first token per sequence or None): one tile, tile edges, odd and even tile counts per
+    # head, several heads per CTA (more tiles than SMs), many sequences, ranges that start inside a tile
+    (1, [1], None),
+    (1, [127, 128, 129], None),
+    (2, [257, 1, 300, 4000], None),
+    (2, [5000, 5121], None),
+    (1, [40000], None),
+    (2, [700, 2048, 33], [130, 2047, 0]),
+    (8, [3000, 1], None),
+]
+
+
+@pytest.mark.parametrize("hkv,lens,first", PREFILL_SHAPES)
+def test_prefill_shapes_match_the_fp32_hash_mlp(device, hkv, lens, first):
+    """The tensor-core prefill over shapes that exercise its tile pairs, head changes and partial ranges: stored codes =
+    sign bits of the fp32 MLP outside the 1e-4 band, and no slot outside [first, S) is written."""
+    hq = 4 * hkv
+    usa = synthetic.make_usa(hq, 128, 5, True)
+    inp = synthetic.make_decode_inputs(311, lens, hq, hkv)
+    cache, ctx = build(device, inp.q, inp.k, inp.v, ha.Budget(16, 0.125, 16), usa)
+    sentinel = 0x5A5A5A5A
+    cache.hash_pages.fill_(sentinel)
+    ft = None if first is None else torch.tensor(first, dtype=torch.int32, device=device)
+    ctx.hash_prefill(ft)
+    torch.cuda.synchronize()
+    ctx.check_status()
+    nets = copy.deepcopy(usa).float().to(device).learning_to_hash_transformation_k
+    shifts = torch.arange(32, device=device, dtype=torch.int64)
+    written = torch.zeros_like(cache.hash_pages, dtype=torch.bool)
+    with torch.no_grad():
+        for b, S in enumerate(lens):
+            f0 = 0 if first is None else first[b]
+            k, _ = cache.read_kv(b)
+            got = cache.read_codes(b)
+            if S > f0:
+                pages, slots = cache._slots(b, f0, S - f0)
+                written[pages, :, slots, :] = True
+            for h in range(hq):
+                pre = nets[h](k[h // 4].float())                                   # [S, 32]
+                want = ((pre > 0).to(torch.int64) << shifts).sum(dim=-1)
+                must = ((pre.abs() >= 1e-4).to(torch.int64) << shifts).sum(dim=-1)
+                bad = ((got[h] ^ want) & must)[f0:] != 0
+                assert not bool(bad.any()), (b, h, int(bad.nonzero()[0]) + f0)
+                if f0 > 0:
+                    assert bool((got[h][:f0] == sentinel).all()), (b, h, "tokens in front of first_token were written")
+    untouched = cache.hash_pages.to(torch.int64) & 0xFFFFFFFF
+    assert bool((untouched[~written] == sentinel).all()), "a slot outside [first_token, S) was written"
 
 
 @pytest.mark.parametrize("bf16_weights", [True, False])
