@@ -24,8 +24,12 @@
 // and the issuer follows the same order, so the GEMM that a phase waits for was issued a whole phase earlier and
 // runs under the other tile's arithmetic.
 //
-// The hi/lo split keeps the pre-activations within ~3e-6 of fp32 arithmetic, which is what makes
+// The hi/lo split keeps the pre-activations within ~1e-6 of fp32 arithmetic, which is what makes
 // the packed codes match the reference bit for bit outside the |x| < 1e-5 band.
+//
+// fp32 weights (hash_prefill_tc_kernel<float>) are split the same way when a head is loaded: a hi and a lo bf16 copy
+// in shared memory, every GEMM multiplies by both (layer 0: X Whi + X Wlo; hidden layers: hi Whi + lo Whi + hi Wlo),
+// and the key-tile ring shrinks from four tiles to two to make room.
 //
 // Follows USA.k_embedding(hard=True) (hashattention/hashattention_llama.py:204-214).
 //
@@ -47,35 +51,44 @@ constexpr int kTcLoadWarp = 1;
 constexpr int kTcEpiWarp0 = 2;                        // epilogue warps kTcEpiWarp0 .. kTcEpiWarp0 + kTcEpiWarps - 1
 constexpr int kTcThreads = (kTcEpiWarps + 2) * 32;
 constexpr int kTcTile = 128;                          // tokens per tile = TMEM lanes
-constexpr int kTcXBufs = 4;                           // key-tile ring
 constexpr uint32_t kTcBlockBytes = 128 * 128;         // one K-half of a 128-row operand: 128 rows x 128 B
 constexpr uint32_t kTcW2BlockBytes = 32 * 128;        // one K-half of W2 (32 rows)
 constexpr uint32_t kTcOffW0 = 0;
 constexpr uint32_t kTcOffW1 = kTcOffW0 + 2 * kTcBlockBytes;
 constexpr uint32_t kTcOffW2 = kTcOffW1 + 2 * kTcBlockBytes;
-constexpr uint32_t kTcOffX = kTcOffW2 + 2 * kTcW2BlockBytes;
-constexpr uint32_t kTcOffBias = kTcOffX + kTcXBufs * 2 * kTcBlockBytes;  // 288 floats
-constexpr uint32_t kTcOffBar = kTcOffBias + 1280;
+constexpr uint32_t kTcWBytes = kTcOffW2 + 2 * kTcW2BlockBytes;  // one copy of a head's weights: 72 KB
+constexpr int kTcMaxXBufs = 4;
 // mbarriers (8 bytes each), by index
-constexpr int kTcBarXFull = 0;                        // [kTcXBufs] the loader's expect-tx arrival + the bytes of the two copies
-constexpr int kTcBarXEmpty = kTcBarXFull + kTcXBufs;  // [kTcXBufs] commit: layer 0 has read the tile
-constexpr int kTcBarAcc = kTcBarXEmpty + kTcXBufs;    // [2 slots][3 layers] commit: accumulator complete
+constexpr int kTcBarXFull = 0;                           // [key-tile ring] the loader's expect-tx arrival + the bytes of the two copies
+constexpr int kTcBarXEmpty = kTcBarXFull + kTcMaxXBufs;  // [key-tile ring] commit: layer 0 has read the tile
+constexpr int kTcBarAcc = kTcBarXEmpty + kTcMaxXBufs;    // [2 slots][3 layers] commit: accumulator complete
 constexpr int kTcBarAct = kTcBarAcc + 6;              // [2 slots] 16 warps: the activations of a hidden layer are written
 constexpr int kTcBarDrained = kTcBarAct + 2;          // 16 epilogue warps + issuer: no GEMM reads the old weights any more
 constexpr int kTcBarWeights = kTcBarDrained + 1;      // 16 epilogue warps: the next head's weights are in place
 constexpr int kTcBarFinal = kTcBarWeights + 1;        // commit: every GEMM of the CTA has completed
 constexpr int kTcNumBars = kTcBarFinal + 1;
-constexpr uint32_t kTcOffTmem = kTcOffBar + 8 * 32;   // tmem base (4 B), abort flag (4 B)
-constexpr uint32_t kTcSmemBytes = kTcOffTmem + 64 + 1024;  // + slack to align the base to 1024 B
 static_assert(kTcNumBars <= 32, "barrier block");
-static_assert(kTcSmemBytes <= 227 * 1024, "shared memory of one CTA");
+// Shared memory of a CTA. bf16 weights: one copy of the head's weights and a ring of four key tiles. fp32 weights are
+// split into a hi and a lo bf16 copy (W = hi + lo to 16 mantissa bits; every GEMM multiplies by both), and the ring
+// holds two tiles.
+template <bool kSplitW>
+struct TcLayout {
+    static constexpr int kXBufs = kSplitW ? 2 : 4;
+    static constexpr uint32_t kOffWLo = kTcWBytes;  // the lo copy (split weights only)
+    static constexpr uint32_t kOffX = kSplitW ? 2 * kTcWBytes : kTcWBytes;
+    static constexpr uint32_t kOffBias = kOffX + kXBufs * 2 * kTcBlockBytes;  // 288 floats
+    static constexpr uint32_t kOffBar = kOffBias + 1280;
+    static constexpr uint32_t kOffTmem = kOffBar + 8 * 32;   // tmem base (4 B), abort flag (4 B)
+    static constexpr uint32_t kSmemBytes = kOffTmem + 64 + 1024;  // + slack to align the base to 1024 B
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
+};
 constexpr uint32_t kTcTmemCols = 512;
 constexpr int kTcSpinLimit = 1 << 22;
 
 struct HashPrefillTcParams {
     const __nv_bfloat16* k_pages;
     uint32_t* hash_pages;
-    const __nv_bfloat16* wk;   // [Hq][36864] bf16
+    const void* wk;            // [Hq][36864] bf16 or fp32
     const float* bk;           // [Hq][288]
     const int32_t* page_table;
     const int32_t* seq_lens;
@@ -232,6 +245,27 @@ __device__ __forceinline__ void tc_load_operand(unsigned char* dst, const __nv_b
     }
 }
 
+// The same from fp32 weights: every weight becomes a hi and a lo bf16 (hi + lo carries 16 mantissa bits), written to
+// two copies of the operand.
+__device__ __forceinline__ void tc_load_operand(unsigned char* dst, unsigned char* dst_lo, const float* src, int rows,
+                                                uint32_t block_bytes, int t, int n) {
+    for (int i = t; i < rows * 16; i += n) {
+        const int row = i >> 4, c16 = i & 15;  // c16: 8 weights = one 16-byte chunk of the bf16 row
+        const float4 a = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * kHeadDim) + 2 * c16);
+        const float4 b = __ldg(reinterpret_cast<const float4*>(src + (size_t)row * kHeadDim) + 2 * c16 + 1);
+        const float w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            hi[j] = tc_pack_bf16(w[2 * j], w[2 * j + 1]);
+            lo[j] = tc_pack_bf16(w[2 * j] - bf16_lo(hi[j]), w[2 * j + 1] - bf16_hi(hi[j]));
+        }
+        const uint32_t off = (c16 >> 3) * block_bytes + tc_swizzled(row, c16 & 7);
+        *reinterpret_cast<uint4*>(dst + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4*>(dst_lo + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
 // bias + SiLU + hi/lo split of 16 accumulator columns v (bit patterns of fp32) of one row. The 16 words that take their
 // place are the A operand of one k-step of the next GEMM: words 0..7 hold the hi halves of the activations (two per
 // word, the even one in the low half), words 8..15 their lo halves.
@@ -342,8 +376,13 @@ struct TcCursor {
     }
 };
 
+template <typename WT>
 __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const HashPrefillTcParams p,
                                                                         const __grid_constant__ CUtensorMap k_map) {
+    constexpr bool kSplitW = sizeof(WT) == 4;  // fp32 weights: hi and lo copies, every GEMM multiplies by both
+    using L = TcLayout<kSplitW>;
+    constexpr int kTcXBufs = L::kXBufs;
+    constexpr uint32_t kTcOffX = L::kOffX, kTcOffBias = L::kOffBias, kTcOffBar = L::kOffBar, kTcOffTmem = L::kOffTmem;
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -358,10 +397,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
     // The weights of head h, by thread t of n. The first head of a CTA follows from its index alone, so its weights
     // are fetched before the dependency wait.
     auto load_head = [&](int h, int t, int n) {
-        const __nv_bfloat16* W = p.wk + (size_t)h * kMlpElems;
-        tc_load_operand(smem + kTcOffW0, W, 128, kTcBlockBytes, t, n);
-        tc_load_operand(smem + kTcOffW1, W + kHidden * kHeadDim, 128, kTcBlockBytes, t, n);
-        tc_load_operand(smem + kTcOffW2, W + kHidden * kHeadDim + kHidden * kHidden, 32, kTcW2BlockBytes, t, n);
+        const WT* W = static_cast<const WT*>(p.wk) + (size_t)h * kMlpElems;
+        if constexpr (kSplitW) {
+            unsigned char* lo = smem + L::kOffWLo;
+            tc_load_operand(smem + kTcOffW0, lo + kTcOffW0, W, 128, kTcBlockBytes, t, n);
+            tc_load_operand(smem + kTcOffW1, lo + kTcOffW1, W + kHidden * kHeadDim, 128, kTcBlockBytes, t, n);
+            tc_load_operand(smem + kTcOffW2, lo + kTcOffW2, W + kHidden * kHeadDim + kHidden * kHidden, 32, kTcW2BlockBytes, t, n);
+        } else {
+            tc_load_operand(smem + kTcOffW0, W, 128, kTcBlockBytes, t, n);
+            tc_load_operand(smem + kTcOffW1, W + kHidden * kHeadDim, 128, kTcBlockBytes, t, n);
+            tc_load_operand(smem + kTcOffW2, W + kHidden * kHeadDim + kHidden * kHidden, 32, kTcW2BlockBytes, t, n);
+        }
         for (int i = t; i < kMlpBias; i += n) s_bias[i] = p.bk[(size_t)h * kMlpBias + i];
     };
     load_head((int)(((long long)blockIdx.x * Hq) / gridDim.x), tid, kTcThreads);
@@ -370,8 +416,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
             for (int i = first; i < first + n; ++i)
                 asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar(i)), "r"(count));
         };
-        init(kTcBarXFull, kTcXBufs, 1);
-        init(kTcBarXEmpty, kTcXBufs, 1);
+        init(kTcBarXFull, kTcMaxXBufs, 1);
+        init(kTcBarXEmpty, kTcMaxXBufs, 1);
         init(kTcBarAcc, 6, 1);
         init(kTcBarAct, 2, kTcEpiWarps);
         init(kTcBarDrained, 1, kTcEpiWarps + 1);
@@ -520,6 +566,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
         const bool issue = lane == 0;
         const uint32_t w0_lo = tc_desc_lo(sbase + kTcOffW0), w1_lo = tc_desc_lo(sbase + kTcOffW1);
         const uint32_t w2_lo = tc_desc_lo(sbase + kTcOffW2), x_lo = tc_desc_lo(sbase + kTcOffX);
+        constexpr uint32_t kWLo = L::kOffWLo >> 4;  // from a descriptor of the hi copy to the lo copy
         // accumulator regions of a slot's current tile: layer 0 (and layer 2) in d_a, layer 1 in d_b; they swap per tile
         uint32_t d_a[2] = {tmem_u, tmem_u + 256u}, d_b[2] = {tmem_u + 128u, tmem_u + 384u};
         uint32_t changes = 0;
@@ -532,9 +579,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
             if (issue) {
                 const uint32_t xb = x_lo + buf * (2 * kTcBlockBytes >> 4);
 #pragma unroll
-                for (uint32_t ks = 0; ks < 8; ++ks)
-                    tc_mma_ss(d_a[slot], tc_desc(xb + tc_koff(ks, kTcBlockBytes)), tc_desc(w0_lo + tc_koff(ks, kTcBlockBytes)),
-                              tc_idesc(128), ks == 0 ? 0u : 1u);
+                for (uint32_t ks = 0; ks < 8; ++ks) {
+                    const uint64_t xdesc = tc_desc(xb + tc_koff(ks, kTcBlockBytes));
+                    tc_mma_ss(d_a[slot], xdesc, tc_desc(w0_lo + tc_koff(ks, kTcBlockBytes)), tc_idesc(128), ks == 0 ? 0u : 1u);
+                    if constexpr (kSplitW)
+                        tc_mma_ss(d_a[slot], xdesc, tc_desc(w0_lo + kWLo + tc_koff(ks, kTcBlockBytes)), tc_idesc(128), 1u);
+                }
                 tc_commit(bar(kTcBarXEmpty + (int)buf));
                 tc_commit(bar(kTcBarAcc + 3 * slot + 0));
             }
@@ -551,9 +601,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
                 const uint32_t idesc = layer == 0 ? tc_idesc(128) : tc_idesc(32);
 #pragma unroll
                 for (uint32_t ks = 0; ks < 8; ++ks) {
-                    const uint64_t bdesc = tc_desc(w_lo + (ks >> 2) * (blk >> 4) + (ks & 3) * 2);
+                    const uint32_t b_lo = w_lo + (ks >> 2) * (blk >> 4) + (ks & 3) * 2;
+                    const uint64_t bdesc = tc_desc(b_lo);
                     tc_mma_ts(d, a + 16 * ks, bdesc, idesc, ks == 0 ? 0u : 1u);
                     tc_mma_ts(d, a + 16 * ks + 8, bdesc, idesc, 1u);
+                    if constexpr (kSplitW) tc_mma_ts(d, a + 16 * ks, tc_desc(b_lo + kWLo), idesc, 1u);  // hi activations x lo weights
                 }
                 tc_commit(bar(kTcBarAcc + 3 * slot + 1 + (int)layer));
             }

@@ -623,16 +623,20 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         return HA_ERR_BAD_ARG;
 
     const int layers = weights->num_layers == 0 ? 3 : weights->num_layers;
-    if (weights->dtype == HA_WEIGHTS_BF16 && layers == 3) {
-        // bf16 weights, the 3-layer MLP: tcgen05 GEMM chain. One CTA per SM (its shared memory holds a head's weights).
+    if (layers == 3) {
+        // the 3-layer MLP: tcgen05 GEMM chain, for bf16 weights and for fp32 weights (split into hi and lo bf16 copies in
+        // shared memory). One CTA per SM (its shared memory holds a head's weights).
         // (a per-device function attribute: set at every call, so that a process driving several GPUs is served)
-        if (cudaFuncSetAttribute(hash_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kTcSmemBytes) != cudaSuccess)
+        const bool f32 = weights->dtype != HA_WEIGHTS_BF16;
+        const size_t smem_bytes = f32 ? TcLayout<true>::kSmemBytes : TcLayout<false>::kSmemBytes;
+        if ((f32 ? cudaFuncSetAttribute(hash_prefill_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes)
+                 : cudaFuncSetAttribute(hash_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem_bytes)) != cudaSuccess)
             return HA_ERR_LAUNCH;
         HashPrefillTcParams t;
         t.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
         t.hash_pages = hash_pages;
-        t.wk = static_cast<const __nv_bfloat16*>(weights->wk);
+        t.wk = weights->wk;
         t.bk = weights->bk;
         t.page_table = page_table;
         t.seq_lens = seq_lens;
@@ -658,16 +662,18 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)gx, 1, 1);
         cfg.blockDim = dim3(kTcThreads);
-        cfg.dynamicSmemBytes = kTcSmemBytes;
+        cfg.dynamicSmemBytes = smem_bytes;
         cfg.stream = static_cast<cudaStream_t>(stream);
         cudaLaunchAttribute attr1[1];
         attr1[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr1[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr1;
         cfg.numAttrs = 1;
-        return cudaLaunchKernelEx(&cfg, hash_prefill_tc_kernel, t, k_map) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+        const cudaError_t e = f32 ? cudaLaunchKernelEx(&cfg, hash_prefill_tc_kernel<float>, t, k_map)
+                                  : cudaLaunchKernelEx(&cfg, hash_prefill_tc_kernel<__nv_bfloat16>, t, k_map);
+        return e == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
     }
-    // fp32 weights, or the 1- and 2-layer hash functions: fp32 arithmetic on the CUDA cores
+    // the 1- and 2-layer hash functions: fp32 arithmetic on the CUDA cores
     HashPrefillParams p;
     p.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
     p.hash_pages = hash_pages;

@@ -99,12 +99,14 @@ PREFILL_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("bf16_weights", [True, False])
 @pytest.mark.parametrize("hkv,lens,first", PREFILL_SHAPES)
-def test_prefill_shapes_match_the_fp32_hash_mlp(device, hkv, lens, first):
-    """The tensor-core prefill over shapes that exercise its tile pairs, head changes and partial ranges: stored codes =
-    sign bits of the fp32 MLP outside the 1e-4 band, and no slot outside [first, S) is written."""
+def test_prefill_shapes_match_the_fp32_hash_mlp(device, hkv, lens, first, bf16_weights):
+    """The tensor-core prefill (bf16 weights, and fp32 weights split into two bf16 copies) over shapes that exercise its
+    tile pairs, head changes and partial ranges: stored codes = sign bits of the fp32 MLP outside the 1e-4 band, and no
+    slot outside [first, S) is written."""
     hq = 4 * hkv
-    usa = synthetic.make_usa(hq, 128, 5, True)
+    usa = synthetic.make_usa(hq, 128, 5, bf16_weights)
     inp = synthetic.make_decode_inputs(311, lens, hq, hkv)
     cache, ctx = build(device, inp.q, inp.k, inp.v, ha.Budget(16, 0.125, 16), usa)
     sentinel = 0x5A5A5A5A
