@@ -58,6 +58,14 @@ constexpr uint32_t kTcOffW1 = kTcOffW0 + 2 * kTcBlockBytes;
 constexpr uint32_t kTcOffW2 = kTcOffW1 + 2 * kTcBlockBytes;
 constexpr uint32_t kTcWBytes = kTcOffW2 + 2 * kTcW2BlockBytes;  // one copy of a head's weights: 72 KB
 constexpr int kTcMaxXBufs = 4;
+constexpr int kTcInfoRing = 16;  // tile records the loader keeps for the epilogue (it runs at most 6 tiles ahead of their use)
+// Where the codes of a tile go: byte offset of row 0's code word in the hash pages, and the rows [row_lo, row_hi) of the
+// tile that hold tokens to encode (none for a tile on a bad page). Written by the loader, read by the epilogue warps.
+struct TcTileInfo {
+    unsigned long long word0;
+    int row_lo, row_hi;
+};
+static_assert(sizeof(TcTileInfo) == 16, "tile record");
 // mbarriers (8 bytes each), by index
 constexpr int kTcBarXFull = 0;                           // [key-tile ring] the loader's expect-tx arrival + the bytes of the two copies
 constexpr int kTcBarXEmpty = kTcBarXFull + kTcMaxXBufs;  // [key-tile ring] commit: layer 0 has read the tile
@@ -79,7 +87,8 @@ struct TcLayout {
     static constexpr uint32_t kOffBias = kOffX + kXBufs * 2 * kTcBlockBytes;  // 288 floats
     static constexpr uint32_t kOffBar = kOffBias + 1280;
     static constexpr uint32_t kOffTmem = kOffBar + 8 * 32;   // tmem base (4 B), abort flag (4 B)
-    static constexpr uint32_t kSmemBytes = kOffTmem + 64 + 1024;  // + slack to align the base to 1024 B
+    static constexpr uint32_t kOffInfo = kOffTmem + 16;      // ring of kTcInfoRing tile records (16 B each)
+    static constexpr uint32_t kSmemBytes = kOffInfo + kTcInfoRing * 16 + 1024;  // + slack to align the base to 1024 B
     static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
 };
 constexpr uint32_t kTcTmemCols = 512;
@@ -383,6 +392,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
     using L = TcLayout<kSplitW>;
     constexpr int kTcXBufs = L::kXBufs;
     constexpr uint32_t kTcOffX = L::kOffX, kTcOffBias = L::kOffBias, kTcOffBar = L::kOffBar, kTcOffTmem = L::kOffTmem;
+    constexpr uint32_t kTcOffInfo = L::kOffInfo;
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -390,6 +400,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
     float* s_bias = reinterpret_cast<float*>(smem + kTcOffBias);
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + kTcOffTmem);
     volatile int* s_abort = reinterpret_cast<volatile int*>(smem + kTcOffTmem + 4);
+    TcTileInfo* s_info = reinterpret_cast<TcTileInfo*>(smem + kTcOffInfo);
     const uint32_t sbase = tc_smem_u32(smem);
     const uint32_t bars = sbase + kTcOffBar;
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
@@ -450,8 +461,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
         const uint32_t sl = (uint32_t)(warp - kTcEpiWarp0) >> 2;  // this warp's 32-column slice of a hidden layer
         const uint32_t row = (uint32_t)(warp & 3) * 32 + lane;    // token row of the tile = tensor-memory lane
         const uint32_t t_base = tmem + (((uint32_t)(warp & 3) * 32u) << 16);
-        TcCursor cur(p, false);
-        const long long total = cur.total;
+        int total, per_head, first_end, head0;  // this CTA's tiles; tiles per head; end of its first head's tiles; that head
+        {
+            const TcCursor cur(p, false);
+            total = (int)cur.total;
+            per_head = (int)cur.per_head;
+            first_end = per_head > 0 ? (int)(cur.per_head - cur.g0 % cur.per_head) : 0;
+            head0 = cur.h;
+        }
         uint32_t cnt_e[2] = {0, 0}, cnt_c[2] = {0, 0}, changes = 0;  // tiles per slot: hidden layers done, codes done; head changes
         bool ok = true;
         // column of this warp's slice in the accumulator of hidden layer `layer` of the slot's tile number `count` (layer 0
@@ -494,8 +511,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
             if (lane == 0) tc_arrive(bar(kTcBarAct + (int)slot));
             if (layer == 1) ++cnt_e[slot];
         };
-        // the codes of the tile in `slot`: thread = token row, each of the row's four warps packs 8 of the 32 sign bits
-        auto codes = [&](uint32_t slot, const TcItem& it) {
+        // the codes of tile i in `slot`: thread = token row, each of the row's four warps packs 8 of the 32 sign bits. Where
+        // they go is in the tile's record (read behind the wait below, which orders it behind the loader's write).
+        auto codes = [&](uint32_t slot, int i) {
             if (!wait(kTcBarAcc + 3 * (int)slot + 2, cnt_c[slot] & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             uint32_t r[8];
@@ -503,54 +521,50 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
             uint32_t code = 0;
 #pragma unroll
             for (int k = 0; k < 8; ++k) code |= (__uint_as_float(r[k]) + s_bias[2 * kHidden + 8 * sl + k] > 0.0f ? 1u : 0u) << k;
-            const int t = it.t0 + (int)row;
-            if (it.store && t < it.S && t >= it.first)
-                reinterpret_cast<uint8_t*>(p.hash_pages)[((it.slot0 + row) * kGroup + it.h % kGroup) * 4 + sl] = (uint8_t)code;
+            const TcTileInfo info = s_info[i % kTcInfoRing];
+            if ((int)row >= info.row_lo && (int)row < info.row_hi)
+                reinterpret_cast<uint8_t*>(p.hash_pages)[info.word0 + row * (kGroup * 4) + sl] = (uint8_t)code;
             ++cnt_c[slot];
             return true;
         };
         // The tiles of a head are worked on in pairs, one tile per slot, in the order
         //     layer 0 of a, [codes of the previous pair's b], layer 0 of b, layer 1 of a, layer 1 of b, codes of a
         // so that the GEMM a phase waits for was issued at least one whole phase earlier.
-        for (long long s0 = 0; s0 < total && ok;) {
-            const long long s1 = min(total, s0 + cur.per_head - (cur.g0 + s0) % cur.per_head);  // end of this head's tiles
+        for (int s0 = 0, seg = 0; s0 < total && ok; ++seg) {
+            const int s1 = min(total, s0 == 0 ? first_end : s0 + per_head);  // end of this head's tiles
             if (s0 > 0) {
                 // the weights change: the issuer and every epilogue warp meet (all GEMMs of the old head have completed),
                 // then the epilogue warps load together
                 __syncwarp();
                 if (lane == 0) tc_arrive(bar(kTcBarDrained));
                 if (!(ok = wait(kTcBarDrained, changes & 1))) break;
-                load_head(cur.head_of(s0), tid - kTcEpiWarp0 * 32, kTcEpiThreads);
+                load_head(head0 + seg, tid - kTcEpiWarp0 * 32, kTcEpiThreads);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) tc_arrive(bar(kTcBarWeights));
                 if (!(ok = wait(kTcBarWeights, changes & 1))) break;
                 ++changes;
             }
-            TcItem it_a, it_b, it_pend;
-            bool pend = false;
-            for (long long a = s0; a < s1 && ok; a += 2) {
+            int pend = -1;  // tile in slot 1 whose codes are due
+            for (int a = s0; a < s1 && ok; a += 2) {
                 const bool has_b = a + 1 < s1;
-                it_a = cur.next();  // (the page-table reads complete under the arithmetic: the items are used by the codes)
-                if (has_b) it_b = cur.next();
                 bool have_a = false, have_b = false;
 #pragma unroll 1
                 for (uint32_t layer = 0; layer < 2 && ok; ++layer) {
                     if (!have_a && !(ok = acquire(0, layer))) break;
                     hidden(0, layer, has_b, 1, layer, cnt_e[1], have_b);
-                    if (layer == 0 && pend && !(ok = codes(1, it_pend))) break;
+                    if (layer == 0 && pend >= 0 && !(ok = codes(1, pend))) break;
                     if (has_b) {
                         if (!have_b && !(ok = acquire(1, layer))) break;
                         hidden(1, layer, layer == 0, 0, 1, cnt_e[0], have_a);
                     } else {
                         have_a = false;
                     }
-                    if (layer == 1) ok = codes(0, it_a);
+                    if (layer == 1) ok = codes(0, a);
                 }
-                pend = has_b;
-                it_pend = it_b;
+                pend = has_b ? a + 1 : -1;
             }
-            if (ok && pend) ok = codes(1, it_pend);
+            if (ok && pend >= 0) ok = codes(1, pend);
             s0 = s1;
         }
     } else if (warp == kTcMmaWarp) {
@@ -653,6 +667,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) hash_prefill_tc_kernel(const Ha
                 const uint32_t buf = (uint32_t)(i % kTcXBufs);
                 if (!tc_wait(bar(kTcBarXEmpty + (int)buf), ((uint32_t)(i / kTcXBufs) & 1) ^ 1, s_abort, p.status)) break;
                 const TcItem it = cur.next();
+                {  // the tile's record for the epilogue, published by the arrival below
+                    TcTileInfo info;
+                    info.word0 = ((unsigned long long)it.slot0 * kGroup + (unsigned)(it.h % kGroup)) * 4ull;
+                    info.row_lo = max(0, it.first - it.t0);
+                    info.row_hi = it.store ? min(kTcTile, it.S - it.t0) : 0;
+                    s_info[i % kTcInfoRing] = info;
+                }
                 const uint32_t full = bar(kTcBarXFull + (int)buf), dst = sbase + kTcOffX + buf * 2 * kTcBlockBytes;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(2 * kTcBlockBytes) : "memory");
                 tc_tma_load(dst, &k_map, 0, (int)it.slot0, full);
