@@ -7,11 +7,11 @@ The directory name is not a Python identifier; load it under the module name
 """
 from . import _lib, partition
 from .cache import PagedHashKVCache
-from .ops import Budget, ChunkRows, HostStepBuffers, SparseDecodeContext, decode_step_host
+from .ops import Budget, ChunkRows, HostStepBuffers, SparseDecodeContext, decode_step_host, set_nvtx
 from .torch_ops import decode_step_op
 from .usa import USA, PackedHashWeights
 
 __all__ = [
     "USA", "PackedHashWeights", "PagedHashKVCache", "Budget", "ChunkRows", "SparseDecodeContext", "HostStepBuffers",
-    "decode_step_host", "decode_step_op", "_lib", "partition",
+    "decode_step_host", "decode_step_op", "set_nvtx", "_lib", "partition",
 ]

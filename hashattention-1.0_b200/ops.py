@@ -72,6 +72,35 @@ def _stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+_nvtx_on = False
+
+
+def set_nvtx(on: bool) -> None:
+    """Profiling aid: wrap every library call of this module in an NVTX range named after the entry point
+    (``hashattn/ha_decode_step`` ...), so that a timeline shows the step as one block. Off by default."""
+    global _nvtx_on
+    _nvtx_on = bool(on)
+
+
+class _call_range:
+    """``with _call_range("ha_decode_step"):`` - an NVTX range when switched on, nothing otherwise."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.pushed = False
+
+    def __enter__(self):
+        if _nvtx_on:
+            torch.cuda.nvtx.range_push("hashattn/" + self.name)
+            self.pushed = True
+        return self
+
+    def __exit__(self, *exc):
+        if self.pushed:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 class SparseDecodeContext:
     """Everything one layer's decode step needs besides q / k_new / v_new: the paged cache, the
     budgets, the packed hash weights, the workspace and the intermediate buffers (query codes,
@@ -140,7 +169,7 @@ class SparseDecodeContext:
         if preact_dbg is not None:
             _check(preact_dbg, "preact_dbg", torch.float32, (self.batch, 2, self.num_q_heads, 32), self.device)
         c = self.cache
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), _call_range("ha_hash_decode"):
             rc = self.lib.ha_hash_decode(
                 self.shape, self.c_weights, q.data_ptr(), k_new.data_ptr() if k_new is not None else None,
                 v_new.data_ptr() if v_new is not None else None, c.k_pages.data_ptr(), c.v_pages.data_ptr(),
@@ -155,7 +184,7 @@ class SparseDecodeContext:
         if first_token is not None:
             _check(first_token, "first_token", torch.int32, (self.batch,), self.device)
         c = self.cache
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), _call_range("ha_hash_prefill"):
             rc = self.lib.ha_hash_prefill(
                 self.shape, self.c_weights, c.k_pages.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
                 c.seq_lens.data_ptr(), first_token.data_ptr() if first_token is not None else None,
@@ -170,7 +199,7 @@ class SparseDecodeContext:
             _check(scores_dbg, "scores_dbg", torch.uint8,
                    (self.batch, self.num_q_heads, self.cache.max_pages * PAGE), self.device)
         c = self.cache
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), _call_range("ha_score_select"):
             rc = self.lib.ha_score_select(
                 self.shape, self.c_budget, q_codes.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
                 c.seq_lens.data_ptr(), self.sel_idx.data_ptr(), self.sel_cnt.data_ptr(),
@@ -185,7 +214,7 @@ class SparseDecodeContext:
         q_codes = self.q_codes if q_codes is None else q_codes
         _check(q_codes, "q_codes", torch.int32, (self.batch, self.num_q_heads), self.device)
         c = self.cache
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), _call_range("ha_score_plan"):
             rc = self.lib.ha_score_plan(
                 self.shape, self.c_budget, q_codes.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
                 c.seq_lens.data_ptr(), self.sel_cnt.data_ptr(), self.workspace.data_ptr(), self.workspace_bytes,
@@ -200,7 +229,7 @@ class SparseDecodeContext:
         out = torch.empty_like(q) if out is None else out
         _check(out, "out", torch.bfloat16, (self.batch, self.num_q_heads, HEAD_DIM), self.device)
         c = self.cache
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), _call_range("ha_select_attend"):
             rc = self.lib.ha_select_attend(
                 self.shape, self.c_budget, q.data_ptr(), c.k_pages.data_ptr(), c.v_pages.data_ptr(),
                 c.page_table.data_ptr(), c.seq_lens.data_ptr(), self.sel_idx.data_ptr(), self.sm_scale,
@@ -223,7 +252,7 @@ class SparseDecodeContext:
         q_codes = self.q_codes if q_codes is None else q_codes
         _check(q_codes, "q_codes", torch.int32, (self.batch, self.num_q_heads), self.device)
         c = self.cache
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), _call_range("ha_score_select_static"):
             rc = self.lib.ha_score_select_static(
                 self.shape, self.c_budget, q_codes.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
                 c.seq_lens.data_ptr(), self.sel_idx.data_ptr(), self.sel_cnt.data_ptr(), self.status.data_ptr(),
@@ -241,7 +270,7 @@ class SparseDecodeContext:
         _check(sel_idx, "sel_idx", torch.int32, (self.batch, self.num_q_heads, self.sel_stride), self.device)
         _check(sel_cnt, "sel_cnt", torch.int32, (self.batch, self.num_q_heads), self.device)
         c = self.cache
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), _call_range("ha_sparse_decode"):
             rc = self.lib.ha_sparse_decode(
                 self.shape, self.c_budget, q.data_ptr(), c.k_pages.data_ptr(), c.v_pages.data_ptr(),
                 c.page_table.data_ptr(), c.seq_lens.data_ptr(), sel_idx.data_ptr(), sel_cnt.data_ptr(),
@@ -265,7 +294,7 @@ class SparseDecodeContext:
             raise ValueError("v_new is required")
         out = torch.empty_like(q) if out is None else out
         _check(out, "out", torch.bfloat16, (self.batch, self.num_q_heads, HEAD_DIM), self.device)
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), _call_range("ha_decode_step_rows"):
             rc = self.lib.ha_decode_step_rows(
                 self.shape, self.c_budget, self.c_weights, q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
                 c.k_pages.data_ptr(), c.v_pages.data_ptr(), c.hash_pages.data_ptr(), c.page_table.data_ptr(),
@@ -282,7 +311,7 @@ class SparseDecodeContext:
         out = torch.empty_like(q) if out is None else out
         _check(out, "out", torch.bfloat16, (self.batch, self.num_q_heads, HEAD_DIM), self.device)
         c = self.cache
-        with torch.cuda.device(self.device):
+        with torch.cuda.device(self.device), _call_range("ha_decode_step"):
             rc = self.lib.ha_decode_step(
                 self.shape, self.c_budget, self.c_weights, q.data_ptr(), k_new.data_ptr(),
                 v_new.data_ptr() if v_new is not None else None, c.k_pages.data_ptr(), c.v_pages.data_ptr(),

@@ -533,6 +533,20 @@ def test_fp32_weights_step(device):
     run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(8, 0.25, 8))
 
 
+def test_step_inside_nvtx_ranges_is_the_same_step(device):
+    """ha.set_nvtx(True) only wraps the library calls in NVTX ranges."""
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(97, [640], 8, 2)
+    budget = ha.Budget(16, 0.125, 16)
+    _, out_plain, _, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget)
+    ha.set_nvtx(True)
+    try:
+        _, out_ranges, _, _ = run_step_and_check(device, usa, inp.q, inp.k, inp.v, budget)
+    finally:
+        ha.set_nvtx(False)
+    assert torch.equal(out_plain, out_ranges)
+
+
 def test_host_buffer_entry_point_equals_device_entry_point(device):
     usa = synthetic.make_usa(8, 128, 0, True)
     inp = synthetic.make_decode_inputs(96, [900, 513], 8, 2)

@@ -148,3 +148,17 @@ def test_decode_step_is_a_registered_torch_operator_without_a_cpu_kernel():
     assert op(*args("meta")) is None
     with pytest.raises(NotImplementedError):
         op(*args("cpu"))
+
+
+def test_nvtx_switch_is_off_by_default_and_costs_nothing_when_off():
+    """ops.set_nvtx: the ranges around the library calls are only opened when switched on."""
+    from hashattention_b200 import ops
+    assert ops._nvtx_on is False
+    with ops._call_range("ha_decode_step") as r:
+        assert r.pushed is False
+    ha.set_nvtx(True)
+    try:
+        assert ops._nvtx_on is True
+    finally:
+        ha.set_nvtx(False)
+    assert ops._nvtx_on is False
