@@ -24,7 +24,8 @@ HA_ERR_SEL_OVERFLOW = 8
 HA_ERR_SCRATCH_LIMIT = 9
 HA_WEIGHTS_BF16 = 0
 HA_WEIGHTS_F32 = 1
-HA_ABI_VERSION = 4
+HA_ABI_VERSION = 5
+HA_HASH_LSH = -1  # ha_hash_weights_t.num_layers of the LSH baseline
 HA_EVAL_SIMPLE = 0
 HA_EVAL_DEPTH = 1
 HA_OPT_CLUSTER_GATHER = 0
@@ -45,7 +46,7 @@ class HaBudget(ctypes.Structure):
 
 class HaHashWeights(ctypes.Structure):
     _fields_ = [("wq", c_void_p), ("bq", c_void_p), ("wk", c_void_p), ("bk", c_void_p), ("dtype", c_int32),
-                ("num_layers", c_int32)]
+                ("num_layers", c_int32), ("lsh_state", c_void_p)]
 
 
 _P = c_void_p

@@ -11,6 +11,7 @@
 #include "common.cuh"
 #include "hash_decode.cuh"
 #include "hash_prefill_tc.cuh"
+#include "lsh.cuh"
 #include "score_select.cuh"
 #include "select_attend.cuh"
 #include "sparse_decode.cuh"
@@ -54,7 +55,8 @@ int check_budget(const ha_budget_t* b) {
 int check_weights(const ha_hash_weights_t* w, bool need_q, bool need_k) {
     if (w == nullptr) return HA_ERR_BAD_ARG;
     if (w->dtype != HA_WEIGHTS_BF16 && w->dtype != HA_WEIGHTS_F32) return HA_ERR_BAD_ARG;
-    if (w->num_layers < 0 || w->num_layers > 3) return HA_ERR_BAD_ARG;
+    if (w->num_layers != HA_HASH_LSH && (w->num_layers < 0 || w->num_layers > 3)) return HA_ERR_BAD_ARG;
+    if (w->num_layers == HA_HASH_LSH && w->lsh_state == nullptr) return HA_ERR_BAD_ARG;
     if (need_q && (w->wq == nullptr || w->bq == nullptr)) return HA_ERR_BAD_ARG;
     if (need_k && (w->wk == nullptr || w->bk == nullptr)) return HA_ERR_BAD_ARG;
     return HA_OK;
@@ -491,6 +493,55 @@ int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* 
     return HA_OK;
 }
 
+static LshParams lsh_params(const ha_shape_t* shape, const ha_hash_weights_t* weights, const void* q, const void* k_new,
+                            const void* v_new, void* k_pages, void* v_pages, uint32_t* hash_pages,
+                            const int32_t* page_table, const int32_t* seq_lens, uint32_t* q_codes, float* preact_dbg,
+                            void* q_stage, int32_t* status) {
+    LshParams l;
+    l.q = static_cast<const __nv_bfloat16*>(q);
+    l.k_new = static_cast<const __nv_bfloat16*>(k_new);
+    l.v_new = static_cast<const __nv_bfloat16*>(v_new);
+    l.w = weights->wk != nullptr ? weights->wk : weights->wq;  // one function for both sides
+    l.bias = weights->bk != nullptr ? weights->bk : weights->bq;
+    l.k_pages = static_cast<__nv_bfloat16*>(k_pages);
+    l.v_pages = static_cast<__nv_bfloat16*>(v_pages);
+    l.hash_pages = hash_pages;
+    l.page_table = page_table;
+    l.seq_lens = seq_lens;
+    l.q_codes = q_codes;
+    l.preact_dbg = preact_dbg;
+    l.q_stage = static_cast<__nv_bfloat16*>(q_stage);
+    l.m = static_cast<float*>(weights->lsh_state);
+    l.stale = static_cast<int32_t*>(weights->lsh_state) + shape->num_kv_heads;
+    l.status = status;
+    l.B = shape->batch;
+    l.Hkv = shape->num_kv_heads;
+    l.max_pages = shape->max_pages;
+    l.num_pages = shape->num_pages;
+    l.only_if_stale = 0;
+    return l;
+}
+
+static cudaError_t launch_lsh_hash_keys(const ha_shape_t* shape, const LshParams& l, bool bf16, cudaStream_t st) {
+    cudaError_t e = bf16 ? cudaFuncSetAttribute(lsh_hash_keys_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)kLshSmemBytes)
+                         : cudaFuncSetAttribute(lsh_hash_keys_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)kLshSmemBytes);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(shape->max_pages, shape->num_kv_heads, shape->batch);
+    cfg.blockDim = dim3(kLshThreads);
+    cfg.dynamicSmemBytes = kLshSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr1[1];
+    attr1[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr1[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr1;
+    cfg.numAttrs = 1;
+    return bf16 ? cudaLaunchKernelEx(&cfg, lsh_hash_keys_kernel<__nv_bfloat16>, l)
+                : cudaLaunchKernelEx(&cfg, lsh_hash_keys_kernel<float>, l);
+}
+
 // ha_hash_decode with an optional device copy of q (q_stage) for the kernels that follow.
 static int hash_decode_impl(const ha_shape_t* shape, const ha_hash_weights_t* weights,
                             const void* q, const void* k_new, const void* v_new,
@@ -506,6 +557,22 @@ static int hash_decode_impl(const ha_shape_t* shape, const ha_hash_weights_t* we
     if (key_side && (hash_pages == nullptr || page_table == nullptr || seq_lens == nullptr))
         return HA_ERR_BAD_ARG;
     if (key_side && v_new != nullptr && (k_pages == nullptr || v_pages == nullptr)) return HA_ERR_BAD_ARG;
+
+    if (weights->num_layers == HA_HASH_LSH) {
+        // the LSH baseline: encode (and, key side, append); then re-hash the kv-heads whose largest key norm the new
+        // keys raised (a launch that returns at once otherwise)
+        LshParams l = lsh_params(shape, weights, q, k_new, v_new, k_pages, v_pages, hash_pages, page_table, seq_lens, q_codes,
+                                 preact_dbg, q_stage, status);
+        const cudaStream_t st = static_cast<cudaStream_t>(stream);
+        const bool bf16 = weights->dtype == HA_WEIGHTS_BF16;
+        const dim3 grid(shape->num_kv_heads, shape->batch);
+        cudaError_t e = bf16 ? launch(lsh_encode_kernel<__nv_bfloat16>, grid, dim3(kLshThreads), st, 1, l)
+                             : launch(lsh_encode_kernel<float>, grid, dim3(kLshThreads), st, 1, l);
+        if (e != cudaSuccess) return HA_ERR_LAUNCH;
+        if (!key_side) return HA_OK;
+        l.only_if_stale = 1;
+        return launch_lsh_hash_keys(shape, l, bf16, st) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    }
 
     HashDecodeParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
@@ -622,6 +689,19 @@ int ha_hash_prefill(const ha_shape_t* shape, const ha_hash_weights_t* weights,
         status == nullptr)
         return HA_ERR_BAD_ARG;
 
+    if (weights->num_layers == HA_HASH_LSH) {
+        // the LSH baseline: the largest key norm per kv-head over the whole cache first, then every key's code (the whole
+        // cache, whatever first_token says: a longer key changes the code of every other key)
+        const LshParams l = lsh_params(shape, weights, nullptr, nullptr, nullptr, const_cast<void*>(k_pages), nullptr, hash_pages,
+                                       page_table, seq_lens, nullptr, nullptr, nullptr, status);
+        const cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (cudaMemsetAsync(weights->lsh_state, 0, 2 * sizeof(int32_t) * shape->num_kv_heads, st) != cudaSuccess)
+            return HA_ERR_LAUNCH;
+        const dim3 grid(shape->max_pages, shape->num_kv_heads, shape->batch);
+        // (after a memset the first kernel is launched without the programmatic attribute's early start: plain order)
+        if (launch(lsh_norm_max_kernel, grid, dim3(kLshThreads), st, 1, l) != cudaSuccess) return HA_ERR_LAUNCH;
+        return launch_lsh_hash_keys(shape, l, weights->dtype == HA_WEIGHTS_BF16, st) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
+    }
     const int layers = weights->num_layers == 0 ? 3 : weights->num_layers;
     if (layers == 3) {
         // the 3-layer MLP: tcgen05 GEMM chain, for bf16 weights and for fp32 weights (split into hi and lo bf16 copies in
@@ -850,6 +930,8 @@ int ha_decode_step_rows(const ha_shape_t* shape, const ha_budget_t* budget,
                         void* out, void* workspace, size_t workspace_bytes,
                         int32_t* status, void* stream) {
     if (budget_lens == nullptr) return check_shape(shape) != HA_OK ? check_shape(shape) : HA_ERR_BAD_ARG;
+    // (the LSH baseline takes its norm bound over the vectors of a call; rows of one chunk would have to share it)
+    if (weights != nullptr && weights->num_layers == HA_HASH_LSH) return HA_ERR_BAD_ARG;
     return decode_step_impl(shape, budget, weights, q, k_new, v_new, nullptr, k_pages, v_pages, hash_pages,
                             page_table, seq_lens, budget_lens, q_codes, sel_idx, sel_cnt, sm_scale, out, workspace,
                             workspace_bytes, status, stream);

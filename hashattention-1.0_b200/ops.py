@@ -126,7 +126,9 @@ class SparseDecodeContext:
         self.shape = _lib.HaShape(self.batch, self.num_kv_heads, GROUP, HEAD_DIM, PAGE, cache.max_pages,
                                   cache.num_pages, self.sel_stride)
         self.c_budget = budget.c_struct()
-        self.c_weights = weights.c_struct()
+        # the LSH baseline keeps, per cache, the largest key norm of every kv-head and a "codes are stale" flag
+        self.lsh_state = torch.zeros(2 * self.num_kv_heads, dtype=torch.int32, device=self.device) if weights.lsh else None
+        self.c_weights = weights.c_struct(self.lsh_state)
         self.workspace_bytes = int(self.lib.ha_workspace_bytes(self.shape, self.c_budget))
         if self.workspace_bytes == 0:
             raise ValueError("invalid shape or budget for the CUDA library")

@@ -36,11 +36,20 @@ class PackedHashWeights:
     wk: torch.Tensor
     bk: torch.Tensor
     dtype_code: int
-    num_layers: int = 3   # Linear layers of the hash function; unused slots of the layout hold zeros
+    num_layers: int = 3   # Linear layers of the hash function; unused slots of the layout hold zeros; 0: the LSH baseline
 
-    def c_struct(self) -> _lib.HaHashWeights:
+    @property
+    def lsh(self) -> bool:
+        return self.num_layers == 0
+
+    def c_struct(self, lsh_state: torch.Tensor | None = None) -> _lib.HaHashWeights:
+        """``lsh_state``: the cache's LSH state (see include/hashattn.h), required in LSH mode."""
+        if self.lsh and lsh_state is None:
+            raise ValueError("the LSH baseline needs the cache's state buffer")
         return _lib.HaHashWeights(self.wq.data_ptr(), self.bq.data_ptr(), self.wk.data_ptr(),
-                                  self.bk.data_ptr(), self.dtype_code, self.num_layers)
+                                  self.bk.data_ptr(), self.dtype_code,
+                                  _lib.HA_HASH_LSH if self.lsh else self.num_layers,
+                                  lsh_state.data_ptr() if lsh_state is not None else None)
 
     def slice_heads(self, h0: int, h1: int) -> "PackedHashWeights":
         """The weights of query heads [h0, h1): what one GPU of a kv-head partition holds."""
@@ -60,14 +69,22 @@ def _mlp(head_dim: int, int_dim: int, final_dim: int, num_layers: int = 3) -> nn
     return nn.Sequential(nn.Linear(head_dim, final_dim))
 
 
+class IpToCS(nn.Module):
+    """Placeholder with the reference's name and position (hashattention/hashattention_llama.py:75-84) so that the
+    Linear(129, 32) behind it keeps its state-dict key ``...{head}.1.{weight,bias}``; the lifting itself
+    (x -> [x, sqrt(relu(M^2 - |x|^2))]) runs in the CUDA kernels."""
+
+    def forward(self, x):
+        raise RuntimeError("evaluated by the CUDA library")
+
+
 class USA(nn.Module):
     """Parameter container with the reference's constructor signature
     (hashattention/hashattention_llama.py:87-139).
 
-    Only the configurations the kernels implement are accepted: 3, 2 or 1 layers, hidden width 128,
-    32 output bits, head_dim 128. Other ``lth_*`` settings (the LSH baseline ``lth_num_layers=0`` among
-    them: its extra input coordinate depends on the largest key norm of the whole call, :75-84, so cached
-    codes would go stale) raise ``NotImplementedError``.
+    Only the configurations the kernels implement are accepted: 3, 2 or 1 layers or the LSH baseline
+    (``lth_num_layers=0``, :130-139: one shared Linear(129, 32) per head with normal weights), hidden width 128,
+    32 output bits, head_dim 128. Other ``lth_*`` settings raise ``NotImplementedError``.
     """
 
     def __init__(self, num_heads: int, head_dim: int, usa_params: dict = DEFAULT_USA_CFG):
@@ -78,16 +95,25 @@ class USA(nn.Module):
         self.lth_final_dim = usa_params["lth_final_dim"]
         self.lth_thold = usa_params["lth_thold"]
         self.num_layers = usa_params.get("lth_num_layers", 3)
-        if self.num_layers not in (1, 2, 3) or (self.int_dim, self.lth_final_dim, head_dim) != (HIDDEN, CODE_BITS, 128):
+        if self.num_layers not in (0, 1, 2, 3) or (self.int_dim, self.lth_final_dim, head_dim) != (HIDDEN, CODE_BITS, 128):
             raise NotImplementedError(
-                "the sm_100a kernels implement lth_num_layers=1..3, lth_init_dim=128, lth_final_dim=32, "
+                "the sm_100a kernels implement lth_num_layers=0..3, lth_init_dim=128, lth_final_dim=32, "
                 f"head_dim=128; got layers={self.num_layers}, int_dim={self.int_dim}, "
                 f"final_dim={self.lth_final_dim}, head_dim={head_dim}"
             )
-        self.learning_to_hash_transformation_k = nn.ModuleList(
-            [_mlp(head_dim, self.int_dim, self.lth_final_dim, self.num_layers) for _ in range(num_heads)])
-        self.learning_to_hash_transformation_q = nn.ModuleList(
-            [_mlp(head_dim, self.int_dim, self.lth_final_dim, self.num_layers) for _ in range(num_heads)])
+        if self.num_layers == 0:
+            # the reference's structure and initialisation order (:130-139): one list under three names
+            self.learning_to_hash_transformation = nn.ModuleList(
+                [nn.Sequential(IpToCS(), nn.Linear(head_dim + 1, self.lth_final_dim)) for _ in range(num_heads)])
+            self.learning_to_hash_transformation_k = self.learning_to_hash_transformation
+            self.learning_to_hash_transformation_q = self.learning_to_hash_transformation
+            for i in range(num_heads):
+                nn.init.normal_(self.learning_to_hash_transformation[i][1].weight)
+        else:
+            self.learning_to_hash_transformation_k = nn.ModuleList(
+                [_mlp(head_dim, self.int_dim, self.lth_final_dim, self.num_layers) for _ in range(num_heads)])
+            self.learning_to_hash_transformation_q = nn.ModuleList(
+                [_mlp(head_dim, self.int_dim, self.lth_final_dim, self.num_layers) for _ in range(num_heads)])
         self._packed: PackedHashWeights | None = None
         # a state dict loaded through this module or any parent invalidates the packed copy
         self.register_load_state_dict_post_hook(lambda module, _incompatible: setattr(module, "_packed", None))
@@ -99,6 +125,13 @@ class USA(nn.Module):
         def slots(net):
             lin = [m for m in net if isinstance(m, nn.Linear)]
             z = lambda *shape: torch.zeros(*shape, dtype=lin[0].weight.dtype, device=lin[0].weight.device)  # noqa: E731
+            if self.num_layers == 0:
+                # Linear(129, 32): columns 0..127 in the W2 slot, column 128 in b0[0..31], the bias in b2
+                w129, b = lin[0].weight, lin[0].bias
+                b0 = z(HIDDEN)
+                b0[:CODE_BITS] = w129[:, self.head_dim]
+                return (torch.cat([z(HIDDEN, self.head_dim).reshape(-1), z(HIDDEN, HIDDEN).reshape(-1),
+                                   w129[:, :self.head_dim].reshape(-1)]), torch.cat([b0, z(HIDDEN), b]))
             first = lin[0] if len(lin) >= 2 else None
             second = lin[1] if len(lin) == 3 else None
             last = lin[-1]
@@ -117,10 +150,11 @@ class USA(nn.Module):
     def packed(self, device=None, refresh: bool = False) -> PackedHashWeights:
         """Kernel-side copy of the parameters. bf16 parameters stay bf16 (the kernels up-cast
         them exactly); anything else is kept as fp32."""
-        device = torch.device(device) if device is not None else self.learning_to_hash_transformation_k[0][0].weight.device
+        first_linear = next(m for m in self.learning_to_hash_transformation_k[0] if isinstance(m, nn.Linear))
+        device = torch.device(device) if device is not None else first_linear.weight.device
         if self._packed is not None and not refresh and self._packed.wq.device == device:
             return self._packed
-        pdtype = self.learning_to_hash_transformation_k[0][0].weight.dtype  # (index 0 is a Linear for every layer count)
+        pdtype = first_linear.weight.dtype
         if pdtype == torch.bfloat16:
             wdtype, code = torch.bfloat16, _lib.HA_WEIGHTS_BF16
         else:

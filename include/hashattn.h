@@ -47,7 +47,7 @@
 extern "C" {
 #endif
 
-#define HA_ABI_VERSION 4
+#define HA_ABI_VERSION 5
 
 /* status codes (return values and contents of the device status word) */
 #define HA_OK 0
@@ -63,6 +63,7 @@ extern "C" {
 
 #define HA_WEIGHTS_BF16 0
 #define HA_WEIGHTS_F32 1
+#define HA_HASH_LSH (-1) /* ha_hash_weights_t.num_layers: the LSH baseline, lth_num_layers == 0 of the reference */
 
 /* Shape of one layer's paged cache as seen by ONE GPU (after any kv-head partitioning). */
 typedef struct ha_shape {
@@ -106,7 +107,16 @@ typedef struct ha_hash_weights {
                          * meaning 3): Linear-SiLU-Linear-SiLU-Linear; 2: Linear(128,128)-SiLU-
                          * Linear(128,32), stored in the W0 and W2 slots; 1: Linear(128,32), stored in
                          * the W2 slot. Unused slots are ignored. The layout per head stays
-                         * [W0 | W1 | W2] and [b0 | b1 | b2].                                 */
+                         * [W0 | W1 | W2] and [b0 | b1 | b2].
+                         * HA_HASH_LSH: the LSH baseline (lth_num_layers == 0 there, :75-84, :130-139): one
+                         * Linear(129,32) per head over [x, sqrt(relu(M^2 - |x|^2))], M = 1e-3 + the largest
+                         * norm of the call; columns 0..127 of its weight in the W2 slot, column 128 in
+                         * b0[0..31], its bias in b2; the key and the query side are the same function.  */
+    void* lsh_state;    /* HA_HASH_LSH only, else ignored: device buffer of 2 * num_kv_heads 32-bit words that
+                         * belongs to the cache - float m[num_kv_heads], the largest key norm cached per
+                         * kv-head (set by ha_hash_prefill, raised by decode steps), then int32
+                         * stale[num_kv_heads]. A step whose new keys raise m re-hashes that kv-head's
+                         * cache, as the reference (which re-hashes every key on every step) implies.      */
 } ha_hash_weights_t;
 
 int ha_abi_version(void);
@@ -262,7 +272,8 @@ int ha_decode_step_rows(const ha_shape_t* shape, const ha_budget_t* budget,
 
 /* Number of kernels one ha_decode_step call enqueues for this shape and budget (the library picks
  * between a single-pass cluster selection and scoring + fused selection/attention); 0 for an
- * invalid shape. For launch accounting; no reference counterpart.     */
+ * invalid shape. For launch accounting; no reference counterpart. (With the LSH baseline, HA_HASH_LSH,
+ * a step enqueues one kernel more: the re-hash pass that returns at once unless the key norm bound rose.) */
 int ha_decode_step_launches(const ha_shape_t* shape, const ha_budget_t* budget);
 /* The kernels of that step by name, in launch order, as a static string (for labelling measurements). */
 const char* ha_decode_step_path(const ha_shape_t* shape, const ha_budget_t* budget);

@@ -38,12 +38,22 @@ def mlp_preact(nets, x: torch.Tensor) -> torch.Tensor:
     outs = []
     for h, layers in enumerate(nets):
         y = x[:, h].to(torch.float32)
+        if layers[0][0].shape[1] == y.shape[-1] + 1:
+            y = ip_to_cs(y)  # the LSH baseline (lth_num_layers == 0, :130-139): Linear(129, 32) over the lifted vector
         for i, (w, b) in enumerate(layers):
             y = F.linear(y, w, b)
             if i + 1 < len(layers):
                 y = F.silu(y)
         outs.append(y)
     return torch.stack(outs, dim=1)
+
+
+def ip_to_cs(x: torch.Tensor) -> torch.Tensor:
+    """IpToCS.forward (hashattention_llama.py:75-84): ``x [..., D] -> [..., D + 1]`` with the extra coordinate
+    sqrt(relu(M^2 - |x|^2)), M = 1e-3 + the largest norm among ALL vectors passed (batch and positions)."""
+    norm = x.norm(dim=-1).unsqueeze(-1)
+    M = norm.max().item() + 1e-3
+    return torch.cat([x, torch.sqrt(F.relu(M ** 2 - norm ** 2))], dim=-1)
 
 
 def nets_from_usa(usa, side: str):

@@ -311,10 +311,25 @@ def layers():
     np.savez_compressed(os.path.join(HERE, "layers.npz"), **arrays)
 
 
+def lsh():
+    """The LSH baseline (lth_num_layers 0, :75-84 and :130-139): two sequences of 300 tokens, 4 query heads, 1 kv head.
+    The norm bound of IpToCS is taken over both sequences; sequence 1's keys are scaled by 1.5 so that it is theirs."""
+    Hq, Hkv, S, init, recent, heavy = 4, 1, 300, 16, 16, 1.0 / 8
+    inp = synthetic.make_decode_inputs(191, [S, S], Hq, Hkv, bf16=True)
+    q, k, v = inp.q, torch.stack(inp.k), torch.stack(inp.v)
+    k[1] = (k[1] * 1.5).bfloat16().float()
+    _, usa, att = reference_modules(Hq, Hkv, init, recent, heavy, layers=0)
+    arrays = dict(meta=np.array([Hq, Hkv, S, init, recent], dtype=np.int64), heavy=np.float64(heavy),
+                  q=bf16_bits(q), k=bf16_bits(k), v=bf16_bits(v))
+    arrays.update(outputs_to_arrays(run_reference(att, usa, q, k, v), prefix=""))
+    np.savez_compressed(os.path.join(HERE, "lsh.npz"), **arrays)
+
+
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["case_a", "edge", "config0", "depth", "rows", "layers"]
+    which = sys.argv[1:] or ["case_a", "edge", "config0", "depth", "rows", "layers", "lsh"]
     for name in which:
-        {"case_a": case_a, "edge": edge, "config0": config0, "depth": depth, "rows": rows, "layers": layers}[name]()
+        {"case_a": case_a, "edge": edge, "config0": config0, "depth": depth, "rows": rows, "layers": layers,
+         "lsh": lsh}[name]()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

@@ -52,6 +52,14 @@ def load_case_a() -> GoldenCase:
                       float(z["heavy"]))
 
 
+def load_lsh() -> GoldenCase:
+    """The LSH baseline (lth_num_layers = 0) recorded from the reference: two sequences that share one norm bound."""
+    z = np.load(os.path.join(GOLDEN, "lsh.npz"))
+    Hq, Hkv, S, init, recent = (int(x) for x in z["meta"])
+    return GoldenCase(z, "", from_bf16_bits(z["q"]), from_bf16_bits(z["k"]), from_bf16_bits(z["v"]), init, recent,
+                      float(z["heavy"]))
+
+
 class DepthCase:
     """case_a's inputs under the depth rule (usa_eval_mode != 'simple'): budget, depth, the
     reference's keep-mask and attention output."""

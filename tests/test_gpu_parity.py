@@ -533,6 +533,101 @@ def test_fp32_weights_step(device):
     run_step_and_check(device, usa, inp.q, inp.k, inp.v, ha.Budget(8, 0.25, 8))
 
 
+# ------------------------------------------------------------------------------------------
+# the LSH baseline (lth_num_layers = 0): the norm bound couples every key of a kv-head, over all sequences
+# ------------------------------------------------------------------------------------------
+def _lsh_check_cache(cache, usa, ks):
+    """Every cached key code against the oracle over the WHOLE batch (IpToCS takes its bound over the call)."""
+    k = torch.stack(ks)
+    _, k_pre = helpers.oracle_preacts(usa, torch.zeros(k.shape[0], usa.num_heads, 128), k)
+    for b in range(k.shape[0]):
+        assert helpers.codes_match(cache.read_codes(b).cpu(), orc.pack_codes(k_pre[b]), orc.band_mask(k_pre[b])), b
+
+
+def test_lsh_baseline_step_matches_reference(device):
+    case = helpers.load_lsh()
+    B, Hq = case.q.shape[0], case.q.shape[1]
+    usa = synthetic.make_usa(Hq, 128, 0, True, num_layers=0)
+    budget = budget_of(case)
+    cache, ctx = build(device, case.q, case.k, case.v, budget, usa, prefill_to=[case.S - 1] * B)
+    ctx.hash_prefill()
+    cache.seq_lens += 1
+    out = ctx.decode_step(case.q.to(device, torch.bfloat16), case.k[:, :, -1].to(device, torch.bfloat16),
+                          case.v[:, :, -1].to(device, torch.bfloat16)).float().cpu()
+    ctx.check_status()
+    q_codes = ctx.q_codes.cpu().to(torch.int64) & ALL_BITS
+    assert helpers.codes_match(q_codes, case.q_codes, case.q_must)
+    same = bool((q_codes == case.q_codes).all())
+    for b in range(B):
+        k_codes = cache.read_codes(b).cpu()
+        assert helpers.codes_match(k_codes, case.k_codes[b], case.k_must[b])
+        same &= bool((k_codes == case.k_codes[b]).all())
+    if same:  # no bit inside the exclusion band differs: the reference's own sets and outputs apply
+        want = orc.heavy_sets(case.mask, case.init, case.recent)
+        for b in range(B):
+            for h in range(Hq):
+                assert torch.equal(heavy_from_device(ctx, b, h), want[b][h]), (b, h)
+        ok, max_abs, rel = helpers.att_close(out, case.out)
+        assert ok, (max_abs, rel)
+    else:
+        pytest.skip("a hash bit inside the exclusion band differs from the recorded run")
+
+
+def test_lsh_baseline_rehashes_when_a_longer_key_arrives(device):
+    """Three steps on two sequences: an ordinary one, one whose new key in sequence 1 is four times as long as anything
+    cached (every code of BOTH sequences changes, as in the reference, which hashes all keys on every step), another
+    ordinary one. After each step all cached codes, the query codes, the selected sets and the output equal the oracle's."""
+    Hq, Hkv, S0, steps = 8, 2, 300, 3
+    usa = synthetic.make_usa(Hq, 128, 3, True, num_layers=0)
+    inp = synthetic.make_decode_inputs(198, [S0 + steps] * 2, Hq, Hkv)
+    ks, vs = [k.clone() for k in inp.k], [v.clone() for v in inp.v]
+    ks[1][:, S0 + 1] = (ks[1][:, S0 + 1] * 4).bfloat16().float()
+    budget = ha.Budget(16, 0.125, 16)
+    cache, ctx = build(device, None, ks, vs, budget, usa, prefill_to=[S0] * 2)
+    ctx.hash_prefill()
+    _lsh_check_cache(cache, usa, [k[:, :S0] for k in ks])
+    gen = torch.Generator().manual_seed(5)
+    norms = []
+    for t in range(steps):
+        S = S0 + t + 1
+        q = torch.randn(2, Hq, 128, generator=gen).bfloat16().float()
+        cache.seq_lens += 1
+        k_new = torch.stack([k[:, S - 1] for k in ks]).to(device, torch.bfloat16)
+        v_new = torch.stack([v[:, S - 1] for v in vs]).to(device, torch.bfloat16)
+        out = ctx.decode_step(q.to(device, torch.bfloat16), k_new, v_new).float().cpu()
+        torch.cuda.synchronize()
+        ctx.check_status()
+        norms.append(float(ctx.lsh_state[:Hkv].view(torch.float32).max()))
+        cur = [k[:, :S] for k in ks]
+        _lsh_check_cache(cache, usa, cur)
+        q_pre, _ = helpers.oracle_preacts(usa, q, torch.stack(cur))
+        q_codes = ctx.q_codes.cpu().to(torch.int64) & ALL_BITS
+        assert helpers.codes_match(q_codes, orc.pack_codes(q_pre), orc.band_mask(q_pre))
+        for b in range(2):
+            scores = orc.hamming_scores(q_codes[b][None], cache.read_codes(b).cpu()[None])
+            mask = orc.select_mask(scores, budget.init_budget, budget.recent_budget, budget.heavy_budget)
+            want = orc.heavy_sets(mask, budget.init_budget, budget.recent_budget)[0]
+            for h in range(Hq):
+                assert torch.equal(heavy_from_device(ctx, b, h), want[h]), (t, b, h)
+            ref = orc.masked_attention(q[b:b + 1], cur[b][None], vs[b][None, :, :S], mask)
+            ok, max_abs, rel = helpers.att_close(out[b:b + 1], ref)
+            assert ok, (t, b, max_abs, rel)
+    assert norms[1] > 1.5 * norms[0] and norms[2] == norms[1], norms  # the bound rose once, with the long key
+
+
+def test_lsh_baseline_refuses_multi_token_chunks(device):
+    usa = synthetic.make_usa(8, 128, 3, True, num_layers=0)
+    inp = synthetic.make_decode_inputs(199, [300], 8, 2)
+    cache, ctx = build(device, None, inp.k, inp.v, ha.Budget(16, 0.125, 16), usa, prefill_to=[296])
+    ctx.hash_prefill()
+    rows = ha.ChunkRows(cache, 4)
+    rctx = ha.SparseDecodeContext(rows, ha.Budget(16, 0.125, 16), usa.packed(device))
+    rows.advance()
+    z = lambda h: torch.zeros(4, h, 128, dtype=torch.bfloat16, device=device)  # noqa: E731
+    with pytest.raises(RuntimeError, match="bad argument|invalid"):
+        rctx.decode_step_rows(z(8), z(2), z(2))
+
+
 def test_step_inside_nvtx_ranges_is_the_same_step(device):
     """ha.set_nvtx(True) only wraps the library calls in NVTX ranges."""
     usa = synthetic.make_usa(8, 128, 0, True)

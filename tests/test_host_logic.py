@@ -21,13 +21,34 @@ def test_usa_state_dict_layout():
 
 
 @pytest.mark.parametrize("params", [
-    {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 0},
+    {"lth_int_dim": 128, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 4},
     {"lth_int_dim": 64, "lth_final_dim": 32, "lth_thold": 0, "lth_num_layers": 3},
     {"lth_int_dim": 128, "lth_final_dim": 64, "lth_thold": 0, "lth_num_layers": 3},
 ])
 def test_usa_rejects_unimplemented_configurations(params):
     with pytest.raises(NotImplementedError):
         ha.USA(8, 128, params)
+
+
+def test_lsh_baseline_module_and_packing():
+    """lth_num_layers = 0: one Linear(129, 32) per head under three names (hashattention_llama.py:130-139); packed as
+    columns 0..127 in the W2 slot, column 128 in b0[0..31], the bias in b2, the same buffers for both sides."""
+    usa = synthetic.make_usa(4, 128, seed=2, bf16=False, num_layers=0)
+    keys = list(usa.state_dict())
+    assert keys[0] == "learning_to_hash_transformation.0.1.weight"
+    assert "learning_to_hash_transformation_k.3.1.bias" in keys and "learning_to_hash_transformation_q.3.1.bias" in keys
+    assert usa.learning_to_hash_transformation_k is usa.learning_to_hash_transformation_q
+    lin = usa.learning_to_hash_transformation[1][1]
+    assert lin.weight.shape == (32, 129) and abs(float(lin.weight.std()) - 1.0) < 0.1
+    p = usa.packed("cpu")
+    assert p.lsh and p.wq.shape == (4, 36864) and torch.equal(p.wq, p.wk) and torch.equal(p.bq, p.bk)
+    w2 = p.wk[1, 128 * 128 * 2:].reshape(32, 128)
+    assert torch.equal(w2, lin.weight[:, :128]) and not bool(p.wk[1, :128 * 128 * 2].any())
+    assert torch.equal(p.bk[1, :32], lin.weight[:, 128]) and torch.equal(p.bk[1, 256:], lin.bias)
+    with pytest.raises(ValueError):
+        p.c_struct()  # the cache's state buffer is required
+    state = torch.zeros(2, dtype=torch.int32)
+    assert p.c_struct(state).num_layers == ha._lib.HA_HASH_LSH
 
 
 def test_packing_layout_and_invalidation():

@@ -37,7 +37,10 @@ def test_load_usa_builds_one_module_per_layer_and_loads_reference_state_dicts(tm
         "0.learning_to_hash_transformation_k.0.2.weight", "0.learning_to_hash_transformation_k.0.2.bias"]
     packed = two[0].packed("cpu")
     assert packed.num_layers == 2 and packed.wk.shape == (4, 36864) and float(packed.wk[:, 16384:32768].abs().max()) == 0.0
-    cfg.lth_num_layers = 0     # the LSH baseline is not implemented
+    cfg.lth_num_layers = 0     # the LSH baseline: one shared Linear(129, 32) per head
+    lsh = hal.load_usa(cfg, None, device="cpu")
+    assert lsh[0].packed("cpu").lsh and lsh[0].learning_to_hash_transformation[0][1].weight.shape == (32, 129)
+    cfg.lth_num_layers = 4     # not a configuration of the reference
     with pytest.raises(NotImplementedError):
         hal.load_usa(cfg, None, device="cpu")
 
