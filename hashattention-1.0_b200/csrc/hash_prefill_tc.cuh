@@ -230,7 +230,7 @@ __device__ __forceinline__ void tc_st16_issue(uint32_t taddr, const uint32_t (&r
 }
 
 // TMA: the box at element column x, row y of the key cache -> shared memory, bytes counted on the mbarrier (the
-// copy reads this GPU's memory only and is not multicast).
+// copy reads this GPU's memory only and has this CTA as its single destination).
 __device__ __forceinline__ void tc_tma_load(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
