@@ -310,6 +310,7 @@ SelectParams select_params(const ha_shape_t* shape, const ha_budget_t* budget, c
     p.heavy_budget = budget->heavy_budget;
     p.eval_mode = budget->eval_mode;
     p.depth = budget->retrieve_depth;
+    p.signal = 0;
     return p;
 }
 
@@ -334,6 +335,7 @@ SelectAttendParams select_attend_params(const ha_shape_t* shape, const ha_budget
     p.partials = partials;
     p.status = status;
     p.status_out = status_out;
+    p.ready = nullptr;
     p.B = shape->batch;
     p.Hkv = shape->num_kv_heads;
     p.max_pages = shape->max_pages;
@@ -782,7 +784,7 @@ static int score_select_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                              const int32_t* page_table, const int32_t* seq_lens, const int32_t* budget_lens,
                              int32_t* sel_idx, int32_t* sel_cnt, uint8_t* scores_dbg,
                              void* workspace, size_t workspace_bytes, int32_t* status, void* stream,
-                             bool plan_only = false) {
+                             bool plan_only = false, bool handover = false) {
     int rc = check_shape(shape);
     if (rc != HA_OK) return rc;
     rc = check_budget(budget);
@@ -794,8 +796,11 @@ static int score_select_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
 
-    const SelectParams p = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
-                                         scores_dbg, status, w.hist, w.plan, w.scores, w.arrive, w.sel_rows, budget_lens);
+    SelectParams p = select_params(shape, budget, q_codes, hash_pages, page_table, seq_lens, sel_idx, sel_cnt,
+                                   scores_dbg, status, w.hist, w.plan, w.scores, w.arrive, w.sel_rows, budget_lens);
+    // handover: the caller launches the selection right behind this call; it then takes each unit's plan as soon as
+    // that unit is ready instead of waiting for the whole scoring grid
+    p.signal = (!plan_only || handover) ? 1 : 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const long long max_tokens = (long long)shape->max_pages * kPage;
     if (!plan_only && use_cluster_select(shape)) {
@@ -807,9 +812,10 @@ static int score_select_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     }
     if (launch_score_hist(shape, p, shape->num_kv_heads, s) != cudaSuccess) return HA_ERR_LAUNCH;
     if (plan_only) return HA_OK;
-    const SelectAttendParams sa = select_attend_params(shape, budget, w.plan, w.scores, w.partials, sel_idx, nullptr,
-                                                       nullptr, nullptr, page_table, seq_lens, budget_lens, 1.0f,
-                                                       nullptr, status, nullptr);
+    SelectAttendParams sa = select_attend_params(shape, budget, w.plan, w.scores, w.partials, sel_idx, nullptr,
+                                                 nullptr, nullptr, page_table, seq_lens, budget_lens, 1.0f,
+                                                 nullptr, status, nullptr);
+    sa.ready = reinterpret_cast<int32_t*>(w.arrive);
     return launch_select_attend(shape, sa, shape->num_kv_heads * kGroup, false, s) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
@@ -817,7 +823,8 @@ static int score_select_impl(const ha_shape_t* shape, const ha_budget_t* budget,
 static int select_attend_impl(const ha_shape_t* shape, const ha_budget_t* budget, const void* q, const void* k_pages,
                               const void* v_pages, const int32_t* page_table, const int32_t* seq_lens,
                               const int32_t* budget_lens, int32_t* sel_idx, float sm_scale, void* out, void* workspace,
-                              size_t workspace_bytes, int32_t* status, void* stream, int32_t* status_out) {
+                              size_t workspace_bytes, int32_t* status, void* stream, int32_t* status_out,
+                              bool handover = false) {
     int rc = check_shape(shape);
     if (rc != HA_OK) return rc;
     rc = check_budget(budget);
@@ -828,9 +835,10 @@ static int select_attend_impl(const ha_shape_t* shape, const ha_budget_t* budget
     if (workspace == nullptr) return HA_ERR_WORKSPACE;
     const Workspace w = carve(shape, budget, workspace);
     if (workspace_bytes < w.bytes) return HA_ERR_WORKSPACE;
-    const SelectAttendParams sa = select_attend_params(shape, budget, w.plan, w.scores, w.partials, sel_idx, q, k_pages,
-                                                       v_pages, page_table, seq_lens, budget_lens, sm_scale, out,
-                                                       status, status_out);
+    SelectAttendParams sa = select_attend_params(shape, budget, w.plan, w.scores, w.partials, sel_idx, q, k_pages,
+                                                 v_pages, page_table, seq_lens, budget_lens, sm_scale, out,
+                                                 status, status_out);
+    if (handover) sa.ready = reinterpret_cast<int32_t*>(w.arrive);  // (the scoring call in front was told the same)
     return launch_select_attend(shape, sa, shape->num_kv_heads * kGroup, true, static_cast<cudaStream_t>(stream)) ==
                    cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
@@ -892,11 +900,11 @@ static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
         // scoring + plan, then selection + attention; the merge kernel, last of the step, also leaves the status
         // word in status_out, if given
         rc = score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, budget_lens, sel_idx, sel_cnt,
-                               nullptr, workspace, workspace_bytes, status, stream, true);
+                               nullptr, workspace, workspace_bytes, status, stream, true, true);
         if (rc != HA_OK) return rc;
         if (status_delivered != nullptr) *status_delivered = status_out != nullptr;
         return select_attend_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, budget_lens, sel_idx,
-                                  sm_scale, out, workspace, workspace_bytes, status, stream, status_out);
+                                  sm_scale, out, workspace, workspace_bytes, status, stream, status_out, true);
     }
     rc = score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, budget_lens, sel_idx, sel_cnt,
                            nullptr, workspace, workspace_bytes, status, stream);

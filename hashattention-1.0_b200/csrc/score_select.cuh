@@ -56,8 +56,8 @@ struct SelectParams {
     const int32_t* seq_lens;
     const int32_t* budget_lens;  // [B] or null: the length the heavy budget is a fraction of, if not seq_lens
     uint32_t* hist;            // workspace: [B][Hkv][4*33][nchunks] per chunk: tokens at or above each score
-    uint32_t* arrive;          // workspace: [B][Hkv][kArriveStride] chunks of the unit that have published, then the unit's
-                               // histogram totals (all 0 between calls)
+    uint32_t* arrive;          // workspace: [B][Hkv][kArriveStride] chunks of the unit that have published, the unit's
+                               // histogram totals, and the unit's ready word (all 0 between calls)
     int32_t* sel_idx;          // [B][Hq][sel_stride] token indices
     int32_t* sel_rows;         // workspace: [B][Hq][sel_stride] page * 256 + slot of the same tokens
     int32_t* sel_cnt;          // [B][Hq]
@@ -70,6 +70,7 @@ struct SelectParams {
     int init_budget, recent_budget;
     double heavy_budget;
     int eval_mode, depth;      // HA_EVAL_*; usa_retrieve_depth (HA_EVAL_DEPTH only)
+    int signal;                // 1: the selection kernel launched right behind consumes the plan unit by unit (ready word)
 };
 
 // One round of one warp: 128 consecutive tokens of one page, token it*32 + lane for it = 0..3.
@@ -220,6 +221,7 @@ __device__ __forceinline__ uint32_t gather_byte(const uint32_t (&a)[NW], int g) 
 constexpr int kPlanChunks = 64;            // chunks per sweep (sequences of more than 64 chunks take several)
 constexpr int kPlanRows = kGroup * kBins;  // 132 (head, bin) rows
 constexpr int kArriveStride = 136;         // words per unit behind p.arrive: the arrival counter, then the 132 totals
+constexpr int kReadyWord = 133;            // ... and the ready word: > 0 while the unit's plan waits for consumers
 
 struct PlanSmem {
     int tot[kPlanRows];
@@ -458,6 +460,16 @@ __global__ void __launch_bounds__(kSelThreads, kShMinCtas) score_hist_kernel(con
     if (!s_last) return;
     __threadfence();
     select_plan(p, b, kvh, r, nchunks_b, s_plan, tid);
+    // ---- hand the unit over: one count per CTA of select_attend_kernel that will take this plan (a chunk of one
+    //      query head each). Those CTAs run while other units are still being scored; each takes its count back,
+    //      so the word is zero again when the step is over.
+    if (p.signal != 0) {
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            atomicAdd(reinterpret_cast<int*>(unit + kReadyWord), nchunks_b * kGroup);
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------

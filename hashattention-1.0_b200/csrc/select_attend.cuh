@@ -35,6 +35,7 @@ constexpr int kSaWorkers = kSaThreads / kSaLanes;    // 16 rows are worked on si
 constexpr int kSaRows = 2;                           // rows a worker keeps in flight per round
 constexpr int kSaRoundRows = kSaWorkers * kSaRows;   // 32
 constexpr int kSaWarps = kSaThreads / 32;
+constexpr int kSaReadyPolls = 1 << 20;               // polls of a unit's ready word (200 ns apart) before a CTA gives up
 constexpr int kSaEdgeSlots = 2;  // CTA 0 of a head attends the sink tokens, CTA 1 the recent ones, CTA 2 + c chunk c
 
 // bf16 operands of the mixed-precision multiply-add are taken as they are stored (exact products, fp32
@@ -63,6 +64,8 @@ struct SelectAttendParams {
     float* partials;              // workspace: [B][Hq][nslots][130]
     int32_t* status;
     int32_t* status_out;          // see SparseDecodeParams
+    int32_t* ready;               // the scoring kernel's per-unit words (stride kArriveStride; word kReadyWord is used), or
+                                  // null: the plan and the score bytes are complete when the kernel in front has ended
     int B, Hkv, max_pages, num_pages, sel_stride, nchunks, nslots;
     int h0;                       // first query head of this launch
     int init_budget, recent_budget;
@@ -259,7 +262,28 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
         const int v = __ldg(pt + min(chunk_start / kPage + tid, p.max_pages - 1));
         s_pages[tid] = v >= 0 && v < p.num_pages ? v : -1;  // tokens of a bad page are no candidates: never selected
     }
-    pdl_wait();
+    if (p.ready == nullptr) {
+        pdl_wait();
+    } else if (active) {
+        // The scoring kernel in front is still running, but all of its CTAs have started (it lets its dependents go
+        // only then), so the unit's plan arrives without any help from this grid. The wait is bounded all the same.
+        if (tid == 0) {
+            int* word = p.ready + ((size_t)b * p.Hkv + kvh) * kArriveStride + kReadyWord;
+            int v, polls = 0;
+            for (;;) {
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+                if (v > 0 || ++polls > kSaReadyPolls) break;
+                __nanosleep(200);
+            }
+            s_wtot[0] = v > 0 ? 1u : 0u;
+            atomicSub(word, 1);  // (also after giving up: the word still returns to zero)
+            if (v <= 0) report(p.status, HA_ERR_TIMEOUT);
+        }
+        __syncthreads();
+        const bool arrived = s_wtot[0] != 0u;
+        __syncthreads();  // (s_wtot is written again below)
+        if (!arrived) return;
+    }
     pdl_launch_dependents();
     if (!active) return;
 
