@@ -30,6 +30,7 @@ HA_EVAL_SIMPLE = 0
 HA_EVAL_DEPTH = 1
 HA_OPT_CLUSTER_GATHER = 0
 HA_OPT_CLUSTER_SELECT = 1
+HA_OPT_PLAN_HANDOVER = 2
 
 
 class HaShape(ctypes.Structure):

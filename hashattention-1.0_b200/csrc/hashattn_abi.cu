@@ -27,6 +27,7 @@ std::atomic<int> g_options[HA_OPT_COUNT_] = {};
 bool g_options_ready = [] {
     g_options[HA_OPT_CLUSTER_GATHER] = -1;
     g_options[HA_OPT_CLUSTER_SELECT] = -1;
+    g_options[HA_OPT_PLAN_HANDOVER] = -1;
     return true;
 }();
 inline int option(int key) { return g_options[key].load(std::memory_order_relaxed); }
@@ -800,7 +801,8 @@ static int score_select_impl(const ha_shape_t* shape, const ha_budget_t* budget,
                                    scores_dbg, status, w.hist, w.plan, w.scores, w.arrive, w.sel_rows, budget_lens);
     // handover: the caller launches the selection right behind this call; it then takes each unit's plan as soon as
     // that unit is ready instead of waiting for the whole scoring grid
-    p.signal = (!plan_only || handover) ? 1 : 0;
+    const int ho = option(HA_OPT_PLAN_HANDOVER);  // 0: off; 2: the selection waits for an announcement that is not made
+    p.signal = ((!plan_only || handover) && ho != 0 && ho != 2) ? 1 : 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const long long max_tokens = (long long)shape->max_pages * kPage;
     if (!plan_only && use_cluster_select(shape)) {
@@ -815,7 +817,7 @@ static int score_select_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     SelectAttendParams sa = select_attend_params(shape, budget, w.plan, w.scores, w.partials, sel_idx, nullptr,
                                                  nullptr, nullptr, page_table, seq_lens, budget_lens, 1.0f,
                                                  nullptr, status, nullptr);
-    sa.ready = reinterpret_cast<int32_t*>(w.arrive);
+    if (ho != 0) sa.ready = reinterpret_cast<int32_t*>(w.arrive);
     return launch_select_attend(shape, sa, shape->num_kv_heads * kGroup, false, s) == cudaSuccess ? HA_OK : HA_ERR_LAUNCH;
 }
 
@@ -897,14 +899,15 @@ static int decode_step_impl(const ha_shape_t* shape, const ha_budget_t* budget,
     if (rc != HA_OK) return rc;
     const void* q_att = q_stage != nullptr ? q_stage : q;
     if (!use_cluster_select(shape)) {
+        const bool handover = option(HA_OPT_PLAN_HANDOVER) != 0;
         // scoring + plan, then selection + attention; the merge kernel, last of the step, also leaves the status
         // word in status_out, if given
         rc = score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, budget_lens, sel_idx, sel_cnt,
-                               nullptr, workspace, workspace_bytes, status, stream, true, true);
+                               nullptr, workspace, workspace_bytes, status, stream, true, handover);
         if (rc != HA_OK) return rc;
         if (status_delivered != nullptr) *status_delivered = status_out != nullptr;
         return select_attend_impl(shape, budget, q_att, k_pages, v_pages, page_table, seq_lens, budget_lens, sel_idx,
-                                  sm_scale, out, workspace, workspace_bytes, status, stream, status_out, true);
+                                  sm_scale, out, workspace, workspace_bytes, status, stream, status_out, handover);
     }
     rc = score_select_impl(shape, budget, q_codes, hash_pages, page_table, seq_lens, budget_lens, sel_idx, sel_cnt,
                            nullptr, workspace, workspace_bytes, status, stream);

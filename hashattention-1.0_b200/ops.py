@@ -138,9 +138,14 @@ class SparseDecodeContext:
         self.q_codes = torch.zeros(self.batch, self.num_q_heads, dtype=torch.int32, device=dev)
         self.sel_idx = torch.zeros(self.batch, self.num_q_heads, self.sel_stride, dtype=torch.int32, device=dev)
         self.sel_cnt = torch.zeros(self.batch, self.num_q_heads, dtype=torch.int32, device=dev)
-        with torch.cuda.device(dev):
+        self.reset_workspace()
+
+    def reset_workspace(self) -> None:
+        """Clears the workspace (``ha_workspace_init``): once before the first call, and again after a step that
+        ended with ``HA_ERR_TIMEOUT`` (its arrival counters and ready words are then in no defined state)."""
+        with torch.cuda.device(self.device):
             _raise_on(self.lib.ha_workspace_init(self.shape, self.c_budget, self.workspace.data_ptr(),
-                                                 self.workspace_bytes, _stream_ptr(dev)), "ha_workspace_init")
+                                                 self.workspace_bytes, _stream_ptr(self.device)), "ha_workspace_init")
 
     # -- argument checks -----------------------------------------------------------------
     def _check_q(self, q):

@@ -123,14 +123,23 @@ int ha_abi_version(void);
 const char* ha_status_str(int status);
 
 /* Process-wide dispatch options (no reference counterpart; the library reads no environment
- * variables). For experiments and tests: results never depend on them, only which kernels run.
+ * variables). For experiments and tests: results never depend on them, only which kernels run
+ * (the one exception, a failure-injection value, is marked).
  *   HA_OPT_CLUSTER_GATHER  -1 library decides, 0 / 1: thread-block-cluster variant of the gather
  *   HA_OPT_CLUSTER_SELECT  -1 library decides (at most 8 (sequence, kv-head) units of at most 65536
  *                          tokens), 0 never, 1 whenever the sequences fit: single-pass cluster kernel
- *                          for scoring + selection                                                */
+ *                          for scoring + selection
+ *   HA_OPT_PLAN_HANDOVER   -1 / 1 inside a step the selection kernel takes the plan of each (sequence,
+ *                          kv-head) as soon as the scoring kernel has finished it (a ready word per unit in
+ *                          the workspace, polled with a bound), 0 it waits for the whole scoring kernel.
+ *                          2 is a failure-injection hook for tests of that bound: the selection waits, the
+ *                          scoring kernel does not announce anything, every waiting CTA gives up after its
+ *                          poll limit (about a second), the step's status is HA_ERR_TIMEOUT, its output is
+ *                          undefined and the workspace has to be cleared again with ha_workspace_init.   */
 #define HA_OPT_CLUSTER_GATHER 0
 #define HA_OPT_CLUSTER_SELECT 1
-#define HA_OPT_COUNT_ 2
+#define HA_OPT_PLAN_HANDOVER 2
+#define HA_OPT_COUNT_ 3
 int ha_set_option(int option_key, int value); /* HA_ERR_BAD_ARG for an unknown key */
 int ha_get_option(int option_key);
 

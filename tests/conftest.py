@@ -34,7 +34,8 @@ def device():
 def lib_option(pkg):
     """Sets dispatch options of the library (ha_set_option) for one test and puts the old values back."""
     from hashattention_b200 import _lib
-    keys = {"cluster_gather": _lib.HA_OPT_CLUSTER_GATHER, "cluster_select": _lib.HA_OPT_CLUSTER_SELECT}
+    keys = {"cluster_gather": _lib.HA_OPT_CLUSTER_GATHER, "cluster_select": _lib.HA_OPT_CLUSTER_SELECT,
+            "plan_handover": _lib.HA_OPT_PLAN_HANDOVER}
     lib = _lib.load()
     saved = {}
 

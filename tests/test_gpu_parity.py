@@ -848,6 +848,37 @@ def test_bad_page_id_and_bad_length_are_reported_through_the_status_word(device)
     assert bool(torch.isfinite(out.float()).all())
 
 
+def test_plan_handover_changes_no_bit_and_its_wait_is_bounded(device, lib_option):
+    """Inside a step the selection kernel takes each (sequence, kv-head) plan through a ready word while other units
+    are still being scored. Switched off (the kernel waits for the whole scoring grid) the step gives the same bits.
+    With the announcement suppressed - the library's failure-injection value - every waiting CTA gives up after its
+    poll limit, the status word says so, and after the workspace is cleared the context works as before."""
+    usa = synthetic.make_usa(8, 128, 0, True)
+    inp = synthetic.make_decode_inputs(104, [5000, 2100], 8, 2)
+    lib_option("cluster_select", 0)  # the scoring + selection/attention kernels, not the single-pass cluster kernel
+    cache, ctx = build(device, inp.q, inp.k, inp.v, ha.Budget(16, 0.125, 16), usa)
+    ctx.hash_prefill()
+    q = inp.q.to(device, torch.bfloat16)
+    kn = torch.stack([k[:, -1] for k in inp.k]).to(device, torch.bfloat16)
+    assert "select_attend" in ctx.step_path()
+    out_on = ctx.decode_step(q, kn, kn).clone()
+    ctx.check_status()
+    sel_on, cnt_on = ctx.sel_idx.clone(), ctx.sel_cnt.clone()
+    lib_option("plan_handover", 0)
+    out_off = ctx.decode_step(q, kn, kn).clone()
+    ctx.check_status()
+    assert torch.equal(out_off, out_on) and torch.equal(ctx.sel_cnt, cnt_on) and torch.equal(ctx.sel_idx, sel_on)
+    lib_option("plan_handover", 2)
+    ctx.decode_step(q, kn, kn)
+    with pytest.raises(RuntimeError, match="wait ran out"):
+        ctx.check_status()
+    lib_option("plan_handover", -1)
+    ctx.reset_workspace()
+    out_again = ctx.decode_step(q, kn, kn)
+    ctx.check_status()
+    assert torch.equal(out_again, out_on)
+
+
 @pytest.mark.parametrize("use_graph", [False, True])
 @pytest.mark.parametrize("pinned", [True, False])
 def test_host_buffer_step_delivers_the_status_word(device, use_graph, pinned):
