@@ -258,11 +258,14 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
     const int c = slot - kSaEdgeSlots;
     const int chunk_start = c * chunk_tokens;
     const bool active = ok && chunk_start < S;
-    if (tid < kChunkPages) {
-        const int v = __ldg(pt + min(chunk_start / kPage + tid, p.max_pages - 1));
-        s_pages[tid] = v >= 0 && v < p.num_pages ? v : -1;  // tokens of a bad page are no candidates: never selected
-    }
+    // (the page ids are requested here and used after the ready word has been asked for: one round trip, not two)
+    int pgv = -1;
+    if (tid < kChunkPages) pgv = __ldg(pt + min(chunk_start / kPage + tid, p.max_pages - 1));
+    auto keep_pages = [&] {
+        if (tid < kChunkPages) s_pages[tid] = pgv >= 0 && pgv < p.num_pages ? pgv : -1;  // tokens of a bad page are no candidates
+    };
     if (p.ready == nullptr) {
+        keep_pages();
         pdl_wait();
     } else if (active) {
         // The scoring kernel in front is still running, but all of its CTAs have started (it lets its dependents go
@@ -279,6 +282,7 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
             atomicSub(word, 1);  // (also after giving up: the word still returns to zero)
             if (v <= 0) report(p.status, HA_ERR_TIMEOUT);
         }
+        keep_pages();
         __syncthreads();
         const bool arrived = s_wtot[0] != 0u;
         __syncthreads();  // (s_wtot is written again below)
