@@ -101,6 +101,9 @@ __device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
     return d;
 }
 
+// asks L2 for the 128-byte line that holds p (no register is written, nothing waits)
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization
 // attribute may start before its predecessor has finished; it must call pdl_wait() before
 // it reads anything the predecessor wrote, and pdl_launch_dependents() lets the successor's

@@ -273,12 +273,26 @@ hash_decode_kernel(const HashDecodeParams p) {
               p.bias[side] + (size_t)h * kMlpBias, warp, lane >> 4, (lane & 15) * 8);
     __shared__ MlpSmem sm[2];
 
-    pdl_wait();
-    pdl_launch_dependents();
-
     const int b_begin = blockIdx.z * p.batch_per_cta;
     const int b_end = min(p.B, b_begin + p.batch_per_cta);
     const int kvh = h / kGroup, g = h % kGroup;
+
+    // The input rows may be products of the kernel in front, so they are read after the wait; asking L2 for their
+    // lines beforehand is harmless either way (L2 is where that kernel's stores land) and saves the DRAM trip when
+    // the rows were written long ago. Not for rows in mapped host memory (q_stage given), which L2 does not hold.
+    if (p.q_stage == nullptr) {
+        for (int i = tid; i < 2 * (b_end - b_begin); i += kHashDecodeThreads) {
+            const int b = b_begin + (i >> 1);
+            const __nv_bfloat16* row = side == 0 ? p.q + ((size_t)b * Hq + h) * kHeadDim
+                                                 : p.k_new + ((size_t)b * p.Hkv + kvh) * kHeadDim;
+            prefetch_l2(row + (i & 1) * (kHeadDim / 2));
+            if (side == 1 && g == 0 && p.v_new != nullptr)
+                prefetch_l2(p.v_new + ((size_t)b * p.Hkv + kvh) * kHeadDim + (i & 1) * (kHeadDim / 2));
+        }
+    }
+
+    pdl_wait();
+    pdl_launch_dependents();
 
     if constexpr (kPairs) {
         // The sequences of this CTA are evaluated two at a time (the pair shares every weight register and its two
