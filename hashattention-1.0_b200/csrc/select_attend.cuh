@@ -394,7 +394,19 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
         idx[pos] = tok;
         if constexpr (kGather) {
             const int pg = s_pages[(tok - chunk_start) / kPage];
-            s_rows[pos] = pg >= 0 ? (pg * p.Hkv + kvh) * kPage + tok % kPage : -1;
+            const int rr = pg >= 0 ? (pg * p.Hkv + kvh) * kPage + tok % kPage : -1;
+            s_rows[pos] = rr;
+            // ask L2 for the row's K and V lines now (both 128-byte lines of each: half a row measured slower than
+            // none): the whole list is on its way before the first round of the gather starts, at no cost in
+            // registers, and the later rounds find their rows in L2
+            if (rr >= 0) {
+                const __nv_bfloat16* kr = p.k_pages + (size_t)rr * kHeadDim;
+                const __nv_bfloat16* vr = p.v_pages + (size_t)rr * kHeadDim;
+                prefetch_l2(kr);
+                prefetch_l2(kr + kHeadDim / 2);
+                prefetch_l2(vr);
+                prefetch_l2(vr + kHeadDim / 2);
+            }
         }
     };
     {
