@@ -22,6 +22,18 @@ def test_header_and_binding_agree():
     assert declared_functions() == sorted(_lib.PROTOTYPES)
 
 
+def test_constants_of_the_binding_are_the_header_s():
+    """Every integer #define of the header that the Python binding mirrors (status codes, options, modes, the ABI
+    version) has the header's value there."""
+    text = re.sub(r"/\*.*?\*/", "", open(HEADER).read(), flags=re.S)
+    defines = {k: int(v, 0) for k, v in re.findall(r"^#define\s+(HA_[A-Z_0-9]+)\s+\(?(-?(?:0x)?[0-9a-fA-F]+)\)?\s*$", text, flags=re.M)}
+    assert {"HA_OK", "HA_ERR_TIMEOUT", "HA_OPT_PLAN_HANDOVER", "HA_ABI_VERSION"} <= set(defines)
+    mirrored = [k for k in defines if hasattr(_lib, k)]
+    assert len(mirrored) >= 12
+    for k in mirrored:
+        assert getattr(_lib, k) == defines[k], k
+
+
 def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(_lib.LIB_PATH)
     for name in declared_functions():
