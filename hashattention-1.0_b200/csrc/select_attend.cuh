@@ -334,6 +334,30 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
         gem |= ((w[k] + ge_add) & 0x80808080u) >> (7 - k);
     }
     const uint32_t eqm = gem & ~gtm;
+    // ask L2 for both lines of a K / V row
+    auto prefetch_row = [&](int rr) {
+        const __nv_bfloat16* kr = p.k_pages + (size_t)rr * kHeadDim;
+        const __nv_bfloat16* vr = p.v_pages + (size_t)rr * kHeadDim;
+        prefetch_l2(kr);
+        prefetch_l2(kr + kHeadDim / 2);
+        prefetch_l2(vr);
+        prefetch_l2(vr + kHeadDim / 2);
+    };
+    // Tokens above the threshold are certain to be attended: their rows are asked for right here, before the scan
+    // and its barriers (per-unit hand-over only: there the page ids are complete behind the ready word's barrier)
+    const bool early = kGather && p.ready != nullptr;
+    if constexpr (kGather) {
+        if (early) {
+            uint32_t mk = gtm;
+            while (mk != 0) {
+                const int j = __ffs(mk) - 1;
+                mk &= mk - 1;
+                const int t = tok00 + (j & 7) + 32 * (j >> 3) - chunk_start;
+                const int pg = s_pages[t / kPage];
+                if (pg >= 0) prefetch_row((pg * p.Hkv + kvh) * kPage + t % kPage);
+            }
+        }
+    }
     // exclusive prefix over the threads (= over the chunk in block order) of the two counts, 16 bits each
     const uint32_t mine = (uint32_t)__popc(gtm) | ((uint32_t)__popc(eqm) << 16);
     uint32_t incl = mine;
@@ -388,7 +412,7 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
     const int n_sel = tot_gt + min(quota, tot_eq);
     const int n_list = max(0, min(n_sel, p.sel_stride - base));  // an overflowing list was reported by the plan
     int32_t* idx = p.sel_idx + ((size_t)b * Hq + h) * p.sel_stride + base;
-    auto emit = [&](int j, int pos) {
+    auto emit = [&](int j, int pos, bool ask) {
         if (pos >= n_list) return;
         const int tok = tok00 + (j & 7) + 32 * (j >> 3);
         idx[pos] = tok;
@@ -399,14 +423,7 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
             // ask L2 for the row's K and V lines now (both 128-byte lines of each: half a row measured slower than
             // none): the whole list is on its way before the first round of the gather starts, at no cost in
             // registers, and the later rounds find their rows in L2
-            if (rr >= 0) {
-                const __nv_bfloat16* kr = p.k_pages + (size_t)rr * kHeadDim;
-                const __nv_bfloat16* vr = p.v_pages + (size_t)rr * kHeadDim;
-                prefetch_l2(kr);
-                prefetch_l2(kr + kHeadDim / 2);
-                prefetch_l2(vr);
-                prefetch_l2(vr + kHeadDim / 2);
-            }
+            if (rr >= 0 && ask) prefetch_row(rr);
         }
     };
     {
@@ -415,14 +432,14 @@ __global__ void __launch_bounds__(kSaThreads, kMinCtas) select_attend_kernel(con
         while (mk != 0) {
             const int j = __ffs(mk) - 1;
             mk &= mk - 1;
-            emit(j, pos++);
+            emit(j, pos++, !early);
         }
         mk = eq_take;
         pos = tot_gt + eq_before;
         while (mk != 0) {
             const int j = __ffs(mk) - 1;
             mk &= mk - 1;
-            emit(j, straddle ? tot_gt + tie_rank(j) : pos++);
+            emit(j, straddle ? tot_gt + tie_rank(j) : pos++, true);
         }
     }
     if constexpr (!kGather) return;
