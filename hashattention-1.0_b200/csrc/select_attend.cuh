@@ -15,6 +15,11 @@
 // and the trip of the row lists through global memory, and the memory system is idle only while a CTA
 // classifies its 1 - 4 KB of score bytes.
 //
+// Inside a decode step the chunk CTAs do not wait for the whole scoring grid: the CTA that finishes the
+// plan of a (sequence, kv-head) announces it in a ready word, a chunk CTA of that unit polls the word
+// (bounded) and goes on, while other units are still being scored. Rows are asked for in L2 as soon as
+// they are known to be attended, so that only the first round of a gather waits for DRAM.
+//
 // Replaces the sort / scatter of compute_mask_multi and the masked softmax . V of the decode branch
 // (hashattention/hashattention_llama.py:430-443, 578-623). Ties at T go to the lowest token indices, as
 // a stable descending sort would pick them: chunks are ranked by the plan, tokens inside the one chunk
