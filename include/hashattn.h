@@ -147,9 +147,10 @@ int ha_get_option(int option_key);
  * (0 if either is invalid). Host-only arithmetic. */
 size_t ha_workspace_bytes(const ha_shape_t* shape, const ha_budget_t* budget);
 
-/* Zeroes the workspace, in particular the arrival counters and histogram totals of the scoring kernel. REQUIRED once
- * after allocating the workspace (and again only if a kernel was aborted): the kernels leave the
- * counters at zero themselves and keep no other state in the workspace between calls.          */
+/* Zeroes the workspace, in particular the arrival counters, histogram totals and ready words of the scoring kernel.
+ * REQUIRED once after allocating the workspace, and again after a step that did not run to its end (a kernel was
+ * aborted, the status word read HA_ERR_TIMEOUT, or a step returned HA_ERR_LAUNCH half-way): the kernels leave
+ * these words at zero themselves and keep no other state in the workspace between calls.                        */
 int ha_workspace_init(const ha_shape_t* shape, const ha_budget_t* budget, void* workspace,
                       size_t workspace_bytes, void* stream);
 
